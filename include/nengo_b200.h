@@ -1,0 +1,169 @@
+/* C ABI of libnengo_b200.so: the sm_100a device layer behind the
+ * nengo_ocl-compatible Python planning surface.
+ *
+ * The reference (nengo_ocl) has no FFI of its own: its device boundary is
+ * PyOpenCL.  Each entry point below names the reference interface it stands
+ * in for (paths relative to the nengo-ocl source tree).  A maintainer of the
+ * reference binds these with ctypes exactly as nengo_ocl_b200/_capi.py does.
+ *
+ * Conventions: every function returns 0 on success or a negative NB2_ERR_*
+ * code (nb2_last_error() then holds a message for the calling thread); no
+ * ownership crosses the boundary; pointers named d_* / without prefix in
+ * kernel entry points are DEVICE pointers owned by the caller; `stream` is a
+ * cudaStream_t passed as void* (NULL = legacy default stream); index tables
+ * are int32 in element units, as in the reference's ragged arrays.
+ */
+#ifndef NENGO_B200_H
+#define NENGO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB2_ABI_VERSION 1
+
+/* ---- runtime: replaces pyopencl Context/CommandQueue/Array --------------
+ * nengo_ocl/simulator.py:209-219 (context + queue), clraggedarray.py:36-62,
+ * 128-196 (to_device, to_host, enqueue_copy), plan.py:85-149 (enqueue loop). */
+const char* nb2_last_error(void);
+int nb2_abi_version(void);
+int nb2_device_count(int* count);
+int nb2_set_device(int ordinal);
+int nb2_device_info(int ordinal, int* sm_count, int* max_threads_per_block, size_t* global_mem,
+                    size_t* shared_mem_per_block_optin, int* cc_major, int* cc_minor);
+int nb2_malloc(void** dptr, size_t bytes);
+int nb2_free(void* dptr);
+int nb2_host_alloc(void** hptr, size_t bytes); /* pinned host memory */
+int nb2_host_free(void* hptr);
+int nb2_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream, int sync);
+int nb2_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream, int sync);
+int nb2_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int nb2_memset(void* dst, int byte_value, size_t bytes, void* stream);
+int nb2_stream_create(void** stream);
+int nb2_stream_destroy(void* stream);
+int nb2_stream_sync(void* stream);
+int nb2_device_sync(void);
+int nb2_event_create(void** event);
+int nb2_event_destroy(void* event);
+int nb2_event_record(void* event, void* stream);
+int nb2_event_sync(void* event);
+int nb2_event_elapsed_ms(void* start, void* stop, float* ms);
+/* Step-loop replay: Plans.call_n_times (plan.py:128-149) becomes a captured
+ * CUDA graph of one (or several) steps launched n times. */
+int nb2_graph_begin(void* stream);
+int nb2_graph_end(void* stream, void** graph_exec);
+int nb2_graph_abort(void* stream);
+int nb2_graph_launch(void* graph_exec, void* stream, int n_times);
+int nb2_graph_destroy(void* graph_exec);
+/* Peer mapping for the multi-GPU exchange (no counterpart: the reference is
+ * single-device, simulator.py:215-219). handle64 is a 64-byte opaque blob. */
+int nb2_ipc_get_handle(void* dptr, void* handle64);
+int nb2_ipc_open_handle(const void* handle64, void** dptr);
+int nb2_ipc_close_handle(void* dptr);
+
+/* ---- ragged gather-GEMV --------------------------------------------------
+ * Replaces clra_gemv.py ref_impl :264-444, reduce_impl :447-670,
+ * many_dots_impl :673-858, block_impl :861-1175 (all four compute
+ * Y = gamma + beta*Y_in + alpha*sum_j A_j X_j).  `gstructure` is the int32
+ * table of cl_geometry_and_textconf (clra_gemv.py:211-261), row stride
+ * `gstride`, D = max dots.  `xstrides` ([n_items][D], may be NULL = all 1)
+ * carries X element strides (honoured by ref_impl/block_impl :371-376,1037).
+ * `worklist` holds n_units int4 = {item row, first row, row count, 0};
+ * row count <= NB2_GEMV_RMAX (CTA kinds) or <= 32 (warp kind).
+ * alphas/betas/gammas: optional per-item float vectors indexed by the item id
+ * stored in the table (float_cl_clra, clra_gemv.py:17-32); NULL = use the
+ * scalar.  `status` (may be NULL) receives NB2_ERR_TIMEOUT if a bounded wait
+ * inside the kernel gave up. */
+#define NB2_GEMV_CTA 0      /* CTA per unit, 128-bit global loads into smem */
+#define NB2_GEMV_CTA_BULK 1 /* CTA per unit, cp.async.bulk + mbarrier staging */
+#define NB2_GEMV_WARP 2     /* warp per unit, tiny items */
+#define NB2_GEMV_ABUF 8192
+#define NB2_GEMV_XBUF 2048
+#define NB2_GEMV_RMAX 1024
+int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, int gstride, int D,
+                    const int* xstrides, const int* worklist, int n_units, const float* A,
+                    const float* X, const float* Yin, float* Y, double alpha, double beta,
+                    double gamma, const float* alphas, const float* betas, const float* gammas,
+                    int* status);
+
+/* ---- elementwise family (clra_nonlinearities.py) -------------------------
+ * All index tables have the layout the reference's plan functions upload. */
+/* plan_timeupdate :113-144 */
+int nb2_timeupdate(void* stream, float* step, float* time, double dt);
+/* plan_reset :147-214; blocks of <=16 elements */
+int nb2_reset(void* stream, int n_blocks, const float* values, const int* sizes, const int* starts,
+              float* Y);
+/* plan_copy :217-304; blocks of 256; inc_mode 0 = set, 1 = inc, 2 = per-block incdata */
+int nb2_copy(void* stream, int n_blocks, int inc_mode, const int* incdata, const int* offsets,
+             const int* shape0s, const int* shape1s, const int* Xstride0s, const int* Xstarts,
+             const float* X, const int* Ystride0s, const int* Ystarts, float* Y);
+/* plan_slicedcopy :307-411; blocks of 16 */
+int nb2_slicedcopy(void* stream, int n_blocks, int inc_mode, const int* incdata,
+                   const int* Xstride0s, const int* Xstarts, const float* X, const int* Ystride0s,
+                   const int* Ystarts, float* Y, const int* Isizes, const int* XIstarts,
+                   const int* XIdata, const int* YIstarts, const int* YIdata);
+/* plan_elementwise_inc :414-574 (outer=1 is the PES delta, simulator.py:1334-1345) */
+int nb2_elementwise_inc(void* stream, int n_blocks, int outer, int inc, const float* alphas,
+                        const int* offsets, const int* Ashape0s, const int* Ashape1s,
+                        const int* Astride0s, const int* Astarts, const float* A,
+                        const int* Xshape0s, const int* Xshape1s, const int* Xstride0s,
+                        const int* Xstarts, const float* X, const int* Yshape0s,
+                        const int* Yshape1s, const int* Ystride0s, const int* Ystarts, float* Y);
+/* plan_linearfilter :577-803 (+ linearfilter_inc ring-position kernel when uses_buf) */
+int nb2_linearfilter(void* stream, int n_blocks, int block_size, int uses_buf, const int* offsets,
+                     const int* shape0s, const int* shape1s, const int* Xstride0s,
+                     const int* Xstride1s, const int* Xstarts, const float* X,
+                     const int* Ystride0s, const int* Ystride1s, const int* Ystarts, float* Y,
+                     const int* Ashape0s, const int* Astarts, const float* A, const int* Bshape0s,
+                     const int* Bstarts, const float* B, const int* Xbufstarts, float* Xbuf,
+                     const int* Ybufstarts, float* Ybuf, int* Xbufpos, int* Ybufpos);
+/* plan_probes :806-951; one CTA of `block_size` threads per probe */
+int nb2_probes(void* stream, int n_probes, int block_size, float* countdowns, int* bufpositions,
+               const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
+               const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
+               float* Y);
+/* plan_presentinput :1678-1759; pres_t may be NULL (table indexed by step) */
+int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
+                     const int* Yshape0s, const int* Ystarts, float* Y, const int* Tstarts,
+                     const float* T, const int* Sshape0s, const int* Sstarts, const float* S);
+
+/* Neuron models generated by _plan_template (:1286-1483): plan_lif :1028-1146,
+ * plan_lif_rate :1149-1197, plan_spiking_rectified_linear :1200-1235,
+ * plan_rectified_linear :1238-1259, plan_sigmoid :1262-1283.  Each variable is
+ * a per-block starts table plus a buffer; a parameter with buf == NULL is the
+ * constant `value` (the reference's static_params). */
+typedef struct {
+  const int* starts;
+  float* buf;
+  float value;
+} nb2_var;
+typedef struct {
+  nb2_var J, V, W, S, N;              /* S = output (spikes or rates); N = adaptation */
+  nb2_var tau, ref, amp, tau_n, inc_n; /* parameters */
+  double dt;
+  int upsample;
+  int adaptive;
+} nb2_neuron_args;
+#define NB2_NEURON_LIF 0
+#define NB2_NEURON_LIF_RATE 1
+#define NB2_NEURON_RELU 2
+#define NB2_NEURON_SPIKING_RELU 3
+#define NB2_NEURON_SIGMOID 4
+int nb2_neurons(void* stream, int kind, int n_blocks, int block_size, const int* sizes,
+                const nb2_neuron_args* args);
+
+/* plan_direct :954-1025: the reference compiles a translated Python function
+ * per node; here the translation is a postfix program run by one interpreter
+ * kernel.  prog: n_ops int32 pairs {opcode, operand}; consts: float pool.
+ * Inputs: up to 2 ragged inputs (starts table + buffer + dim); one output. */
+int nb2_direct(void* stream, int n_items, const int* prog, int n_ops, const float* consts,
+               int out_dim, const int* in0_starts, const float* in0, const int* in1_starts,
+               const float* in1, const int* out_starts, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NENGO_B200_H */

@@ -1,0 +1,352 @@
+// Elementwise ragged kernels: clock, reset, copy, sliced copy, elementwise
+// increment (incl. the PES outer product), linear filters, probes and table
+// playback.  Each kernel consumes the index tables that the matching
+// reference plan function uploads (nengo_ocl/clra_nonlinearities.py), so the
+// host-side plans are interchangeable.  This translation unit is compiled
+// with -fmad=false: every a*b+c below is a separate multiply and add, as in
+// the CPU restatement the results are checked against.
+#include "nb2_common.cuh"
+#include "../../include/nengo_b200.h"
+
+// ---- plan_timeupdate (clra_nonlinearities.py:119-133) ----------------------
+__global__ void nb2_timeupdate_kernel(float* step, float* time, double dt) {
+  const float s = step[0] + 1.0f;
+  step[0] = s;
+  time[0] = (float)(dt * (double)s);  // dt is a double literal in the reference source
+}
+
+extern "C" int nb2_timeupdate(void* stream, float* step, float* time, double dt) {
+  NB2_REQUIRE(step && time, "null pointer");
+  nb2_timeupdate_kernel<<<1, 1, 0, nb2_stream(stream)>>>(step, time, dt);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_reset (:154-172) --------------------------------------------------
+__global__ void nb2_reset_kernel(int n_blocks, const float* __restrict__ values,
+                                 const int* __restrict__ sizes, const int* __restrict__ starts,
+                                 float* Y) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = t >> 4;
+  const int i = t & 15;
+  if (n < n_blocks && i < sizes[n]) Y[starts[n] + i] = values[n];
+}
+
+extern "C" int nb2_reset(void* stream, int n_blocks, const float* values, const int* sizes,
+                         const int* starts, float* Y) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(values && sizes && starts && Y, "null pointer");
+  const long long threads = (long long)n_blocks * 16;
+  nb2_reset_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, nb2_stream(stream)>>>(
+      n_blocks, values, sizes, starts, Y);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_copy (:225-262) ---------------------------------------------------
+__global__ void nb2_copy_kernel(int inc_mode, const int* __restrict__ incdata,
+                                const int* __restrict__ offsets, const int* __restrict__ shape0s,
+                                const int* __restrict__ shape1s, const int* __restrict__ Xstride0s,
+                                const int* __restrict__ Xstarts, const float* X,
+                                const int* __restrict__ Ystride0s, const int* __restrict__ Ystarts,
+                                float* Y) {
+  const int n = blockIdx.x;
+  const int ij = threadIdx.x + offsets[n];
+  const int shape1 = shape1s[n];
+  const int i = ij / shape1;
+  const int j = ij - i * shape1;
+  if (i >= shape0s[n]) return;
+  const int xo = Xstarts[n] + i * Xstride0s[n] + j;
+  const int yo = Ystarts[n] + i * Ystride0s[n] + j;
+  const bool inc = inc_mode == 1 || (inc_mode == 2 && incdata[n]);
+  if (inc) Y[yo] += X[xo];
+  else Y[yo] = X[xo];
+}
+
+extern "C" int nb2_copy(void* stream, int n_blocks, int inc_mode, const int* incdata,
+                        const int* offsets, const int* shape0s, const int* shape1s,
+                        const int* Xstride0s, const int* Xstarts, const float* X,
+                        const int* Ystride0s, const int* Ystarts, float* Y) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(offsets && shape0s && shape1s && Xstride0s && Xstarts && X && Ystride0s && Ystarts && Y,
+              "null pointer");
+  NB2_REQUIRE(inc_mode != 2 || incdata, "incdata required for inc_mode 2");
+  nb2_copy_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(inc_mode, incdata, offsets, shape0s, shape1s,
+                                                           Xstride0s, Xstarts, X, Ystride0s, Ystarts, Y);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_slicedcopy (:321-364) ---------------------------------------------
+__global__ void nb2_slicedcopy_kernel(int n_blocks, int inc_mode, const int* __restrict__ incdata,
+                                      const int* __restrict__ Xstride0s,
+                                      const int* __restrict__ Xstarts, const float* X,
+                                      const int* __restrict__ Ystride0s,
+                                      const int* __restrict__ Ystarts, float* Y,
+                                      const int* __restrict__ Isizes,
+                                      const int* __restrict__ XIstarts,
+                                      const int* __restrict__ XIdata,
+                                      const int* __restrict__ YIstarts,
+                                      const int* __restrict__ YIdata) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = t >> 4;
+  const int i = t & 15;
+  if (n >= n_blocks || i >= Isizes[n]) return;
+  const float* a = X + Xstarts[n];
+  float* b = Y + Ystarts[n];
+  const int ai = XIdata[XIstarts[n] + i] * Xstride0s[n];
+  const int bi = YIdata[YIstarts[n] + i] * Ystride0s[n];
+  const bool inc = inc_mode == 1 || (inc_mode == 2 && incdata[n]);
+  if (inc) b[bi] += a[ai];
+  else b[bi] = a[ai];
+}
+
+extern "C" int nb2_slicedcopy(void* stream, int n_blocks, int inc_mode, const int* incdata,
+                              const int* Xstride0s, const int* Xstarts, const float* X,
+                              const int* Ystride0s, const int* Ystarts, float* Y, const int* Isizes,
+                              const int* XIstarts, const int* XIdata, const int* YIstarts,
+                              const int* YIdata) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(Xstride0s && Xstarts && X && Ystride0s && Ystarts && Y && Isizes && XIstarts && XIdata &&
+                  YIstarts && YIdata,
+              "null pointer");
+  NB2_REQUIRE(inc_mode != 2 || incdata, "incdata required for inc_mode 2");
+  const long long threads = (long long)n_blocks * 16;
+  nb2_slicedcopy_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, nb2_stream(stream)>>>(
+      n_blocks, inc_mode, incdata, Xstride0s, Xstarts, X, Ystride0s, Ystarts, Y, Isizes, XIstarts, XIdata,
+      YIstarts, YIdata);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_elementwise_inc (:449-525) ----------------------------------------
+__device__ __forceinline__ float nb2_get_element(const float* data, int shape0, int shape1, int stride0,
+                                                 int i, int j) {
+  if (shape0 == 1 && shape1 == 1) return data[0];
+  if (shape0 == 1) return data[j];
+  if (shape1 == 1) return data[i * stride0];
+  return data[i * stride0 + j];
+}
+
+__global__ void nb2_elementwise_inc_kernel(
+    int outer, int inc, const float* __restrict__ alphas, const int* __restrict__ offsets,
+    const int* __restrict__ Ashape0s, const int* __restrict__ Ashape1s,
+    const int* __restrict__ Astride0s, const int* __restrict__ Astarts, const float* A,
+    const int* __restrict__ Xshape0s, const int* __restrict__ Xshape1s,
+    const int* __restrict__ Xstride0s, const int* __restrict__ Xstarts, const float* X,
+    const int* __restrict__ Yshape0s, const int* __restrict__ Yshape1s,
+    const int* __restrict__ Ystride0s, const int* __restrict__ Ystarts, float* Y) {
+  const int n = blockIdx.x;
+  const int ij = threadIdx.x + offsets[n];
+  const float* a = A + Astarts[n];
+  const float* x = X + Xstarts[n];
+  float* y = Y + Ystarts[n];
+  const int Ystride0 = Ystride0s[n];
+  const int Yshape0 = Yshape0s[n];
+  const int Yshape1 = Yshape1s[n];
+  const int i = ij / Yshape1;
+  const int j = ij - i * Yshape1;
+  if (i >= Yshape0) return;
+  float aa, xx;
+  if (outer) {
+    aa = nb2_get_element(a, Ashape0s[n], 1, Astride0s[n], i, 0);
+    xx = nb2_get_element(x, Xshape0s[n], 1, Xstride0s[n], j, 0);
+  } else {
+    aa = nb2_get_element(a, Ashape0s[n], Ashape1s[n], Astride0s[n], i, j);
+    xx = nb2_get_element(x, Xshape0s[n], Xshape1s[n], Xstride0s[n], i, j);
+  }
+  const float alpha = alphas ? alphas[n] : 1.0f;
+  const float v = alpha * aa * xx;
+  if (inc) y[i * Ystride0 + j] += v;
+  else y[i * Ystride0 + j] = v;
+}
+
+extern "C" int nb2_elementwise_inc(void* stream, int n_blocks, int outer, int inc, const float* alphas,
+                                   const int* offsets, const int* Ashape0s, const int* Ashape1s,
+                                   const int* Astride0s, const int* Astarts, const float* A,
+                                   const int* Xshape0s, const int* Xshape1s, const int* Xstride0s,
+                                   const int* Xstarts, const float* X, const int* Yshape0s,
+                                   const int* Yshape1s, const int* Ystride0s, const int* Ystarts,
+                                   float* Y) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(offsets && Ashape0s && Ashape1s && Astride0s && Astarts && A && Xshape0s && Xshape1s &&
+                  Xstride0s && Xstarts && X && Yshape0s && Yshape1s && Ystride0s && Ystarts && Y,
+              "null pointer");
+  nb2_elementwise_inc_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(
+      outer, inc, alphas, offsets, Ashape0s, Ashape1s, Astride0s, Astarts, A, Xshape0s, Xshape1s, Xstride0s,
+      Xstarts, X, Yshape0s, Yshape1s, Ystride0s, Ystarts, Y);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_linearfilter (:604-711) -------------------------------------------
+__global__ void nb2_linearfilter_kernel(
+    int uses_buf, const int* __restrict__ offsets, const int* __restrict__ shape0s,
+    const int* __restrict__ shape1s, const int* __restrict__ Xstride0s,
+    const int* __restrict__ Xstride1s, const int* __restrict__ Xstarts, const float* x,
+    const int* __restrict__ Ystride0s, const int* __restrict__ Ystride1s,
+    const int* __restrict__ Ystarts, float* y, const int* __restrict__ Ashape0s,
+    const int* __restrict__ Astarts, const float* __restrict__ Adata,
+    const int* __restrict__ Bshape0s, const int* __restrict__ Bstarts,
+    const float* __restrict__ Bdata, const int* __restrict__ Xbufstarts, float* Xbufdata,
+    const int* __restrict__ Ybufstarts, float* Ybufdata, const int* __restrict__ Xbufpos,
+    const int* __restrict__ Ybufpos) {
+  const int k = blockIdx.x;
+  const int ij = threadIdx.x + offsets[k];
+  const int shape0 = shape0s[k];
+  const int shape1 = shape1s[k];
+  const int i = ij / shape1;
+  const int j = ij - i * shape1;
+  if (i >= shape0) return;
+  const int xij = Xstarts[k] + i * Xstride0s[k] + j * Xstride1s[k];
+  const int yij = Ystarts[k] + i * Ystride0s[k] + j * Ystride1s[k];
+  const int na = Ashape0s[k];
+  const int nb = Bshape0s[k];
+  const float* a = Adata + Astarts[k];
+  const float* b = Bdata + Bstarts[k];
+
+  if (na == 0 && nb == 1) {
+    y[yij] = b[0] * x[xij];
+  } else if (na == 1 && nb == 1) {
+    y[yij] = b[0] * x[xij] - a[0] * y[yij];
+  } else if (uses_buf) {
+    float* xbuf = Xbufdata + Xbufstarts[k];
+    float* ybuf = Ybufdata + Ybufstarts[k];
+    const int ix = Xbufpos[k];
+    const int iy = Ybufpos[k];
+    const int iy1 = (iy > 0) ? iy - 1 : na - 1;
+    const int size = shape0 * shape1;
+    float yi = b[0] * x[xij];
+    if (nb > 1) {
+      xbuf[ix * size + ij] = x[xij];
+      for (int p = 1; p < nb; p++) yi += b[p] * xbuf[((ix + p) % nb) * size + ij];
+    }
+    if (na > 0) {
+      yi -= a[0] * y[yij];
+      if (na > 1) {
+        for (int p = 1; p < na; p++) yi -= a[p] * ybuf[((iy + p) % na) * size + ij];
+        ybuf[iy1 * size + ij] = yi;
+      }
+    }
+    y[yij] = yi;
+  }
+}
+
+__global__ void nb2_linearfilter_inc_kernel(int n, const int* __restrict__ Ashape0s,
+                                            const int* __restrict__ Bshape0s, int* Xbufpos,
+                                            int* Ybufpos) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int ix = Xbufpos[k];
+  const int iy = Ybufpos[k];
+  Xbufpos[k] = (ix > 0) ? ix - 1 : Bshape0s[k] - 1;
+  Ybufpos[k] = (iy > 0) ? iy - 1 : Ashape0s[k] - 1;
+}
+
+extern "C" int nb2_linearfilter(void* stream, int n_blocks, int block_size, int uses_buf,
+                                const int* offsets, const int* shape0s, const int* shape1s,
+                                const int* Xstride0s, const int* Xstride1s, const int* Xstarts,
+                                const float* X, const int* Ystride0s, const int* Ystride1s,
+                                const int* Ystarts, float* Y, const int* Ashape0s, const int* Astarts,
+                                const float* A, const int* Bshape0s, const int* Bstarts, const float* B,
+                                const int* Xbufstarts, float* Xbuf, const int* Ybufstarts, float* Ybuf,
+                                int* Xbufpos, int* Ybufpos) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
+  NB2_REQUIRE(offsets && shape0s && shape1s && Xstride0s && Xstride1s && Xstarts && X && Ystride0s &&
+                  Ystride1s && Ystarts && Y && Ashape0s && Astarts && A && Bshape0s && Bstarts && B,
+              "null pointer");
+  NB2_REQUIRE(!uses_buf || (Xbufstarts && Xbuf && Ybufstarts && Ybuf && Xbufpos && Ybufpos),
+              "ring buffers required when uses_buf");
+  cudaStream_t s = nb2_stream(stream);
+  nb2_linearfilter_kernel<<<n_blocks, block_size, 0, s>>>(
+      uses_buf, offsets, shape0s, shape1s, Xstride0s, Xstride1s, Xstarts, X, Ystride0s, Ystride1s, Ystarts, Y,
+      Ashape0s, Astarts, A, Bshape0s, Bstarts, B, Xbufstarts, Xbuf, Ybufstarts, Ybuf, Xbufpos, Ybufpos);
+  NB2_LAUNCH_CHECK();
+  if (uses_buf) {
+    nb2_linearfilter_inc_kernel<<<(n_blocks + 255) / 256, 256, 0, s>>>(n_blocks, Ashape0s, Bshape0s, Xbufpos,
+                                                                       Ybufpos);
+    NB2_LAUNCH_CHECK();
+  }
+  return NB2_OK;
+}
+
+// ---- plan_probes (:831-902) -------------------------------------------------
+__global__ void nb2_probes_kernel(float* countdowns, int* bufpositions,
+                                  const float* __restrict__ periods, const int* __restrict__ Xstarts,
+                                  const int* __restrict__ Xshape0s, const int* __restrict__ Xshape1s,
+                                  const int* __restrict__ Xstride0s,
+                                  const int* __restrict__ Xstride1s, const float* X,
+                                  const int* __restrict__ Ystarts, float* Y) {
+  const int n = blockIdx.x;
+  const float countdown = countdowns[n];
+  const int bufpos = bufpositions[n];
+  __syncthreads();  // everyone has read the counters before thread 0 rewrites them
+  if (countdown <= 0.0f) {
+    const int ni = Xshape0s[n];
+    const int nj = Xshape1s[n];
+    const int n_dims = ni * nj;
+    const int sti = Xstride0s[n];
+    const int stj = Xstride1s[n];
+    const float* x = X + Xstarts[n];
+    float* y = Y + Ystarts[n] + bufpos * n_dims;
+    for (int ij = threadIdx.x; ij < n_dims; ij += blockDim.x) {
+      const int i = ij / nj;
+      const int j = ij - i * nj;
+      y[ij] = x[i * sti + j * stj];
+    }
+    if (threadIdx.x == 0) {
+      countdowns[n] = countdown + periods[n] - 1.0f;
+      bufpositions[n] = bufpos + 1;
+    }
+  } else if (threadIdx.x == 0) {
+    countdowns[n] = countdown - 1.0f;
+  }
+}
+
+extern "C" int nb2_probes(void* stream, int n_probes, int block_size, float* countdowns,
+                          int* bufpositions, const float* periods, const int* Xstarts,
+                          const int* Xshape0s, const int* Xshape1s, const int* Xstride0s,
+                          const int* Xstride1s, const float* X, const int* Ystarts, float* Y) {
+  if (n_probes == 0) return NB2_OK;
+  NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
+  NB2_REQUIRE(countdowns && bufpositions && periods && Xstarts && Xshape0s && Xshape1s && Xstride0s &&
+                  Xstride1s && X && Ystarts && Y,
+              "null pointer");
+  nb2_probes_kernel<<<n_probes, block_size, 0, nb2_stream(stream)>>>(
+      countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+// ---- plan_presentinput (:1694-1730) -----------------------------------------
+__global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float dt,
+                                        const int* __restrict__ Yshape0s,
+                                        const int* __restrict__ Ystarts, float* Y,
+                                        const int* __restrict__ Tstarts, const float* T,
+                                        const int* __restrict__ Sshape0s,
+                                        const int* __restrict__ Sstarts,
+                                        const float* __restrict__ S) {
+  const int k = blockIdx.x;
+  const int m = Yshape0s[k];
+  float* y = Y + Ystarts[k];
+  const float* s = S + Sstarts[k];
+  const int it = (int)T[Tstarts[k]];
+  const int nt = Sshape0s[k];
+  int ti;
+  if (pres_t) ti = (int)(((float)it - 0.5f) * (dt / pres_t[k])) % nt;
+  else ti = it % nt;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) y[i] = s[m * ti + i];
+}
+
+extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
+                                const int* Yshape0s, const int* Ystarts, float* Y, const int* Tstarts,
+                                const float* T, const int* Sshape0s, const int* Sstarts, const float* S) {
+  if (n_items == 0) return NB2_OK;
+  NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
+  NB2_REQUIRE(Yshape0s && Ystarts && Y && Tstarts && T && Sshape0s && Sstarts && S, "null pointer");
+  nb2_presentinput_kernel<<<n_items, block_size, 0, nb2_stream(stream)>>>(
+      pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, S);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}

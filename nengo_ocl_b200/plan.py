@@ -1,0 +1,281 @@
+"""Plans: prepared kernel launches, and the step loop that replays them.
+
+API of the reference's ``nengo_ocl/plan.py:12-149`` (``BasePlan``,
+``PythonPlan``, ``Plan``, ``Plans`` with ``call_n_times`` /
+``enqueue_n_times``), re-designed for CUDA:
+
+* a ``Plan`` wraps a launch closure that issues one or more kernels on the
+  queue's stream through the C ABI (the reference wraps a pyopencl kernel and
+  ``enqueue_nd_range_kernel``, plan.py:85-91);
+* ``Plans.call_n_times(n)`` captures one pass over all device plans into a
+  CUDA graph once and replays it (optionally ``unroll`` steps per graph), so
+  the per-step cost is one graph launch instead of one Python-issued launch
+  per plan per step (plan.py:137-149).  A ``PythonPlan`` in the list splits
+  the step into graph segments with a host callback in between;
+* profiling brackets every plan with CUDA events on the launching stream and
+  fills ``ctimes`` (kernel seconds); ``atimes``/``btimes`` (queue/submit
+  latencies in OpenCL) are recorded as 0.
+"""
+
+import ctypes
+import time
+
+from nengo_ocl_b200 import _capi
+
+
+class BasePlan:
+    def __init__(self, name="", tag=None, flops_per_call=None, bw_per_call=None):
+        self.name = name
+        self.tag = tag
+        self.atimes = []
+        self.btimes = []
+        self.ctimes = []
+        self.n_calls = 0
+        self.flops_per_call = flops_per_call
+        self.bw_per_call = bw_per_call
+
+    def _label(self):
+        return "%s%s" % (self.name, ": %s" % self.tag if self.tag else "")
+
+    def __str__(self):
+        return "<%s>" % self._label()
+
+    def __repr__(self):
+        return "%s{%s}" % (self.__class__.__name__, self._label())
+
+    def update_profiling(self):
+        pass
+
+
+class PythonPlan(BasePlan):
+    """A host callback executed between device plans."""
+
+    def __init__(self, function, **kwargs):
+        super().__init__(**kwargs)
+        self.function = function
+
+    def __call__(self, profiling=False):
+        t0 = time.time() if profiling else 0.0
+        self.function()
+        if profiling:
+            self.atimes.append(0)
+            self.btimes.append(0)
+            self.ctimes.append(time.time() - t0)
+            self.n_calls += 1
+
+
+class _Event:
+    """Completion handle returned by ``Plan.enqueue`` (``wait()`` like a cl.Event)."""
+
+    def __init__(self, queue):
+        self.queue = queue
+
+    def wait(self):
+        self.queue.finish()
+
+
+class Plan(BasePlan):
+    """A prepared device launch.
+
+    Parameters
+    ----------
+    queue : CommandQueue
+    kern : callable(stream)
+        Issues the kernel(s) on ``stream`` via the C ABI.
+    gsize, lsize : tuples
+        Logical NDRange, kept for parity with the reference's plans.
+    n_launches : int
+        Kernels issued per call (for launch accounting).
+    """
+
+    def __init__(self, queue, kern, gsize, lsize=None, n_launches=1, **kwargs):
+        super().__init__(**kwargs)
+        self.queue = queue
+        self.kern = kern
+        self.gsize = self._format_size(gsize)
+        self.lsize = self._format_size(lsize) if lsize is not None else None
+        self.n_launches = n_launches
+        self._events_to_profile = []
+
+    @staticmethod
+    def _format_size(size):
+        assert size is not None
+        size = tuple(int(s) for s in size)
+        assert len(size) > 0
+        assert all(s > 0 for s in size)
+        return size
+
+    def __call__(self, profiling=False):
+        self.enqueue(profiling=profiling).wait()
+
+    def enqueue(self, wait_for=None, profiling=False):
+        stream = self.queue.stream
+        if profiling:
+            e0, e1 = ctypes.c_void_p(), ctypes.c_void_p()
+            _capi.call("nb2_event_create", ctypes.byref(e0))
+            _capi.call("nb2_event_create", ctypes.byref(e1))
+            _capi.call("nb2_event_record", e0, stream)
+            self.kern(stream)
+            _capi.call("nb2_event_record", e1, stream)
+            self._events_to_profile.append((e0, e1))
+        else:
+            self.kern(stream)
+        return _Event(self.queue)
+
+    def update_profiling(self):
+        for e0, e1 in self._events_to_profile:
+            _capi.call("nb2_event_sync", e1)
+            ms = ctypes.c_float()
+            _capi.call("nb2_event_elapsed_ms", e0, e1, ctypes.byref(ms))
+            _capi.call("nb2_event_destroy", e0)
+            _capi.call("nb2_event_destroy", e1)
+            self.atimes.append(0.0)
+            self.btimes.append(0.0)
+            self.ctimes.append(1e-3 * ms.value)
+            self.n_calls += 1
+        self._events_to_profile[:] = []
+
+    def __str__(self):
+        return "<%s %s %s>" % (self._label(), self.gsize, self.lsize)
+
+    def __repr__(self):
+        return "%s{%s %s %s}" % (self.__class__.__name__, self._label(), self.gsize, self.lsize)
+
+
+class _Graph:
+    def __init__(self, handle):
+        self.handle = handle
+
+    def __del__(self):
+        try:
+            _capi.lib().nb2_graph_destroy(ctypes.c_void_p(self.handle))
+        except Exception:
+            pass
+
+
+class Plans:
+    """Ordered plan list = one simulator step; replays it n times."""
+
+    def __init__(self, planlist, profiling, use_graph=True, unroll=1):
+        self.plans = list(planlist)
+        self.profiling = profiling
+        self.use_graph = use_graph
+        self.unroll = max(1, int(unroll))
+        self._segments = None  # list of ("graph", _Graph, _Graph_unrolled) / ("python", plan)
+        self.kernel_launches = 0  # device kernels issued so far (graph nodes count)
+
+    def __call__(self):
+        return self.call_n_times(1)
+
+    def __len__(self):
+        return len(self.plans)
+
+    def __getitem__(self, i):
+        return self.plans[i]
+
+    def __iter__(self):
+        return iter(self.plans)
+
+    @property
+    def queue(self):
+        for p in self.plans:
+            if hasattr(p, "queue"):
+                return p.queue
+        return None
+
+    @property
+    def launches_per_step(self):
+        return sum(getattr(p, "n_launches", 0) for p in self.plans)
+
+    def invalidate(self):
+        """Drop captured graphs (call after changing the plan list)."""
+        self._segments = None
+
+    def call_n_times(self, n):
+        self.enqueue_n_times(n)
+        q = self.queue
+        if q is not None:
+            q.finish()
+        if self.profiling:
+            for p in self.plans:
+                p.update_profiling()
+
+    # -- execution ----------------------------------------------------------
+    def _capture(self, plans, repeat):
+        q = self.queue
+        _capi.call("nb2_graph_begin", q.stream)
+        try:
+            for _ in range(repeat):
+                for p in plans:
+                    p.kern(q.stream)
+        except Exception:
+            _capi.lib().nb2_graph_abort(q.stream)
+            raise
+        g = ctypes.c_void_p()
+        _capi.call("nb2_graph_end", q.stream, ctypes.byref(g))
+        return _Graph(g.value)
+
+    def _build_segments(self):
+        segments = []
+        run = []
+        for p in self.plans:
+            if hasattr(p, "enqueue"):
+                run.append(p)
+            else:
+                if run:
+                    segments.append(("graph", run))
+                    run = []
+                segments.append(("python", p))
+        if run:
+            segments.append(("graph", run))
+        built = []
+        only_device = len(segments) == 1 and segments[0][0] == "graph"
+        for kind, payload in segments:
+            if kind == "graph":
+                g1 = self._capture(payload, 1)
+                gu = self._capture(payload, self.unroll) if (only_device and self.unroll > 1) else None
+                built.append(("graph", payload, g1, gu))
+            else:
+                built.append(("python", payload))
+        self._segments = built
+
+    def enqueue_n_times(self, n):
+        if n <= 0 or not self.plans:
+            return None
+        q = self.queue
+        if q is None:  # python-only plan list
+            for _ in range(n):
+                for p in self.plans:
+                    p(profiling=self.profiling)
+            return None
+        if self.profiling or not self.use_graph:
+            for _ in range(n):
+                for p in self.plans:
+                    if hasattr(p, "enqueue"):
+                        p.enqueue(profiling=self.profiling)
+                    else:
+                        q.finish()
+                        p(profiling=self.profiling)
+            self.kernel_launches += n * self.launches_per_step
+            return _Event(q)
+        if self._segments is None:
+            self._build_segments()
+        segs = self._segments
+        if len(segs) == 1 and segs[0][0] == "graph":
+            _, _, g1, gu = segs[0]
+            left = n
+            if gu is not None and left >= self.unroll:
+                _capi.call("nb2_graph_launch", ctypes.c_void_p(gu.handle), q.stream, left // self.unroll)
+                left %= self.unroll
+            if left:
+                _capi.call("nb2_graph_launch", ctypes.c_void_p(g1.handle), q.stream, left)
+        else:
+            for _ in range(n):
+                for seg in segs:
+                    if seg[0] == "graph":
+                        _capi.call("nb2_graph_launch", ctypes.c_void_p(seg[2].handle), q.stream, 1)
+                    else:
+                        q.finish()
+                        seg[1](profiling=False)
+        self.kernel_launches += n * self.launches_per_step
+        return _Event(q)

@@ -1,0 +1,296 @@
+"""CPU oracle for whole-model parity: a direct interpreter of an operator list.
+
+TEST INFRASTRUCTURE ONLY (checker for the CUDA simulator; never imported by
+the product package).
+
+It does not share the product's planning code: operators are topologically
+sorted one by one with the rule sets -> incs -> reads -> updates and executed
+with the float32 kernel restatements of ``oracle.kernels``, on plain numpy
+arrays (one per base signal).  It therefore also checks the product's operator
+merging, grouping and fusion, not only its kernels.  The per-operator
+arithmetic follows what the reference launches for that operator type
+(nengo_ocl/simulator.py:746-1345): e.g. all ``DotInc`` into one target are
+summed first and added to the target once (``MultiDotInc``), a lowpass
+``LinearFilter`` is ``y = b0*x - a0*y``, PES writes
+``delta = alpha * outer(error, pre)``.  Dot products are accumulated in
+float64 and rounded to float32 once (order-independent reference value).
+"""
+
+import numpy as np
+
+from oracle import kernels as K
+
+f32 = np.float32
+
+
+def _toposort(operators):
+    """Kahn's algorithm over the per-signal phase order (stable in list order)."""
+    by_base = {}
+    for i, op in enumerate(operators):
+        for phase, kind in enumerate(("sets", "incs", "reads", "updates")):
+            for sig in getattr(op, kind):
+                by_base.setdefault(sig.base, [[], [], [], []])[phase].append((sig, i))
+    succ = [set() for _ in operators]
+    npred = [0] * len(operators)
+    for phases in by_base.values():
+        for pa in range(4):
+            for pb in range(pa + 1, 4):
+                for sa, ia in phases[pa]:
+                    for sb, ib in phases[pb]:
+                        if ia != ib and ib not in succ[ia] and sa.may_share_memory(sb):
+                            succ[ia].add(ib)
+                            npred[ib] += 1
+    ready = [i for i, n in enumerate(npred) if n == 0]
+    order = []
+    import heapq
+
+    heapq.heapify(ready)
+    while ready:
+        i = heapq.heappop(ready)
+        order.append(i)
+        for j in succ[i]:
+            npred[j] -= 1
+            if npred[j] == 0:
+                heapq.heappush(ready, j)
+    if len(order) != len(operators):
+        raise ValueError("cycle in operator graph")
+    return [operators[i] for i in order]
+
+
+class OracleSimulator:
+    """Runs ``model`` (nengo_ocl_b200.model.Model-like) step by step on the CPU."""
+
+    def __init__(self, model, dt=None):
+        self.model = model
+        self.dt = float(model.dt if dt is None else dt)
+        self.signals = {}
+        for op in model.operators:
+            for sig in op.all_signals:
+                b = sig.base
+                if b not in self.signals:
+                    self.signals[b] = np.array(b.initial_value, dtype=np.float32, order="C")
+        for p in model.probes:
+            b = model.sig[p]["in"].base
+            if b not in self.signals:
+                self.signals[b] = np.array(b.initial_value, dtype=np.float32, order="C")
+        ops = list(model.operators)
+        # all DotIncs into one target form one multi-term product (MultiDotInc.compress)
+        self._dot_groups = {}
+        merged = []
+        for op in ops:
+            if type(op).__name__ == "DotInc":
+                key = id(op.Y)
+                if key in self._dot_groups:
+                    self._dot_groups[key].append(op)
+                    continue
+                self._dot_groups[key] = [op]
+            merged.append(op)
+        self._ops = _toposort(self._merge_view(merged))
+        self._filter_state = {}
+        self.probe_data = {p: [] for p in model.probes}
+        self.n_steps = 0
+
+    def _merge_view(self, merged):
+        """Give a merged DotInc head the reads of its whole group for ordering."""
+        out = []
+        for op in merged:
+            if type(op).__name__ == "DotInc" and len(self._dot_groups[id(op.Y)]) > 1:
+                group = self._dot_groups[id(op.Y)]
+                proxy = _DotGroup(group)
+                out.append(proxy)
+            else:
+                out.append(op)
+        return out
+
+    # -- signal access ---------------------------------------------------------
+    def view(self, sig):
+        base = self.signals[sig.base].reshape(-1)
+        isz = base.itemsize
+        return np.lib.stride_tricks.as_strided(
+            base[sig.elemoffset:], shape=sig.shape, strides=tuple(s * isz for s in sig.elemstrides))
+
+    def __getitem__(self, sig):
+        return np.array(self.view(sig))
+
+    # -- stepping --------------------------------------------------------------
+    def run_steps(self, n):
+        for _ in range(n):
+            self.step()
+
+    def step(self):
+        for op in self._ops:
+            getattr(self, "_do_" + type(op).__name__)(op)
+        self.n_steps += 1
+        for p in self.model.probes:
+            period = 1 if p.sample_every is None else max(p.sample_every / self.dt, 1)
+            # same float countdown rule as the probes kernel
+            st = self._filter_state.setdefault(("probe", p), [f32(period - 1)])
+            if st[0] <= 0:
+                self.probe_data[p].append(self[self.model.sig[p]["in"]])
+                st[0] = f32(f32(st[0] + f32(period)) - f32(1))
+            else:
+                st[0] = f32(st[0] - f32(1))
+
+    # -- operators --------------------------------------------------------------
+    def _do_TimeUpdate(self, op):
+        s = f32(self.view(op.step)[()] + f32(1))
+        self.view(op.step)[...] = s
+        self.view(op.time)[...] = f32(self.dt * float(s))
+
+    def _do_Reset(self, op):
+        self.view(op.dst)[...] = f32(op.value)
+
+    def _do_Copy(self, op):
+        src, dst = self.view(op.src), self.view(op.dst)
+        if op.src_slice is not None:
+            src = src[op.src_slice]
+        if op.dst_slice is not None:
+            if op.inc:
+                dst[op.dst_slice] = dst[op.dst_slice] + src
+            else:
+                dst[op.dst_slice] = src
+        elif op.inc:
+            dst[...] = dst + src
+        else:
+            dst[...] = src
+
+    def _dot_terms(self, ops):
+        acc = None
+        for op in ops:
+            A, X = self.view(op.A), self.view(op.X)
+            if A.ndim == 0 or A.size == 1 and A.ndim < 2:
+                term = A.reshape(()).astype(np.float64) * X.astype(np.float64)
+            elif A.ndim == 1:
+                term = np.atleast_1d(A.astype(np.float64) @ X.astype(np.float64))
+            else:
+                term = A.astype(np.float64) @ X.astype(np.float64)
+            acc = term if acc is None else acc + term
+        return acc.astype(np.float32)
+
+    def _do_DotInc(self, op):
+        y = self.view(op.Y)
+        y[...] = y + self._dot_terms([op]).reshape(y.shape)
+
+    def _do__DotGroup(self, op):
+        y = self.view(op.Y)
+        y[...] = y + self._dot_terms(op.group).reshape(y.shape)
+
+    def _do_ElementwiseInc(self, op):
+        A, X, Y = self.view(op.A), self.view(op.X), self.view(op.Y)
+        Y[...] = Y + (A * X).astype(np.float32)
+
+    def _do_SimNeurons(self, op):
+        nt = op.neurons
+        kind = type(nt).__name__
+        J = self.view(op.J)
+        out = self.view(op.output)
+        if kind in ("LIF", "AdaptiveLIF"):
+            V = self.view(op.state["voltage"])
+            W = self.view(op.state["refractory_time"])
+            n = J.size
+            tau = np.full(n, nt.tau_rc, np.float32)
+            ref = np.full(n, nt.tau_ref, np.float32)
+            amp = np.full(n, nt.amplitude, np.float32)
+            if kind == "AdaptiveLIF":
+                Nn = self.view(op.state["adaptation"])
+                v, w, s, nn = K.lif(self.dt, J, V, W, tau, ref, amp, N=Nn,
+                                    tau_n=np.full(n, nt.tau_n, np.float32),
+                                    inc_n=np.full(n, nt.inc_n, np.float32))
+                Nn[...] = nn
+            else:
+                v, w, s = K.lif(self.dt, J, V, W, tau, ref, amp)
+            V[...], W[...], out[...] = v, w, s
+        elif kind == "LIFRate":
+            out[...] = K.lif_rate(J, f32(nt.tau_rc), f32(nt.tau_ref), f32(nt.amplitude))
+        elif kind == "RectifiedLinear":
+            out[...] = K.relu(J, f32(nt.amplitude))
+        elif kind == "SpikingRectifiedLinear":
+            V = self.view(op.state["voltage"])
+            v, s = K.spiking_relu(self.dt, J, V, f32(nt.amplitude))
+            V[...], out[...] = v, s
+        elif kind == "Sigmoid":
+            out[...] = K.sigmoid(J, f32(nt.tau_ref))
+        else:
+            raise ValueError("Unsupported neuron type %r" % kind)
+
+    def _do_SimProcess(self, op):
+        proc = op.process
+        names = [c.__name__ for c in type(proc).__mro__]
+        out = self.view(op.output)
+        if "LinearFilter" in names:
+            num, den = proc.discrete_tf(self.dt)
+            b = num.astype(np.float32)
+            a = den.astype(np.float32)
+            x = self.view(op.input)
+            na, nb = len(a), len(b)
+            if na == 0 and nb == 1:
+                new = b[0] * x
+            elif na == 1 and nb == 1:
+                new = b[0] * x - a[0] * out
+            else:
+                st = self._filter_state.setdefault(
+                    op, dict(xb=np.zeros((nb, x.size), np.float32), yb=np.zeros((na, x.size), np.float32),
+                             ix=0, iy=0))
+                ix, iy = st["ix"], st["iy"]
+                iy1 = iy - 1 if iy > 0 else na - 1
+                xf = x.reshape(-1)
+                yi = b[0] * xf
+                if nb > 1:
+                    st["xb"][ix] = xf
+                    for p in range(1, nb):
+                        yi = yi + b[p] * st["xb"][(ix + p) % nb]
+                if na > 0:
+                    yi = yi - a[0] * out.reshape(-1)
+                    if na > 1:
+                        for p in range(1, na):
+                            yi = yi - a[p] * st["yb"][(iy + p) % na]
+                        st["yb"][iy1] = yi
+                st["ix"] = ix - 1 if ix > 0 else nb - 1
+                st["iy"] = iy - 1 if iy > 0 else na - 1
+                new = yi.reshape(out.shape)
+            new = new.astype(np.float32)
+            out[...] = out + new if op.mode == "inc" else new
+        elif "WhiteSignal" in names:
+            it = int(self.view(self.model.step)[()])
+            table = proc.signal.astype(np.float32)
+            out[...] = table[it % table.shape[0]].reshape(out.shape)
+        elif "PresentInput" in names:
+            it = int(self.view(self.model.step)[()])
+            table = proc.inputs.reshape(proc.inputs.shape[0], -1).astype(np.float32)
+            v = f32(f32(f32(it) - f32(0.5)) * f32(f32(self.dt) / f32(proc.presentation_time)))
+            ti = int(np.fmod(int(v), table.shape[0]))
+            out[...] = table[ti].reshape(out.shape)
+        else:
+            raise NotImplementedError(type(proc).__name__)
+
+    def _do_SimPES(self, op):
+        pre = self.view(op.pre_filtered)
+        err = self.view(op.error)
+        delta = self.view(op.delta)
+        alpha = f32(-op.learning_rate * self.dt / pre.shape[0])
+        delta[...] = ((alpha * err)[:, None] * pre[None, :]).astype(np.float32)
+
+    def _do_SimPyFunc(self, op):
+        args = []
+        if op.t is not None:
+            args.append(float(self.view(op.t)[()]))
+        if op.x is not None:
+            args.append(np.array(self.view(op.x), dtype=np.float64))
+        y = op.fn(*args)
+        if op.output is not None:
+            self.view(op.output)[...] = np.asarray(y, dtype=np.float32).reshape(op.output.shape)
+
+
+class _DotGroup:
+    """Several DotIncs into one target, executed as one multi-term product."""
+
+    def __init__(self, group):
+        self.group = group
+        self.Y = group[0].Y
+        self.sets, self.updates = [], []
+        self.incs = [self.Y]
+        self.reads = [s for op in group for s in (op.A, op.X)]
+
+    @property
+    def all_signals(self):
+        return self.incs + self.reads

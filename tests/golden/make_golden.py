@@ -1,0 +1,284 @@
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Run where the reference source tree is mounted:
+
+    python tests/golden/make_golden.py /path/to/nengo-ocl
+
+It imports the reference's planning modules under the stand-ins of
+``refstubs.py``, calls its own ``plan_*`` functions on seeded inputs and stores
+
+* ``tables.npz``  -- the exact int32 index tables, launch sizes and bw/flops
+  figures those planners upload (bit-exact targets for the planning code), and
+* ``kernels.npz`` -- inputs and outputs of the reference's own kernel source
+  executed on the CPU (``oracle/refkernels.py``) for the neuron models, the
+  linear filter and the small elementwise kernels (pins for ``oracle/kernels.py``).
+
+The fixtures are small; the tests read only the ``.npz`` files.
+"""
+
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, HERE)
+
+import refstubs  # noqa: E402
+
+
+def main(reference_root):
+    mods = refstubs.install(reference_root)
+    from oracle import refkernels  # noqa: E402
+
+    RA = mods["raggedarray"].RaggedArray
+    CLRA = mods["clraggedarray"].CLRaggedArray
+    gemv = mods["clra_gemv"]
+    nl = mods["clra_nonlinearities"]
+    queue = refstubs.Queue()
+    ra = lambda arrays, dtype=np.float32: RA(arrays, dtype=dtype)
+    tables = {}
+    kernels = {}
+
+    def capture(fn):
+        n0, p0 = len(refstubs.CAPTURE), len(refstubs.PROGRAMS)
+        out = fn()
+        return out, refstubs.CAPTURE[n0:], refstubs.PROGRAMS[p0:]
+
+    # ---------------- GEMV index plans ----------------
+    def gemv_case(tag, A, X, Y, A_js, X_js, alpha, beta, gamma):
+        clA, clX, clY = CLRA(queue, A), CLRA(queue, X), CLRA(queue, Y)
+        for pname in ("plan_many_dots_gemv", "plan_reduce_gemv", "plan_block_gemv", "plan_ragged_gather_gemv"):
+            try:
+                prog, cap, _ = capture(lambda: getattr(gemv, pname)(
+                    queue, alpha, clA, A_js, clX, X_js, beta, clY, gamma=gamma))
+            except Exception as e:  # the dispatcher's ref_impl fallback is broken upstream
+                tables["%s/%s/error" % (tag, pname)] = np.array(type(e).__name__)
+                continue
+            key = "%s/%s" % (tag, pname)
+            tables[key + "/n_plans"] = np.array(len(prog.plans))
+            for i, plan in enumerate(prog.plans):
+                tables["%s/plan%d/gsize" % (key, i)] = np.array(plan.gsize)
+                tables["%s/plan%d/lsize" % (key, i)] = np.array(plan.lsize if plan.lsize else ())
+                tables["%s/plan%d/bw" % (key, i)] = np.array(plan.bw_per_call or 0)
+                tables["%s/plan%d/flops" % (key, i)] = np.array(plan.flops_per_call or 0)
+                tables["%s/plan%d/name" % (key, i)] = np.array(plan.name)
+            if pname == "plan_block_gemv":
+                tables[key + "/gstructure"] = cap[0]
+                tables[key + "/Ybuf_size"] = np.array(cap[1].size)
+                for j, nm in enumerate(["Yshape0s", "Yinstride0s", "Yinstarts", "Ystride0s", "Ystarts"]):
+                    tables[key + "/reduce_" + nm] = cap[2 + j]
+                tables[key + "/reduce_inds_starts"] = cap[7]
+                tables[key + "/reduce_inds_shape0s"] = cap[8]
+                tables[key + "/reduce_inds_buf"] = cap[12]
+            elif pname in ("plan_many_dots_gemv", "plan_reduce_gemv"):
+                tables[key + "/gstructure"] = cap[0]
+            else:
+                for j, arr in enumerate(cap):
+                    tables["%s/gstructure%d" % (key, j)] = arr
+
+    A = ra([[[0.1, 0.2], [0.3, 0.4]], [[0.5, 0.6]]])
+    X = ra([[3, 5]])
+    Y = ra([[0.0], [2, 3]])
+    gemv_case("basic", A, X, Y, ra([[1], [0]], np.int32), ra([[0], [0]], np.int32), 1.0, 1.0, 0.0)
+
+    rng = np.random.RandomState(1234)
+    ND = 20
+    A_shapes = [(10, 1 + ii % 2) for ii in range(ND)]
+    X_shapes = [(1 + ii % 2, 1) for ii in range(ND)]
+    A = ra([0.1 + rng.rand(*s) for s in A_shapes])
+    X = ra([0.1 + rng.rand(*s) for s in X_shapes])
+    Y = ra([0.1 + rng.rand(10, 1)])
+    gemv_case("manydots20", A, X, Y, ra([range(ND)], np.int32), ra([range(ND)], np.int32), 0.5, 0.6, 0.7)
+
+    # scaled-down configuration-2 workload (same generator as the benchmark)
+    from nengo_ocl_b200.synth import gemv_workload
+
+    hA, hA_js, hX, hX_js, hY = gemv_workload(seed=1, n_outputs=64)
+    toref = lambda r: RA.from_buffer(r.buf.copy(), r.starts, r.shape0s, r.shape1s, r.stride0s, r.stride1s)
+    gemv_case("config2_k64", toref(hA), toref(hX), toref(hY), toref(hA_js), toref(hX_js), 0.5, 0.1, 0.0)
+
+    # ---------------- elementwise / neuron block tables ----------------
+    rng = np.random.RandomState(7)
+    sizes = [100, 1000, 37, 2049]
+    J = ra([rng.normal(scale=1.2, size=n) for n in sizes])
+    V = ra([rng.uniform(0, 1, size=n) for n in sizes])
+    W = ra([rng.uniform(-5e-3, 5e-3, size=n) for n in sizes])
+    S = ra([np.zeros(n) for n in sizes])
+    taus = [0.02, 0.05, 0.015, 0.08]
+    T = ra([t * np.ones(n) for t, n in zip(taus, sizes)])
+    clJ, clV, clW, clS, clT = (CLRA(queue, r) for r in (J, V, W, S, T))
+    for upsample in (1, 4):
+        for r, c in ((V, clV), (W, clW), (S, clS)):
+            c.cl_buf._arr[...] = r.buf
+        plan, cap, progs = capture(lambda: nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0,
+                                                       upsample=upsample))
+        key = "lif_up%d" % upsample
+        tables[key + "/gsize"] = np.array(plan.gsize)
+        tables[key + "/bw"] = np.array(plan.bw_per_call)
+        tables[key + "/sizes"] = cap[0]
+        for j, nm in enumerate(["J", "V", "W", "outV", "outW", "outS", "tau"]):
+            tables["%s/%s_starts" % (key, nm)] = cap[1 + j]
+        refkernels.run_plan(plan, progs[-1], "cl_lif")
+        kernels[key + "/J"] = J.buf.copy()
+        kernels[key + "/V0"] = V.buf.copy()
+        kernels[key + "/W0"] = W.buf.copy()
+        kernels[key + "/tau"] = T.buf.copy()
+        kernels[key + "/V1"] = clV.cl_buf._arr.copy()
+        kernels[key + "/W1"] = clW.cl_buf._arr.copy()
+        kernels[key + "/S1"] = clS.cl_buf._arr.copy()
+    kernels["lif/sizes"] = np.array(sizes)
+
+    # several consecutive LIF steps on one population (state carried)
+    n = 4096
+    Jm = ra([rng.uniform(-1, 4, size=n)])
+    Vm = ra([np.zeros(n)])
+    Wm = ra([np.zeros(n)])
+    Sm = ra([np.zeros(n)])
+    clJm, clVm, clWm, clSm = (CLRA(queue, r) for r in (Jm, Vm, Wm, Sm))
+    plan, cap, progs = capture(lambda: nl.plan_lif(queue, 1e-3, clJm, clVm, clWm, clSm, 2e-3, 0.02, 1.0))
+    spikes = []
+    for _ in range(50):
+        refkernels.run_plan(plan, progs[-1], "cl_lif")
+        spikes.append(clSm.cl_buf._arr.copy())
+    kernels["lif50/J"] = Jm.buf.copy()
+    kernels["lif50/V"] = clVm.cl_buf._arr.copy()
+    kernels["lif50/W"] = clWm.cl_buf._arr.copy()
+    kernels["lif50/spike_counts"] = (np.array(spikes) > 0).sum(axis=0).astype(np.int32)
+
+    # LIF rate / ReLU / spiking ReLU / sigmoid
+    R = ra([np.zeros(n) for n in sizes])
+    clR = CLRA(queue, R)
+    plan, cap, progs = capture(lambda: nl.plan_lif_rate(queue, 1e-3, clJ, clR, 2e-3, clT, 1.0))
+    refkernels.run_plan(plan, progs[-1], "cl_lif_rate")
+    kernels["lif_rate/R"] = clR.cl_buf._arr.copy()
+    amp = CLRA(queue, ra([1.5 * np.ones(n) for n in sizes]))
+    plan, cap, progs = capture(lambda: nl.plan_rectified_linear(queue, clJ, clR, amp))
+    refkernels.run_plan(plan, progs[-1], "cl_relu")
+    kernels["relu/R"] = clR.cl_buf._arr.copy()
+    clV.cl_buf._arr[...] = V.buf
+    plan, cap, progs = capture(lambda: nl.plan_spiking_rectified_linear(queue, 1e-3, clJ, clV, clR, amp))
+    clJ.cl_buf._arr[...] = J.buf * 300
+    refkernels.run_plan(plan, progs[-1], "cl_spikingrelu")
+    kernels["spikingrelu/J"] = clJ.cl_buf._arr.copy()
+    kernels["spikingrelu/V1"] = clV.cl_buf._arr.copy()
+    kernels["spikingrelu/S"] = clR.cl_buf._arr.copy()
+    clJ.cl_buf._arr[...] = J.buf * 30
+    plan, cap, progs = capture(lambda: nl.plan_sigmoid(queue, clJ, clR, 0.0025))
+    refkernels.run_plan(plan, progs[-1], "cl_sigmoid")
+    kernels["sigmoid/J"] = clJ.cl_buf._arr.copy()
+    kernels["sigmoid/R"] = clR.cl_buf._arr.copy()
+    clJ.cl_buf._arr[...] = J.buf
+
+    # copy / elementwise_inc / reset / slicedcopy tables + executed outputs
+    rng = np.random.RandomState(11)
+    shapes = [(3, 5), (1, 1), (700, 1), (40, 13)]
+    Xc = ra([rng.normal(size=s) for s in shapes])
+    Yc = ra([rng.normal(size=s) for s in shapes])
+    clXc, clYc = CLRA(queue, Xc), CLRA(queue, Yc)
+    incs = np.array([0, 1, 1, 0], dtype=np.int32)
+    plan, cap, progs = capture(lambda: nl.plan_copy(queue, clXc, clYc, incs))
+    tables["copy/gsize"] = np.array(plan.gsize)
+    for j, nm in enumerate(["offsets", "shape0s", "shape1s", "Xstride0s", "Xstarts", "Ystride0s", "Ystarts",
+                            "incs"]):
+        tables["copy/" + nm] = cap[j]
+    refkernels.run_plan(plan, progs[-1], "copy")
+    kernels["copy/X"] = Xc.buf.copy()
+    kernels["copy/Y0"] = Yc.buf.copy()
+    kernels["copy/Y1"] = clYc.cl_buf._arr.copy()
+
+    Ae = ra([rng.normal(size=s) for s in [(3, 5), (1, 1), (700, 1), (1, 13)]])
+    Xe = ra([rng.normal(size=s) for s in [(3, 1), (1, 1), (1, 1), (40, 13)]])
+    clAe, clXe = CLRA(queue, Ae), CLRA(queue, Xe)
+    clYc.cl_buf._arr[...] = Yc.buf
+    plan, cap, progs = capture(lambda: nl.plan_elementwise_inc(queue, clAe, clXe, clYc))
+    tables["ewinc/gsize"] = np.array(plan.gsize)
+    tables["ewinc/offsets"] = cap[0]
+    tables["ewinc/Astarts"] = cap[4]
+    tables["ewinc/Ystarts"] = cap[12]
+    refkernels.run_plan(plan, progs[-1], "elementwise_inc")
+    kernels["ewinc/A"] = Ae.buf.copy()
+    kernels["ewinc/X"] = Xe.buf.copy()
+    kernels["ewinc/Y1"] = clYc.cl_buf._arr.copy()
+
+    # PES-style outer product with per-item alpha, set (inc=False)
+    Eo = ra([rng.normal(size=(d, 1)) for d in (4, 1, 16)])
+    Po = ra([rng.normal(size=(n, 1)) for n in (50, 300, 1024)])
+    Do = ra([np.zeros((d, n)) for d, n in ((4, 50), (1, 300), (16, 1024))])
+    clEo, clPo, clDo = CLRA(queue, Eo), CLRA(queue, Po), CLRA(queue, Do)
+    alpha = np.array([-1e-4 * 1e-3 / n for n in (50, 300, 1024)])
+    plan, cap, progs = capture(lambda: nl.plan_elementwise_inc(queue, clEo, clPo, clDo, alpha=alpha,
+                                                               outer=True, inc=False))
+    refkernels.run_plan(plan, progs[-1], "elementwise_inc")
+    kernels["outer/E"] = Eo.buf.copy()
+    kernels["outer/P"] = Po.buf.copy()
+    kernels["outer/alpha"] = alpha
+    kernels["outer/D"] = clDo.cl_buf._arr.copy()
+
+    # reset
+    Yr = ra([rng.normal(size=s) for s in [(3, 5), (1, 1), (70, 1), (4, 13)]])
+    clYr = CLRA(queue, Yr)
+    vals = refstubs.to_device(queue, np.array([0.0, 1.5, -2.0, 7.0], dtype=np.float32))
+    plan, cap, progs = capture(lambda: nl.plan_reset(queue, clYr, vals))
+    tables["reset/gsize"] = np.array(plan.gsize)
+    tables["reset/lsize"] = np.array(plan.lsize)
+    tables["reset/sizes"] = cap[0]
+    tables["reset/starts"] = cap[1]
+    tables["reset/values"] = cap[2]
+    refkernels.run_plan(plan, progs[-1], "reset")
+    kernels["reset/Y1"] = clYr.cl_buf._arr.copy()
+
+    # slicedcopy
+    Xs = ra([rng.normal(size=(n, 1)) for n in (10, 50, 33)])
+    Ys = ra([rng.normal(size=(n, 1)) for n in (20, 50, 40)])
+    xi = [np.arange(10)[::2], np.arange(50)[::-1].copy(), np.arange(33)[5:25]]
+    yi = [np.arange(20)[3:8], np.arange(50), np.arange(40)[::2]]
+    clXs, clYs = CLRA(queue, Xs), CLRA(queue, Ys)
+    clXi, clYi = CLRA(queue, ra(xi, np.int32)), CLRA(queue, ra(yi, np.int32))
+    incs3 = np.array([1, 0, 1], dtype=np.int32)
+    plan, cap, progs = capture(lambda: nl.plan_slicedcopy(queue, clXs, clYs, clXi, clYi, incs3))
+    tables["slicedcopy/gsize"] = np.array(plan.gsize)
+    tables["slicedcopy/sizes"] = cap[4]
+    tables["slicedcopy/XIstarts"] = cap[5]
+    tables["slicedcopy/YIstarts"] = cap[6]
+    refkernels.run_plan(plan, progs[-1], "slicedcopy")
+    kernels["slicedcopy/X"] = Xs.buf.copy()
+    kernels["slicedcopy/Y0"] = Ys.buf.copy()
+    kernels["slicedcopy/Y1"] = clYs.cl_buf._arr.copy()
+
+    # linear filters: lowpass (na=1, nb=1), pure gain (na=0), and a 2nd-order IIR
+    dens = [[-0.9], [], [-1.6, 0.64]]
+    nums = [[0.1], [0.5], [0.02, 0.02]]
+    shapes = [(300, 1), (5, 1), (64, 1)]
+    Xf = ra([rng.normal(size=s) for s in shapes])
+    Yf = ra([np.zeros(s) for s in shapes])
+    Af = ra(dens)
+    Bf = ra(nums)
+    Xb = ra([np.zeros((len(b), s[0])) for b, s in zip(nums, shapes)])
+    Yb = ra([np.zeros((len(a), s[0])) for a, s in zip(dens, shapes)])
+    cl = [CLRA(queue, r) for r in (Xf, Yf, Af, Bf, Xb, Yb)]
+    plans, cap, progs = capture(lambda: nl.plan_linearfilter(queue, *cl))
+    tables["linearfilter/gsize"] = np.array(plans[0].gsize)
+    tables["linearfilter/lsize"] = np.array(plans[0].lsize)
+    tables["linearfilter/offsets"] = cap[2]
+    xs_seq, ys_seq = [], []
+    for step in range(6):
+        xnew = rng.normal(size=Xf.buf.shape).astype(np.float32)
+        cl[0].cl_buf._arr[...] = xnew
+        refkernels.run_plan_grouped(plans[0], progs[-1], "linearfilter", passes=2, group_axis=1)
+        if len(plans) > 1:
+            refkernels.run_plan(plans[1], progs[-1], "linearfilter_inc")
+        xs_seq.append(xnew.copy())
+        ys_seq.append(cl[1].cl_buf._arr.copy())
+    kernels["linearfilter/xs"] = np.array(xs_seq)
+    kernels["linearfilter/ys"] = np.array(ys_seq)
+
+    np.savez_compressed(os.path.join(HERE, "tables.npz"), **tables)
+    np.savez_compressed(os.path.join(HERE, "kernels.npz"), **kernels)
+    print("wrote %d table entries, %d kernel entries" % (len(tables), len(kernels)))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

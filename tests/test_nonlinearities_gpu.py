@@ -1,0 +1,235 @@
+"""Elementwise / neuron / filter / probe plans on the GPU through the C ABI,
+against the CPU oracle and the outputs of the reference's own kernels
+(tests/golden/kernels.npz).  Structure follows the reference's
+nengo_ocl/tests/test_clra_nonlinearities.py:35-406.
+
+Tolerances: copy / reset / sliced copy / elementwise / relu / spiking relu /
+linear filter are mul-add only and compiled without FMA contraction: bit-exact.
+Kernels calling expm1/log1p/exp differ from the oracle by the math library:
+rtol 1e-5, atol 1e-6."""
+
+import numpy as np
+import pytest
+
+from nengo_ocl_b200 import cura_nonlinearities as nl
+from nengo_ocl_b200.curaggedarray import CUDARaggedArray as CLRA
+from nengo_ocl_b200.raggedarray import RaggedArray
+from nengo_ocl_b200.runtime import to_device
+from oracle import kernels as K
+
+pytestmark = pytest.mark.gpu
+RA = lambda arrays, dtype=np.float32: RaggedArray(arrays, dtype=dtype)
+
+
+def ragged_like(buf, shapes):
+    out = RA([np.zeros(s) for s in shapes])
+    out.buf[...] = buf
+    return out
+
+
+def test_lif_step_matches_reference_kernel(queue, golden_kernels, golden_tables):
+    g = golden_kernels
+    sizes = [int(s) for s in g["lif/sizes"]]
+    split = lambda buf: RA(np.split(buf, np.cumsum(sizes)[:-1]))
+    for up in (1, 4):
+        key = "lif_up%d/" % up
+        clJ, clV, clW = (CLRA(queue, split(g[key + k])) for k in ("J", "V0", "W0"))
+        clS = CLRA(queue, RA([np.zeros(n) for n in sizes]))
+        clT = CLRA(queue, split(g[key + "tau"]))
+        plan = nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0, upsample=up)
+        # block tables equal the reference's
+        t = golden_tables
+        assert plan.gsize == tuple(t["lif_up%d/gsize" % up])
+        assert np.array_equal(plan.tables["sizes"], t["lif_up%d/sizes" % up])
+        assert np.array_equal(plan.tables["J_starts"], t["lif_up%d/J_starts" % up])
+        assert plan.bw_per_call == int(t["lif_up%d/bw" % up])
+        plan()
+        assert np.allclose(clV.cl_buf.get(), g[key + "V1"], rtol=1e-5, atol=1e-6)
+        assert np.allclose(clW.cl_buf.get(), g[key + "W1"], rtol=1e-5, atol=1e-6)
+        assert np.array_equal(clS.cl_buf.get(), g[key + "S1"])
+
+
+def test_lif_large_populations_vs_oracle(queue):
+    """reference test_lif_step sizes (12k-35k neurons), float parameters"""
+    rng = np.random.RandomState(5)
+    dt = 1e-3
+    n_neurons = [12345, 23456, 34567]
+    J = RA([rng.normal(scale=1.2, size=n) for n in n_neurons])
+    V = RA([rng.uniform(low=0, high=1, size=n) for n in n_neurons])
+    W = RA([rng.uniform(low=-5 * dt, high=5 * dt, size=n) for n in n_neurons])
+    OS = RA([np.zeros(n) for n in n_neurons])
+    taus = rng.uniform(low=15e-3, high=80e-3, size=len(n_neurons))
+    T = RA([t * np.ones(n) for t, n in zip(taus, n_neurons)])
+    clJ, clV, clW, clOS, clT = (CLRA(queue, r) for r in (J, V, W, OS, T))
+    plan = nl.plan_lif(queue, dt, clJ, clV, clW, clOS, 2e-3, clT, 1.0)
+    v, w, s = K.lif(dt, J.buf, V.buf, W.buf, T.buf, np.float32(2e-3), np.float32(1.0))
+    plan()
+    assert (s > 0).sum() > 50
+    gs = clOS.cl_buf.get()
+    flips = (gs > 0) != (s > 0)
+    assert flips.mean() < 1e-4  # a 1-ulp voltage difference at threshold may flip a spike
+    ok = ~flips
+    assert np.allclose(clV.cl_buf.get()[ok], v[ok], rtol=1e-5, atol=1e-6)
+    assert np.allclose(clW.cl_buf.get()[ok], w[ok], rtol=1e-5, atol=1e-6)
+    assert np.array_equal(gs[ok], s[ok])
+    assert np.array_equal(clJ.cl_buf.get(), J.buf)
+
+
+def test_lif_fifty_steps(queue, golden_kernels):
+    g = golden_kernels
+    n = g["lif50/J"].size
+    clJ = CLRA(queue, RA([g["lif50/J"]]))
+    clV, clW, clS = (CLRA(queue, RA([np.zeros(n)])) for _ in range(3))
+    plan = nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, 0.02, 1.0)
+    counts = np.zeros(n, dtype=np.int32)
+    for _ in range(50):
+        plan()
+        counts += clS.cl_buf.get() > 0
+    moved = np.abs(counts - g["lif50/spike_counts"])
+    assert moved.max() <= 1 and (moved > 0).mean() < 2e-3
+    same = moved == 0
+    assert np.allclose(clV.cl_buf.get()[same], g["lif50/V"][same], rtol=1e-4, atol=1e-5)
+
+
+def test_rate_and_static_neurons(queue, golden_kernels):
+    g = golden_kernels
+    sizes = [int(s) for s in g["lif/sizes"]]
+    split = lambda buf: RA(np.split(np.asarray(buf, dtype=np.float32), np.cumsum(sizes)[:-1]))
+    clJ = CLRA(queue, split(g["lif_up1/J"]))
+    clT = CLRA(queue, split(g["lif_up1/tau"]))
+    clR = CLRA(queue, RA([np.zeros(n) for n in sizes]))
+    nl.plan_lif_rate(queue, 1e-3, clJ, clR, 2e-3, clT, 1.0)()
+    assert np.allclose(clR.cl_buf.get(), g["lif_rate/R"], rtol=1e-5, atol=1e-6)
+    amp = CLRA(queue, RA([1.5 * np.ones(n) for n in sizes]))
+    nl.plan_rectified_linear(queue, clJ, clR, amp)()
+    assert np.array_equal(clR.cl_buf.get(), g["relu/R"])
+    clJ2 = CLRA(queue, split(g["spikingrelu/J"]))
+    clV = CLRA(queue, split(g["lif_up1/V0"]))
+    nl.plan_spiking_rectified_linear(queue, 1e-3, clJ2, clV, clR, amp)()
+    assert np.array_equal(clV.cl_buf.get(), g["spikingrelu/V1"])
+    assert np.array_equal(clR.cl_buf.get(), g["spikingrelu/S"])
+    clJ3 = CLRA(queue, split(g["sigmoid/J"]))
+    nl.plan_sigmoid(queue, clJ3, clR, 0.0025)()
+    assert np.allclose(clR.cl_buf.get(), g["sigmoid/R"], rtol=1e-5, atol=1e-6)
+
+
+def test_copy_and_elementwise_and_reset_and_slicedcopy(queue, golden_kernels, golden_tables):
+    g, t = golden_kernels, golden_tables
+    shapes = [(3, 5), (1, 1), (700, 1), (40, 13)]
+    clX = CLRA(queue, ragged_like(g["copy/X"], shapes))
+    clY = CLRA(queue, ragged_like(g["copy/Y0"], shapes))
+    plan = nl.plan_copy(queue, clX, clY, np.array([0, 1, 1, 0], dtype=np.int32))
+    assert np.array_equal(plan.tables["offsets"], t["copy/offsets"])
+    plan()
+    assert np.array_equal(clY.cl_buf.get(), g["copy/Y1"])
+
+    clA = CLRA(queue, ragged_like(g["ewinc/A"], [(3, 5), (1, 1), (700, 1), (1, 13)]))
+    clXe = CLRA(queue, ragged_like(g["ewinc/X"], [(3, 1), (1, 1), (1, 1), (40, 13)]))
+    clY = CLRA(queue, ragged_like(g["copy/Y0"], shapes))
+    nl.plan_elementwise_inc(queue, clA, clXe, clY)()
+    assert np.array_equal(clY.cl_buf.get(), g["ewinc/Y1"])
+
+    dims = ((4, 50), (1, 300), (16, 1024))
+    clE = CLRA(queue, ragged_like(g["outer/E"], [(d, 1) for d, _ in dims]))
+    clP = CLRA(queue, ragged_like(g["outer/P"], [(n, 1) for _, n in dims]))
+    clD = CLRA(queue, RA([np.ones(s) for s in dims]))
+    nl.plan_elementwise_inc(queue, clE, clP, clD, alpha=g["outer/alpha"], outer=True, inc=False)()
+    assert np.array_equal(clD.cl_buf.get(), g["outer/D"])
+
+    clYr = CLRA(queue, RA([np.ones(s) for s in [(3, 5), (1, 1), (70, 1), (4, 13)]]))
+    vals = to_device(queue, np.array([0.0, 1.5, -2.0, 7.0], dtype=np.float32))
+    plan = nl.plan_reset(queue, clYr, vals)
+    assert plan.gsize == tuple(t["reset/gsize"]) and plan.lsize == tuple(t["reset/lsize"])
+    plan()
+    assert np.array_equal(clYr.cl_buf.get(), g["reset/Y1"])
+
+    clXs = CLRA(queue, ragged_like(g["slicedcopy/X"], [(10, 1), (50, 1), (33, 1)]))
+    clYs = CLRA(queue, ragged_like(g["slicedcopy/Y0"], [(20, 1), (50, 1), (40, 1)]))
+    xi = [np.arange(10)[::2], np.arange(50)[::-1].copy(), np.arange(33)[5:25]]
+    yi = [np.arange(20)[3:8], np.arange(50), np.arange(40)[::2]]
+    plan = nl.plan_slicedcopy(queue, clXs, clYs, CLRA(queue, RA(xi, np.int32)), CLRA(queue, RA(yi, np.int32)),
+                              np.array([1, 0, 1], dtype=np.int32))
+    plan()
+    assert np.array_equal(clYs.cl_buf.get(), g["slicedcopy/Y1"])
+
+
+def test_elementwise_inc_broadcasting_vs_numpy(queue, rng):
+    """reference test_elementwise_inc (:194-251): scalar / row / column operands"""
+    Yshapes = [(1, 1), (2, 1), (1, 5), (3, 4), (300, 1)]
+    Ashapes = [(1, 1), (1, 1), (1, 5), (3, 1), (1, 1)]
+    Xshapes = [(1, 1), (2, 1), (1, 1), (3, 4), (300, 1)]
+    A = RA([rng.normal(size=s) for s in Ashapes])
+    X = RA([rng.normal(size=s) for s in Xshapes])
+    Y = RA([rng.normal(size=s) for s in Yshapes])
+    clA, clX, clY = CLRA(queue, A), CLRA(queue, X), CLRA(queue, Y)
+    nl.plan_elementwise_inc(queue, clA, clX, clY)()
+    K.elementwise_inc(A, X, Y)
+    assert np.array_equal(clY.cl_buf.get(), Y.buf)
+
+
+def test_linearfilter_sequence(queue, golden_kernels):
+    g = golden_kernels
+    dens = [[-0.9], [], [-1.6, 0.64]]
+    nums = [[0.1], [0.5], [0.02, 0.02]]
+    shapes = [(300, 1), (5, 1), (64, 1)]
+    cl = [CLRA(queue, RA([np.zeros(s) for s in shapes])) for _ in range(2)]
+    cl += [CLRA(queue, RA(dens)), CLRA(queue, RA(nums))]
+    cl += [CLRA(queue, RA([np.zeros((len(b), s[0])) for b, s in zip(nums, shapes)])),
+           CLRA(queue, RA([np.zeros((len(a), s[0])) for a, s in zip(dens, shapes)]))]
+    plans = nl.plan_linearfilter(queue, *cl)
+    for step in range(6):
+        cl[0].cl_buf.set(g["linearfilter/xs"][step])
+        for p in plans:
+            p()
+        assert np.array_equal(cl[1].cl_buf.get(), g["linearfilter/ys"][step]), step
+
+
+def test_lowpass_many_items(queue, rng):
+    n_items = 3000
+    X = RA([rng.normal(size=(rng.randint(1, 20), 1)) for _ in range(n_items)])
+    Y = RA([rng.normal(size=X[i].shape) for i in range(n_items)])
+    a = rng.uniform(-0.99, -0.5, size=n_items)
+    A = RA([[v] for v in a])
+    B = RA([[1 + v] for v in a])
+    Xb = RA([np.zeros((1, X[i].shape[0])) for i in range(n_items)])
+    Yb = RA([np.zeros((1, X[i].shape[0])) for i in range(n_items)])
+    cl = [CLRA(queue, r) for r in (X, Y, A, B, Xb, Yb)]
+    (plan,) = nl.plan_linearfilter(queue, *cl)
+    xp, yp = np.zeros(n_items, np.int32), np.zeros(n_items, np.int32)
+    for _ in range(3):
+        plan()
+        K.linearfilter(X, Y, A, B, Xb, Yb, xp, yp)
+    assert np.array_equal(cl[1].cl_buf.get(), Y.buf)
+
+
+def test_probes_timeupdate_presentinput(queue, rng):
+    step = CLRA(queue, RA([[0.0]]))
+    time = CLRA(queue, RA([[0.0]]))
+    tplan = nl.plan_timeupdate(queue, step, time, 0.001)
+    sig = RA([rng.normal(size=(4, 3)), rng.normal(size=(7, 1)), rng.normal(size=(1, 1))])
+    sig.add_views([sig.starts[0] + 1], [4], [1], [3], [1])  # a column view of item 0
+    X = CLRA(queue, sig)
+    n_pre = 8
+    periods = [1, 2, 1, 3]
+    Y = CLRA(queue, RA([np.zeros((n_pre, int(s))) for s in sig.sizes]))
+    pplan = nl.plan_probes(queue, periods, X, Y)
+    table = RA([rng.normal(size=(5, 2)), rng.normal(size=(3, 4))])
+    S = CLRA(queue, table)
+    out = CLRA(queue, RA([np.zeros(2), np.zeros(4)]))
+    tt = step[[0, 0]]
+    iplan = nl.plan_presentinput(queue, out, tt, S, 0.001)
+    cd = np.asarray(periods, np.float32) - 1
+    pos = np.zeros(4, np.int32)
+    Yh = RA([np.zeros((n_pre, int(s))) for s in sig.sizes])
+    for i in range(6):
+        tplan()
+        iplan()
+        pplan()
+        K.probes(cd, pos, np.asarray(periods, np.float32), sig, Yh)
+        assert step[0][0, 0] == i + 1
+        assert time[0][0, 0] == np.float32(0.001 * (i + 1))
+        assert np.array_equal(out[0][:, 0], table[0][(i + 1) % 5])
+        assert np.array_equal(out[1][:, 0], table[1][(i + 1) % 3])
+    assert np.array_equal(pplan.cl_bufpositions.get(), pos)
+    assert pos.tolist() == [6, 3, 6, 2]
+    assert np.array_equal(Y.cl_buf.get(), Yh.buf)

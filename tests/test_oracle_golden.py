@@ -1,0 +1,171 @@
+"""Pin the CPU oracle: known answers from the reference's own tests, and
+outputs of the reference's own kernel source executed on the CPU
+(tests/golden/kernels.npz, made by tests/golden/make_golden.py)."""
+
+import numpy as np
+import pytest
+
+from nengo_ocl_b200.raggedarray import RaggedArray
+from oracle import kernels as K
+
+RA = lambda arrays, dtype=np.float32: RaggedArray(arrays, dtype=dtype)
+
+
+def ragged_like(buf, shapes):
+    """Ragged array with the given item shapes and flat contents."""
+    out = RA([np.zeros(s) for s in shapes])
+    out.buf[...] = buf
+    return out
+
+
+# ---- GEMV known answers (reference tests/test_clra_gemv.py:60-93) --------------
+@pytest.mark.parametrize("fn", [K.gemv_ref, K.gemv_many_dots, K.gemv_block])
+def test_gemv_basic_known_answer(fn):
+    A = RA([[[0.1, 0.2], [0.3, 0.4]], [[0.5, 0.6]]])
+    X = RA([[3, 5]])
+    Y = RA([[0.0], [2, 3]])
+    A_js = RA([[1], [0]], dtype=np.int32)
+    X_js = RA([[0], [0]], dtype=np.int32)
+    fn(1.0, A, A_js, X, X_js, 1.0, Y)
+    assert np.allclose(Y[0].ravel(), [4.5])
+    assert np.allclose(Y[1].ravel(), [3.3, 5.9])
+
+
+def _check_from_shapes(fn, A_shapes, X_shapes, A_js, X_js, alpha=0.5, beta=0.6, gamma=0.7):
+    """reference tests/test_clra_gemv.py:165-215 (RandomState(1234))"""
+    rng = np.random.RandomState(1234)
+    A = RA([0.1 + rng.rand(*shp) for shp in A_shapes])
+    X = RA([0.1 + rng.rand(*shp) for shp in X_shapes])
+    Y = RA([0.1 + rng.rand(A_shapes[A_js[ii][0]][0], X_shapes[X_js[ii][0]][1]) for ii in range(len(A_js))])
+    Y0 = [np.array(Y[i]) for i in range(len(Y))]
+    A_js = RA(A_js, dtype=np.int32)
+    X_js = RA(X_js, dtype=np.int32)
+    fn(alpha, A, A_js, X, X_js, beta, Y, gamma=gamma)
+    for i in range(len(A_js)):
+        ref = gamma + beta * Y0[i] + alpha * sum(
+            np.dot(A[aj], X[xj]) for aj, xj in zip(A_js[i].ravel(), X_js[i].ravel()))
+        assert np.allclose(ref, Y[i], atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("fn", [K.gemv_ref, K.gemv_many_dots, K.gemv_block])
+def test_gemv_shapes_family(fn):
+    _check_from_shapes(fn, [(1, 1)], [(1, 1)], [[0]], [[0]])
+    _check_from_shapes(fn, [(10, 1)], [(1, 1)], [[0]], [[0]])
+    _check_from_shapes(fn, [(2001, 1)], [(1, 1)], [[0]], [[0]])
+    for ND in (2, 20, 100):
+        _check_from_shapes(fn, [(10, 1 + ii % 2) for ii in range(ND)], [(1 + ii % 2, 1) for ii in range(ND)],
+                           [range(ND)], [range(ND)])
+    _check_from_shapes(fn, [(200, ii + 1) for ii in range(20)], [(ii + 1, 1) for ii in range(20)],
+                       [range(20)], [range(20)])
+    _check_from_shapes(fn, [(40, 300)], [(300, 1)], [[0]], [[0]])
+
+
+def test_gemv_variants_agree_with_exact_value(rng):
+    from nengo_ocl_b200.synth import gemv_workload
+
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=24, max_rows=64)
+    outs = []
+    for fn in (K.gemv_ref, K.gemv_many_dots, K.gemv_block):
+        Yc = RaggedArray.from_buffer(Y.buf.copy(), Y.starts, Y.shape0s, Y.shape1s, Y.stride0s, Y.stride1s)
+        fn(0.5, A, A_js, X, X_js, 0.1, Yc)
+        outs.append(Yc)
+    vals, mags = K.gemv_exact(0.5, A, A_js, X, X_js, 0.1, Y)
+    for Yc in outs:
+        for i in range(len(Y)):
+            # float32 evaluation error is bounded relative to the sum of |terms|
+            assert np.all(np.abs(Yc[i][:, 0] - vals[i]) <= 1e-5 * mags[i] + 1e-7)
+
+
+# ---- kernels executed from the reference's own source --------------------------
+def test_lif_matches_reference_kernel(golden_kernels):
+    g = golden_kernels
+    for up in (1, 4):
+        key = "lif_up%d/" % up
+        V, W, S = K.lif(1e-3, g[key + "J"], g[key + "V0"], g[key + "W0"], g[key + "tau"],
+                        np.float32(2e-3), np.float32(1.0), upsample=up)
+        # same formula, libm vs correctly-rounded expm1/log1p: a few ulp at most
+        assert np.allclose(V, g[key + "V1"], rtol=1e-5, atol=1e-6)
+        assert np.allclose(W, g[key + "W1"], rtol=1e-5, atol=1e-6)
+        assert np.array_equal(S > 0, g[key + "S1"] > 0)
+        assert np.array_equal(S, g[key + "S1"])
+        assert (S > 0).sum() >= 1  # the spiking branch is exercised (more so in the 50-step test)
+
+
+def test_lif_fifty_steps_matches_reference_kernel(golden_kernels):
+    g = golden_kernels
+    J = g["lif50/J"]
+    V = np.zeros_like(J)
+    W = np.zeros_like(J)
+    counts = np.zeros(J.shape, dtype=np.int32)
+    for _ in range(50):
+        V, W, S = K.lif(1e-3, J, V, W, np.float32(0.02), np.float32(2e-3), np.float32(1.0))
+        counts += S > 0
+    assert counts.sum() > 1000
+    # a 1-ulp difference in V next to the threshold can move a spike by one step
+    moved = np.abs(counts - g["lif50/spike_counts"])
+    assert moved.max() <= 1 and (moved > 0).mean() < 2e-3
+    same = moved == 0
+    assert np.allclose(V[same], g["lif50/V"][same], rtol=1e-4, atol=1e-5)
+
+
+def test_rate_neurons_match_reference_kernels(golden_kernels):
+    g = golden_kernels
+    J = g["lif_up1/J"]
+    tau = g["lif_up1/tau"]
+    assert np.allclose(K.lif_rate(J, tau, np.float32(2e-3), np.float32(1.0)), g["lif_rate/R"], rtol=1e-5,
+                       atol=1e-6)
+    assert np.array_equal(K.relu(J, np.float32(1.5)), g["relu/R"])
+    V1, S = K.spiking_relu(1e-3, g["spikingrelu/J"], g["lif_up1/V0"], np.float32(1.5))
+    assert np.array_equal(V1, g["spikingrelu/V1"]) and np.array_equal(S, g["spikingrelu/S"])
+    assert np.allclose(K.sigmoid(g["sigmoid/J"], np.float32(0.0025)), g["sigmoid/R"], rtol=1e-5, atol=1e-6)
+
+
+def test_copy_elementwise_reset_slicedcopy_match_reference_kernels(golden_kernels):
+    g = golden_kernels
+    shapes = [(3, 5), (1, 1), (700, 1), (40, 13)]
+    X = ragged_like(g["copy/X"], shapes)
+    Y = ragged_like(g["copy/Y0"], shapes)
+    K.copy(X, Y, [0, 1, 1, 0])
+    assert np.array_equal(Y.buf, g["copy/Y1"])
+
+    A = ragged_like(g["ewinc/A"], [(3, 5), (1, 1), (700, 1), (1, 13)])
+    Xe = ragged_like(g["ewinc/X"], [(3, 1), (1, 1), (1, 1), (40, 13)])
+    Y = ragged_like(g["copy/Y0"], shapes)
+    K.elementwise_inc(A, Xe, Y)
+    assert np.array_equal(Y.buf, g["ewinc/Y1"])
+
+    dims = ((4, 50), (1, 300), (16, 1024))
+    E = ragged_like(g["outer/E"], [(d, 1) for d, _ in dims])
+    P = ragged_like(g["outer/P"], [(n, 1) for _, n in dims])
+    D = RA([np.zeros(s) for s in dims])
+    K.elementwise_inc(E, P, D, alpha=g["outer/alpha"], outer=True, inc=False)
+    assert np.array_equal(D.buf, g["outer/D"])
+
+    Yr = RA([np.ones(s) for s in [(3, 5), (1, 1), (70, 1), (4, 13)]])
+    K.reset(Yr, [0.0, 1.5, -2.0, 7.0])
+    assert np.array_equal(Yr.buf, g["reset/Y1"])
+
+    Xs = ragged_like(g["slicedcopy/X"], [(10, 1), (50, 1), (33, 1)])
+    Ys = ragged_like(g["slicedcopy/Y0"], [(20, 1), (50, 1), (40, 1)])
+    xi = [np.arange(10)[::2], np.arange(50)[::-1].copy(), np.arange(33)[5:25]]
+    yi = [np.arange(20)[3:8], np.arange(50), np.arange(40)[::2]]
+    K.slicedcopy(Xs, Ys, RA(xi, np.int32), RA(yi, np.int32), [1, 0, 1])
+    assert np.array_equal(Ys.buf, g["slicedcopy/Y1"])
+
+
+def test_linearfilter_matches_reference_kernel(golden_kernels):
+    g = golden_kernels
+    dens = [[-0.9], [], [-1.6, 0.64]]
+    nums = [[0.1], [0.5], [0.02, 0.02]]
+    shapes = [(300, 1), (5, 1), (64, 1)]
+    X = RA([np.zeros(s) for s in shapes])
+    Y = RA([np.zeros(s) for s in shapes])
+    A, B = RA(dens), RA(nums)
+    Xb = RA([np.zeros((len(b), s[0])) for b, s in zip(nums, shapes)])
+    Yb = RA([np.zeros((len(a), s[0])) for a, s in zip(dens, shapes)])
+    xpos = np.zeros(3, dtype=np.int32)
+    ypos = np.zeros(3, dtype=np.int32)
+    for step in range(6):
+        X.buf[...] = g["linearfilter/xs"][step]
+        K.linearfilter(X, Y, A, B, Xb, Yb, xpos, ypos)
+        assert np.array_equal(Y.buf, g["linearfilter/ys"][step]), step

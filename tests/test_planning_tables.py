@@ -1,0 +1,168 @@
+"""Integer index plans are bit-identical to what the reference's planners
+upload (tests/golden/tables.npz, captured from the reference's own plan_*
+functions by tests/golden/make_golden.py).  Host-only: no device needed."""
+
+import numpy as np
+import pytest
+
+from nengo_ocl_b200 import cura_gemv, cura_nonlinearities as nl
+from nengo_ocl_b200.raggedarray import RaggedArray
+from nengo_ocl_b200.synth import gemv_workload
+
+RA = lambda arrays, dtype=np.float32: RaggedArray(arrays, dtype=dtype)
+
+
+class HostQueue:
+    """Enough of a queue for the host-side planners."""
+
+    class device:
+        max_work_group_size = 1024
+
+
+def gemv_cases():
+    A = RA([[[0.1, 0.2], [0.3, 0.4]], [[0.5, 0.6]]])
+    X = RA([[3, 5]])
+    Y = RA([[0.0], [2, 3]])
+    yield "basic", (A, RA([[1], [0]], np.int32), X, RA([[0], [0]], np.int32), Y), (1.0, 1.0, 0.0)
+    rng = np.random.RandomState(1234)
+    ND = 20
+    A = RA([0.1 + rng.rand(10, 1 + ii % 2) for ii in range(ND)])
+    X = RA([0.1 + rng.rand(1 + ii % 2, 1) for ii in range(ND)])
+    Y = RA([0.1 + rng.rand(10, 1)])
+    yield "manydots20", (A, RA([range(ND)], np.int32), X, RA([range(ND)], np.int32), Y), (0.5, 0.6, 0.7)
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=64)
+    yield "config2_k64", (A, A_js, X, X_js, Y), (0.5, 0.1, 0.0)
+
+
+@pytest.mark.parametrize("case", list(gemv_cases()), ids=lambda c: c[0])
+def test_gemv_index_tables_match_reference(case, golden_tables):
+    tag, (A, A_js, X, X_js, Y), (alpha, beta, gamma) = case
+    g = golden_tables
+    prog = cura_gemv.gemv_geometry(HostQueue(), alpha, A, A_js, X, X_js, beta, Y, gamma=gamma)
+    items = list(range(len(Y)))
+
+    # per-item table of many_dots / reduce (cl_geometry_and_textconf)
+    table, _, D, n_vars, stride = prog.gstructure_table(items)
+    for pname in ("plan_many_dots_gemv", "plan_reduce_gemv"):
+        ref = g["%s/%s/gstructure" % (tag, pname)]
+        assert table.dtype == ref.dtype == np.int32
+        assert np.array_equal(table, ref)
+    assert tuple(g[tag + "/plan_many_dots_gemv/plan0/gsize"]) == prog.many_dots_launch_shape(items)[0]
+    assert tuple(g[tag + "/plan_many_dots_gemv/plan0/lsize"]) == prog.many_dots_launch_shape(items)[1]
+    assert tuple(g[tag + "/plan_reduce_gemv/plan0/gsize"]) == prog.reduce_launch_shape(items)[0]
+    assert tuple(g[tag + "/plan_reduce_gemv/plan0/lsize"]) == prog.reduce_launch_shape(items)[1]
+    assert int(g[tag + "/plan_many_dots_gemv/plan0/bw"]) == cura_gemv.bw_from_geometry(prog.geometry, items)
+    assert int(g[tag + "/plan_many_dots_gemv/plan0/flops"]) == cura_gemv.flops_from_geometry(prog.geometry, items)
+
+    # 32 x 128 tile table and reduce tables of block_impl
+    t = prog.block_tile_tables(items)
+    key = tag + "/plan_block_gemv"
+    assert np.array_equal(t["gstructure"], g[key + "/gstructure"])
+    assert t["Ybuf_size"] == int(g[key + "/Ybuf_size"])
+    red = t["reduce"]
+    for col, nm in enumerate(["Yshape0s", "Yinstride0s", "Yinstarts", "Ystride0s", "Ystarts"]):
+        assert np.array_equal(red[:, col], g[key + "/reduce_" + nm])
+    flat = RA(t["reduce_inds"], dtype=np.int32)
+    assert np.array_equal(flat.starts, g[key + "/reduce_inds_starts"])
+    assert np.array_equal(flat.shape0s, g[key + "/reduce_inds_shape0s"])
+    assert np.array_equal(flat.buf, g[key + "/reduce_inds_buf"])
+    assert tuple(g[key + "/plan0/gsize"]) == (4, 32, len(t["gstructure"]))
+    assert tuple(g[key + "/plan1/gsize"]) == (32, len(red))
+    assert int(g[key + "/plan1/bw"]) == t["bw_reduce"]
+
+
+def test_dispatcher_item_split_matches_reference(golden_tables):
+    """plan_ragged_gather_gemv: <=2 terms with a long inner product -> reduce,
+    rest -> many_dots (nengo_ocl/clra_gemv.py:1206-1232)."""
+    g = golden_tables
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=64)
+    prog = cura_gemv.gemv_geometry(HostQueue(), 0.5, A, A_js, X, X_js, 0.1, Y)
+    geo = prog.geometry
+    long_dots = [i for i in range(len(Y)) if len(geo[i]["dots"]) <= 2
+                 and max([0] + [d["a_shape1"] for d in geo[i]["dots"]]) > 16]
+    rest = [i for i in range(len(Y)) if i not in set(long_dots)]
+    key = "config2_k64/plan_ragged_gather_gemv"
+    assert int(g[key + "/n_plans"]) == 2
+    assert np.array_equal(prog.gstructure_table(long_dots)[0], g[key + "/gstructure0"])
+    assert np.array_equal(prog.gstructure_table(rest)[0], g[key + "/gstructure1"])
+    assert tuple(g[key + "/plan0/gsize"]) == prog.reduce_launch_shape(long_dots)[0]
+    assert tuple(g[key + "/plan1/gsize"]) == prog.many_dots_launch_shape(rest)[0]
+
+
+def test_worklist_covers_every_row_once():
+    A, A_js, X, X_js, Y = gemv_workload(seed=3, n_outputs=200)
+    prog = cura_gemv.gemv_geometry(HostQueue(), 1.0, A, A_js, X, X_js, 1.0, Y)
+    table, _, D, _, _ = prog.gstructure_table(range(len(Y)))
+    cta, warp = cura_gemv.build_worklist(table, D)
+    seen = [np.zeros(int(m), dtype=int) for m in Y.shape0s]
+    for item, r0, cnt, _ in np.vstack([cta, warp]):
+        assert cnt >= 1
+        seen[item][r0:r0 + cnt] += 1
+    assert all((s == 1).all() for s in seen)
+    assert (warp[:, 2] <= 32).all() and (cta[:, 2] <= 1024).all()
+    # staged rows of a unit fit the shared-memory buffer when a single row does
+    n_dots = table[:, 4 * D + 2]
+    for item, r0, cnt, _ in cta:
+        row = table[item, 3 * D:3 * D + n_dots[item]].sum()
+        if row * 8 <= 8192 - 4 * n_dots[item] - 4:
+            assert cnt * row + 4 * n_dots[item] + 4 <= 8192
+
+
+# ---- blockify tables of the elementwise / neuron plans -------------------------
+def test_template_block_tables_match_reference(golden_tables):
+    g = golden_tables
+    sizes = [100, 1000, 37, 2049]
+    J = RA([np.zeros(n) for n in sizes])
+    best = None
+    for bs in [16, 32, 64, 128, 256, 512, 1024]:
+        s, inds, starts = nl.blockify_vector(bs, J)
+        if best is None or len(s) < len(best[1]):
+            best = (bs, s, inds, starts)
+    bs, s, inds, starts = best
+    for up in (1, 4):
+        key = "lif_up%d" % up
+        assert tuple(g[key + "/gsize"]) == (bs, len(s))
+        assert np.array_equal(s, g[key + "/sizes"])
+        for nm in ["J", "V", "W", "outV", "outW", "outS", "tau"]:
+            assert np.array_equal(starts, g["%s/%s_starts" % (key, nm)])
+        assert int(g[key + "/bw"]) == 7 * 4 * sum(sizes)
+
+
+def test_copy_elementwise_reset_slicedcopy_tables_match_reference(golden_tables):
+    g = golden_tables
+    shapes = [(3, 5), (1, 1), (700, 1), (40, 13)]
+    X = RA([np.zeros(s) for s in shapes])
+    sizes, inds, offsets = nl.blockify_ij(256, X)
+    assert tuple(g["copy/gsize"]) == (256, len(sizes))
+    assert np.array_equal(offsets, g["copy/offsets"])
+    assert np.array_equal(X.shape0s[inds], g["copy/shape0s"])
+    assert np.array_equal(X.shape1s[inds], g["copy/shape1s"])
+    assert np.array_equal(X.stride0s[inds], g["copy/Xstride0s"])
+    assert np.array_equal(X.starts[inds], g["copy/Xstarts"])
+    assert np.array_equal(np.array([0, 1, 1, 0])[inds], g["copy/incs"])
+    assert np.array_equal(offsets, g["ewinc/offsets"])
+    assert np.array_equal(X.starts[inds], g["ewinc/Ystarts"])
+    A = RA([np.zeros(s) for s in [(3, 5), (1, 1), (700, 1), (1, 13)]])
+    assert np.array_equal(A.starts[inds], g["ewinc/Astarts"])
+
+    Yr = RA([np.zeros(s) for s in [(3, 5), (1, 1), (70, 1), (4, 13)]])
+    rs, rinds, rstarts = nl.blockify_matrix(16, Yr)
+    assert np.array_equal(rs, g["reset/sizes"])
+    assert np.array_equal(rstarts, g["reset/starts"])
+    assert np.array_equal(np.array([0.0, 1.5, -2.0, 7.0], np.float32)[rinds], g["reset/values"])
+    assert tuple(g["reset/lsize"]) == (16, 16)
+    assert tuple(g["reset/gsize"]) == (16, -(-len(rs) // 16) * 16)
+
+    xi = RA([np.arange(10)[::2], np.arange(50)[::-1].copy(), np.arange(33)[5:25]], np.int32)
+    yi = RA([np.arange(20)[3:8], np.arange(50), np.arange(40)[::2]], np.int32)
+    ss, sinds, (xs, ys) = nl.blockify_vectors(16, [xi, yi])
+    assert np.array_equal(ss, g["slicedcopy/sizes"])
+    assert np.array_equal(xs, g["slicedcopy/XIstarts"])
+    assert np.array_equal(ys, g["slicedcopy/YIstarts"])
+    assert tuple(g["slicedcopy/gsize"]) == (16, -(-len(ss) // 16) * 16)
+
+    Xf = RA([np.zeros(s) for s in [(300, 1), (5, 1), (64, 1)]])
+    fs, finds, foffs = nl.blockify_ij(256, Xf)
+    assert tuple(g["linearfilter/lsize"]) == (256, 1)
+    assert tuple(g["linearfilter/gsize"]) == (256, len(fs))
+    assert np.array_equal(foffs, g["linearfilter/offsets"])
