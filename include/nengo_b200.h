@@ -80,6 +80,8 @@ int nb2_ipc_close_handle(void* dptr);
 #define NB2_GEMV_CTA 0      /* CTA per unit, 128-bit global loads into smem */
 #define NB2_GEMV_CTA_BULK 1 /* CTA per unit, cp.async.bulk + mbarrier staging */
 #define NB2_GEMV_WARP 2     /* warp per unit, tiny items */
+#define NB2_GEMV_ROWS 4     /* CTA per row group, direct global loads, 8 rows per thread;
+                               worklist .w = log2(lanes per row), row count <= 8 * (256 >> .w) */
 #define NB2_GEMV_ABUF 8192
 #define NB2_GEMV_XBUF 2048
 #define NB2_GEMV_RMAX 1024
@@ -88,6 +90,23 @@ int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, int gstride, 
                     const float* X, const float* Yin, float* Y, double alpha, double beta,
                     double gamma, const float* alphas, const float* betas, const float* gammas,
                     int* status);
+
+/* The main GEMV path: persistent CTAs, each a producer warp + 8 consumer warps
+ * over a 3-stage shared-memory ring fed by cp.async.bulk / cp.async copies.
+ * Same math and reference counterparts as nb2_gemv_ragged.  `records`:
+ * n_records x 32 int32 work records (layout documented in
+ * nengo_ocl_b200/cura_gemv.py:build_pipe_records); `ranges`: n_ctas x 2 int32
+ * [begin, end) record ranges, one per CTA; record i of a range is consumed by
+ * warp i % NB2_PIPE_CONSUMER_WARPS (chains are interleaved accordingly). */
+#define NB2_PIPE_STAGE_FLOATS 1408
+#define NB2_PIPE_XBUF 192
+#define NB2_PIPE_RMAX 128
+#define NB2_PIPE_STAGES 16
+#define NB2_PIPE_CONSUMER_WARPS 8
+int nb2_gemv_pipelined(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
+                       const float* A, const float* X, const float* Yin, float* Y, double alpha,
+                       double beta, double gamma, const float* alphas, const float* betas,
+                       const float* gammas, int* status);
 
 /* ---- elementwise family (clra_nonlinearities.py) -------------------------
  * All index tables have the layout the reference's plan functions upload. */

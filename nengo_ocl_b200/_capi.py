@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libnengo_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "nengo_b200.h")
 
 NB2_ERR_TIMEOUT = -4
-GEMV_CTA, GEMV_CTA_BULK, GEMV_WARP = 0, 1, 2
+GEMV_CTA, GEMV_CTA_BULK, GEMV_WARP, GEMV_PIPE = 0, 1, 2, 3
 GEMV_ABUF, GEMV_XBUF, GEMV_RMAX = 8192, 2048, 1024
 NEURON_LIF, NEURON_LIF_RATE, NEURON_RELU, NEURON_SPIKING_RELU, NEURON_SIGMOID = range(5)
 
@@ -72,6 +72,8 @@ _SIGNATURES = {
     "nb2_ipc_close_handle": [_P],
     "nb2_gemv_ragged": [_P, c_int, _P, c_int, c_int, _P, _P, c_int, _P, _P, _P, _P, c_double, c_double,
                         c_double, _P, _P, _P, _P],
+    "nb2_gemv_pipelined": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, c_double, c_double, _P, _P, _P,
+                           _P],
     "nb2_timeupdate": [_P, _P, _P, c_double],
     "nb2_reset": [_P, c_int, _P, _P, _P, _P],
     "nb2_copy": [_P, c_int, c_int] + [_P] * 10,

@@ -23,6 +23,7 @@ COMMON = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-I", os.path
 UNITS = [
     ("nb2_runtime.cu", []),
     ("nb2_gemv.cu", []),
+    ("nb2_gemv_pipe.cu", []),
     ("nb2_elementwise.cu", ["-fmad=false"]),
     ("nb2_neurons.cu", ["-fmad=false"]),
     ("nb2_direct.cu", ["-fmad=false"]),

@@ -304,6 +304,76 @@ nb2_gemv_warp_kernel(const GemvParams p) {
   }
 }
 
+
+// ---- row-group kernel -------------------------------------------------------
+// One CTA per unit of up to 8 * P rows (P = 256 / G).  G = 2^logG lanes share a
+// row and stride over its columns, so a warp reads 32 / G contiguous row
+// chunks; every thread owns 8 rows (8 independent accumulators, 8 loads in
+// flight per column step) and loads each gathered x value once for all of
+// them.  A is read straight from global memory: with ~2048 resident threads
+// per SM each holding >= 8 outstanding 4-byte loads, enough bytes are in flight
+// to cover HBM latency without a shared-memory ring.
+#define ROWS_PER_THREAD 8
+__global__ void __launch_bounds__(GEMV_THREADS)
+nb2_gemv_rows_kernel(const GemvParams p) {
+  const int tid = threadIdx.x;
+  const int4 unit = p.worklist[blockIdx.x];
+  const int* __restrict__ g = p.gstructure + (size_t)unit.x * p.gstride;
+  const int r0 = unit.y;
+  const int R = unit.z;
+  const int logG = unit.w;
+  const int G = 1 << logG;
+  const int P = GEMV_THREADS >> logG;
+  const int lg = tid & (G - 1);
+  const int row0 = tid >> logG;
+  const int D = p.D;
+  const int n_dots = __ldg(g + 4 * D + 2);
+  const int* xst = p.xstrides ? p.xstrides + (size_t)unit.x * D : nullptr;
+
+  float acc[ROWS_PER_THREAD];
+  int roff[ROWS_PER_THREAD];
+#pragma unroll
+  for (int j = 0; j < ROWS_PER_THREAD; ++j) {
+    acc[j] = 0.0f;
+    roff[j] = r0 + min(row0 + j * P, R - 1);  // rows past the end re-read the last row
+  }
+  if (row0 < R) {
+    for (int ii = 0; ii < n_dots; ++ii) {
+      const int N = __ldg(g + 3 * D + ii);
+      const int s0 = __ldg(g + 2 * D + ii);
+      const float* __restrict__ a = p.A + __ldg(g + 1 * D + ii) + lg;
+      const int xs = xst ? __ldg(xst + ii) : 1;
+      const float* __restrict__ x = p.X + __ldg(g + ii) + (size_t)lg * xs;
+      const float* ap[ROWS_PER_THREAD];
+#pragma unroll
+      for (int j = 0; j < ROWS_PER_THREAD; ++j) ap[j] = a + (size_t)roff[j] * s0;
+#pragma unroll 2
+      for (int c = lg; c < N; c += G) {
+        const float xv = __ldg(x);
+        x += (size_t)G * xs;
+#pragma unroll
+        for (int j = 0; j < ROWS_PER_THREAD; ++j) {
+          acc[j] = fmaf(__ldg(ap[j]), xv, acc[j]);
+          ap[j] += G;
+        }
+      }
+    }
+  }
+  const int y_in_start = __ldg(g + 4 * D + 0);
+  const int y_start = __ldg(g + 4 * D + 1);
+  const int bb = __ldg(g + 4 * D + 4);
+#pragma unroll
+  for (int j = 0; j < ROWS_PER_THREAD; ++j) {
+    float t = acc[j];
+    for (int off = G >> 1; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    const int r = row0 + j * P;
+    if (lg == 0 && r < R) {
+      const float yin = p.Yin[y_in_start + r0 + r];
+      p.Y[y_start + r0 + r] = gemv_epilogue(p, bb, yin, t);
+    }
+  }
+}
+
 static const size_t kGemvSmem = (size_t)(GEMV_ABUF + GEMV_XBUF + GEMV_RMAX) * sizeof(float);
 
 // Opt in to >48 KB dynamic shared memory once per device and kernel variant.
@@ -347,6 +417,8 @@ extern "C" int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, in
   } else if (kind == NB2_GEMV_CTA) {
     NB2_CUDA(gemv_optin_smem(0));
     nb2_gemv_cta_kernel<0><<<n_units, GEMV_THREADS, kGemvSmem, s>>>(p);
+  } else if (kind == NB2_GEMV_ROWS) {
+    nb2_gemv_rows_kernel<<<n_units, GEMV_THREADS, 0, s>>>(p);
   } else {
     NB2_REQUIRE(false, "unknown gemv kind");
   }

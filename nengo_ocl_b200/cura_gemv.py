@@ -22,7 +22,7 @@ from nengo_ocl_b200.plan import Plan
 from nengo_ocl_b200.runtime import zeros
 
 # default staging variant of the CTA kernel (can be overridden per planner call)
-DEFAULT_CTA_KIND = _capi.GEMV_CTA_BULK
+DEFAULT_CTA_KIND = 3  # GEMV_PIPE
 
 
 def float_cl_clra(queue, arg, cl_dtype, N):
@@ -140,6 +140,201 @@ def build_worklist(gstructure, D):
     cta_units[:, 1] = r0
     cta_units[:, 2] = cnt
     return cta_units, warp_units
+
+
+GEMV_ROWS = 4  # row-group kernel, direct global loads (csrc/nb2_gemv.cu)
+ROWS_PER_THREAD = 8
+
+
+def build_rows_worklist(gstructure, D):
+    """Units for the row-group kernel: {item row, first row, rows, log2 G}.
+
+    G lanes per row = next power of two >= the widest term (at most 32), so a
+    warp's loads cover contiguous row chunks; a unit spans 8 * (256 / G) rows.
+    Tiny items still go to the warp kernel."""
+    n_items = gstructure.shape[0]
+    empty = np.zeros((0, 4), dtype=np.int32)
+    if n_items == 0:
+        return empty, empty
+    n_dots = gstructure[:, 4 * D + 2].astype(np.int64)
+    M = gstructure[:, 4 * D + 3].astype(np.int64)
+    if D > 0:
+        Ns = gstructure[:, 3 * D:4 * D].astype(np.int64)
+        mask = np.arange(D)[None, :] < n_dots[:, None]
+        row_floats = (Ns * mask).sum(axis=1)
+        wmax = np.maximum((Ns * mask).max(axis=1), 1)
+    else:
+        row_floats = np.zeros(n_items, dtype=np.int64)
+        wmax = np.ones(n_items, dtype=np.int64)
+    small = (M <= 32) & (M * row_floats <= 1024) & (n_dots <= 64)
+    rows = np.arange(n_items)
+    warp_rows = rows[small & (M > 0)]
+    warp_units = np.zeros((len(warp_rows), 4), dtype=np.int32)
+    warp_units[:, 0] = warp_rows
+    warp_units[:, 2] = M[warp_rows]
+    big = rows[~small & (M > 0)]
+    if len(big) == 0:
+        return empty, warp_units
+    logG = np.minimum(np.ceil(np.log2(wmax[big])).astype(np.int64), 5)
+    Mb = M[big]
+    # few rows: widen G so that the threads of the CTA are not left idle
+    logG = np.maximum(logG, np.minimum(5, np.floor(np.log2(np.maximum(256 * ROWS_PER_THREAD // np.maximum(Mb, 1), 1)))
+                                       .astype(np.int64) - 3))
+    logG = np.clip(logG, 0, 5)
+    R = ROWS_PER_THREAD * (256 >> logG)
+    n_units = -(-Mb // R)
+    Re = -(-Mb // n_units)
+    item_of_unit = np.repeat(big, n_units)
+    first_unit = np.cumsum(n_units) - n_units
+    local = np.arange(int(n_units.sum())) - np.repeat(first_unit, n_units)
+    r0 = local * np.repeat(Re, n_units)
+    cnt = np.minimum(np.repeat(Re, n_units), np.repeat(Mb, n_units) - r0)
+    units = np.zeros((len(item_of_unit), 4), dtype=np.int32)
+    units[:, 0] = item_of_unit
+    units[:, 1] = r0
+    units[:, 2] = cnt
+    units[:, 3] = np.repeat(logG, n_units)
+    return units, warp_units
+
+
+PIPE_STAGE_FLOATS, PIPE_XBUF, PIPE_RMAX, PIPE_MAXSEG, PIPE_REC = 1408, 192, 128, 4, 32
+GEMV_PIPE = 3  # persistent producer/consumer kernel (csrc/nb2_gemv_pipe.cu)
+PIPE_CTAS_PER_SM = 2
+PIPE_CONSUMER_WARPS = 8
+
+
+def _pipe_template(R, terms):
+    """Pack the (term, column chunk) segments of one row range into records.
+
+    ``terms`` = [(N, s0, contiguous)]; returns a list of records, each a list of
+    (term index, c0, w, aoff_base, xoff).  ``aoff_base`` is 4-aligned; 3 floats of
+    slack follow it so the staged copy can keep the 16-byte phase of its source.
+    """
+    records, cur, used_a, used_x = [], [], 0, 0
+    for ti, (N, s0) in enumerate(terms):
+        c0 = 0
+        while c0 < N:
+            base = (used_a + 3) & ~3
+            w = min(N - c0, (PIPE_STAGE_FLOATS - base - 3) // R, PIPE_XBUF - used_x)
+            if w <= 0 or len(cur) == PIPE_MAXSEG:
+                records.append(cur)
+                cur, used_a, used_x = [], 0, 0
+                continue
+            cur.append((ti, c0, w, base, used_x))
+            used_a = base + 3 + R * w
+            used_x += w
+            c0 += w
+    records.append(cur)
+    return records
+
+
+def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
+    """Work records and per-CTA record ranges for ``nb2_gemv_pipelined``.
+
+    Record layout (32 int32): [0] flags (1 = first of its chain, 2 = last),
+    [1] rows, [2] Y_in element index of the first row, [3] Y element index,
+    [4] item id, [5] segment count, then per segment 6 ints at 8 + 6q:
+    A element index of (first row, first column), columns, A row stride,
+    X element index, X stride, (x offset << 16 | a offset) in the stage buffers.
+    Returns ``(records, ranges, warp_units)``; tiny items go to the warp kernel.
+    """
+    n_items = gstructure.shape[0]
+    n_dots = gstructure[:, 4 * D + 2].astype(np.int64) if n_items else np.zeros(0, np.int64)
+    M = gstructure[:, 4 * D + 3].astype(np.int64) if n_items else np.zeros(0, np.int64)
+    recs = []
+    chain_start = []  # record index where each chain starts
+    warp_rows = []
+    for row in range(n_items):
+        m, nd = int(M[row]), int(n_dots[row])
+        if m == 0:
+            continue
+        g = gstructure[row]
+        Ns = [int(v) for v in g[3 * D:3 * D + nd]]
+        row_floats = sum(Ns)
+        if m <= 32 and m * row_floats <= 1024 and nd <= 64:
+            warp_rows.append(row)
+            continue
+        s0s = [int(v) for v in g[2 * D:2 * D + nd]]
+        astarts = [int(v) for v in g[1 * D:1 * D + nd]]
+        xstarts = [int(v) for v in g[0:nd]]
+        xstr = [int(v) for v in xstrides[row, :nd]] if nd else []
+        R = (PIPE_STAGE_FLOATS - 8 * max(nd, 1)) // max(row_floats, 1)
+        R = max(R, min(m, 8))
+        R = max(1, min(R, PIPE_RMAX, m))
+        n_units = -(-m // R)
+        R = -(-m // n_units)
+        template = _pipe_template(R, list(zip(Ns, s0s)))
+        y_in0, y0, bb = int(g[4 * D + 0]), int(g[4 * D + 1]), int(g[4 * D + 4])
+        n_rec = len(template)
+        block = np.zeros((n_units, n_rec, PIPE_REC), dtype=np.int64)
+        r0 = np.arange(n_units, dtype=np.int64) * R
+        rows_u = np.minimum(R, m - r0)
+        for k, segs in enumerate(template):
+            block[:, k, 0] = (1 if k == 0 else 0) | (2 if k == n_rec - 1 else 0)
+            block[:, k, 1] = rows_u
+            block[:, k, 2] = y_in0 + r0
+            block[:, k, 3] = y0 + r0
+            block[:, k, 4] = bb
+            block[:, k, 5] = len(segs)
+            for q, (ti, c0, w, base, xoff) in enumerate(segs):
+                gidx = astarts[ti] + r0 * s0s[ti] + c0
+                o = 8 + 6 * q
+                block[:, k, o + 0] = gidx
+                block[:, k, o + 1] = w
+                block[:, k, o + 2] = s0s[ti]
+                block[:, k, o + 3] = xstarts[ti] + c0 * xstr[ti]
+                block[:, k, o + 4] = xstr[ti]
+                block[:, k, o + 5] = (xoff << 16) | (base + (gidx & 3))
+        base_index = sum(b.shape[0] for b in recs)
+        flat = block.reshape(n_units * n_rec, PIPE_REC)
+        chain_start.extend((base_index + np.arange(n_units) * n_rec).tolist())
+        recs.append(flat)
+    warp_units = np.zeros((len(warp_rows), 4), dtype=np.int32)
+    if warp_rows:
+        warp_units[:, 0] = warp_rows
+        warp_units[:, 2] = M[warp_rows]
+    if not recs:
+        return np.zeros((0, PIPE_REC), np.int32), np.zeros((0, 2), np.int32), warp_units
+    records = np.concatenate(recs, axis=0)
+    assert records.max() < 2 ** 31
+    records = records.astype(np.int32)
+    # cost of a record = staged floats + a fixed overhead; chains are never split
+    nseg = records[:, 5].astype(np.int64)
+    cost = np.full(len(records), 256, dtype=np.int64)
+    for q in range(PIPE_MAXSEG):
+        cost += np.where(q < nseg, records[:, 1].astype(np.int64) * records[:, 8 + 6 * q + 1], 0)
+    chain_start = np.asarray(chain_start, dtype=np.int64)
+    chain_len = np.diff(np.concatenate([chain_start, [len(records)]]))
+    csum = np.concatenate([[0], np.cumsum(cost)])
+    chain_cost_end = csum[chain_start + chain_len]
+    n_ctas = int(min(len(chain_start), n_ctas_max))
+    targets = csum[-1] * np.arange(1, n_ctas) / n_ctas
+    cut = np.unique(np.concatenate([[0], np.searchsorted(chain_cost_end, targets, side="left") + 1,
+                                    [len(chain_start)]]))
+    cut = cut[cut <= len(chain_start)]
+    # Within a CTA, record i is consumed by warp i % NW: deal the CTA's chains to the
+    # warps round-robin and interleave the per-warp sequences (padding with empty records).
+    NW = PIPE_CONSUMER_WARPS
+    out_blocks, ranges, pos = [], [], 0
+    for c0, c1 in zip(cut[:-1], cut[1:]):
+        lens = chain_len[c0:c1]
+        first, last = chain_start[c0], chain_start[c1 - 1] + chain_len[c1 - 1]
+        if (lens == 1).all():
+            block = records[first:last]
+        else:
+            seqs = [[] for _ in range(NW)]
+            for j in range(c1 - c0):
+                st = chain_start[c0 + j]
+                seqs[j % NW].extend(range(st, st + lens[j]))
+            depth = max(len(q) for q in seqs)
+            block = np.zeros((depth * NW, PIPE_REC), dtype=np.int32)
+            for w, q in enumerate(seqs):
+                block[w:len(q) * NW:NW] = records[q]
+        out_blocks.append(block)
+        ranges.append((pos, pos + len(block)))
+        pos += len(block)
+    records = np.concatenate(out_blocks, axis=0)
+    return records, np.asarray(ranges, dtype=np.int32), warp_units
 
 
 class gemv_prog:
@@ -273,40 +468,56 @@ class gemv_prog:
         items = list(items)
         self._check_supported(per_item_scales)
         table, xstrides, D, _, stride = self.gstructure_table(items)
-        cta_units, warp_units = build_worklist(table, D)
         queue = self.queue
+        cta_kind = self.cta_kind
+        if cta_kind == GEMV_PIPE:
+            n_ctas_max = PIPE_CTAS_PER_SM * getattr(queue.device, "sm_count", 148)
+            records, ranges, warp_units = build_pipe_records(table, xstrides, D, n_ctas_max)
+            cta_units = np.zeros((0, 4), dtype=np.int32)
+        elif cta_kind == GEMV_ROWS:
+            cta_units, warp_units = build_rows_worklist(table, D)
+            records = ranges = np.zeros((0, 2), dtype=np.int32)
+        else:
+            cta_units, warp_units = build_worklist(table, D)
+            records = ranges = np.zeros((0, 2), dtype=np.int32)
         d_table = to_device(queue, table)
         d_xstr = to_device(queue, xstrides[:, :max(D, 1)]) if np.any(xstrides != 1) else None
         d_cta = to_device(queue, cta_units) if len(cta_units) else None
         d_warp = to_device(queue, warp_units) if len(warp_units) else None
+        d_records = to_device(queue, records) if len(records) else None
+        d_ranges = to_device(queue, ranges) if len(ranges) else None
         status = zeros(queue, (1,), np.int32)
         A, X, Y, Y_in = self.A.cl_buf, self.X.cl_buf, self.Y.cl_buf, self.Y_in.cl_buf
         alpha = self.float_alpha if self.float_alpha is not None else 1.0
         beta = self.float_beta if self.float_beta is not None else 1.0
         gamma = self.float_gamma if self.float_gamma is not None else 0.0
         p = lambda arr: None if arr is None else arr.ptr
-        cta_kind = self.cta_kind
-        n_cta, n_warp = len(cta_units), len(warp_units)
+        n_cta, n_warp, n_rec, n_ranges = len(cta_units), len(warp_units), len(records), len(ranges)
         fn = _capi.lib().nb2_gemv_ragged
+        fn_pipe = _capi.lib().nb2_gemv_pipelined
         check = _capi.check
+        scales = (alpha, beta, gamma, p(self.cl_alpha), p(self.cl_beta), p(self.cl_gamma), status.ptr)
 
         def launch(stream):
+            if n_rec:
+                check(fn_pipe(stream, d_records.ptr, n_rec, d_ranges.ptr, n_ranges, A.ptr, X.ptr, Y_in.ptr, Y.ptr,
+                              *scales))
             if n_cta:
                 check(fn(stream, cta_kind, d_table.ptr, stride, D, p(d_xstr), d_cta.ptr, n_cta, A.ptr, X.ptr,
-                         Y_in.ptr, Y.ptr, alpha, beta, gamma, p(self.cl_alpha), p(self.cl_beta),
-                         p(self.cl_gamma), status.ptr))
+                         Y_in.ptr, Y.ptr, *scales))
             if n_warp:
                 check(fn(stream, _capi.GEMV_WARP, d_table.ptr, stride, D, p(d_xstr), d_warp.ptr, n_warp, A.ptr,
-                         X.ptr, Y_in.ptr, Y.ptr, alpha, beta, gamma, p(self.cl_alpha), p(self.cl_beta),
-                         p(self.cl_gamma), status.ptr))
+                         X.ptr, Y_in.ptr, Y.ptr, *scales))
 
-        plan = Plan(queue, launch, gsize, lsize, n_launches=int(n_cta > 0) + int(n_warp > 0), name=name,
-                    tag=self.tag, bw_per_call=bw_from_geometry(self.geometry, items),
+        plan = Plan(queue, launch, gsize, lsize, n_launches=int(n_cta > 0) + int(n_warp > 0) + int(n_rec > 0),
+                    name=name, tag=self.tag, bw_per_call=bw_from_geometry(self.geometry, items),
                     flops_per_call=flops_from_geometry(self.geometry, items))
-        plan.full_args = (d_table, d_xstr, d_cta, d_warp, status, A, X, Y, Y_in, self.cl_alpha, self.cl_beta,
-                          self.cl_gamma)  # keep device arrays alive
+        plan.full_args = (d_table, d_xstr, d_cta, d_warp, d_records, d_ranges, status, A, X, Y, Y_in,
+                          self.cl_alpha, self.cl_beta, self.cl_gamma)  # keep device arrays alive
         plan.gstructure = table
         plan.worklist = (cta_units, warp_units)
+        plan.records = records
+        plan.ranges = ranges
         plan.status = status
         plan.description = self.geometry_summary(items) if items else "empty"
         return plan

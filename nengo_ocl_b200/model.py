@@ -37,8 +37,11 @@ class Signal:
             self.shape = tuple(initial_value.shape)
             self._base = None
             self.elemoffset = 0
-            self.elemstrides = tuple(s // initial_value.itemsize for s in
-                                     np.ascontiguousarray(initial_value).strides)
+            strides, acc = [], 1
+            for n in reversed(self.shape):  # C order
+                strides.append(acc)
+                acc *= n
+            self.elemstrides = tuple(reversed(strides))
         else:
             assert base._base is None, "views must reference a base signal"
             self._initial_value = None

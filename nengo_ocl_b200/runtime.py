@@ -127,6 +127,9 @@ class DeviceArray:
             self._base = base  # keeps the owner alive
         self.data = self.base_data + self.offset
 
+    def __len__(self):
+        return self.shape[0] if self.shape else 1
+
     @property
     def ctype(self):
         return {"float32": "float", "int32": "int"}[self.dtype.name]

@@ -1,0 +1,852 @@
+"""Simulator: runs an operator-level model on one B200 through the C ABI.
+
+Public surface of the reference's ``nengo_ocl.Simulator``
+(nengo_ocl/simulator.py:145-1449): same constructor arguments, context-manager
+use, ``run / run_steps / step / reset / close / clear_probes / trange``,
+``data``, ``signals``, ``sim[signal]``, ``dt / n_steps / time``,
+``print_plans / print_profiling``.  Build = simplify operators, merge DotIncs
+into MultiDotIncs, group with the planner, pack every dense signal into ONE
+float32 ragged array in HBM (views become extra ragged items), and turn each
+operator group into a plan (``_plan_<OperatorType>``).  What differs is the
+device layer: plans launch hand-written CUDA kernels, the step list is replayed
+as a CUDA graph, groups that form the ensemble pattern (bias copy, encoder
+GEMV, neuron update, decoder GEMV, synapse, PES) are fused into one kernel, and
+probe buffers are drained with one bounded copy per probe.
+"""
+
+import logging
+import os
+import warnings
+from collections import defaultdict
+from collections.abc import Mapping
+from io import StringIO
+
+import numpy as np
+
+from nengo_ocl_b200 import _capi
+from nengo_ocl_b200.ast_conversion import DeviceFunction
+from nengo_ocl_b200.cura_gemv import plan_block_gemv
+from nengo_ocl_b200.cura_nonlinearities import (
+    plan_copy,
+    plan_direct,
+    plan_elementwise_inc,
+    plan_lif,
+    plan_lif_rate,
+    plan_linearfilter,
+    plan_presentinput,
+    plan_probes,
+    plan_rectified_linear,
+    plan_reset,
+    plan_sigmoid,
+    plan_slicedcopy,
+    plan_spiking_rectified_linear,
+    plan_timeupdate,
+)
+from nengo_ocl_b200.curaggedarray import CUDARaggedArray, to_device
+from nengo_ocl_b200.operators import MultiDotInc, simplify_operators
+from nengo_ocl_b200.plan import BasePlan, Plans, PythonPlan
+from nengo_ocl_b200.planners import greedy_planner
+from nengo_ocl_b200.raggedarray import RaggedArray
+from nengo_ocl_b200.runtime import CommandQueue, create_some_context
+from nengo_ocl_b200.utils import groupby, indent, split, stable_unique
+
+logger = logging.getLogger(__name__)
+
+
+class SimulatorClosed(RuntimeError):
+    """Raised by run/step/reset on a closed simulator."""
+
+
+class ReadonlyError(AttributeError):
+    pass
+
+
+class ValidationError(ValueError):
+    pass
+
+
+class ViewBuilder:
+    """Maps every signal (base or view) to an item of the packed ragged array.
+
+    Views become extra items that alias their base: ``start = base.start +
+    elemoffset`` with the view's element strides (reference simulator.py:72-142)."""
+
+    def __init__(self, bases, rarray):
+        self.sidx = {bb: ii for ii, bb in enumerate(bases)}
+        assert len(bases) == len(self.sidx)
+        self.rarray = rarray
+        self.starts, self.shape0s, self.shape1s, self.stride0s, self.stride1s, self.names = [], [], [], [], [], []
+        self._A_views, self._X_views, self._YYB_views = {}, {}, {}
+
+    def append_view(self, sig):
+        if sig in self.sidx:
+            return
+        if not sig.is_view:
+            raise ValueError("can only append views of known signals", sig)
+        assert sig.size and sig.ndim <= 2
+        idx = self.sidx[sig.base]
+        shape0 = sig.shape[0] if sig.ndim > 0 else 1
+        shape1 = sig.shape[1] if sig.ndim > 1 else 1
+        self.starts.append(int(self.rarray.starts[idx]) + sig.elemoffset)
+        self.shape0s.append(shape0)
+        self.shape1s.append(shape1)
+        self.stride0s.append(sig.elemstrides[0] if shape0 > 1 else 1)
+        self.stride1s.append(sig.elemstrides[1] if shape1 > 1 else 1)
+        self.names.append(getattr(sig, "name", ""))
+        self.sidx[sig] = len(self.sidx)
+
+    def add_views_to(self, rarray):
+        rarray.add_views(self.starts, self.shape0s, self.shape1s, self.stride0s, self.stride1s, names=self.names)
+
+    def setup_views(self, ops):
+        views = [sig for op in ops for sig in op.all_signals]
+        for op in ops:
+            if isinstance(op, MultiDotInc):
+                A_views, X_views, Y_view, Y_in_view, beta_view = op.get_views()
+                views.extend(A_views + X_views + [Y_view, Y_in_view] + ([beta_view] if beta_view else []))
+                self._A_views[op] = A_views
+                self._X_views[op] = X_views
+                self._YYB_views[op] = [Y_view, Y_in_view, beta_view]
+        for view in views:
+            if not getattr(view, "sparse", False):
+                self.append_view(view)
+
+
+class SimulationData(Mapping):
+    """``sim.data[probe]`` -> array of recorded samples; also build parameters."""
+
+    def __init__(self, raw):
+        self.raw = raw
+        self._cache = {}
+
+    def __getitem__(self, key):
+        rval = self.raw[key]
+        if isinstance(rval, list):
+            cached = self._cache.get(key)
+            if cached is None or len(cached) != len(rval):
+                cached = np.asarray(rval)
+                cached.setflags(write=False)
+                self._cache[key] = cached
+            return cached
+        return rval
+
+    def __iter__(self):
+        return iter(self.raw)
+
+    def __len__(self):
+        return len(self.raw)
+
+    def reset(self, key=None):
+        if key is None:
+            self._cache.clear()
+        else:
+            self._cache.pop(key, None)
+
+
+class Simulator:
+    """Runs a model on a B200.
+
+    Parameters
+    ----------
+    network : nengo.Network or None
+        Built with nengo's builder when the nengo package is importable.
+    dt, seed, model
+        As in ``nengo.Simulator``; ``model`` may be a prebuilt
+        ``nengo_ocl_b200.model.Model`` (then ``network`` is None).
+    context : runtime.Context, optional
+        Device to run on (default: ``LOCAL_RANK`` or device 0).
+    n_prealloc_probes : int
+        Steps buffered on the device between probe drains.
+    profiling : bool, optional
+        Time every plan with CUDA events (disables graph replay); defaults to
+        the environment variable ``NENGO_OCL_PROFILING``.
+    if_python_code : 'none' | 'warn' | 'error'
+        Reaction when a Python function cannot be translated for the device.
+    planner : callable
+        Operator grouping function (see ``nengo_ocl_b200.planners``).
+    fuse : bool
+        Fuse ensemble-pattern operator groups into one kernel per step.
+    """
+
+    some_context = None
+
+    def Array(self, val, dtype=np.float32):
+        return to_device(self.queue, np.asarray(val, dtype=dtype))
+
+    def RaggedArray(self, listofarrays, **kwargs):
+        return CUDARaggedArray.from_arrays(self.queue, listofarrays, **kwargs)
+
+    def __init__(self, network, dt=0.001, seed=None, model=None, context=None, n_prealloc_probes=32,
+                 profiling=None, if_python_code="none", planner=greedy_planner, progress_bar=True, fuse=True,
+                 graph_unroll=8):
+        self.closed = False
+        self.model = None
+        if context is None and Simulator.some_context is None:
+            Simulator.some_context = create_some_context()
+        if profiling is None:
+            profiling = int(os.getenv("NENGO_OCL_PROFILING", "0"))
+        self.context = Simulator.some_context if context is None else context
+        self.profiling = profiling
+        self.queue = CommandQueue(self.context, profiling=bool(profiling))
+        if if_python_code not in ["none", "warn", "error"]:
+            raise ValueError("%r not a valid value for `if_python_code`" % if_python_code)
+        self.if_python_code = if_python_code
+        self.n_prealloc_probes = n_prealloc_probes
+        self.progress_bar = progress_bar
+        self.fuse = fuse
+
+        # --- model
+        if model is None:
+            model = self._build_with_nengo(network, dt)
+        elif network is not None:
+            model.build(network)
+        self.model = model
+
+        # --- operators: simplify, merge dot products, group
+        all_operators = list(self.model.operators)
+        operators = simplify_operators(all_operators)
+        operators = list(map(MultiDotInc.convert_to, operators))
+        operators = MultiDotInc.compress(operators)
+        op_groups = planner(operators)
+        assert len([typ for typ, _ in op_groups if typ.__name__ == "Reset"]) < 2, "All resets not planned together"
+        self.operators = operators
+        self.op_groups = op_groups
+
+        # --- signals: every dense base in one ragged array, views appended
+        all_signals = stable_unique(sig for op in all_operators for sig in op.all_signals)
+        all_signals += [self.model.sig[p]["in"] for p in self.model.probes
+                        if self.model.sig[p]["in"] not in set(all_signals)]
+        all_bases = stable_unique(sig.base for sig in all_signals)
+        sigdict = {}
+        for op in all_operators:
+            op.init_signals(sigdict)
+        for base in all_bases:
+            if base not in sigdict:
+                sigdict[base] = np.array(base.initial_value, dtype=np.float64)
+        if any(getattr(s, "sparse", False) for s in all_signals):
+            raise NotImplementedError("sparse signals are not supported")
+        self.base_reshapes = {}
+        dense = []
+        for base in all_bases:
+            x = np.asarray(sigdict[base])
+            if x.ndim > 2:
+                self.base_reshapes[base] = x.shape
+                x = x.reshape(-1, 1)
+            dense.append(x)
+        dense_data = RaggedArray(dense, names=[getattr(sb, "name", "") for sb in all_bases], dtype=np.float32,
+                                 align=True)
+        view_builder = ViewBuilder(all_bases, dense_data)
+        view_builder.setup_views(operators)
+        for probe in self.model.probes:
+            view_builder.append_view(self.model.sig[probe]["in"])
+        view_builder.add_views_to(dense_data)
+        self.all_bases = all_bases
+        self.sidx = {k: np.int32(v) for k, v in view_builder.sidx.items()}
+        self._A_views = view_builder._A_views
+        self._X_views = view_builder._X_views
+        self._YYB_views = view_builder._YYB_views
+        self._initial_buf = dense_data.buf.copy()
+        self.all_data = CUDARaggedArray(self.queue, dense_data)
+        self._probe_outputs = dict(getattr(self.model, "params", {}))
+        self.data = SimulationData(self._probe_outputs)
+
+        if seed is None:
+            net_seed = getattr(network, "seed", None) if network is not None else getattr(self.model, "seed", None)
+            seed = net_seed + 1 if net_seed is not None else np.random.randint(2 ** 31 - 1)
+        self.seed = seed
+        self.rng = np.random.RandomState(self.seed)
+
+        # --- plans
+        self._raggedarrays_to_reset = {}
+        self._python_rngs = {}
+        self._device_state_to_reset = []
+        self.fused_groups = []
+        plans = []
+        groups = list(op_groups)
+        if self.fuse:
+            from nengo_ocl_b200.fusion import fuse_ensemble_groups
+
+            groups = fuse_ensemble_groups(self, groups)
+        for op_type, op_list in groups:
+            plans.extend(self._plan_op_group(op_type, op_list))
+        plans.extend(self._plan_probes())
+        self._plans = Plans(plans, self.profiling, unroll=graph_unroll)
+        self.rng = None
+        self._n_steps = 0
+        self._time = 0.0
+        self._reset_probes()
+
+    @staticmethod
+    def _build_with_nengo(network, dt):
+        try:
+            import nengo  # noqa: F401
+            from nengo.builder import Model as NengoModel
+        except ImportError as e:
+            raise ImportError(
+                "building from a nengo Network needs the nengo package; pass "
+                "`model=` (a nengo_ocl_b200.model.Model) instead") from e
+        model = NengoModel(dt=float(dt), label="%s, dt=%f" % (network, dt))
+        if network is not None:
+            model.build(network)
+        return model
+
+    def __del__(self):
+        if not getattr(self, "closed", True):
+            warnings.warn("Simulator with model=%s was deallocated while open. Please close simulators "
+                          "manually to ensure resources are properly freed." % self.model, ResourceWarning)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc_value, traceback):
+        self.close()
+
+    def __getitem__(self, item):
+        """Internally shaped (always 2-D) value of a signal."""
+        return self.all_data[self.sidx[item]]
+
+    def __getstate__(self):
+        raise NotImplementedError("this simulator does not support pickling")
+
+    def __setstate__(self, state):
+        raise NotImplementedError("this simulator does not support pickling")
+
+    @property
+    def dt(self):
+        return self.model.dt
+
+    @dt.setter
+    def dt(self, dummy):
+        raise ReadonlyError("dt is read-only")
+
+    @property
+    def n_steps(self):
+        return self._n_steps
+
+    @property
+    def time(self):
+        return self._time
+
+    @property
+    def signals(self):
+        """Get/set properly shaped signal values (0-d, 1-d or 2-d)."""
+        sim = self
+
+        class Accessor(Mapping):
+            def __iter__(_):
+                return iter(sim.all_bases)
+
+            def __len__(_):
+                return len(sim.all_bases)
+
+            def __getitem__(_, item):
+                raw = sim.all_data[sim.sidx[item]]
+                if item.ndim == 0:
+                    return raw[0, 0]
+                if item.ndim == 1:
+                    return raw.ravel()
+                if item.ndim == 2:
+                    return raw
+                raise NotImplementedError()
+
+            def __setitem__(_, item, val):
+                incoming = np.asarray(val)
+                if item.ndim == 0:
+                    assert incoming.size == 1
+                    sim.all_data[sim.sidx[item]] = incoming
+                elif item.ndim == 1:
+                    assert (item.size,) == incoming.shape
+                    sim.all_data[sim.sidx[item]] = incoming[:, None]
+                elif item.ndim == 2:
+                    assert item.shape == incoming.shape
+                    sim.all_data[sim.sidx[item]] = incoming
+                else:
+                    raise NotImplementedError()
+
+            def __str__(self_):
+                sio = StringIO()
+                for k in self_:
+                    print(k, self_[k], file=sio)
+                return sio.getvalue()
+
+        return Accessor()
+
+    # --- simulation control ---------------------------------------------------
+    def clear_probes(self):
+        for probe in self.model.probes:
+            self._probe_outputs[probe] = []
+        self.data.reset()
+
+    def close(self):
+        self.closed = True
+        self.context = None
+        self.queue = None
+        self.all_data = None
+        self._plans = None
+        self._raggedarrays_to_reset = None
+        self._cl_probe_plan = None
+
+    def _probe(self):
+        """Drain the device-side probe ring buffers into ``data``."""
+        self._probe_step_time()
+        plan = self._cl_probe_plan
+        if plan is None:
+            return
+        self.queue.finish()
+        bufpositions = plan.cl_bufpositions.get()
+        for i, probe in enumerate(self.model.probes):
+            n_buffered = int(bufpositions[i])
+            if n_buffered:
+                shape = self.model.sig[probe]["in"].shape
+                width = int(plan.Y.shape1s[i])
+                raw = plan.Y.cl_buf.read_region(int(plan.Y.starts[i]), n_buffered * width)
+                self._probe_outputs[probe].extend(raw.reshape((n_buffered,) + tuple(shape)))
+        plan.cl_bufpositions.fill(0)
+        self.queue.finish()
+
+    def _probe_step_time(self):
+        self._n_steps = int(self.signals[self.model.step].item())
+        self._time = float(self.signals[self.model.time].item())
+
+    def _reset_probes(self):
+        if self._cl_probe_plan is not None:
+            self._cl_probe_plan.cl_bufpositions.fill(0)
+            self._cl_probe_plan.cl_countdowns.set(self._cl_probe_plan.periods - 1)
+        for probe in self.model.probes:
+            self._probe_outputs[probe] = []
+        self.data.reset()
+        self._probe_step_time()
+
+    def reset(self, seed=None):
+        if self.closed:
+            raise SimulatorClosed("Cannot reset closed Simulator.")
+        if seed is not None:
+            raise NotImplementedError("Seed changing not implemented")
+        # one upload restores every signal (readonly ones are unchanged by construction)
+        self.all_data.cl_buf.set(self._initial_buf)
+        for clra, ra in self._raggedarrays_to_reset.items():
+            clra.cl_buf.set(ra.buf)
+        for darray, host in self._device_state_to_reset:
+            darray.set(host)
+        for rng, state in self._python_rngs.items():
+            rng.set_state(state)
+        self._reset_probes()
+
+    def run(self, time_in_seconds, progress_bar=None):
+        if time_in_seconds < 0:
+            raise ValidationError("Must be positive (got %g)" % (time_in_seconds,))
+        steps = int(np.round(float(time_in_seconds) / self.dt))
+        if steps == 0:
+            warnings.warn("%g results in running for 0 timesteps. Simulator still at time %g."
+                          % (time_in_seconds, self.time))
+        else:
+            self.run_steps(steps, progress_bar=progress_bar)
+
+    def run_steps(self, steps, progress_bar=True):
+        if self.closed:
+            raise SimulatorClosed("Simulator cannot run because it is closed.")
+        if self.n_steps + steps >= 2 ** 24:
+            raise ValueError("Cannot handle more than 2**24 steps")  # step is a float32 signal
+        if steps < 0:
+            raise ValueError("Cannot run for negative steps (got %r)" % (steps,))
+        while steps > 0:
+            B = min(steps, self._max_steps_between_probes)
+            self._plans.call_n_times(B)
+            self._probe()
+            steps -= B
+        if self.profiling > 1:
+            self.print_profiling()
+
+    def step(self):
+        return self.run_steps(1, progress_bar=False)
+
+    def trange(self, sample_every=None, dt=None):
+        if dt is not None:
+            if sample_every is not None:
+                raise ValidationError("Cannot specify both `dt` and `sample_every`.")
+            warnings.warn("`dt` is deprecated. Use `sample_every` instead.", DeprecationWarning)
+            sample_every = dt
+        period = 1 if sample_every is None else sample_every / self.dt
+        steps = np.arange(1, self.n_steps + 1)
+        return self.dt * steps[steps % period < 1]
+
+    # --- planning ---------------------------------------------------------------
+    def _plan_probes(self):
+        plans = []
+        if len(self.model.probes) == 0:
+            self._max_steps_between_probes = self.n_prealloc_probes
+            self._cl_probe_plan = None
+        else:
+            n_prealloc = self.n_prealloc_probes
+            probes = self.model.probes
+            periods = [max(1 if p.sample_every is None else p.sample_every / self.dt, 1) for p in probes]
+            X = self.all_data[[self.sidx[self.model.sig[p]["in"]] for p in probes]]
+            Y = self.RaggedArray([np.zeros((n_prealloc, self.model.sig[p]["in"].size)) for p in probes],
+                                 dtype=np.float32)
+            cl_plan = plan_probes(self.queue, periods, X, Y)
+            self._max_steps_between_probes = n_prealloc * int(min(periods))
+            self._cl_probe_plan = cl_plan
+            plans.append(cl_plan)
+        assert self._max_steps_between_probes >= 1
+        return plans
+
+    def _plan_op_group(self, op_type, ops):
+        return getattr(self, "_plan_" + op_type.__name__)(ops)
+
+    def _plan_SimProbe(self, ops):
+        return []
+
+    def _plan_FusedEnsembles(self, groups):
+        from nengo_ocl_b200.fusion import plan_fused_ensembles
+
+        return plan_fused_ensembles(self, groups)
+
+    def _plan_MultiDotInc(self, ops):
+        constant_bs = [op for op in ops if op._float_beta is not None]
+        vector_bs = [op for op in ops if op._signal_beta is not None and op._signal_beta.ndim == 1]
+        if len(constant_bs) + len(vector_bs) != len(ops):
+            raise NotImplementedError()
+        if vector_bs:
+            raise NotImplementedError("signal-valued beta")
+        return self._sig_gemv(
+            constant_bs, lambda op: self._A_views[op], lambda op: self._X_views[op],
+            lambda op: self._YYB_views[op][0], lambda op: self._YYB_views[op][1],
+            beta=[op._float_beta for op in constant_bs], gamma=[op.gamma for op in constant_bs],
+            tag="c-beta-%d" % len(constant_bs))
+
+    def _sig_gemv(self, ops, A_js_fn, X_js_fn, Y_fn, Y_in_fn=None, alpha=1.0, beta=1.0, gamma=0.0, tag=None):
+        if len(ops) == 0:
+            return []
+        all_data, sidx = self.all_data, self.sidx
+        A_js = RaggedArray([[sidx[ss] for ss in A_js_fn(op)] for op in ops], dtype=np.int32)
+        X_js = RaggedArray([[sidx[ss] for ss in X_js_fn(op)] for op in ops], dtype=np.int32)
+        Y_sigs = [Y_fn(item) for item in ops]
+        Y_in_sigs = [Y_in_fn(item) for item in ops] if Y_in_fn else Y_sigs
+        Y = all_data[[sidx[sig] for sig in Y_sigs]]
+        Y_in = all_data[[sidx[sig] for sig in Y_in_sigs]]
+        rval = plan_block_gemv(self.queue, alpha, all_data, A_js, all_data, X_js, beta, Y, Y_in=Y_in, gamma=gamma,
+                               tag=tag)
+        return rval.plans
+
+    def _plan_TimeUpdate(self, ops):
+        (op,) = ops
+        step = self.all_data[[self.sidx[op.step]]]
+        time = self.all_data[[self.sidx[op.time]]]
+        return [plan_timeupdate(self.queue, step, time, self.model.dt)]
+
+    def _plan_Reset(self, ops):
+        targets = self.all_data[[self.sidx[op.dst] for op in ops]]
+        values = self.Array([op.value for op in ops])
+        return [plan_reset(self.queue, targets, values)]
+
+    def _plan_Copy(self, ops):
+        copies, ops = split(ops, lambda op: (op.src_slice is None and op.dst_slice is None))
+        plans = []
+        if copies:
+            X = self.all_data[[self.sidx[op.src] for op in copies]]
+            Y = self.all_data[[self.sidx[op.dst] for op in copies]]
+            incs = np.array([op.inc for op in copies], dtype=np.int32)
+            plans.append(plan_copy(self.queue, X, Y, incs))
+        if ops:
+            inds = lambda ary, i: np.arange(ary.size, dtype=np.int32)[Ellipsis if i is None else i]
+            xinds = [inds(op.src, op.src_slice) for op in ops]
+            yinds = [inds(op.dst, op.dst_slice) for op in ops]
+            if any(len(i) != len(set(i.tolist())) for i in xinds + yinds):
+                raise NotImplementedError("Duplicates in indices")
+            X = self.all_data[[self.sidx[op.src] for op in ops]]
+            Y = self.all_data[[self.sidx[op.dst] for op in ops]]
+            Xinds = self.RaggedArray(xinds, dtype=np.int32)
+            Yinds = self.RaggedArray(yinds, dtype=np.int32)
+            incs = np.array([op.inc for op in ops], dtype=np.int32)
+            plans.append(plan_slicedcopy(self.queue, X, Y, Xinds, Yinds, incs))
+        return plans
+
+    def _plan_ElementwiseInc(self, ops):
+        A = self.all_data[[self.sidx[op.A] for op in ops]]
+        X = self.all_data[[self.sidx[op.X] for op in ops]]
+        Y = self.all_data[[self.sidx[op.Y] for op in ops]]
+        return [plan_elementwise_inc(self.queue, A, X, Y)]
+
+    # ---- python functions ---------------------------------------------------
+    def _plan_SimPyFunc(self, ops):
+        plans = []
+        for fn, group in groupby(ops, lambda op: op.fn):
+            plans.extend(self._plan_python_fn(fn, ts=[op.t for op in group], xs=[op.x for op in group],
+                                              ys=[op.output for op in group]))
+        return plans
+
+    def _plan_python_fn(self, fn, ts, xs, ys):
+        assert len(ts) == len(xs) == len(ys)
+        assert all(t is None for t in ts) or all(t is not None for t in ts)
+        assert all(x is None for x in xs) or all(x is not None for x in xs)
+        assert all(y is None for y in ys) or all(y is not None for y in ys)
+        if ts[0] is not None:
+            assert all(t is self.model.time for t in ts)
+        size = lambda sig: sig.size if sig is not None else None
+        fn_name = getattr(fn, "__name__", type(fn).__name__)
+        plans, unplanned = [], []
+        for _, group in groupby(zip(ts, xs, ys), lambda s: size(s[1])):
+            tt, xx, yy = zip(*group)
+            if size(yy[0]) is None:
+                self._found_python_code("Function %r could not be converted for the device since it has "
+                                        "no outputs." % fn_name)
+                unplanned.extend(zip(tt, xx, yy))
+                continue
+            if self.if_python_code == "error":
+                plans.append(self._plan_fn_on_device(fn, tt, xx, yy, fn_name))
+            else:
+                try:
+                    plans.append(self._plan_fn_on_device(fn, tt, xx, yy, fn_name))
+                except Exception as e:  # pylint: disable=broad-except
+                    self._found_python_code("Function %r could not be converted for the device due to %s%s"
+                                            % (fn_name, type(e).__name__, e.args))
+                    unplanned.extend(zip(tt, xx, yy))
+        if unplanned:
+            tt, xx, yy = zip(*unplanned)
+            plans.append(self._plan_fn_in_python(fn, tt, xx, yy, fn_name))
+        return plans
+
+    def _found_python_code(self, message):
+        if self.if_python_code == "error":
+            raise RuntimeError(message)
+        if self.if_python_code == "warn":
+            warnings.warn(message, RuntimeWarning)
+
+    def _plan_fn_on_device(self, fn, tt, xx, yy, fn_name):
+        t_in = tt[0] is not None
+        x_in = xx[0] is not None
+        x_dim = xx[0].size if x_in else None
+        y_dim = yy[0].size
+        assert all(y.size == y_dim and y.ndim == 1 for y in yy)
+        if x_in:
+            assert all(x.size == x_dim and x.ndim == 1 for x in xx)
+        in_dims = ([1] if t_in else []) + ([x_dim] if x_in else [])
+        dev_fn = DeviceFunction(fn, in_dims=in_dims, out_dim=y_dim)
+        inputs = []
+        if t_in:
+            inputs.append(self.all_data[[self.sidx[t] for t in tt]])
+        if x_in:
+            inputs.append(self.all_data[[self.sidx[x] for x in xx]])
+        output = self.all_data[[self.sidx[y] for y in yy]]
+        return plan_direct(self.queue, dev_fn.code, dev_fn.init, dev_fn.translator.arg_names[:len(inputs)], inputs,
+                           output, tag=fn_name)
+
+    def _plan_fn_in_python(self, fn, tt, xx, yy, fn_name):
+        t_in = tt[0] is not None
+        t_idx = self.sidx[self.model.time]
+        ix_iy = [(self.sidx[x] if x is not None else None, self.sidx[y] if y is not None else None)
+                 for x, y in zip(xx, yy)]
+        m2v = lambda x: x[:, 0] if x.ndim == 2 and x.shape[1] == 1 else x
+        v2m = lambda x: x[:, None] if x.ndim == 1 else x
+
+        def step():
+            t = float(self.all_data[t_idx][0, 0] if t_in else 0)
+            for ix, iy in ix_iy:
+                args = [t] if t_in else []
+                args += [m2v(self.all_data[ix])] if ix is not None else []
+                y = fn(*args)
+                if iy is not None:
+                    self.all_data[iy] = v2m(np.asarray(y, dtype=np.float32))
+
+        return PythonPlan(step, name="python_fn", tag=fn_name)
+
+    # ---- neurons ----------------------------------------------------------------
+    def _plan_SimNeurons(self, all_ops):
+        plans = []
+        for neuron_class, ops in groupby(all_ops, lambda op: op.neurons.__class__):
+            attr_name = "_plan_%s" % neuron_class.__name__
+            if not hasattr(self, attr_name):
+                raise ValueError("Unsupported neuron type '%s'" % neuron_class.__name__)
+            plans.extend(getattr(self, attr_name)(ops))
+        return plans
+
+    def _sigs(self, ops, fn):
+        return self.all_data[[self.sidx[fn(op)] for op in ops]]
+
+    def _param(self, ops, fn):
+        """A python float when all ops agree, else a per-neuron ragged array
+        (what the reference always builds, simulator.py:1054-1063)."""
+        values = [float(fn(op)) for op in ops]
+        if len(set(values)) == 1:
+            return values[0]
+        return self.RaggedArray([v * np.ones(op.J.size) for v, op in zip(values, ops)], dtype=np.float32)
+
+    def _plan_LIF(self, ops):
+        if not all(op.neurons.min_voltage == 0 for op in ops):
+            raise NotImplementedError("LIF min voltage")
+        return [plan_lif(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
+                         self._sigs(ops, lambda op: op.state["voltage"]),
+                         self._sigs(ops, lambda op: op.state["refractory_time"]),
+                         self._sigs(ops, lambda op: op.output),
+                         self._param(ops, lambda op: op.neurons.tau_ref),
+                         self._param(ops, lambda op: op.neurons.tau_rc),
+                         self._param(ops, lambda op: op.neurons.amplitude))]
+
+    def _plan_LIFRate(self, ops):
+        return [plan_lif_rate(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
+                              self._sigs(ops, lambda op: op.output),
+                              self._param(ops, lambda op: op.neurons.tau_ref),
+                              self._param(ops, lambda op: op.neurons.tau_rc),
+                              self._param(ops, lambda op: op.neurons.amplitude))]
+
+    def _plan_AdaptiveLIF(self, ops):
+        return [plan_lif(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
+                         self._sigs(ops, lambda op: op.state["voltage"]),
+                         self._sigs(ops, lambda op: op.state["refractory_time"]),
+                         self._sigs(ops, lambda op: op.output),
+                         self._param(ops, lambda op: op.neurons.tau_ref),
+                         self._param(ops, lambda op: op.neurons.tau_rc),
+                         self._param(ops, lambda op: op.neurons.amplitude),
+                         N=self._sigs(ops, lambda op: op.state["adaptation"]),
+                         tau_n=self._param(ops, lambda op: op.neurons.tau_n),
+                         inc_n=self._param(ops, lambda op: op.neurons.inc_n))]
+
+    def _plan_AdaptiveLIFRate(self, ops):
+        return [plan_lif_rate(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
+                              self._sigs(ops, lambda op: op.output),
+                              self._param(ops, lambda op: op.neurons.tau_ref),
+                              self._param(ops, lambda op: op.neurons.tau_rc),
+                              self._param(ops, lambda op: op.neurons.amplitude),
+                              N=self._sigs(ops, lambda op: op.state["adaptation"]),
+                              tau_n=self._param(ops, lambda op: op.neurons.tau_n),
+                              inc_n=self._param(ops, lambda op: op.neurons.inc_n))]
+
+    def _plan_RectifiedLinear(self, ops):
+        J = self._sigs(ops, lambda op: op.J)
+        amp = self.RaggedArray([op.neurons.amplitude * np.ones(op.J.size) for op in ops], dtype=J.dtype)
+        return [plan_rectified_linear(self.queue, J, self._sigs(ops, lambda op: op.output), amp)]
+
+    def _plan_SpikingRectifiedLinear(self, ops):
+        J = self._sigs(ops, lambda op: op.J)
+        amp = self.RaggedArray([op.neurons.amplitude * np.ones(op.J.size) for op in ops], dtype=J.dtype)
+        return [plan_spiking_rectified_linear(self.queue, self.model.dt, J,
+                                              self._sigs(ops, lambda op: op.state["voltage"]),
+                                              self._sigs(ops, lambda op: op.output), amp)]
+
+    def _plan_Sigmoid(self, ops):
+        return [plan_sigmoid(self.queue, self._sigs(ops, lambda op: op.J), self._sigs(ops, lambda op: op.output),
+                             self._param(ops, lambda op: op.neurons.tau_ref))]
+
+    # ---- processes --------------------------------------------------------------
+    def _plan_SimProcess(self, all_ops):
+        plan_groups = defaultdict(list)
+        python_ops = []
+        for process_class, ops in groupby(all_ops, lambda op: type(op.process)):
+            for cls in process_class.__mro__:
+                attrname = "_plan_" + cls.__name__
+                if hasattr(self, attrname):
+                    plan_groups[attrname].extend(ops)
+                    break
+            else:
+                python_ops.extend(ops)
+        plans = [p for attr, ops in plan_groups.items() for p in getattr(self, attr)(ops)]
+        plans += [p for op in python_ops for p in self._plan_python_process(op)]
+        return plans
+
+    def _plan_python_process(self, op):
+        shape = lambda s: s.shape if s is not None else (0,)
+        rng = op.process.get_rng(self.rng)
+        state = op.process.make_state(shape(op.input), shape(op.output), self.model.dt, dtype=None)
+        fn = op.process.make_step(shape(op.input), shape(op.output), self.model.dt, rng=rng, state=state)
+        plans = self._plan_python_fn(fn, [op.t], [op.input], [op.output])
+        self._python_rngs[rng] = rng.get_state()
+        return plans
+
+    def linear_filter_coefficients(self, op):
+        """(num, den[1:]) of the discrete filter of a LinearFilter process op."""
+        proc = op.process
+        if hasattr(proc, "discrete_tf"):
+            return proc.discrete_tf(self.model.dt)
+        # a nengo LinearFilter: discretise through its own make_step (state space -> tf)
+        from scipy.signal import ss2tf
+
+        state = proc.make_state(op.input.shape, op.output.shape, self.model.dt, dtype=None)
+        f = proc.make_step(op.input.shape, op.output.shape, self.model.dt, rng=None, state=state)
+        if f.A.size == 0:
+            num, den = np.asarray(f.D).flatten(), np.array([1.0])
+        else:
+            num, den = ss2tf(f.A, f.B, f.C, f.D)
+            num = num.flatten()
+        if den[0] != 1.0:
+            raise ValidationError("First element of the denominator must be 1")
+        return (num[1:] if num[0] == 0 else num), den[1:]
+
+    def _plan_LinearFilter(self, ops):
+        if any(op.mode != "update" and op.mode != "set" for op in ops):
+            raise NotImplementedError("LinearFilter in 'inc' mode")
+        nums, dens = zip(*(self.linear_filter_coefficients(op) for op in ops))
+        A = self.RaggedArray(dens, dtype=np.float32)
+        B = self.RaggedArray(nums, dtype=np.float32)
+        X = self.all_data[[self.sidx[op.input] for op in ops]]
+        Y = self.all_data[[self.sidx[op.output] for op in ops]]
+        Xbuf0 = RaggedArray([np.zeros(shape) for shape in zip(B.sizes, X.sizes)], dtype=np.float32)
+        Ybuf0 = RaggedArray([np.zeros(shape) for shape in zip(A.sizes, Y.sizes)], dtype=np.float32)
+        Xbuf = CUDARaggedArray(self.queue, Xbuf0)
+        Ybuf = CUDARaggedArray(self.queue, Ybuf0)
+        self._raggedarrays_to_reset[Xbuf] = Xbuf0
+        self._raggedarrays_to_reset[Ybuf] = Ybuf0
+        plans = plan_linearfilter(self.queue, X, Y, A, B, Xbuf, Ybuf)
+        for p in plans:
+            if getattr(p, "Xbufpos", None) is not None and p.Xbufpos.size:
+                self._device_state_to_reset.append((p.Xbufpos, np.zeros(p.Xbufpos.size, np.int32)))
+                self._device_state_to_reset.append((p.Ybufpos, np.zeros(p.Ybufpos.size, np.int32)))
+        return plans
+
+    def _plan_WhiteSignal(self, ops):
+        Y = self.all_data[[self.sidx[op.output] for op in ops]]
+        t = self.all_data[[self.sidx[self.model.step] for _ in ops]]
+        signals = self.RaggedArray([np.asarray(op.process.signal).reshape(len(op.process.signal), -1)
+                                    for op in ops], dtype=np.float32)
+        return [plan_presentinput(self.queue, Y, t, signals, self.model.dt)]
+
+    def _plan_PresentInput(self, ops):
+        ps = [op.process for op in ops]
+        Y = self.all_data[[self.sidx[op.output] for op in ops]]
+        t = self.all_data[[self.sidx[self.model.step] for _ in ops]]
+        inputs = self.RaggedArray([p.inputs.reshape(p.inputs.shape[0], -1) for p in ps], dtype=np.float32)
+        pres_t = self.Array([p.presentation_time for p in ps])
+        return [plan_presentinput(self.queue, Y, t, inputs, self.model.dt, pres_t=pres_t)]
+
+    def _plan_SimPES(self, ops):
+        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
+        error = self.all_data[[self.sidx[op.error] for op in ops]]
+        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
+        alpha = np.array([-op.learning_rate * self.model.dt / op.pre_filtered.shape[0] for op in ops])
+        return [plan_elementwise_inc(self.queue, error, pre, delta, alpha=alpha, outer=True, inc=False)]
+
+    # ---- reporting ---------------------------------------------------------------
+    def print_plans(self):
+        print(" Plans ".center(80, "-"))
+        for plan in self._plans:
+            print("%r" % plan)
+            if hasattr(plan, "description"):
+                print(indent(plan.description, 4))
+
+    def print_profiling(self, sort=None):
+        """Table of n_calls, runtime, GF/s, GB/s per plan (needs ``profiling=True``)."""
+        if not self.profiling:
+            print("Profiling not enabled!")
+            return
+        table = []
+        for p in self._plans:
+            if isinstance(p, BasePlan):
+                t = sum(p.ctimes)
+                calls_per_sec = p.n_calls / t if t > 0 else np.nan
+                gfps = 1e-9 * p.flops_per_call * calls_per_sec if p.flops_per_call is not None else np.nan
+                gbps = 1e-9 * p.bw_per_call * calls_per_sec if p.bw_per_call is not None else np.nan
+                table.append((p.n_calls, t, gfps, gbps, str(p)))
+        if sort is not None:
+            table.sort(key=lambda x: x[abs(sort)], reverse=sort >= 0)
+        print(" Profiling ".center(80, "-"))
+        print("%8s|%10s|%10s|%10s|" % ("n_calls", "runtime", "GF/s", "GB/s"))
+        for r in table:
+            print("%8d|%10.3f|%10.3f|%10.3f| %s" % r)
+        print("-" * 80)
+        times = np.array([r[1] for r in table], dtype=np.float64)
+
+        def wmean(col):
+            x = np.array([r[col] for r in table], dtype=np.float64)
+            m = ~np.isnan(x)
+            return (x[m] * times[m]).sum() / times[m].sum() if times[m].sum() > 0 else np.nan
+
+        print("totals:\t%2.3f\t%2.3f\t%2.3f" % (times.sum(), wmean(2), wmean(3)))

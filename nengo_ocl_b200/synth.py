@@ -44,3 +44,251 @@ def gemv_workload(seed=1, n_outputs=4096, max_terms=4, max_rows=1024, max_cols=6
     return (RaggedArray(A, dtype=np.float32, align=align), RaggedArray(A_js, dtype=np.int32),
             RaggedArray(X, dtype=np.float32, align=align), RaggedArray(X_js, dtype=np.int32),
             RaggedArray(Y, dtype=np.float32, align=align))
+
+
+# ---- operator-level network construction ------------------------------------------
+class Ensemble:
+    """Signals and parameters of one population (what an ensemble build yields)."""
+
+    def __init__(self, n, d, label):
+        self.n_neurons, self.dimensions, self.label = n, d, label
+
+
+class NetBuilder:
+    """Emits the operators a nengo build of ensembles / nodes / decoded
+    connections / PES rules produces, directly into a ``Model``."""
+
+    def __init__(self, dt=0.001, seed=0, label=None):
+        self.model = m.Model(dt=dt, label=label, seed=seed)
+        self.rng = np.random.RandomState(seed)
+        self.ensembles = []
+        self.connections = []
+
+    # -- populations ------------------------------------------------------------
+    def ensemble(self, n, d, label=None, radius=1.0, max_rates=(200.0, 400.0), intercepts=(-1.0, 1.0),
+                 neuron_type=None, encoders=None, params_from=None):
+        """Reset input, copy bias into J, J += scaled_encoders . input, neuron update."""
+        mdl = self.model
+        label = label or "ens%d" % len(self.ensembles)
+        nt = neuron_type or m.LIF()
+        ens = Ensemble(n, d, label)
+        ens.neuron_type, ens.radius = nt, radius
+        if params_from is not None:  # share build parameters (not state) with a template ensemble
+            enc, gain, bias = params_from.encoders, params_from.gain, params_from.bias
+        else:
+            rng = self.rng
+            if encoders is None:
+                encoders = rng.standard_normal(size=(n, d))
+                encoders /= np.linalg.norm(encoders, axis=1, keepdims=True)
+            enc = np.asarray(encoders, dtype=np.float64)
+            rates = rng.uniform(max_rates[0], max_rates[1], size=n)
+            icpt = rng.uniform(intercepts[0], intercepts[1], size=n)
+            gain, bias = nt.gain_bias(rates, icpt)
+        ens.encoders, ens.gain, ens.bias = enc, gain, bias
+        ens.sig_in = m.Signal(np.zeros(d), name="%s.in" % label)
+        ens.sig_J = m.Signal(np.zeros(n), name="%s.neurons.in" % label)
+        ens.sig_out = m.Signal(np.zeros(n), name="%s.neurons.out" % label)
+        ens.sig_enc = m.Signal(enc * (gain / radius)[:, None], name="%s.scaled_encoders" % label, readonly=True)
+        ens.sig_bias = m.Signal(bias, name="%s.bias" % label, readonly=True)
+        state = {}
+        for name in nt.state_names:
+            state[name] = m.Signal(np.zeros(n), name="%s.%s" % (label, name))
+        ens.state = state
+        mdl.add_op(m.Reset(ens.sig_in))
+        mdl.add_op(m.Copy(ens.sig_bias, ens.sig_J))
+        mdl.add_op(m.DotInc(ens.sig_enc, ens.sig_in, ens.sig_J, tag="%s.encode" % label))
+        mdl.add_op(m.SimNeurons(nt, ens.sig_J, ens.sig_out, state=state))
+        mdl.n_neurons += n
+        self.ensembles.append(ens)
+        return ens
+
+    def solve_decoders(self, ens, function=None, n_eval=None, reg=0.1, rng=None):
+        """Regularised least squares of the target function on random points in
+        the ensemble's represented ball -> decoders of shape (d_out, n)."""
+        rng = rng or self.rng
+        d = ens.dimensions
+        n_eval = n_eval or max(750, 2 * ens.n_neurons)
+        pts = rng.standard_normal(size=(n_eval, d))
+        pts *= (rng.uniform(size=(n_eval, 1)) ** (1.0 / d)) / np.linalg.norm(pts, axis=1, keepdims=True)
+        pts *= ens.radius
+        J = (pts / ens.radius) @ ens.encoders.T * ens.gain + ens.bias
+        A = ens.neuron_type.rates(J)
+        target = pts if function is None else np.array([np.atleast_1d(function(p)) for p in pts])
+        sigma = reg * A.max()
+        G = A.T @ A + n_eval * sigma ** 2 * np.eye(ens.n_neurons)
+        return np.linalg.solve(G, A.T @ target).T
+
+    # -- inputs -------------------------------------------------------------------
+    def node_fn(self, fn, size_out, label="node"):
+        out = m.Signal(np.zeros(size_out), name="<Node %s>.out" % label)
+        self.model.add_op(m.SimPyFunc(out, fn, self.model.time, None))
+        return out
+
+    def node_process(self, process, size_out, label="node"):
+        out = m.Signal(np.zeros(size_out), name="<Node %s>.out" % label)
+        self.model.add_op(m.SimProcess(process, None, out, self.model.time, mode="set"))
+        return out
+
+    def node_const(self, value, label="node"):
+        return m.Signal(np.asarray(value, dtype=np.float64), name="<Node %s>.out" % label, readonly=True)
+
+    # -- connections ----------------------------------------------------------------
+    def synapse(self, sig, tau, label="synapse"):
+        """Filtered copy of ``sig`` (updated at the end of the step)."""
+        if tau is None:
+            return sig
+        out = m.Signal(np.zeros(sig.shape), name="%s.filtered" % label)
+        self.model.add_op(m.SimProcess(m.Lowpass(tau), sig, out, self.model.time, mode="update"))
+        return out
+
+    def connect_signal(self, src, dst, synapse=None, transform=None, label="conn"):
+        """src -> [transform] -> [synapse] -> dst (increment)."""
+        mdl = self.model
+        sig = src
+        if transform is not None:
+            T = np.asarray(transform, dtype=np.float64)
+            w = m.Signal(T, name="%s.weights" % label, readonly=True)
+            weighted = m.Signal(np.zeros(T.shape[0] if T.ndim == 2 else src.shape), name="%s.weighted" % label)
+            mdl.add_op(m.Reset(weighted))
+            mdl.add_op(m.DotInc(w, src, weighted, tag="%s.transform" % label))
+            sig = weighted
+        sig = self.synapse(sig, synapse, label)
+        mdl.add_op(m.Copy(sig, dst, inc=True))
+        return sig
+
+    def connect_decoded(self, pre, dst, decoders, synapse=0.005, label=None, pes=None):
+        """Decoded connection from ensemble ``pre`` into signal ``dst``.
+
+        ``pes`` = dict(learning_rate, error (Signal), pre_synapse) adds the PES rule:
+        a lowpass of the presynaptic activities, the delta operator and the
+        increment of the decoders by the previous step's delta."""
+        mdl = self.model
+        label = label or "conn%d" % len(self.connections)
+        dec = np.asarray(decoders, dtype=np.float64)
+        w = m.Signal(dec, name="%s.weights" % label, readonly=pes is None)
+        weighted = m.Signal(np.zeros(dec.shape[0]), name="%s.weighted" % label)
+        mdl.add_op(m.Reset(weighted))
+        mdl.add_op(m.DotInc(w, pre.sig_out, weighted, tag="%s.decode" % label))
+        out = self.synapse(weighted, synapse, label)
+        if dst is not None:
+            mdl.add_op(m.Copy(out, dst, inc=True))
+        conn = dict(pre=pre, weights=w, weighted=weighted, out=out, label=label)
+        if pes is not None:
+            pre_f = m.Signal(np.zeros(pre.n_neurons), name="%s.pes.pre_filtered" % label)
+            mdl.add_op(m.SimProcess(m.Lowpass(pes.get("pre_synapse", 0.005)), pre.sig_out, pre_f, mdl.time,
+                                    mode="update"))
+            delta = m.Signal(np.zeros(dec.shape), name="%s.pes.delta" % label)
+            mdl.add_op(m.SimPES(pre_f, pes["error"], delta, pes["learning_rate"]))
+            mdl.add_op(m.Copy(delta, w, inc=True, tag="%s.pes.apply" % label))
+            conn.update(pre_filtered=pre_f, delta=delta, error=pes["error"])
+        self.connections.append(conn)
+        return conn
+
+    def probe(self, sig, synapse=None, sample_every=None, label=None):
+        filtered = self.synapse(sig, synapse, label or "probe")
+        return self.model.add_probe(filtered, sample_every=sample_every, label=label)
+
+    def probe_decoded(self, ens, synapse=0.01, function=None, label=None):
+        dec = self.solve_decoders(ens, function=function)
+        conn = self.connect_decoded(ens, None, dec, synapse=synapse, label=label or "%s.probe" % ens.label)
+        return self.model.add_probe(conn["out"], label=label or "%s.probe" % ens.label)
+
+
+# ---- configuration 1: two-ensemble communication channel ------------------------
+def two_ensemble_model(seed=0, n_neurons=100, dt=0.001):
+    """Node(sin t) -> A (100 LIF, 1-d) -> x**2 -> B (100 LIF, 1-d); both decoded
+    outputs probed through a 0.01 s lowpass."""
+    nb = NetBuilder(dt=dt, seed=seed, label="two ensembles")
+    stim = nb.node_fn(lambda t: np.sin(t), 1, label="stim")
+    A = nb.ensemble(n_neurons, 1, label="A")
+    B = nb.ensemble(n_neurons, 1, label="B")
+    nb.connect_signal(stim, A.sig_in, synapse=None, label="stim->A")
+    nb.connect_decoded(A, B.sig_in, nb.solve_decoders(A, function=lambda x: x ** 2), synapse=0.005, label="A->B")
+    pA = nb.probe_decoded(A, synapse=0.01, label="A.probe")
+    pB = nb.probe_decoded(B, synapse=0.01, label="B.probe")
+    nb.model.info = dict(probes=dict(A=pA, B=pB), ensembles=nb.ensembles, connections=nb.connections)
+    return nb.model
+
+
+# ---- configuration 4: Watts-Strogatz ring of ensembles --------------------------
+def watts_strogatz_edges(n, k, p, rng):
+    """Ring lattice with k neighbours per side; each edge's source is rewired
+    with probability p (no self loops, no duplicate edges per target)."""
+    edges = []
+    for i in range(n):
+        sources = [(i + o) % n for o in range(-k, k + 1) if o != 0]
+        for j, s in enumerate(sources):
+            if rng.uniform() < p:
+                s = int(rng.randint(n))
+                while s == i or s in sources:
+                    s = int(rng.randint(n))
+                sources[j] = s
+        edges.extend((s, i) for s in sources)
+    return edges
+
+
+def watts_strogatz_model(seed=2, n_ensembles=4096, n_neurons=50, k=4, p=0.1, synapse=0.01, dt=0.001,
+                         n_templates=16, n_probes=4):
+    """Every edge is a decoded connection (identity decoders scaled by a U(-1,1)
+    weight) with its own lowpass state; sin(t) drives ensemble 0.  Ensemble
+    parameters are drawn for ``n_templates`` distinct ensembles and reused
+    round-robin to bound the build time (each ensemble still owns its arrays)."""
+    nb = NetBuilder(dt=dt, seed=seed, label="watts-strogatz")
+    rng = nb.rng
+    templates, decoders, ens = [], [], []
+    for i in range(n_ensembles):
+        t = templates[i % n_templates] if i >= n_templates else None
+        e = nb.ensemble(n_neurons, 1, label="e%d" % i, params_from=t)
+        if t is None:
+            templates.append(e)
+            decoders.append(nb.solve_decoders(e))
+        ens.append(e)
+    edges = watts_strogatz_edges(n_ensembles, k, p, rng)
+    weights = rng.uniform(-1, 1, size=len(edges))
+    for (s, d), wgt in zip(edges, weights):
+        nb.connect_decoded(ens[s], ens[d].sig_in, wgt * decoders[s % n_templates], synapse=synapse,
+                           label="e%d->e%d" % (s, d))
+    stim = nb.node_fn(lambda t: np.sin(t), 1, label="stim")
+    nb.connect_signal(stim, ens[0].sig_in, synapse=None, label="stim->e0")
+    probes = [nb.model.add_probe(ens[i].sig_in, label="e%d.in" % i)
+              for i in np.linspace(0, n_ensembles - 1, n_probes).astype(int)]
+    nb.model.info = dict(probes=probes, ensembles=nb.ensembles, connections=nb.connections, edges=edges)
+    return nb.model
+
+
+# ---- configuration 5: large PES learning model -----------------------------------
+def pes_learning_model(seed=3, n_ensembles=4096, n_neurons=1024, dimensions=16, learning_rate=1e-4,
+                       synapse=0.01, pre_synapse=0.005, dt=0.001, sim_time=0.5, n_templates=8, n_probes=4,
+                       error_cutoff=5.0):
+    """Each ensemble has one decoded connection to a random other ensemble with
+    a PES rule; the error of every rule is band-limited white noise (5 Hz)
+    played back from a table.  Parameters/decoders come from ``n_templates``
+    solved ensembles reused round-robin (every ensemble owns its own arrays)."""
+    nb = NetBuilder(dt=dt, seed=seed, label="pes learning")
+    rng = nb.rng
+    templates, decoders, ens = [], [], []
+    for i in range(n_ensembles):
+        t = templates[i % n_templates] if i >= n_templates else None
+        e = nb.ensemble(n_neurons, dimensions, label="e%d" % i, params_from=t)
+        if t is None:
+            templates.append(e)
+            decoders.append(nb.solve_decoders(e, n_eval=2 * n_neurons))
+        ens.append(e)
+    n_table = int(round(sim_time / dt))
+    targets = rng.randint(n_ensembles - 1, size=n_ensembles)
+    targets = np.where(targets >= np.arange(n_ensembles), targets + 1, targets)  # never itself
+    for i, e in enumerate(ens):
+        err_proc = m.WhiteSignal(sim_time, error_cutoff, rms=0.3, seed=int(rng.randint(2 ** 31 - 1)), dt=dt,
+                                 size_out=dimensions)
+        assert err_proc.signal.shape == (n_table, dimensions)
+        err_node = nb.node_process(err_proc, dimensions, label="err%d" % i)
+        err_in = m.Signal(np.zeros(dimensions), name="c%d.pes.in" % i)
+        nb.model.add_op(m.Reset(err_in))
+        nb.model.add_op(m.Copy(err_node, err_in, inc=True))
+        nb.connect_decoded(e, ens[int(targets[i])].sig_in, decoders[i % n_templates], synapse=synapse,
+                           label="c%d" % i, pes=dict(learning_rate=learning_rate, error=err_in,
+                                                     pre_synapse=pre_synapse))
+    probes = [nb.model.add_probe(nb.connections[i]["out"], label="c%d.out" % i)
+              for i in np.linspace(0, n_ensembles - 1, n_probes).astype(int)]
+    nb.model.info = dict(probes=probes, ensembles=nb.ensembles, connections=nb.connections, targets=targets)
+    return nb.model

@@ -1,0 +1,134 @@
+"""Operator simplification, MultiDotInc merging and the greedy planner on the
+host (cases of the reference's nengo_ocl/tests/test_operators.py:9-86,
+test_planners.py:41-47 and the merge in test_simulator.py:14-38)."""
+
+import numpy as np
+import pytest
+
+from nengo_ocl_b200 import model as m
+from nengo_ocl_b200 import operators as ops_mod
+from nengo_ocl_b200 import synth
+from nengo_ocl_b200.operators import MultiDotInc, remove_unmodified_resets, remove_zero_incs, simplify_operators
+from nengo_ocl_b200.planners import greedy_planner, operator_dependency_graph, _dependency_graph_fast
+
+
+def test_signal_views():
+    base = m.Signal(np.arange(24.0).reshape(4, 6), name="base")
+    v = base[1:3, ::2]
+    assert v.is_view and v.base is base and v.shape == (2, 3)
+    assert v.elemoffset == 6 and v.elemstrides == (6, 2)
+    assert np.array_equal(v.initial_value, np.arange(24.0).reshape(4, 6)[1:3, ::2])
+    col = base[:, 2]
+    assert col.shape == (4,) and col.elemstrides == (6,) and col.elemoffset == 2
+    r = col.reshape(4, 1)
+    assert r.elemstrides == (6, 6) and r.shape == (4, 1)
+    assert base[0].may_share_memory(base[0, 2:4]) and not base[0].may_share_memory(base[1])
+    assert not base.may_share_memory(m.Signal(np.zeros(3)))
+    with pytest.raises(ValueError):
+        v.reshape(6)
+
+
+def test_multidotinc_convert_and_compress():
+    a = m.Signal(np.zeros(2), name="a")
+    A, B = m.Signal(np.eye(2)), m.Signal(np.eye(2))
+    x, y = m.Signal(np.ones(2)), m.Signal(np.ones(2))
+    d1, d2 = m.DotInc(A, x, a), m.DotInc(B, y, a)
+    other = m.Reset(a)
+    converted = [MultiDotInc.convert_to(op) for op in (other, d1, d2)]
+    assert converted[0] is other and all(isinstance(c, MultiDotInc) for c in converted[1:])
+    assert converted[1].incs == [a] and converted[1].sets == [] and set(converted[1].reads) == {A, x}
+    merged = MultiDotInc.compress(converted)
+    mdis = [op for op in merged if isinstance(op, MultiDotInc)]
+    assert len(mdis) == 1 and mdis[0].As == [A, B] and mdis[0].Xs == [x, y]
+    # a beta != 1 op sets its target, and absorbs increments of the same view
+    setter = MultiDotInc(a, a, beta=0.5, gamma=1.0)
+    setter.add_AX(A, x)
+    inc = MultiDotInc.convert_to(m.DotInc(B, y, a))
+    out = MultiDotInc.compress([setter, inc])
+    assert out == [setter] and setter.As == [A, B] and setter.sets == [a]
+
+
+def test_multidotinc_views_swap_scalar_a():
+    y = m.Signal(np.zeros(3))
+    s = m.Signal(np.array(2.0))
+    x = m.Signal(np.ones(3))
+    op = MultiDotInc.convert_to(m.DotInc(s.reshape(1, 1), x, y)) if False else None
+    mdi = MultiDotInc(y, y, 1, 0)
+    mdi.As.append(s.reshape(1, 1)), mdi.Xs.append(x)
+    A_views, X_views, Y_view, Y_in_view, beta_view = mdi.get_views()
+    assert A_views[0].shape == (3, 1) and X_views[0].shape == (1, 1)  # roles swapped
+    assert Y_view.shape == (3, 1) and beta_view is None
+    bad = MultiDotInc(y, y, 1, 0)
+    bad.As.append(m.Signal(np.zeros((2, 3)))), bad.Xs.append(x)
+    with pytest.raises(ValueError):
+        bad.get_views()
+
+
+def test_remove_unmodified_resets_and_zero_incs():
+    a = m.Signal(np.zeros(2), name="a")
+    b = m.Signal(np.zeros(2), name="b")
+    zero = m.Signal(np.zeros(2), name="zero")
+    x = m.Signal(np.ones(2), name="x")
+    A = m.Signal(np.eye(2))
+    ops = [m.Reset(a, value=3.0), m.Reset(b), m.DotInc(A, zero, b), m.DotInc(A, x, b), m.Copy(zero, a, inc=False)]
+    out = remove_zero_incs(ops)
+    # the zero-input DotInc disappears; the zero-input Copy (a set) becomes a Reset of its target
+    assert sum(isinstance(o, m.DotInc) for o in out) == 1
+    assert sum(isinstance(o, m.Copy) for o in out) == 0 and sum(isinstance(o, m.Reset) for o in out) == 3
+    out = remove_unmodified_resets([m.Reset(a, value=3.0), m.Reset(b), m.DotInc(A, x, b)])
+    assert len(out) == 2 and np.all(a.initial_value == 3.0)
+    assert ops_mod.simplifications == [remove_unmodified_resets, remove_zero_incs]
+    assert len(simplify_operators([m.Reset(a)])) == 0
+
+
+def test_dependency_graph_fast_equals_reference_rule():
+    mdl = synth.pes_learning_model(n_ensembles=6, n_neurons=16, dimensions=2, n_templates=2, n_probes=1,
+                                   sim_time=0.05)
+    ops = MultiDotInc.compress(list(map(MultiDotInc.convert_to, simplify_operators(list(mdl.operators)))))
+    slow = operator_dependency_graph(ops)
+    fast = _dependency_graph_fast(ops)
+    assert {k: set(v) for k, v in slow.items()} == {k: set(v) for k, v in fast.items()}
+
+
+def test_greedy_planner_groups_respect_dependencies():
+    mdl = synth.two_ensemble_model()
+    ops = MultiDotInc.compress(list(map(MultiDotInc.convert_to, simplify_operators(list(mdl.operators)))))
+    groups = greedy_planner(ops)
+    assert sum(len(g) for _, g in groups) == len(ops)
+    assert len([t for t, _ in groups if t is m.Reset]) == 1  # all resets planned together
+    position = {op: i for i, (_, g) in enumerate(groups) for op in g}
+    for op, later in operator_dependency_graph(ops).items():
+        for op2 in later:
+            assert position[op] < position[op2]
+    for typ, g in groups:
+        assert all(type(op) is typ for op in g)
+        written = [s for op in g for s in list(op.sets) + list(op.incs) + list(op.updates)]
+        for i, s in enumerate(written):
+            assert not any(s.may_share_memory(s2) for s2 in written[i + 1:])
+    cyc_a, cyc_b = m.Signal(np.zeros(1)), m.Signal(np.zeros(1))
+    with pytest.raises(ValueError):
+        greedy_planner([m.Copy(cyc_a, cyc_b), m.Copy(cyc_b, cyc_a)])
+
+
+def test_lowpass_and_linear_filter_coefficients():
+    num, den = m.Lowpass(0.01).discrete_tf(0.001)
+    a = np.exp(-0.1)
+    assert np.allclose(num, [1 - a]) and np.allclose(den, [-a])
+    num2, den2 = m.LinearFilter([1.0], [0.01, 1.0]).discrete_tf(0.001)
+    assert np.allclose(num2, num) and np.allclose(den2, den)
+    num3, den3 = m.Alpha(0.01).discrete_tf(0.001)
+    assert len(num3) == 2 and len(den3) == 2
+    assert np.isclose(num3.sum() / (1 + den3.sum()), 1.0)  # unit DC gain
+
+
+def test_function_translation_to_postfix():
+    from nengo_ocl_b200.ast_conversion import DeviceFunction, OPS
+
+    f = DeviceFunction(lambda t: np.sin(t), [1])
+    assert f.program == [(OPS["IN0"], 0), (OPS["SIN"], 0), (OPS["STORE"], 0)]
+    g = DeviceFunction(lambda t, x: [x[0] * x[1], t + 2.5], [1, 2])
+    assert g.out_dim == 2 and g.constants == [2.5]
+    with pytest.raises(NotImplementedError):
+        DeviceFunction(lambda x: sorted(x), [3])
+    with pytest.raises(NotImplementedError):
+        DeviceFunction(lambda t: [t, t], [1], out_dim=3)

@@ -166,3 +166,69 @@ def test_copy_elementwise_reset_slicedcopy_tables_match_reference(golden_tables)
     assert tuple(g["linearfilter/lsize"]) == (256, 1)
     assert tuple(g["linearfilter/gsize"]) == (256, len(fs))
     assert np.array_equal(foffs, g["linearfilter/offsets"])
+
+
+def _emulate_pipe_records(records, ranges, A, X, Yin, alpha, beta, gamma):
+    """Host emulation of what nb2_gemv_pipelined does with its work records."""
+    Y = Yin.copy()
+    assert ranges[0, 0] == 0 and ranges[-1, 1] == len(records)
+    assert np.array_equal(ranges[1:, 0], ranges[:-1, 1])
+    NW = cura_gemv.PIPE_CONSUMER_WARPS
+    for b, e in ranges:
+        for warp in range(NW):  # record i of a CTA range belongs to consumer warp i % NW
+            acc = None
+            for rec in records[b + warp:e:NW]:
+                flags, R, y_in, y, bb, nseg = rec[:6]
+                if R == 0:
+                    assert flags == 0 and nseg == 0  # padding record
+                    continue
+                assert 1 <= R <= cura_gemv.PIPE_RMAX and 0 <= nseg <= cura_gemv.PIPE_MAXSEG
+                if flags & 1:
+                    acc = np.zeros(R, dtype=np.float64)
+                assert acc is not None and len(acc) == R, "a chain stays within one warp"
+                used = []
+                for q in range(nseg):
+                    gidx, w, s0, xstart, xstride, packed = rec[8 + 6 * q: 14 + 6 * q]
+                    aoff, xoff = packed & 0xFFFF, packed >> 16
+                    assert aoff % 4 == gidx % 4  # staged copy keeps the 16-byte phase of its source
+                    assert aoff + R * w <= cura_gemv.PIPE_STAGE_FLOATS and xoff + w <= cura_gemv.PIPE_XBUF
+                    used.append((aoff, aoff + R * w))
+                    rows = gidx + np.arange(R)[:, None] * s0 + np.arange(w)[None, :]
+                    acc += A[rows].astype(np.float64) @ X[xstart + np.arange(w) * xstride].astype(np.float64)
+                used.sort()
+                assert all(a1 <= b0 for (_, a1), (b0, _) in zip(used, used[1:]))  # segments do not overlap
+                if flags & 2:
+                    Y[y:y + R] = gamma + beta * Yin[y_in:y_in + R] + alpha * acc
+                    acc = None
+    return Y
+
+
+@pytest.mark.parametrize("case", ["config2", "long_rows_many_terms"])
+def test_pipe_records_cover_the_product(case):
+    if case == "config2":
+        A, A_js, X, X_js, Y = gemv_workload(seed=5, n_outputs=150)
+    else:
+        rng = np.random.RandomState(0)
+        shapes = [(700, 3000), (700, 5), (9, 1200), (9, 40), (2, 1), (1000, 1)]
+        A = RA([rng.normal(size=s) for s in shapes] + [rng.normal(size=(40, 7)) for _ in range(12)])
+        X = RA([rng.normal(size=(s[1], 1)) for s in shapes] + [rng.normal(size=(7, 1)) for _ in range(12)])
+        Y = RA([rng.normal(size=(700, 1)), rng.normal(size=(9, 1)), rng.normal(size=(2, 1)),
+                rng.normal(size=(1000, 1)), rng.normal(size=(40, 1))])
+        A_js = RA([[0, 1], [2, 3], [4], [5], list(range(6, 18))], np.int32)
+        X_js = A_js
+    prog = cura_gemv.gemv_geometry(HostQueue(), 0.5, A, A_js, X, X_js, 0.1, Y)
+    table, xstrides, D, _, _ = prog.gstructure_table(range(len(Y)))
+    records, ranges, warp = cura_gemv.build_pipe_records(table, xstrides, D, n_ctas_max=444)
+    assert records.dtype == np.int32 and records.shape[1] == 32
+    got = _emulate_pipe_records(records, ranges, A.buf, X.buf, Y.buf, 0.5, 0.1, 0.0)
+    from oracle import kernels as K
+
+    vals, _ = K.gemv_exact(0.5, A, A_js, X, X_js, 0.1, Y)
+    done_by_warp = set(int(table[r, 4 * D + 4]) for r in warp[:, 0])
+    for i in range(len(Y)):
+        lo = int(Y.starts[i])
+        if i in done_by_warp:
+            assert np.array_equal(got[lo:lo + len(vals[i])], Y.buf[lo:lo + len(vals[i])])
+        else:
+            assert np.allclose(got[lo:lo + len(vals[i])], vals[i], rtol=1e-6, atol=1e-6)
+    assert len(ranges) <= 444
