@@ -182,6 +182,32 @@ int nb2_direct(void* stream, int n_items, const int* prog, int n_ops, const floa
                int out_dim, const int* in0_starts, const float* in0, const int* in1_starts,
                const float* in1, const int* out_starts, float* out);
 
+/* ---- fused ensemble step --------------------------------------------------
+ * One launch replaces, for every population matching the pattern, the
+ * reference's per-step sequence plan_copy (bias) + plan_block_gemv (encoders,
+ * clra_gemv.py:861-1175) + plan_lif (clra_nonlinearities.py:1028-1146) +
+ * plan_reset + plan_block_gemv (decoders) + plan_linearfilter (:577-803) and,
+ * with PES, plan_linearfilter (activity filter) + plan_elementwise_inc(outer)
+ * (simulator.py:1334-1345) + plan_copy (decoders += delta).
+ * `data` is the one packed signal buffer; all table entries are int32 element
+ * offsets into it (floats stored as bit patterns):
+ *   ens_table  [n][16]: n, J (-1 = not stored), V, W, S (-1 = not stored), bias,
+ *                       n_terms, first term, n_conns, first conn, tau_rc, tau_ref,
+ *                       amplitude, 0, 0, 0
+ *   term_table [..][4]: encoder start (row-major n x d), d, x start, x stride
+ *   conn_table [..][16]: decoder start (row-major d_c x n), d_c, decoded start,
+ *                       filtered start (-1 = no synapse), b0, a0, pes flag, error
+ *                       start, activity-filter state start, its b0, its a0, alpha
+ * large_ids / small_ids list the ensembles run by a 256-thread CTA (n <=
+ * NB2_FUSED_MAX_NEURONS) or by one warp (n <= NB2_FUSED_SMALL_NEURONS); the sum
+ * of the d of an ensemble's terms must be <= NB2_FUSED_MAX_INPUT. */
+#define NB2_FUSED_MAX_NEURONS 4096
+#define NB2_FUSED_SMALL_NEURONS 256
+#define NB2_FUSED_MAX_INPUT 512
+int nb2_ensemble_step(void* stream, int n_large, const int* large_ids, int n_small, const int* small_ids,
+                      const int* ens_table, const int* term_table, const int* conn_table, float* data,
+                      double dt);
+
 #ifdef __cplusplus
 }
 #endif

@@ -194,6 +194,7 @@ class Simulator:
         self.n_prealloc_probes = n_prealloc_probes
         self.progress_bar = progress_bar
         self.fuse = fuse
+        self._planner = planner
 
         # --- model
         if model is None:
