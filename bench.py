@@ -1,0 +1,326 @@
+"""Benchmark of the simulator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): the large PES learning model -- 4096 ensembles
+x 1024 LIF neurons x 16 dimensions, one decoded connection per ensemble with a
+PES rule, lowpass synapses, band-limited white-noise error inputs -- built
+from seeded synthetic parameters (``nengo_ocl_b200.synth.pes_learning_model``).
+One "step" is one simulated time step (dt = 1 ms) of the whole model.
+
+Printed JSON (one line, rank 0):
+  value      neuron updates per second with all inputs resident in HBM, timed on
+             the device with CUDA events around K graph-replayed steps;
+  e2e        the same through ``Simulator.run_steps`` with the error-input tables
+             in pinned host memory (uploaded every batch of steps) and the probe
+             buffers read back to the host, wall clock around the call;
+  roofline   the fused ensemble-step kernel: algorithmic bytes per launch over
+             its CUDA-event time, against the measured HBM copy bandwidth;
+  gemv       the ragged gather-GEMV microbenchmark (configuration 2), GB/s;
+  cpu_baseline  the CPU oracle (numpy restatement of the reference's kernels)
+             on a bounded slice of the same workload.
+``--impl reference`` times that CPU oracle alone, on the host cores.
+With N > 1 (torchrun, one rank per GPU) every rank simulates its shard of the
+ensembles and the decoded signals are exchanged each step.
+"""
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FULL = dict(n_ensembles=4096, n_neurons=1024, dimensions=16)
+WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device=0):
+        self.rows = []
+        self.proc = None
+        self.device = device
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+class Events:
+    def __init__(self, capi):
+        self.capi = capi
+        self.e0, self.e1 = ctypes.c_void_p(), ctypes.c_void_p()
+        capi.call("nb2_event_create", ctypes.byref(self.e0))
+        capi.call("nb2_event_create", ctypes.byref(self.e1))
+
+    def start(self, stream):
+        self.capi.call("nb2_event_record", self.e0, stream)
+
+    def stop_ms(self, stream):
+        self.capi.call("nb2_event_record", self.e1, stream)
+        self.capi.call("nb2_event_sync", self.e1)
+        ms = ctypes.c_float()
+        self.capi.call("nb2_event_elapsed_ms", self.e0, self.e1, ctypes.byref(ms))
+        return ms.value
+
+
+def cpu_oracle_rate(n_ensembles, steps, warmup=2):
+    """Neuron updates per second of the CPU oracle on a slice of the workload."""
+    from nengo_ocl_b200 import synth
+    from oracle.simulator import OracleSimulator
+
+    mdl = synth.pes_learning_model(n_ensembles=n_ensembles, n_neurons=FULL["n_neurons"],
+                                   dimensions=FULL["dimensions"], n_templates=min(8, n_ensembles), n_probes=2)
+    ora = OracleSimulator(mdl)
+    ora.run_steps(warmup)
+    t0 = time.perf_counter()
+    ora.run_steps(steps)
+    dt = time.perf_counter() - t0
+    return mdl.n_neurons * steps / dt, dt / steps, mdl.n_neurons
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    n_ens = 512
+    rate, s_per_step, n_neurons = cpu_oracle_rate(n_ens, args.steps, warmup=min(max(args.warmup, 1), 3))
+    cores = len(os.sched_getaffinity(0))
+    sample = "%d of 4096 ensembles (%d neurons), %d steps" % (n_ens, n_neurons, args.steps)
+    line = {
+        "impl": "reference", "metric": "neuron_updates_per_s", "value": rate, "unit": "neuron-updates/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * s_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": rate, "unit": "neuron-updates/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": rate, "unit": "neuron-updates/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "steps_per_s_of_sample": 1.0 / s_per_step,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def gemv_microbench(queue, capi, reps=20):
+    """Configuration 2: 4096 outputs, 1-4 terms, rows U[1,1024], columns U[1,64]."""
+    from nengo_ocl_b200 import cura_gemv
+    from nengo_ocl_b200.curaggedarray import CUDARaggedArray
+    from nengo_ocl_b200.synth import gemv_workload
+
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=4096)
+    clA, clX, clY = CUDARaggedArray(queue, A), CUDARaggedArray(queue, X), CUDARaggedArray(queue, Y)
+    prog = cura_gemv.plan_fused_gemv(queue, 0.5, clA, A_js, clX, X_js, 0.1, clY)
+    plan = prog.plans[0]
+    for _ in range(3):
+        plan()
+    ev = Events(capi)
+    times = []
+    for _ in range(reps):
+        ev.start(queue.stream)
+        plan.kern(queue.stream)
+        times.append(ev.stop_ms(queue.stream))
+    ms = float(np.median(times))
+    return {"workload": "ragged gather-GEMV, 4096 outputs x 1-4 terms, M U[1,1024], N U[1,64], seed 1",
+            "bytes_per_call": int(plan.bw_per_call), "ms_per_call": ms,
+            "achieved_gbs": plan.bw_per_call / ms / 1e6, "launches_per_call": plan.n_launches,
+            "status": int(plan.status.get()[0])}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ensembles", type=int, default=FULL["n_ensembles"], help="ensembles per GPU")
+    ap.add_argument("--no-gemv", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        args.steps = min(args.steps, 60)  # bounded sample: about 0.2 s of CPU time per step
+        run_reference(args, rank)
+        return
+
+    from nengo_ocl_b200 import _capi, synth
+    from nengo_ocl_b200.runtime import create_some_context
+    from nengo_ocl_b200.simulator import Simulator
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = create_some_context(local_rank)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    K, W = args.steps, max(args.warmup, 3)
+    t_build = time.perf_counter()
+    mdl = synth.pes_learning_model(seed=3 + rank, n_ensembles=args.ensembles, n_neurons=FULL["n_neurons"],
+                                   dimensions=FULL["dimensions"], sim_time=0.5)
+    n_neurons = mdl.n_neurons
+    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True)
+    build_s = time.perf_counter() - t_build
+    plans = sim._plans
+    fused = [p for p in plans if p.name == "fused_ensemble_step"]
+    assert fused, "the fused ensemble kernel must be on the path"
+    fused_plan = fused[0]
+    queue = sim.queue
+    ev = Events(_capi)
+
+    # ---- value: device-timed, inputs resident ---------------------------------
+    sim._upload_inputs(min(W, sim._max_steps_between_probes))
+    plans.call_n_times(min(W, sim._max_steps_between_probes))
+    sim._probe()
+    B = sim._max_steps_between_probes
+    for st in sim._input_streams:  # make the whole window resident for the device-only timing
+        pass
+    barrier()
+    _capi.call("nb2_device_sync")
+    with ClockSampler(local_rank) as clocks:
+        done, total_ms = 0, 0.0
+        while done < K:
+            b = min(B, K - done)
+            sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
+            _capi.call("nb2_stream_sync", queue.stream)
+            ev.start(queue.stream)
+            plans.enqueue_n_times(b)
+            total_ms += ev.stop_ms(queue.stream)
+            sim._probe()               # drain outside the timed region
+            done += b
+        barrier()
+        _capi.call("nb2_device_sync")
+    total_ms = max_over_ranks(total_ms)
+    ms_per_step = total_ms / K
+    value = world * n_neurons * K / (total_ms / 1e3)
+    launches = K * plans.launches_per_step
+
+    # ---- roofline: the fused kernel, CUDA events around every launch -----------
+    times = []
+    for _ in range(min(K, 30)):
+        for p in plans:
+            if p is fused_plan:
+                ev.start(queue.stream)
+                p.kern(queue.stream)
+                times.append(ev.stop_ms(queue.stream))
+            else:
+                p.kern(queue.stream)
+    _capi.call("nb2_stream_sync", queue.stream)
+    sim._probe()
+    fused_ms = float(np.mean(times))
+    peak, peak_src = measured_peak_gbs()
+    achieved = fused_plan.bw_per_call / fused_ms / 1e6
+    roofline = {"bound": "hbm", "kernel": "nb2_ensemble_step_kernel", "achieved": achieved, "peak": peak,
+                "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "algorithmic_bytes_per_launch": int(fused_plan.bw_per_call), "ms_per_launch": fused_ms,
+                "share_of_step": fused_ms / ms_per_step}
+
+    # ---- e2e: public API, host tables in, probe data out ------------------------
+    barrier()
+    _capi.call("nb2_device_sync")
+    t0 = time.perf_counter()
+    sim.run_steps(K)
+    _capi.call("nb2_device_sync")
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    probe_bytes = sum(4 * int(mdl.sig[p]["in"].size) for p in mdl.probes) + 4 * len(mdl.probes) / B + 8.0 / B
+    e2e = {"value": world * n_neurons * K / e2e_s, "unit": "neuron-updates/s",
+           "h2d_bytes_per_step": int(sim.h2d_bytes_per_step), "d2h_bytes_per_step": int(round(probe_bytes)),
+           "steps_per_s": K / e2e_s}
+
+    line = {
+        "metric": "neuron_updates_per_s", "value": value, "unit": "neuron-updates/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "ensembles_per_gpu": args.ensembles, "neurons_per_gpu": n_neurons,
+                   "l2": "working set per step (~0.9 GB) exceeds the 126 MB L2", "build_s": round(build_s, 1),
+                   "plans_per_step": len(plans), "graph_unroll": plans.unroll},
+        "steps_per_s": K / (total_ms / 1e3), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and not args.no_gemv:
+        line["gemv"] = gemv_microbench(queue, _capi)
+        line["gemv"]["frac"] = line["gemv"]["achieved_gbs"] / peak
+    if rank == 0 and not args.no_cpu and world == 1:
+        n_ens = 512
+        rate, s_per_step, nn = cpu_oracle_rate(n_ens, 40)
+        line["cpu_baseline"] = {"value": rate, "unit": "neuron-updates/s", "cores": len(os.sched_getaffinity(0)),
+                                "kind": "port", "sample": "%d of 4096 ensembles (%d neurons), 40 steps" % (n_ens, nn)}
+    sim.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

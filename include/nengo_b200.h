@@ -144,10 +144,13 @@ int nb2_probes(void* stream, int n_probes, int block_size, float* countdowns, in
                const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
                const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
                float* Y);
-/* plan_presentinput :1678-1759; pres_t may be NULL (table indexed by step) */
+/* plan_presentinput :1678-1759; pres_t may be NULL (table indexed by step);
+ * Sstride0s may be NULL (table rows packed, as in the reference) or give the
+ * row stride of every table (tables that are column blocks of one buffer) */
 int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
                      const int* Yshape0s, const int* Ystarts, float* Y, const int* Tstarts,
-                     const float* T, const int* Sshape0s, const int* Sstarts, const float* S);
+                     const float* T, const int* Sshape0s, const int* Sstarts, const int* Sstride0s,
+                     const float* S);
 
 /* Neuron models generated by _plan_template (:1286-1483): plan_lif :1028-1146,
  * plan_lif_rate :1149-1197, plan_spiking_rectified_linear :1200-1235,

@@ -326,6 +326,7 @@ __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float 
                                         const int* __restrict__ Tstarts, const float* T,
                                         const int* __restrict__ Sshape0s,
                                         const int* __restrict__ Sstarts,
+                                        const int* __restrict__ Sstride0s,
                                         const float* __restrict__ S) {
   const int k = blockIdx.x;
   const int m = Yshape0s[k];
@@ -336,17 +337,19 @@ __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float 
   int ti;
   if (pres_t) ti = (int)(((float)it - 0.5f) * (dt / pres_t[k])) % nt;
   else ti = it % nt;
-  for (int i = threadIdx.x; i < m; i += blockDim.x) y[i] = s[m * ti + i];
+  const int row = Sstride0s ? Sstride0s[k] : m;  // table rows are packed unless a stride table is given
+  for (int i = threadIdx.x; i < m; i += blockDim.x) y[i] = s[(size_t)row * ti + i];
 }
 
 extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
                                 const int* Yshape0s, const int* Ystarts, float* Y, const int* Tstarts,
-                                const float* T, const int* Sshape0s, const int* Sstarts, const float* S) {
+                                const float* T, const int* Sshape0s, const int* Sstarts,
+                                const int* Sstride0s, const float* S) {
   if (n_items == 0) return NB2_OK;
   NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
   NB2_REQUIRE(Yshape0s && Ystarts && Y && Tstarts && T && Sshape0s && Sstarts && S, "null pointer");
   nb2_presentinput_kernel<<<n_items, block_size, 0, nb2_stream(stream)>>>(
-      pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, S);
+      pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

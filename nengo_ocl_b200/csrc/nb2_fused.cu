@@ -38,7 +38,7 @@
 #define FUSED_SMALL_N NB2_FUSED_SMALL_NEURONS
 
 // table layouts (ints; floats stored as bit patterns)
-enum { E_N = 0, E_J, E_V, E_W, E_S, E_BIAS, E_NTERMS, E_TERM0, E_NCONN, E_CONN0, E_TAU, E_REF, E_AMP, E_STRIDE = 16 };
+enum { E_N = 0, E_J, E_V, E_W, E_S, E_BIAS, E_NTERMS, E_TERM0, E_NCONN, E_CONN0, E_TAU, E_REF, E_AMP, E_FLAGS, E_STRIDE = 16 };
 enum { T_A = 0, T_D, T_X, T_XS, T_STRIDE = 4 };
 enum { C_W = 0, C_D, C_WEIGHTED, C_FILT, C_B0, C_A0, C_PES, C_ERR, C_PF, C_PFB0, C_PFA0, C_ALPHA, C_STRIDE = 16 };
 
@@ -66,14 +66,14 @@ __device__ __forceinline__ float fused_lif(float J, float& V, float& W, float ta
 
 // TPE = threads per ensemble (32 or 256); NEMAX = staged neurons per ensemble
 template <int TPE, int NEMAX>
-__global__ void __launch_bounds__(FUSED_THREADS, 4)
+__global__ void __launch_bounds__(FUSED_THREADS, 3)
 nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* __restrict__ ens_table,
                          const int* __restrict__ term_table, const int* __restrict__ conn_table,
                          float* data, float dt, float dt_inv) {
   constexpr int GROUPS = FUSED_THREADS / TPE;     // ensembles per CTA
   constexpr int WARPS = TPE / 32;                 // warps per ensemble
-  __shared__ float s_spk[GROUPS][NEMAX];
-  __shared__ float s_x[GROUPS][FUSED_MAX_X];
+  __shared__ __align__(16) float s_spk[GROUPS][NEMAX];
+  __shared__ __align__(16) float s_x[GROUPS][FUSED_MAX_X];
   __shared__ float s_red[GROUPS][WARPS][FUSED_RCH];
   __shared__ float s_ae[GROUPS][FUSED_RCH];
 
@@ -85,6 +85,8 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
   const bool active = slot < n_ens;
   const int* e = ens_table + (size_t)(active ? ens_ids[slot] : 0) * E_STRIDE;
   const int n = active ? e[E_N] : 0;
+  // 128-bit path: n, every encoder width and every array start are multiples of 4 (set by the host)
+  const bool vec = active && (e[E_FLAGS] & 1);
 
   auto group_sync = [&]() {
     if (TPE == 32) __syncwarp();
@@ -114,6 +116,47 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
     float* W = data + e[E_W];
     float* S = e[E_S] >= 0 ? data + e[E_S] : nullptr;
     float* Jout = e[E_J] >= 0 ? data + e[E_J] : nullptr;
+    if (vec) {
+      // four consecutive neurons per thread: 16 independent 128-bit encoder loads in flight
+      const int n4 = n >> 2;
+      for (int i4 = t; i4 < n4; i4 += TPE) {
+        const int i = i4 << 2;
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int xoff = 0;
+        for (int k = 0; k < n_terms; ++k) {
+          const int d4 = terms[k * T_STRIDE + T_D] >> 2;
+          const float4* rows =
+              reinterpret_cast<const float4*>(data + terms[k * T_STRIDE + T_A]) + (size_t)i * d4;
+          const float4* xv = reinterpret_cast<const float4*>(&s_x[grp][xoff]);
+          for (int c = 0; c < d4; ++c) {
+            const float4 x4 = xv[c];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 a = __ldg(rows + (size_t)j * d4 + c);
+              sum[j] = fmaf(a.x, x4.x, sum[j]);
+              sum[j] = fmaf(a.y, x4.y, sum[j]);
+              sum[j] = fmaf(a.z, x4.z, sum[j]);
+              sum[j] = fmaf(a.w, x4.w, sum[j]);
+            }
+          }
+          xoff += d4 << 2;
+        }
+        const float4 b4 = *reinterpret_cast<const float4*>(bias + i);
+        float4 v4 = *reinterpret_cast<float4*>(V + i);
+        float4 w4 = *reinterpret_cast<float4*>(W + i);
+        float4 J4, s4;
+        J4.x = b4.x + sum[0]; J4.y = b4.y + sum[1]; J4.z = b4.z + sum[2]; J4.w = b4.w + sum[3];
+        s4.x = fused_lif(J4.x, v4.x, w4.x, tau, ref, amp, dt, dt_inv);
+        s4.y = fused_lif(J4.y, v4.y, w4.y, tau, ref, amp, dt, dt_inv);
+        s4.z = fused_lif(J4.z, v4.z, w4.z, tau, ref, amp, dt, dt_inv);
+        s4.w = fused_lif(J4.w, v4.w, w4.w, tau, ref, amp, dt, dt_inv);
+        *reinterpret_cast<float4*>(V + i) = v4;
+        *reinterpret_cast<float4*>(W + i) = w4;
+        if (S) *reinterpret_cast<float4*>(S + i) = s4;
+        if (Jout) *reinterpret_cast<float4*>(Jout + i) = J4;
+        *reinterpret_cast<float4*>(&s_spk[grp][i]) = s4;
+      }
+    } else
     for (int i = t; i < n; i += TPE) {
       float sum = 0.0f;
       int xoff = 0;
@@ -166,6 +209,43 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
       float acc[FUSED_RCH];
 #pragma unroll
       for (int r = 0; r < FUSED_RCH; ++r) acc[r] = 0.0f;
+      if (vec) {
+        // 128-bit loads of 8 decoder rows at a time: all loads of a half-pass are issued
+        // before the (possibly aliasing) PES stores of the same rows
+        const int n4 = n >> 2;
+        for (int i4 = t; i4 < n4; i4 += TPE) {
+          const float4 s4 = *reinterpret_cast<const float4*>(&s_spk[grp][i4 << 2]);
+          float4 p4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (pes) p4 = *reinterpret_cast<const float4*>(pf + (i4 << 2));
+#pragma unroll
+          for (int h = 0; h < FUSED_RCH; h += 8) {
+            float4 wv[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (h + r < nr) wv[r] = *(reinterpret_cast<const float4*>(Wd + (size_t)(r0 + h + r) * n) + i4);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (h + r < nr) {
+                float a = acc[h + r];
+                a = fmaf(wv[r].x, s4.x, a);
+                a = fmaf(wv[r].y, s4.y, a);
+                a = fmaf(wv[r].z, s4.z, a);
+                a = fmaf(wv[r].w, s4.w, a);
+                acc[h + r] = a;
+                if (pes) {
+                  const float ae = s_ae[grp][h + r];
+                  float4 o;
+                  o.x = wv[r].x + ae * p4.x;
+                  o.y = wv[r].y + ae * p4.y;
+                  o.z = wv[r].z + ae * p4.z;
+                  o.w = wv[r].w + ae * p4.w;
+                  *(reinterpret_cast<float4*>(Wd + (size_t)(r0 + h + r) * n) + i4) = o;
+                }
+              }
+            }
+          }
+        }
+      } else
       for (int i = t; i < n; i += TPE) {
         const float s = s_spk[grp][i];
         const float p = pes ? pf[i] : 0.0f;

@@ -422,8 +422,10 @@ def plan_presentinput(queue, Y, t, signals, dt, pres_t=None, tag=None):
 
     max_len = int(min(max(Y.shape0s), get_mwgs(queue)))
     fn, check = _capi.lib().nb2_presentinput, _capi.check
+    packed = bool((signals.stride0s == signals.shape1s).all())
     args = (N, max_len, _ptr(pres_t), float(dt), Y.cl_shape0s.ptr, Y.cl_starts.ptr, Y.cl_buf.ptr,
-            t.cl_starts.ptr, t.cl_buf.ptr, signals.cl_shape0s.ptr, signals.cl_starts.ptr, signals.cl_buf.ptr)
+            t.cl_starts.ptr, t.cl_buf.ptr, signals.cl_shape0s.ptr, signals.cl_starts.ptr,
+            None if packed else signals.cl_stride0s.ptr, signals.cl_buf.ptr)
 
     def launch(stream):
         check(fn(stream, *args))

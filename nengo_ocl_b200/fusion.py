@@ -13,8 +13,9 @@ and which is executed by ``nb2_ensemble_step`` (csrc/nb2_fused.cu).
 Per population (a ``SimNeurons`` operator with LIF neurons) the pattern is:
 
 * ``J``: set by one un-sliced ``Copy`` (the bias) and incremented by exactly one
-  ``MultiDotInc`` whose terms are dense row-major ``(n, d)`` matrices; nothing
-  else reads or writes ``J``;
+  ``MultiDotInc`` whose terms are dense row-major ``(n, d)`` matrices (or by
+  none, when the simplifier removed a product with a constant-zero input);
+  nothing else reads or writes ``J``;
 * each decoded connection: a one-term ``MultiDotInc`` ``decoded += W . spikes``
   with row-major ``(d_c, n)`` weights onto a signal that is otherwise only
   reset to zero; optionally a first-order ``LinearFilter`` process (lowpass or
@@ -121,14 +122,16 @@ def find_fusable(sim, operators):
         jw = writers.get(J, [])
         bias_ops = [op for op, kind, s in jw if _is_type(op, "Copy") and kind == "sets" and s is J]
         enc_ops = [op for op, kind, s in jw if isinstance(op, MultiDotInc) and kind == "incs" and s is J]
-        if len(jw) != 2 or len(bias_ops) != 1 or len(enc_ops) != 1:
+        if len(bias_ops) != 1 or len(enc_ops) > 1 or len(jw) != 1 + len(enc_ops):
             continue
-        bias_op, enc_op = bias_ops[0], enc_ops[0]
+        # (an ensemble whose input is known to be zero has had its encoder product removed)
+        bias_op, enc_op = bias_ops[0], (enc_ops[0] if enc_ops else None)
         if bias_op.src_slice is not None or bias_op.dst_slice is not None or bias_op.src.is_view:
             continue
         if [op for op, _ in readers.get(J, [])] != [nop]:
             continue
-        A_views, X_views = sim._A_views[enc_op], sim._X_views[enc_op]
+        A_views = sim._A_views[enc_op] if enc_op is not None else []
+        X_views = sim._X_views[enc_op] if enc_op is not None else []
         if not all(_dense_rowmajor(A) and A.shape[0] == n and X.shape == (A.shape[1], 1)
                    for A, X in zip(A_views, X_views)):
             continue
@@ -136,7 +139,7 @@ def find_fusable(sim, operators):
             continue
         member = dict(neurons=nop, J=J, out=out, n=n, bias=bias_op.src, enc_terms=list(zip(A_views, X_views)),
                       state=[nop.state["voltage"], nop.state["refractory_time"]], conns=[],
-                      ops=[nop, bias_op, enc_op])
+                      ops=[nop, bias_op] + ([enc_op] if enc_op is not None else []))
 
         # --- decoded connections reading the spikes
         out_readers = [op for op, s in readers.get(out, []) if s is out]
@@ -250,6 +253,12 @@ def fused_tables(sim, members):
                 crow[8] = st(c["pre_filtered"])
                 crow[9], crow[10], crow[11] = _fbits(c["pf_b0"]), _fbits(c["pf_a0"]), _fbits(c["alpha"])
             conns.append(crow)
+        # 128-bit path when the neuron count, every encoder width and every array start are multiples of 4
+        first_conn = row[9]
+        offsets = [row[2], row[3], row[5]] + ([row[4]] if row[4] >= 0 else [])
+        offsets += [v for trow in terms[row[7]:] for v in (trow[0], trow[1])]
+        offsets += [v for crow in conns[first_conn:] for v in (crow[0],) + ((crow[8],) if crow[6] else ())]
+        row[13] = int(mem["n"] % 4 == 0 and all(v % 4 == 0 for v in offsets))
         ens.append(row)
     as32 = lambda rows, width: np.asarray(rows, dtype=np.int32).reshape(-1, width)
     return as32(ens, 16), as32(terms, 4), as32(conns, 16)

@@ -14,6 +14,7 @@ GEMV, neuron update, decoder GEMV, synapse, PES) are fused into one kernel, and
 probe buffers are drained with one bounded copy per probe.
 """
 
+import ctypes
 import logging
 import os
 import warnings
@@ -47,7 +48,7 @@ from nengo_ocl_b200.operators import MultiDotInc, simplify_operators
 from nengo_ocl_b200.plan import BasePlan, Plans, PythonPlan
 from nengo_ocl_b200.planners import greedy_planner
 from nengo_ocl_b200.raggedarray import RaggedArray
-from nengo_ocl_b200.runtime import CommandQueue, create_some_context
+from nengo_ocl_b200.runtime import CommandQueue, DeviceArray, create_some_context
 from nengo_ocl_b200.utils import groupby, indent, split, stable_unique
 
 logger = logging.getLogger(__name__)
@@ -166,6 +167,11 @@ class Simulator:
         Operator grouping function (see ``nengo_ocl_b200.planners``).
     fuse : bool
         Fuse ensemble-pattern operator groups into one kernel per step.
+    graph_unroll : int
+        Steps captured per CUDA graph (fewer graph launches per batch).
+    stream_inputs : bool
+        Keep input tables (WhiteSignal) in pinned host memory and upload only the
+        rows of the next batch of steps before it runs.
     """
 
     some_context = None
@@ -178,7 +184,7 @@ class Simulator:
 
     def __init__(self, network, dt=0.001, seed=None, model=None, context=None, n_prealloc_probes=32,
                  profiling=None, if_python_code="none", planner=greedy_planner, progress_bar=True, fuse=True,
-                 graph_unroll=8):
+                 graph_unroll=8, stream_inputs=False):
         self.closed = False
         self.model = None
         if context is None and Simulator.some_context is None:
@@ -195,6 +201,9 @@ class Simulator:
         self.progress_bar = progress_bar
         self.fuse = fuse
         self._planner = planner
+        self.stream_inputs = stream_inputs
+        self._input_streams = []
+        self.h2d_bytes_per_step = 0
 
         # --- model
         if model is None:
@@ -452,6 +461,7 @@ class Simulator:
             raise ValueError("Cannot run for negative steps (got %r)" % (steps,))
         while steps > 0:
             B = min(steps, self._max_steps_between_probes)
+            self._upload_inputs(B)
             self._plans.call_n_times(B)
             self._probe()
             steps -= B
@@ -796,9 +806,49 @@ class Simulator:
     def _plan_WhiteSignal(self, ops):
         Y = self.all_data[[self.sidx[op.output] for op in ops]]
         t = self.all_data[[self.sidx[self.model.step] for _ in ops]]
-        signals = self.RaggedArray([np.asarray(op.process.signal).reshape(len(op.process.signal), -1)
-                                    for op in ops], dtype=np.float32)
+        tables = [np.asarray(op.process.signal).reshape(len(op.process.signal), -1) for op in ops]
+        if self.stream_inputs and len({len(tb) for tb in tables}) == 1:
+            return [self._plan_streamed_tables(Y, t, tables)]
+        signals = self.RaggedArray(tables, dtype=np.float32)
         return [plan_presentinput(self.queue, Y, t, signals, self.model.dt)]
+
+    def _plan_streamed_tables(self, Y, t, tables):
+        """Input tables kept in pinned host memory; the device holds a window of
+        as many rows as there are steps between two probe drains, refilled from
+        the host before every batch of steps (``_upload_inputs``).  All tables
+        are column blocks of one (rows x total width) buffer, so a refill is at
+        most three contiguous copies."""
+        widths = np.array([tb.shape[1] for tb in tables], dtype=np.int64)
+        total = int(widths.sum())
+        n_table = len(tables[0])
+        periods = [max(1 if p.sample_every is None else p.sample_every / self.dt, 1) for p in self.model.probes]
+        window = int(self.n_prealloc_probes) * (int(min(periods)) if periods else 1)
+        hptr = ctypes.c_void_p()
+        _capi.call("nb2_host_alloc", ctypes.byref(hptr), n_table * total * 4)
+        host = np.ctypeslib.as_array(ctypes.cast(hptr, ctypes.POINTER(ctypes.c_float)), shape=(n_table, total))
+        host[...] = np.concatenate(tables, axis=1)
+        dev = DeviceArray(self.queue, (window * total,), np.float32)
+        cols = np.concatenate([[0], np.cumsum(widths)[:-1]])
+        signals = CUDARaggedArray.from_buffer(self.queue, dev, cols, [window] * len(tables), widths,
+                                              [total] * len(tables), [1] * len(tables))
+        self._input_streams.append(dict(host=host, hptr=hptr, dev=dev, total=total, n_table=n_table, window=window))
+        self.h2d_bytes_per_step += 4 * total
+        return plan_presentinput(self.queue, Y, t, signals, self.model.dt)
+
+    def _upload_inputs(self, n_steps):
+        """Refill the device windows with the table rows of the next ``n_steps`` steps."""
+        for st in self._input_streams:
+            first = self._n_steps + 1  # the clock is incremented before the tables are read
+            assert n_steps <= st["window"]
+            done = 0
+            while done < n_steps:
+                step = first + done
+                src, dst = step % st["n_table"], step % st["window"]
+                run = min(n_steps - done, st["n_table"] - src, st["window"] - dst)
+                _capi.call("nb2_memcpy_h2d", ctypes.c_void_p(st["dev"].data + dst * st["total"] * 4),
+                           ctypes.c_void_p(st["host"].ctypes.data + src * st["total"] * 4), run * st["total"] * 4,
+                           self.queue.stream, 0)
+                done += run
 
     def _plan_PresentInput(self, ops):
         ps = [op.process for op in ops]

@@ -29,7 +29,7 @@ sys.path.insert(0, HERE)
 import refstubs  # noqa: E402
 
 
-def main(reference_root):
+def main(reference_root, write_fixtures=True):
     mods = refstubs.install(reference_root)
     from oracle import refkernels  # noqa: E402
 
@@ -275,9 +275,11 @@ def main(reference_root):
     kernels["linearfilter/xs"] = np.array(xs_seq)
     kernels["linearfilter/ys"] = np.array(ys_seq)
 
-    np.savez_compressed(os.path.join(HERE, "tables.npz"), **tables)
-    np.savez_compressed(os.path.join(HERE, "kernels.npz"), **kernels)
-    print("wrote %d table entries, %d kernel entries" % (len(tables), len(kernels)))
+    if write_fixtures:
+        np.savez_compressed(os.path.join(HERE, "tables.npz"), **tables)
+        np.savez_compressed(os.path.join(HERE, "kernels.npz"), **kernels)
+        print("wrote %d table entries, %d kernel entries" % (len(tables), len(kernels)))
+    return tables, kernels
 
 
 if __name__ == "__main__":

@@ -170,8 +170,19 @@ def small_pes(seed=3, **kw):
     return synth.pes_learning_model(seed=seed, **args)
 
 
+def wide_pes(seed=3):
+    # the shape of the benchmark model (1024 neurons, 16 dimensions): CTA-per-ensemble, 128-bit path
+    return small_pes(seed=seed, n_ensembles=6, n_neurons=1024, dimensions=16, n_templates=2)
+
+
+def odd_pes(seed=3):
+    # sizes that are not multiples of 4: scalar path of the CTA-per-ensemble kernel
+    return small_pes(seed=seed, n_ensembles=5, n_neurons=301, dimensions=3, n_templates=2)
+
+
 @pytest.mark.parametrize("fuse", [False, True])
-@pytest.mark.parametrize("make", [small_ws, small_pes], ids=["watts_strogatz", "pes"])
+@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes],
+                         ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3"])
 def test_scaled_configs_match_oracle_per_step(make, fuse):
     mdl = make()
     ora = OracleSimulator(mdl)
