@@ -152,6 +152,13 @@ int nb2_presentinput(void* stream, int n_items, int block_size, const float* pre
                      const float* T, const int* Sshape0s, const int* Sstarts, const int* Sstride0s,
                      const float* S);
 
+/* Reset-then-accumulate in one launch: the reference runs plan_reset (:147-214)
+ * and then one plan_copy(inc) (:217-304) per group of non-overlapping targets.
+ * blocks [n_blocks][4] = {dst start, elements (<= 256), first source, n sources};
+ * src_starts holds the element offset of every (block, source) pair; sources are
+ * added in order starting from zero. */
+int nb2_gather_sum(void* stream, int n_blocks, const int* blocks, const int* src_starts, float* data);
+
 /* Neuron models generated by _plan_template (:1286-1483): plan_lif :1028-1146,
  * plan_lif_rate :1149-1197, plan_spiking_rectified_linear :1200-1235,
  * plan_rectified_linear :1238-1259, plan_sigmoid :1262-1283.  Each variable is

@@ -353,3 +353,30 @@ extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
+
+// ---- gather-sum: Y = sum of sources ------------------------------------------
+// One launch for the pattern "reset a signal to zero, then increment it by
+// several whole-signal copies" (plan_reset :147-214 followed by one plan_copy
+// :217-304 per group of non-overlapping targets in the reference).  Sources are
+// added in operator order starting from zero, so the result is bit-identical to
+// the reset + sequential increments.
+// blocks: [n_blocks][4] = {dst start, element count (<= 256), first source, source count};
+// src_starts: element offset of every (block, source) pair.
+__global__ void nb2_gather_sum_kernel(const int4* __restrict__ blocks, const int* __restrict__ src_starts,
+                                      float* data) {
+  const int4 b = blocks[blockIdx.x];
+  const int i = threadIdx.x;
+  if (i >= b.y) return;
+  float sum = 0.0f;
+  for (int k = 0; k < b.w; ++k) sum += data[src_starts[b.z + k] + i];
+  data[b.x + i] = sum;
+}
+
+extern "C" int nb2_gather_sum(void* stream, int n_blocks, const int* blocks, const int* src_starts, float* data) {
+  if (n_blocks == 0) return NB2_OK;
+  NB2_REQUIRE(blocks && src_starts && data, "null pointer");
+  nb2_gather_sum_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(reinterpret_cast<const int4*>(blocks),
+                                                                 src_starts, data);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}

@@ -212,10 +212,13 @@ def fuse_ensemble_groups(sim, groups, planner=None):
     planner = planner or getattr(sim, "_planner", None) or greedy_planner
     operators = sim.operators
     members, consumed = find_fusable(sim, operators)
-    if not members:
+    gathers, gathered = find_gather_sums([op for op in operators if op not in consumed])
+    if not members and not gathers:
         return groups
-    fused = FusedEnsembles(members)
-    new_ops = [op for op in operators if op not in consumed] + [fused]
+    consumed = set(consumed) | gathered
+    new_ops = [op for op in operators if op not in consumed] + gathers
+    if members:
+        new_ops.append(FusedEnsembles(members))
     try:
         new_groups = planner(new_ops)
     except ValueError:
@@ -319,4 +322,69 @@ def plan_fused_ensembles(sim, ops):
                               for mem in members)
     plan.description = "ensembles: %d; neurons: %d; connections: %d (PES: %d)" % (
         len(members), n_neurons, len(conns), int(sum(c[6] for c in conns.tolist())) if len(conns) else 0)
+    return [plan]
+
+
+# ---- reset + whole-signal increments -> one gather-sum ---------------------------
+class GatherSum(Operator):
+    """``dst = sum(srcs)``: a signal that is reset to zero and then only
+    incremented by whole-signal copies."""
+
+    def __init__(self, dst, srcs, ops):
+        Operator.__init__(self, tag="gather-%d" % len(srcs))
+        self.dst, self.srcs, self.ops = dst, list(srcs), list(ops)
+        self.sets = [dst]
+        self.reads = list(srcs)
+
+
+def find_gather_sums(operators):
+    """Signals written only by ``Reset(0)`` and un-sliced ``Copy(inc=True)`` ops."""
+    writers = {}
+    for op in operators:
+        for kind in ("sets", "incs", "updates"):
+            for s in getattr(op, kind):
+                writers.setdefault(s.base, []).append((op, kind, s))
+    gathers, consumed = [], set()
+    for base, ws in writers.items():
+        if base.is_view or len(ws) < 2:
+            continue
+        resets = [op for op, kind, s in ws if _is_type(op, "Reset") and s is base and op.value == 0]
+        copies = [op for op, kind, s in ws if _is_type(op, "Copy") and kind == "incs" and s is base
+                  and op.src_slice is None and op.dst_slice is None and op.src.size == base.size
+                  and (op.src.ndim <= 1 and (op.src.size <= 1 or op.src.elemstrides[-1] == 1))]
+        if len(resets) != 1 or len(resets) + len(copies) != len(ws) or base.ndim > 1:
+            continue
+        ordered = [op for op in operators if op in set(copies)]  # operator order = summation order
+        gathers.append(GatherSum(base, [op.src for op in ordered], resets + ordered))
+        consumed.update(resets + ordered)
+    return gathers, consumed
+
+
+def plan_gather_sums(sim, ops):
+    """One launch for all gather-sums of a group (csrc: nb2_gather_sum)."""
+    starts, sidx = sim.all_data.starts, sim.sidx
+    blocks, srcs = [], []
+    n_bytes = 0
+    for op in ops:
+        d0, size = int(starts[sidx[op.dst]]), op.dst.size
+        s0 = [int(starts[sidx[s]]) for s in op.srcs]
+        for off in range(0, size, 256):
+            blocks.append([d0 + off, min(256, size - off), len(srcs), len(s0)])
+            srcs.extend(s + off for s in s0)
+        n_bytes += 4 * size * (len(s0) + 1)
+    queue = sim.queue
+    d_blocks = to_device(queue, np.asarray(blocks, dtype=np.int32).reshape(-1, 4))
+    d_srcs = to_device(queue, np.asarray(srcs + [0], dtype=np.int32))
+    data = sim.all_data.cl_buf
+    fn, check = _capi.lib().nb2_gather_sum, _capi.check
+    args = (len(blocks), d_blocks.ptr, d_srcs.ptr, data.ptr)
+
+    def launch(stream):
+        check(fn(stream, *args))
+
+    plan = Plan(queue, launch, (256, max(len(blocks), 1)), lsize=(256, 1), name="gather_sum",
+                tag="%d signals" % len(ops))
+    plan.full_args = (d_blocks, d_srcs, data)
+    plan.bw_per_call = n_bytes
+    plan.description = "signals: %d; sources: %d" % (len(ops), len(srcs))
     return [plan]

@@ -512,6 +512,11 @@ class Simulator:
 
         return plan_fused_ensembles(self, groups)
 
+    def _plan_GatherSum(self, ops):
+        from nengo_ocl_b200.fusion import plan_gather_sums
+
+        return plan_gather_sums(self, ops)
+
     def _plan_MultiDotInc(self, ops):
         constant_bs = [op for op in ops if op._float_beta is not None]
         vector_bs = [op for op in ops if op._signal_beta is not None and op._signal_beta.ndim == 1]
