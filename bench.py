@@ -154,13 +154,13 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def gemv_microbench(queue, capi, reps=20):
+def gemv_microbench(queue, capi, reps=20, n_outputs=4096):
     """Configuration 2: 4096 outputs, 1-4 terms, rows U[1,1024], columns U[1,64]."""
     from nengo_ocl_b200 import cura_gemv
     from nengo_ocl_b200.curaggedarray import CUDARaggedArray
     from nengo_ocl_b200.synth import gemv_workload
 
-    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=4096)
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=n_outputs)
     clA, clX, clY = CUDARaggedArray(queue, A), CUDARaggedArray(queue, X), CUDARaggedArray(queue, Y)
     prog = cura_gemv.plan_fused_gemv(queue, 0.5, clA, A_js, clX, X_js, 0.1, clY)
     plan = prog.plans[0]
@@ -173,7 +173,7 @@ def gemv_microbench(queue, capi, reps=20):
         plan.kern(queue.stream)
         times.append(ev.stop_ms(queue.stream))
     ms = float(np.median(times))
-    return {"workload": "ragged gather-GEMV, 4096 outputs x 1-4 terms, M U[1,1024], N U[1,64], seed 1",
+    return {"workload": "ragged gather-GEMV, %d outputs x 1-4 terms, M U[1,1024], N U[1,64], seed 1" % n_outputs,
             "bytes_per_call": int(plan.bw_per_call), "ms_per_call": ms,
             "achieved_gbs": plan.bw_per_call / ms / 1e6, "launches_per_call": plan.n_launches,
             "status": int(plan.status.get()[0])}
@@ -187,6 +187,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ensembles", type=int, default=FULL["n_ensembles"], help="ensembles per GPU")
     ap.add_argument("--no-gemv", action="store_true")
+    ap.add_argument("--gemv-only", action="store_true", help="run only the GEMV microbenchmark (for profiling)")
+    ap.add_argument("--gemv-outputs", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
 
@@ -223,6 +225,15 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.gemv_only:
+        from nengo_ocl_b200.runtime import CommandQueue
+
+        peak, _ = measured_peak_gbs()
+        out = gemv_microbench(CommandQueue(ctx), _capi, reps=max(args.steps, 1), n_outputs=args.gemv_outputs)
+        out["frac"] = out["achieved_gbs"] / peak
+        print(json.dumps({"gemv": out}), flush=True)
+        return
 
     K, W = args.steps, max(args.warmup, 3)
     t_build = time.perf_counter()
