@@ -240,10 +240,16 @@ def main():
 
     K, W = args.steps, max(args.warmup, 3)
     t_build = time.perf_counter()
-    mdl = synth.pes_learning_model(seed=3 + rank, n_ensembles=args.ensembles, n_neurons=FULL["n_neurons"],
-                                   dimensions=FULL["dimensions"], sim_time=0.5)
+    # weak scaling: every GPU simulates `--ensembles` ensembles of one network of world * ensembles
+    mdl = synth.pes_learning_shard(seed=3, n_ensembles=args.ensembles * world, rank=rank, world=world,
+                                   n_neurons=FULL["n_neurons"], dimensions=FULL["dimensions"], sim_time=0.5)
     n_neurons = mdl.n_neurons
-    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True)
+    exchange = None
+    if world > 1:
+        from nengo_ocl_b200.exchange import TorchComm
+
+        exchange = (mdl.info["exchange"], TorchComm())
+    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True, exchange=exchange)
     build_s = time.perf_counter() - t_build
     plans = sim._plans
     fused = [p for p in plans if p.name == "fused_ensemble_step"]
@@ -320,7 +326,10 @@ def main():
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "ensembles_per_gpu": args.ensembles, "neurons_per_gpu": n_neurons,
                    "l2": "working set per step (~0.9 GB) exceeds the 126 MB L2", "build_s": round(build_s, 1),
-                   "plans_per_step": len(plans), "graph_unroll": plans.unroll},
+                   "plans_per_step": len(plans), "graph_unroll": plans.unroll,
+                   "parallelism": "ensemble blocks, 1 rank per GPU, per-step peer push of decoded signals"
+                                  if world > 1 else "single GPU",
+                   "exchange_bytes_per_step_per_gpu": 4 * mdl.info["segment"][1] * (world - 1)},
         "steps_per_s": K / (total_ms / 1e3), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
         "clocks": clocks.summary(),
     }

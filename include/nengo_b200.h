@@ -218,6 +218,23 @@ int nb2_ensemble_step(void* stream, int n_large, const int* large_ids, int n_sma
                       const int* ens_table, const int* term_table, const int* conn_table, float* data,
                       double dt);
 
+/* ---- multi-GPU exchange of decoded signals ---------------------------------
+ * No counterpart in the reference (single device, simulator.py:215-219).  Every
+ * rank holds a replica of one exchange signal of world*seg floats and owns
+ * segment `rank`.  nb2_exchange_push (end of a step) stores the local segment
+ * into every peer's staging buffer (2 * world * seg floats, alternating by step
+ * parity) through peer pointers and publishes the step number in the peer's
+ * flag array (world ints); nb2_exchange_wait (start of the next step) waits at
+ * most timeout_s for all peers' flags and copies the staged segments into the
+ * replica.  `ctl`: 8 ints of local device memory, zero-initialised (step
+ * counter, block counter, status = NB2_ERR_TIMEOUT after a timed-out wait).
+ * peer_staging / peer_flags: device arrays of `world` pointers (entry `rank`
+ * unused) obtained with nb2_ipc_open_handle. */
+int nb2_exchange_wait(void* stream, int* ctl, const int* flags, const float* staging, float* replica,
+                      int rank, int world, int seg, double timeout_s);
+int nb2_exchange_push(void* stream, int* ctl, float* const* peer_staging, int* const* peer_flags,
+                      const float* replica, int rank, int world, int seg);
+
 #ifdef __cplusplus
 }
 #endif

@@ -98,6 +98,22 @@ def _is_linear_filter(op):
     return _is_type(op, "SimProcess") and any(c.__name__ == "LinearFilter" for c in type(op.process).__mro__)
 
 
+def _extent(sig):
+    lo = sig.elemoffset
+    return lo, lo + sum((n - 1) * abs(st) for n, st in zip(sig.shape, sig.elemstrides)) + 1
+
+
+def _writers_overlapping(writers, cache, sig):
+    """Number of writer entries of ``sig.base`` whose element range overlaps ``sig``."""
+    base = sig.base
+    if base not in cache:
+        ext = np.array([_extent(w[2]) for w in writers.get(base, [])], dtype=np.int64).reshape(-1, 2)
+        cache[base] = (ext[:, 0], ext[:, 1])
+    los, his = cache[base]
+    lo, hi = _extent(sig)
+    return int(np.count_nonzero((los < hi) & (his > lo)))
+
+
 def find_fusable(sim, operators):
     """Match the ensemble pattern; returns (members, consumed operators)."""
     writers, readers = {}, {}
@@ -108,6 +124,7 @@ def find_fusable(sim, operators):
         for s in op.reads:
             readers.setdefault(s.base, []).append((op, s))
 
+    extents = {}  # base -> (lo, hi) arrays of its writers' element ranges, built on demand
     members, consumed = [], set()
     for nop in operators:
         if not _is_type(nop, "SimNeurons") or type(nop.neurons).__name__ != "LIF":
@@ -160,12 +177,12 @@ def find_fusable(sim, operators):
                         pes=False, ops=[dop, resets[0]])
             # synapse on the decoded value
             wr = [op for op, s in readers.get(weighted, []) if s is weighted]
+            # the filtered value may be a packed slice of a larger signal (an exchange buffer)
             filt = [op for op in wr if _is_linear_filter(op) and op.mode == "update" and op.input is weighted
-                    and not op.output.is_view]
+                    and op.output.ndim == 1 and (op.output.size == 1 or op.output.elemstrides[0] == 1)]
             if len(filt) == 1 and len(wr) == 1:
                 coef = _first_order(sim, filt[0])
-                fw = writers.get(filt[0].output, [])
-                if coef is not None and len(fw) == 1:
+                if coef is not None and _writers_overlapping(writers, extents, filt[0].output) == 1:
                     conn.update(filtered=filt[0].output, b0=coef[0], a0=coef[1])
                     conn["ops"].append(filt[0])
             # PES on the decoders
@@ -344,6 +361,7 @@ def find_gather_sums(operators):
         for kind in ("sets", "incs", "updates"):
             for s in getattr(op, kind):
                 writers.setdefault(s.base, []).append((op, kind, s))
+    order = {op: i for i, op in enumerate(operators)}
     gathers, consumed = [], set()
     for base, ws in writers.items():
         if base.is_view or len(ws) < 2:
@@ -354,7 +372,7 @@ def find_gather_sums(operators):
                   and (op.src.ndim <= 1 and (op.src.size <= 1 or op.src.elemstrides[-1] == 1))]
         if len(resets) != 1 or len(resets) + len(copies) != len(ws) or base.ndim > 1:
             continue
-        ordered = [op for op in operators if op in set(copies)]  # operator order = summation order
+        ordered = sorted(copies, key=order.get)  # operator order = summation order
         gathers.append(GatherSum(base, [op.src for op in ordered], resets + ordered))
         consumed.update(resets + ordered)
     return gathers, consumed

@@ -169,6 +169,10 @@ class Simulator:
         Fuse ensemble-pattern operator groups into one kernel per step.
     graph_unroll : int
         Steps captured per CUDA graph (fewer graph launches per batch).
+    exchange : (Signal, communicator), optional
+        Multi-GPU run: the signal every rank replicates and of which this rank owns
+        segment ``comm.rank`` (see ``nengo_ocl_b200.exchange``); other ranks' segments
+        are refreshed before every step.
     stream_inputs : bool
         Keep input tables (WhiteSignal) in pinned host memory and upload only the
         rows of the next batch of steps before it runs.
@@ -184,7 +188,7 @@ class Simulator:
 
     def __init__(self, network, dt=0.001, seed=None, model=None, context=None, n_prealloc_probes=32,
                  profiling=None, if_python_code="none", planner=greedy_planner, progress_bar=True, fuse=True,
-                 graph_unroll=8, stream_inputs=False):
+                 graph_unroll=8, stream_inputs=False, exchange=None):
         self.closed = False
         self.model = None
         if context is None and Simulator.some_context is None:
@@ -280,6 +284,17 @@ class Simulator:
         for op_type, op_list in groups:
             plans.extend(self._plan_op_group(op_type, op_list))
         plans.extend(self._plan_probes())
+        self._exchange = None
+        if exchange is not None:
+            from nengo_ocl_b200.exchange import Exchange
+
+            sig, comm = exchange
+            assert sig.size % comm.world == 0 and not sig.is_view
+            start = int(self.all_data.starts[self.sidx[sig]])
+            self._exchange = Exchange(self.queue, comm, self.all_data.cl_buf.data + 4 * start,
+                                      sig.size // comm.world)
+            wait, push = self._exchange.plans()
+            plans = wait + plans + push
         self._plans = Plans(plans, self.profiling, unroll=graph_unroll)
         self.rng = None
         self._n_steps = 0
@@ -389,6 +404,11 @@ class Simulator:
 
     def close(self):
         self.closed = True
+        if getattr(self, "_exchange", None) is not None:
+            self._exchange.close()
+        for st in getattr(self, "_input_streams", []):
+            _capi.lib().nb2_host_free(st["hptr"])
+        self._input_streams = []
         self.context = None
         self.queue = None
         self.all_data = None
@@ -440,6 +460,8 @@ class Simulator:
             darray.set(host)
         for rng, state in self._python_rngs.items():
             rng.set_state(state)
+        if self._exchange is not None:
+            self._exchange.reset()
         self._reset_probes()
 
     def run(self, time_in_seconds, progress_bar=None):
@@ -464,6 +486,9 @@ class Simulator:
             self._upload_inputs(B)
             self._plans.call_n_times(B)
             self._probe()
+            if self._exchange is not None and self._exchange.status() != 0:
+                raise RuntimeError("multi-GPU exchange: a peer did not publish its step within %.1f s"
+                                   % self._exchange.timeout_s)
             steps -= B
         if self.profiling > 1:
             self.print_profiling()

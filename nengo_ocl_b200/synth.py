@@ -133,11 +133,13 @@ class NetBuilder:
         return m.Signal(np.asarray(value, dtype=np.float64), name="<Node %s>.out" % label, readonly=True)
 
     # -- connections ----------------------------------------------------------------
-    def synapse(self, sig, tau, label="synapse"):
-        """Filtered copy of ``sig`` (updated at the end of the step)."""
+    def synapse(self, sig, tau, label="synapse", out=None):
+        """Filtered copy of ``sig`` (updated at the end of the step), optionally
+        written into a given signal (e.g. a slice of an exchange buffer)."""
         if tau is None:
             return sig
-        out = m.Signal(np.zeros(sig.shape), name="%s.filtered" % label)
+        if out is None:
+            out = m.Signal(np.zeros(sig.shape), name="%s.filtered" % label)
         self.model.add_op(m.SimProcess(m.Lowpass(tau), sig, out, self.model.time, mode="update"))
         return out
 
@@ -156,7 +158,7 @@ class NetBuilder:
         mdl.add_op(m.Copy(sig, dst, inc=True))
         return sig
 
-    def connect_decoded(self, pre, dst, decoders, synapse=0.005, label=None, pes=None):
+    def connect_decoded(self, pre, dst, decoders, synapse=0.005, label=None, pes=None, out_signal=None):
         """Decoded connection from ensemble ``pre`` into signal ``dst``.
 
         ``pes`` = dict(learning_rate, error (Signal), pre_synapse) adds the PES rule:
@@ -169,7 +171,7 @@ class NetBuilder:
         weighted = m.Signal(np.zeros(dec.shape[0]), name="%s.weighted" % label)
         mdl.add_op(m.Reset(weighted))
         mdl.add_op(m.DotInc(w, pre.sig_out, weighted, tag="%s.decode" % label))
-        out = self.synapse(weighted, synapse, label)
+        out = self.synapse(weighted, synapse, label, out=out_signal)
         if dst is not None:
             mdl.add_op(m.Copy(out, dst, inc=True))
         conn = dict(pre=pre, weights=w, weighted=weighted, out=out, label=label)
@@ -291,4 +293,61 @@ def pes_learning_model(seed=3, n_ensembles=4096, n_neurons=1024, dimensions=16, 
     probes = [nb.model.add_probe(nb.connections[i]["out"], label="c%d.out" % i)
               for i in np.linspace(0, n_ensembles - 1, n_probes).astype(int)]
     nb.model.info = dict(probes=probes, ensembles=nb.ensembles, connections=nb.connections, targets=targets)
+    return nb.model
+
+
+# ---- sharded form of the PES model (one shard per GPU) ---------------------------
+def pes_learning_shard(seed=3, n_ensembles=4096, rank=0, world=1, n_neurons=1024, dimensions=16,
+                       learning_rate=1e-4, synapse=0.01, pre_synapse=0.005, dt=0.001, sim_time=0.5,
+                       n_templates=8, n_probes=4, error_cutoff=5.0):
+    """Shard ``rank`` of ``world`` of the PES learning model with ``n_ensembles``
+    ensembles in total (``n_ensembles`` must be a multiple of ``world``).
+
+    The whole network is described by seeded draws that do not depend on the
+    rank (template parameters, connection targets, error seeds); a shard then
+    instantiates only its contiguous block of ensembles, their outgoing
+    connections and the increments of its own ensembles' inputs.  The filtered
+    output of connection ``g`` lives in slot ``g`` of one ``exchange`` signal
+    (``n_ensembles * dimensions`` floats, identical layout on every rank): a
+    rank writes the slots of its own connections and reads any slot, so the only
+    cross-rank data per step are the other ranks' segments of that signal.
+    With ``world == 1`` this is the complete model."""
+    assert n_ensembles % world == 0
+    n_local = n_ensembles // world
+    lo = rank * n_local
+    nb = NetBuilder(dt=dt, seed=seed, label="pes learning shard %d/%d" % (rank, world))
+    # rank-independent description of the network
+    trng = np.random.RandomState(seed)
+    nb.rng = trng
+    scratch = NetBuilder(dt=dt, seed=seed)  # template ensembles are solved outside the shard's model
+    scratch.rng = trng
+    templates = [scratch.ensemble(n_neurons, dimensions, label="template%d" % k) for k in range(n_templates)]
+    decoders = [scratch.solve_decoders(t, n_eval=2 * n_neurons) for t in templates]
+    grng = np.random.RandomState(seed + 1)
+    targets = grng.randint(n_ensembles - 1, size=n_ensembles)
+    targets = np.where(targets >= np.arange(n_ensembles), targets + 1, targets)
+    err_seeds = np.random.RandomState(seed + 2).randint(2 ** 31 - 1, size=n_ensembles)
+
+    exchange = m.Signal(np.zeros(n_ensembles * dimensions), name="exchange")
+    slot = lambda g: exchange[g * dimensions:(g + 1) * dimensions]
+    ens = {}
+    for g in range(lo, lo + n_local):
+        ens[g] = nb.ensemble(n_neurons, dimensions, label="e%d" % g, params_from=templates[g % n_templates])
+    # inputs of local ensembles: every connection (from any rank) that targets them
+    for g in np.flatnonzero((targets >= lo) & (targets < lo + n_local)):
+        nb.model.add_op(m.Copy(slot(int(g)), ens[int(targets[g])].sig_in, inc=True))
+    for g in range(lo, lo + n_local):
+        err_proc = m.WhiteSignal(sim_time, error_cutoff, rms=0.3, seed=int(err_seeds[g]), dt=dt, size_out=dimensions)
+        err_node = nb.node_process(err_proc, dimensions, label="err%d" % g)
+        err_in = m.Signal(np.zeros(dimensions), name="c%d.pes.in" % g)
+        nb.model.add_op(m.Reset(err_in))
+        nb.model.add_op(m.Copy(err_node, err_in, inc=True))
+        nb.connect_decoded(ens[g], None, decoders[g % n_templates], synapse=synapse, label="c%d" % g,
+                           pes=dict(learning_rate=learning_rate, error=err_in, pre_synapse=pre_synapse),
+                           out_signal=slot(g))
+    probe_ids = [lo + int(i) for i in np.linspace(0, n_local - 1, n_probes).astype(int)]
+    probes = [nb.model.add_probe(slot(g), label="c%d.out" % g) for g in probe_ids]
+    nb.model.info = dict(probes=probes, probe_ids=probe_ids, ensembles=nb.ensembles, connections=nb.connections,
+                         targets=targets, exchange=exchange, segment=(lo * dimensions, n_local * dimensions),
+                         rank=rank, world=world)
     return nb.model

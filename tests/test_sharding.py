@@ -1,0 +1,92 @@
+"""Sharding by ensemble block and the per-step exchange, on the CPU.
+
+The multi-GPU path partitions the ensembles across ranks and exchanges one
+segment of the `exchange` signal per rank and step.  Here the ranks are gloo
+processes running the CPU oracle on their shard and exchanging segments with an
+all-gather: the union of the shards must reproduce the unsharded model exactly
+(the arithmetic of every ensemble is unchanged by sharding)."""
+
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KW = dict(seed=5, n_ensembles=8, n_neurons=48, dimensions=4, n_templates=2, n_probes=2, sim_time=0.05)
+STEPS = 25
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from nengo_ocl_b200 import synth
+    from nengo_ocl_b200.exchange import TorchComm, shard_ranges
+    from oracle.simulator import OracleSimulator
+
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    comm = TorchComm()
+    assert (comm.rank, comm.world) == (rank, world)
+    assert comm.all_gather_object(("r", rank)) == [("r", r) for r in range(world)]
+    mdl = synth.pes_learning_shard(rank=rank, world=world, **KW)
+    lo, n = mdl.info["segment"]
+    assert (lo // KW["dimensions"], (lo + n) // KW["dimensions"]) == shard_ranges(KW["n_ensembles"], world)[rank]
+    ora = OracleSimulator(mdl)
+    ex = mdl.info["exchange"]
+    for _ in range(STEPS):
+        ora.step()
+        mine = torch.from_numpy(np.ascontiguousarray(ora[ex][lo:lo + n]))
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)  # the push/wait pair of the GPU path
+        ora.view(ex)[...] = torch.cat(parts).numpy()
+    np.save(os.path.join(out_dir, "exchange_%d.npy" % rank), ora[ex])
+    np.save(os.path.join(out_dir, "probe_%d.npy" % rank), np.array(ora.probe_data[mdl.probes[0]]))
+    comm.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_model(tmp_path):
+    import torch.multiprocessing as mp
+
+    sys.path.insert(0, ROOT)
+    from nengo_ocl_b200 import synth
+    from oracle.simulator import OracleSimulator
+
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    full = synth.pes_learning_shard(rank=0, world=1, **KW)
+    ora = OracleSimulator(full)
+    ora.run_steps(STEPS)
+    ref = ora[full.info["exchange"]]
+    assert np.abs(ref).max() > 0.01
+    for r in range(world):
+        got = np.load(tmp_path / ("exchange_%d.npy" % r))
+        assert np.array_equal(got, ref)
+    # probe 0 of rank 0 is the slot of connection 0, which the full model probes first too
+    assert np.array_equal(np.load(tmp_path / "probe_0.npy"), np.array(ora.probe_data[full.probes[0]]))
+
+
+def test_shard_structure():
+    sys.path.insert(0, ROOT)
+    from nengo_ocl_b200 import synth
+
+    shards = [synth.pes_learning_shard(rank=r, world=4, **KW) for r in range(4)]
+    full = synth.pes_learning_shard(rank=0, world=1, **KW)
+    assert sum(s.n_neurons for s in shards) == full.n_neurons
+    assert all(np.array_equal(s.info["targets"], full.info["targets"]) for s in shards)
+    segs = [s.info["segment"] for s in shards]
+    assert [lo for lo, _ in segs] == [0, 8, 16, 24] and all(n == 8 for _, n in segs)
+    # every connection is instantiated exactly once across the shards
+    labels = sorted(c["label"] for s in shards for c in s.info["connections"])
+    assert labels == sorted(c["label"] for c in full.info["connections"])
+    with pytest.raises(AssertionError):
+        synth.pes_learning_shard(rank=0, world=3, **KW)
