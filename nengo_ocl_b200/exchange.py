@@ -155,6 +155,10 @@ class Exchange:
         self.comm.barrier()
 
     def close(self):
+        """Collective: no rank unmaps or frees while a peer may still push into it."""
+        if self.world > 1 and self._opened:
+            self.queue.finish()
+            self.comm.barrier()
         for p in self._opened:
             try:
                 _capi.lib().nb2_ipc_close_handle(p)

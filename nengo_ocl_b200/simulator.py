@@ -300,6 +300,10 @@ class Simulator:
         self._n_steps = 0
         self._time = 0.0
         self._reset_probes()
+        if self._exchange is not None:
+            # every rank has planned and uploaded before any rank starts to wait on a peer
+            self.queue.finish()
+            self._exchange.comm.barrier()
 
     @staticmethod
     def _build_with_nengo(network, dt):

@@ -82,3 +82,32 @@ def test_two_gpus_match_unsharded_oracle(tmp_path):
     p0 = np.load(tmp_path / "probe_0.npy")
     assert p0.shape == (STEPS, KW["dimensions"])
     assert np.sqrt(np.mean((p0 - np.array(ora.probe_data[full.probes[0]])) ** 2)) < 1e-3
+
+
+def test_wait_gives_up_and_reports(queue):
+    """A flag that nothing sets: the wait runs out after its limit, records the
+    status, leaves the replica untouched and the context usable."""
+    import ctypes
+
+    from nengo_ocl_b200 import _capi
+    from nengo_ocl_b200.runtime import to_device, zeros
+
+    world, seg = 2, 64
+    ctl = to_device(queue, np.array([1, 0, 0, 0, 0, 0, 0, 0], dtype=np.int32))  # epoch 1: one step was pushed
+    flags = zeros(queue, (world,), np.int32)
+    staging = to_device(queue, np.full(2 * world * seg, 7.0, dtype=np.float32))
+    replica = to_device(queue, np.arange(world * seg, dtype=np.float32))
+    _capi.call("nb2_exchange_wait", queue.stream, ctl.ptr, flags.ptr, staging.ptr, replica.ptr, 0, world, seg,
+               ctypes.c_double(0.05))
+    queue.finish()
+    assert ctl.get()[2] == _capi.NB2_ERR_TIMEOUT
+    assert np.array_equal(replica.get(), np.arange(world * seg, dtype=np.float32))
+    # the same call with the flag published copies the peer's segment
+    ctl.set(np.array([1, 0, 0, 0, 0, 0, 0, 0], dtype=np.int32))
+    flags.set(np.array([0, 1], dtype=np.int32))
+    _capi.call("nb2_exchange_wait", queue.stream, ctl.ptr, flags.ptr, staging.ptr, replica.ptr, 0, world, seg,
+               ctypes.c_double(0.05))
+    queue.finish()
+    got = replica.get()
+    assert ctl.get()[2] == 0
+    assert np.array_equal(got[:seg], np.arange(seg, dtype=np.float32)) and np.all(got[seg:] == 7.0)
