@@ -101,6 +101,13 @@ def declared_symbols():
     return sorted(set(re.findall(r"\b(nb2_[a-z0-9_]+)\s*\(", text)))
 
 
+def header_constants(prefix):
+    """Integer ``#define``s of the C header whose names start with ``prefix``."""
+    with open(HEADER_PATH) as f:
+        text = f.read()
+    return {k: int(v) for k, v in re.findall(r"#define\s+(%s[A-Z0-9_]*)\s+(\d+)\b" % prefix, text)}
+
+
 def lib():
     """Load the shared library (once) and attach argument types."""
     global _lib

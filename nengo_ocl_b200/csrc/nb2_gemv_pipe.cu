@@ -4,54 +4,67 @@
 //
 // Same math as the reference's four OpenCL GEMV variants (nengo_ocl/
 // clra_gemv.py:264-1175).  The kernel is bandwidth-bound (0.5 flop/byte), so
-// the design is about keeping HBM busy:
+// the design is about keeping HBM busy with as few instructions per byte as
+// possible:
 //
 //  * The host cuts every output item into work records of roughly equal bytes
-//    (<= NB2_PIPE_STAGE_FLOATS staged matrix elements, <= 4 (term, column
-//    chunk) segments).  Records of one row range form a chain (several records
-//    when an item has many terms or long rows).
-//  * Persistent CTAs (a multiple of the SM count) each own a contiguous range
-//    of records, balanced by bytes, so neighbouring CTAs stream neighbouring
-//    memory.
-//  * Inside a CTA eight producer warps and eight consumer warps share a ring of
-//    16 shared-memory stages; every consumer warp works on records of its own
-//    and owns two stages, so one can load while the other is consumed.  A
-//    producer reads the next record and launches its copies into shared memory
-//    without waiting for them: the contiguous matrix rows go
-//    through 1-D bulk async copies (cp.async.bulk, completion counted in bytes
-//    on an mbarrier), ragged heads/tails, gathered X segments and the Y_in rows
-//    through 4-byte cp.async copies tracked by the same mbarrier.
-//  * Each consumer thread owns up to four output rows and a strided subset of
-//    the columns, loads each x value once for its four rows, reads the staged
-//    rows with a per-thread column rotation (bank-conflict avoidance), keeps
-//    the running sums in registers across all segments and records of a chain
-//    and finishes with one shuffle reduction and a single-pass epilogue.  There
-//    is no scratch buffer and no second reduction kernel.
+//    (<= NB2_PIPE_STAGE_FLOATS staged floats, <= 4 terms or column chunks,
+//    whole rows whenever a row fits).  Records of one row range form a chain
+//    (several records when an item has many terms or very long rows).
+//  * Persistent CTAs own contiguous ranges of records, balanced by bytes, so
+//    neighbouring CTAs stream neighbouring memory.
+//  * Inside a CTA a ring of shared-memory stages connects producer lanes and
+//    consumer warp groups.  Record i of the CTA uses stage i % STAGES, is
+//    issued by the one producer lane that owns this stage and consumed by
+//    warp group i % GROUPS.  A producer lane waits until its stage is free and
+//    issues nothing but 1-D bulk async copies (cp.async.bulk, completion
+//    counted in bytes on the stage's mbarrier): one copy per matrix segment,
+//    one per gathered X segment, one for the Y_in rows, and the NEXT record of
+//    this stage (so the lane reads its work from shared memory and holds no
+//    record in registers).  Sources that do not start or end on a 16-byte
+//    boundary are copied as the enclosing 16-byte-aligned window and indexed
+//    from the remainder, so there are no per-element copies at all.
+//  * Consumers map one lane to one output row (up to 4 rows per lane, 32 lanes
+//    apart) and walk the row's columns linearly: the x value of a column is one
+//    broadcast shared-memory load for the whole warp, row elements are loaded
+//    with immediate offsets, the running sums stay in registers across all
+//    segments and records of a chain, and the epilogue needs no reduction.
+//    Segments whose width is a multiple of 8 would put the lanes of a warp in
+//    the same few banks; those walk the columns diagonally instead (lane l
+//    starts at column l mod w).  There is no scratch buffer and no second
+//    reduction kernel.
 //
-// Every mbarrier wait is bounded; on timeout the CTA records NB2_ERR_TIMEOUT
-// in the status word, stops issuing, drains its own cp.async copies and exits.
+// Every mbarrier wait is bounded by the global timer; on timeout the CTA
+// records NB2_ERR_TIMEOUT in the status word, stops issuing, waits (bounded)
+// for the copies it has in flight and exits.
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
 
 #define PIPE_STAGES NB2_PIPE_STAGES
-#define PIPE_NW NB2_PIPE_CONSUMER_WARPS  // consumer warps, each works on its own record
-#define PIPE_NP 8                        // producer warps (record i is issued by warp i % NP)
-#define PIPE_CONSUMERS 32                // threads that share one record
+#define PIPE_NC NB2_PIPE_CONSUMER_WARPS   // consumer warps
+#define PIPE_W NB2_PIPE_WARPS_PER_RECORD  // warps that share one record (each takes a row range)
+#define PIPE_GROUPS (PIPE_NC / PIPE_W)    // record i belongs to warp group i % GROUPS
+#ifndef PIPE_NP
+#define PIPE_NP 2  // producer warps
+#endif
+#define PIPE_LB (PIPE_STAGES / PIPE_NP)  // active lanes per producer warp, one stage each
 #define PIPE_ROWS_PER_THREAD 4
-#define PIPE_THREADS (32 * (PIPE_NW + PIPE_NP))
-#define PIPE_A NB2_PIPE_STAGE_FLOATS  // staged matrix floats per stage
-#define PIPE_X NB2_PIPE_XBUF          // staged x floats per stage
+#define PIPE_THREADS (32 * (PIPE_NC + PIPE_NP))
+#define PIPE_A NB2_PIPE_STAGE_FLOATS  // staged floats per stage (matrix rows and x segments share the pool)
 #define PIPE_R NB2_PIPE_RMAX          // max rows per record
 #define PIPE_REC 32                   // ints per record
 #define PIPE_MAXSEG 4
-#define PIPE_SPIN_LIMIT (1 << 22)
+#define PIPE_WAIT_NS 1000000000ull  // limit of one barrier wait
+#define PIPE_SUSPEND_NS 20000u      // a waiting thread is suspended by the hardware for up to this long per poll
 
-// Record i uses stage i % STAGES and is consumed by warp i % NW.  With STAGES a
-// multiple of NW every stage is always consumed by the same warp, so a warp can
-// only wait for phase r of a stage after it has itself consumed phase r-1:
-// parity waits can never be a whole round behind.
-static_assert(PIPE_STAGES % PIPE_NW == 0, "each stage must belong to one consumer warp");
-static_assert(PIPE_STAGES % PIPE_NP == 0, "each stage must belong to one producer warp");
+// Stage s is always filled by the same producer lane and (STAGES a multiple of
+// GROUPS) always drained by the same warp group, so a waiter can only wait for
+// phase r of a barrier after it has itself seen phase r-1: parity waits can
+// never be a whole round behind.
+static_assert(PIPE_NC % PIPE_W == 0 && PIPE_STAGES % PIPE_GROUPS == 0, "each stage must belong to one warp group");
+static_assert(PIPE_STAGES % PIPE_NP == 0 && PIPE_LB <= 32, "each stage must belong to one producer lane");
+static_assert(PIPE_R == 32 * PIPE_ROWS_PER_THREAD * PIPE_W, "rows per record = 4 rows per lane in every warp");
+static_assert(PIPE_THREADS <= 1024, "CTA size");
 
 struct PipeParams {
   const int* records;  // [n_records][32]
@@ -68,30 +81,48 @@ struct PipeParams {
 };
 
 struct __align__(128) PipeStage {
-  float a[PIPE_A];
-  float x[PIPE_X];
-  float yin[PIPE_R];
-  int rec[PIPE_REC];
+  float buf[PIPE_A];
+  float yin[PIPE_R + 8];
+  int rec[2][PIPE_REC];  // record of round m in slot m & 1
 };
 
 __device__ __forceinline__ uint32_t pipe_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(pipe_smem(dst)), "l"(src) : "memory");
+__device__ __forceinline__ unsigned long long pipe_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
 }
 
-// Bounded parity wait. Returns false on timeout.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
-  uint32_t done = 0;
-  for (int spins = 0; spins < PIPE_SPIN_LIMIT; ++spins) {
-    asm volatile(
-        "{\n .reg .pred q;\n mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n selp.u32 %0, 1, 0, q;\n}"
-        : "=r"(done)
-        : "r"(pipe_smem(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
+__device__ __forceinline__ bool mbar_try(unsigned long long* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred q;\n mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2, %3;\n selp.u32 %0, 1, 0, q;\n}"
+      : "=r"(done)
+      : "r"(pipe_smem(bar)), "r"(parity), "r"(PIPE_SUSPEND_NS)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded parity wait.  Returns false on timeout or when another warp of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, const volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (int spins = 0;; ++spins) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spins & 3) == 3) {
+      if (*abort_flag) return false;
+      const unsigned long long t = pipe_timer();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > PIPE_WAIT_NS) return false;
+    }
   }
-  return false;
+}
+
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   pipe_smem(dst)),
+               "l"(src), "r"(bytes), "r"(pipe_smem(bar))
+               : "memory");
 }
 
 __device__ __forceinline__ float pipe_epilogue(const PipeParams& p, int bb, float yin, float sum) {
@@ -104,7 +135,51 @@ __device__ __forceinline__ float pipe_epilogue(const PipeParams& p, int bb, floa
   return (float)((double)pre + p.alpha * (double)sum);
 }
 
-__global__ void __launch_bounds__(PIPE_THREADS, 1) nb2_gemv_pipe_kernel(const PipeParams p) {
+// One segment of one record for one consumer lane: NR rows, all w columns.
+// MODE 0: x staged in shared memory, columns in order (the x load is a broadcast);
+// MODE 1: x staged, diagonal walk (lane l starts at column l mod w) for widths
+//         whose row pitch would put all lanes into a few banks;
+// MODE 2: x read from global memory with a stride.
+template <int NR, int MODE>
+__device__ __forceinline__ void pipe_segment(const float* __restrict__ a, const float* __restrict__ x, int xstride,
+                                             int w, int lane, const int (&roff)[4], float (&acc)[4]) {
+  const float* a0 = a + roff[0] * w;
+  const float* a1 = a + roff[NR > 1 ? 1 : 0] * w;
+  const float* a2 = a + roff[NR > 2 ? 2 : 0] * w;
+  const float* a3 = a + roff[NR > 3 ? 3 : 0] * w;
+  if (MODE == 1) {
+    int cc = lane % w;
+#pragma unroll 4
+    for (int c = 0; c < w; ++c) {
+      const float xv = x[cc];
+      acc[0] = fmaf(a0[cc], xv, acc[0]);
+      if (NR > 1) acc[1] = fmaf(a1[cc], xv, acc[1]);
+      if (NR > 2) acc[2] = fmaf(a2[cc], xv, acc[2]);
+      if (NR > 3) acc[3] = fmaf(a3[cc], xv, acc[3]);
+      ++cc;
+      if (cc == w) cc = 0;
+    }
+  } else {
+#pragma unroll 4
+    for (int c = 0; c < w; ++c) {
+      const float xv = MODE == 0 ? x[c] : __ldg(x + (size_t)c * xstride);
+      acc[0] = fmaf(a0[c], xv, acc[0]);
+      if (NR > 1) acc[1] = fmaf(a1[c], xv, acc[1]);
+      if (NR > 2) acc[2] = fmaf(a2[c], xv, acc[2]);
+      if (NR > 3) acc[3] = fmaf(a3[c], xv, acc[3]);
+    }
+  }
+}
+
+template <int NR>
+__device__ __forceinline__ void pipe_segment_mode(const float* a, const float* xs, const float* xg, int xstride,
+                                                  int w, int lane, const int (&roff)[4], float (&acc)[4]) {
+  if (xs == nullptr) pipe_segment<NR, 2>(a, xg, xstride, w, lane, roff, acc);
+  else if ((w & 7) == 0) pipe_segment<NR, 1>(a, xs, 1, w, lane, roff, acc);
+  else pipe_segment<NR, 0>(a, xs, 1, w, lane, roff, acc);
+}
+
+__global__ void __launch_bounds__(PIPE_THREADS, NB2_PIPE_CTAS_PER_SM) nb2_gemv_pipe_kernel(const PipeParams p) {
   extern __shared__ __align__(128) unsigned char pipe_raw[];
   PipeStage* stages = reinterpret_cast<PipeStage*>(pipe_raw);
   __shared__ __align__(8) unsigned long long full_bar[PIPE_STAGES];
@@ -118,10 +193,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) nb2_gemv_pipe_kernel(const Pi
 
   if (tid == 0) {
     for (int s = 0; s < PIPE_STAGES; ++s) {
-      // full: 32 producer lanes (cp.async completion arrivals) + 1 expect_tx arrival
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&full_bar[s])), "r"(33));
-      // empty: one arrival by the consumer warp that owned the record
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&empty_bar[s])), "r"(1));
+      // full: the producer lane's expect_tx arrival; the copies complete the byte count
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&full_bar[s])), "r"(1));
+      // empty: one arrival per consumer warp of the group that owned the record
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&empty_bar[s])), "r"(PIPE_W));
     }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,154 +204,131 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) nb2_gemv_pipe_kernel(const Pi
   __syncthreads();
 
   const int wid = tid >> 5;
-  if (wid >= PIPE_NW) {
-    // ======================= producer warps =======================
-    const int first = wid - PIPE_NW;
-    int next = first < n ? __ldg(p.records + (size_t)(range.x + first) * PIPE_REC + lane) : 0;
-    for (int i = first; i < n; i += PIPE_NP) {
-      const int s = i % PIPE_STAGES;
-      const int round = i / PIPE_STAGES;
-      const int my = next;  // record i; this warp's next record is fetched while this one is issued
-      if (i + PIPE_NP < n) next = __ldg(p.records + (size_t)(range.x + i + PIPE_NP) * PIPE_REC + lane);
-      if (round > 0) {
-        if (!mbar_wait(&empty_bar[s], (uint32_t)((round - 1) & 1)) || *(volatile int*)&s_abort) {
-          if (lane == 0) { s_abort = 1; if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT); }
-          break;
+  if (wid >= PIPE_NC) {
+    // ======================= producer lanes =======================
+    if (lane >= PIPE_LB) return;
+    const int s = (wid - PIPE_NC) * PIPE_LB + lane;  // this lane's stage
+    if (s >= n) return;
+    PipeStage& st = stages[s];
+    unsigned long long* full = &full_bar[s];
+    const int4* rp = reinterpret_cast<const int4*>(p.records + (size_t)range.x * PIPE_REC);
+    {  // the first record of this stage comes straight from global memory
+      int4* dst = reinterpret_cast<int4*>(st.rec[0]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] = __ldg(rp + (size_t)s * 8 + j);
+    }
+    int issued = -1;  // last round this lane issued
+    bool ok = true;
+    for (int m = 0, i = s; i < n; ++m, i += PIPE_STAGES) {
+      if (m > 0 && !mbar_wait(&empty_bar[s], (uint32_t)((m - 1) & 1), &s_abort)) {
+        ok = false;
+        break;
+      }
+      // (for m > 0 the record landed with the copies of round m - 1, which the consumers have drained)
+      const int* r = st.rec[m & 1];
+      const int nseg = r[5];
+      const int yin_bytes = r[7];
+      const bool more = i + PIPE_STAGES < n;
+      uint32_t tx = (uint32_t)yin_bytes + (more ? PIPE_REC * 4u : 0u);
+      int4 sg[PIPE_MAXSEG];  // window index and bytes of A and X
+      int offs[PIPE_MAXSEG];
+#pragma unroll
+      for (int q = 0; q < PIPE_MAXSEG; ++q) {
+        if (q < nseg) {
+          const int2 lo = *reinterpret_cast<const int2*>(r + 8 + 6 * q);
+          const int2 hi = *reinterpret_cast<const int2*>(r + 8 + 6 * q + 2);
+          sg[q] = make_int4(lo.x, lo.y, hi.x, hi.y);
+          offs[q] = r[8 + 6 * q + 5];
+          tx += (uint32_t)lo.y + (uint32_t)max(hi.y, 0);
         }
       }
-      PipeStage& st = stages[s];
-      st.rec[lane] = my;
-      const int flags = __shfl_sync(0xffffffffu, my, 0);
-      const int R = __shfl_sync(0xffffffffu, my, 1);
-      const int y_in = __shfl_sync(0xffffffffu, my, 2);
-      const int nseg = __shfl_sync(0xffffffffu, my, 5);
-      uint32_t bulk_bytes = 0;
-      for (int q = 0; q < nseg; ++q) {
-        const int gidx = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 0);
-        const int w = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 1);
-        const int s0 = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 2);
-        const int xstart = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 3);
-        const int xstride = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 4);
-        const int aoff_xoff = __shfl_sync(0xffffffffu, my, 8 + 6 * q + 5);
-        const int aoff = aoff_xoff & 0xffff;
-        const int xoff = aoff_xoff >> 16;
-        for (int c = lane; c < w; c += 32) cp_async4(&st.x[xoff + c], p.X + xstart + (size_t)c * xstride);
-        const int len = R * w;
-        const float* src = p.A + gidx;
-        float* dst = st.a + aoff;
-        if (s0 == w || R == 1) {
-          const int head = min(len, (4 - (gidx & 3)) & 3);
-          const int body = (len - head) & ~3;
-          const int tail0 = head + body;
-          if (lane < head) cp_async4(dst + lane, src + lane);
-          if (lane >= 8 && lane - 8 < len - tail0) cp_async4(dst + tail0 + lane - 8, src + tail0 + lane - 8);
-          if (body > 0 && lane == 0) {
-            asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                    "r"(pipe_smem(dst + head)), "l"(src + head), "r"((uint32_t)body * 4u),
-                "r"(pipe_smem(&full_bar[s]))
-                : "memory");
-          }
-          bulk_bytes += (uint32_t)body * 4u;
-        } else {
-          for (int e = lane; e < len; e += 32) {
-            const int r = e / w;
-            const int c = e - r * w;
-            cp_async4(dst + e, src + (size_t)r * s0 + c);
-          }
-        }
-      }
-      if (flags & 2)
-        for (int r = lane; r < R; r += 32) cp_async4(&st.yin[r], p.Yin + y_in + r);
-      // this lane's cp.async copies arrive on the barrier when they land
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(pipe_smem(&full_bar[s]))
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx)
                    : "memory");
-      __syncwarp();  // record words of all lanes are written before the release below
-      if (lane == 0) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(&full_bar[s])),
-                     "r"(bulk_bytes)
-                     : "memory");
+#pragma unroll
+      for (int q = 0; q < PIPE_MAXSEG; ++q) {
+        if (q < nseg) {
+          bulk_copy(st.buf + ((offs[q] & 0xffff) & ~3), p.A + sg[q].x, (uint32_t)sg[q].y, full);
+          if (sg[q].w > 0) bulk_copy(st.buf + ((offs[q] >> 16) & ~3), p.X + sg[q].z, (uint32_t)sg[q].w, full);
+        }
+      }
+      if (yin_bytes > 0) bulk_copy(st.yin, p.Yin + (r[2] & ~3), (uint32_t)yin_bytes, full);
+      if (more) bulk_copy(st.rec[(m + 1) & 1], rp + (size_t)(i + PIPE_STAGES) * 8, PIPE_REC * 4u, full);
+      issued = m;
+    }
+    if (!ok && !*(volatile int*)&s_abort) {
+      s_abort = 1;
+      if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
+    }
+    // copies of the last issued round may still be in flight if the consumers gave up: a
+    // lane does not leave before its own copies have landed (bounded)
+    if (issued >= 0) {
+      const unsigned long long t0 = pipe_timer();
+      while (!mbar_try(full, (uint32_t)(issued & 1)) && pipe_timer() - t0 < PIPE_WAIT_NS) {
       }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
     return;
   }
 
   // ========================= consumer warps =========================
-  // Thread mapping per record (rows R <= 512, fixed along a chain so the sums
-  // stay in registers): record i of the CTA's list belongs to consumer warp
-  // i % NW (the host interleaves the chains accordingly); each lane owns up to
-  // 4 rows row0 + j*P and the columns g, g+G, g+2G, ... of every segment, with
-  // G * P = 32 lanes.  The
-  // x value of a column is loaded once and used for the thread's 4 rows.  The
-  // column order is rotated per thread so that lanes working on different rows
-  // of a warp hit different shared-memory banks.
+  // Record i of the CTA's list belongs to warp group i % GROUPS (the host
+  // interleaves the chains accordingly); warp v of the group takes the rows
+  // [v * RW, (v + 1) * RW) of the record, RW = ceil(R / W), lane l the rows
+  // l, l + 32, l + 64, l + 96 of that range.  R is fixed along a chain, so the
+  // sums stay in registers.
+  const int group = wid % PIPE_GROUPS;
+  const int v = wid / PIPE_GROUPS;
   float acc[PIPE_ROWS_PER_THREAD] = {0.0f, 0.0f, 0.0f, 0.0f};
-  for (int i = wid; i < n; i += PIPE_NW) {
+  for (int i = group; i < n; i += PIPE_GROUPS) {
     const int s = i % PIPE_STAGES;
-    const uint32_t parity = (uint32_t)((i / PIPE_STAGES) & 1);
-    if (!mbar_wait(&full_bar[s], parity)) {
-      if (lane == 0) { s_abort = 1; if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT); }
+    const int m = i / PIPE_STAGES;
+    if (!mbar_wait(&full_bar[s], (uint32_t)(m & 1), &s_abort)) {
+      if (lane == 0 && !*(volatile int*)&s_abort) {
+        s_abort = 1;
+        if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
+      }
       break;
     }
     const PipeStage& st = stages[s];
-    const int flags = st.rec[0];
-    const int R = st.rec[1];
-    const int nseg = st.rec[5];
-    // G = lanes per row: largest power of two with ceil(R/4) * G <= 128 (at most 32)
-    const int quarter = (R + PIPE_ROWS_PER_THREAD - 1) / PIPE_ROWS_PER_THREAD;
-    int logG = 0;
-    while (logG < 5 && (quarter << (logG + 1)) <= PIPE_CONSUMERS) ++logG;
-    const int G = 1 << logG;
-    const int P = PIPE_CONSUMERS >> logG;  // rows per pass
-    const int g = lane & (G - 1);
-    const int row0 = lane >> logG;
+    const int* rec = st.rec[m & 1];
+    const int4 h0 = *reinterpret_cast<const int4*>(rec);      // flags, rows, y_in, y
+    const int4 h1 = *reinterpret_cast<const int4*>(rec + 4);  // item, segments, -, yin bytes
+    const int flags = h0.x, R = h0.y, nseg = h1.y;
+    const int RW = PIPE_W == 1 ? R : (R + PIPE_W - 1) / PIPE_W;
+    const int rbase = v * RW;
+    const int rows = min(RW, R - rbase);  // rows of this warp (may be <= 0)
     if (flags & 1) {
 #pragma unroll
       for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) acc[j] = 0.0f;
     }
-    if (row0 < R) {
-      // rows beyond R re-read the last valid row; their sums are discarded
+#ifndef PIPE_EXP_NOMATH
+    if (rows > 0) {
+      // lanes beyond the last row re-read it; their sums are discarded
       int roff[PIPE_ROWS_PER_THREAD];
 #pragma unroll
-      for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) roff[j] = min(row0 + j * P, R - 1);
+      for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) roff[j] = rbase + min(lane + 32 * j, rows - 1);
+      const int NR = (rows + 31) >> 5;
       for (int q = 0; q < nseg; ++q) {
-        const int w = st.rec[8 + 6 * q + 1];
-        const int aoff_xoff = st.rec[8 + 6 * q + 5];
-        const float* a = st.a + (aoff_xoff & 0xffff) + g;
-        const float* x = st.x + (aoff_xoff >> 16) + g;
-        const int K = (w - g + G - 1) >> logG;  // columns of this lane
-        if (K <= 0) continue;
-        const int shift = row0 & ((1 << (31 - __clz(K))) - 1);
-        const float* a0 = a + roff[0] * w;
-        const float* a1 = a + roff[1] * w;
-        const float* a2 = a + roff[2] * w;
-        const float* a3 = a + roff[3] * w;
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          const int kbeg = half ? 0 : shift;
-          const int kend = half ? shift : K;
-#pragma unroll 4
-          for (int k = kbeg; k < kend; ++k) {
-            const int col = k << logG;
-            const float xv = x[col];
-            acc[0] = fmaf(a0[col], xv, acc[0]);
-            acc[1] = fmaf(a1[col], xv, acc[1]);
-            acc[2] = fmaf(a2[col], xv, acc[2]);
-            acc[3] = fmaf(a3[col], xv, acc[3]);
-          }
-        }
+        const int2 xf = *reinterpret_cast<const int2*>(rec + 8 + 6 * q + 2);  // x index, x bytes / -stride
+        const int2 wf = *reinterpret_cast<const int2*>(rec + 8 + 6 * q + 4);  // columns, offsets
+        const float* a = st.buf + (wf.y & 0xffff);
+        const float* xs = xf.y > 0 ? st.buf + (wf.y >> 16) : nullptr;
+        const float* xg = p.X + xf.x;
+        if (NR == 1) pipe_segment_mode<1>(a, xs, xg, -xf.y, wf.x, lane, roff, acc);
+        else if (NR == 2) pipe_segment_mode<2>(a, xs, xg, -xf.y, wf.x, lane, roff, acc);
+        else pipe_segment_mode<4>(a, xs, xg, -xf.y, wf.x, lane, roff, acc);
       }
     }
-    if (flags & 2) {
-      const int y = st.rec[3];
-      const int bb = st.rec[4];
+#endif
+    if ((flags & 2) && rows > 0) {
+      const int y_in = h0.z + rbase, y = h0.w + rbase, bb = h1.x;
+      const bool staged = h1.w > 0;
 #pragma unroll
       for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) {
-        float t = acc[j];
-        for (int off = G >> 1; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-        const int r = row0 + j * P;
-        if (g == 0 && r < R) p.Y[y + r] = pipe_epilogue(p, bb, st.yin[r], t);
+        const int r = lane + 32 * j;
+        if (r < rows) {
+          const float yin = staged ? st.yin[(h0.z & 3) + rbase + r] : p.Yin[y_in + r];
+          p.Y[y + r] = pipe_epilogue(p, bb, yin, acc[j]);
+        }
       }
     }
     __syncwarp();
@@ -294,6 +346,8 @@ extern "C" int nb2_gemv_pipelined(void* stream, const int* records, int n_record
                                   const float* betas, const float* gammas, int* status) {
   if (n_records == 0 || n_ctas == 0) return NB2_OK;
   NB2_REQUIRE(records && ranges && A && X && Yin && Y, "null pointer");
+  NB2_REQUIRE((((uintptr_t)records | (uintptr_t)A | (uintptr_t)X | (uintptr_t)Yin) & 15) == 0,
+              "records, A, X and Y_in must be 16-byte aligned");
   static bool optin[64] = {};
   int dev = 0;
   NB2_CUDA(cudaGetDevice(&dev));

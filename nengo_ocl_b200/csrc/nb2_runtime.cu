@@ -52,7 +52,9 @@ int nb2_device_info(int ordinal, int* sm_count, int* max_threads_per_block,
 int nb2_malloc(void** dptr, size_t bytes) {
   NB2_REQUIRE(dptr != NULL, "dptr");
   *dptr = NULL;
-  if (bytes == 0) bytes = 16;  // keep a valid, distinct pointer for empty arrays
+  // whole 256-byte granules: a valid, distinct pointer for empty arrays, and kernels that
+  // stage 16-byte-aligned windows may read up to the next 16-byte boundary past the end
+  bytes = bytes ? (bytes + 255) & ~(size_t)255 : 256;
   NB2_CUDA(cudaMalloc(dptr, bytes));
   return NB2_OK;
 }

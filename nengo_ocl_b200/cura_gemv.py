@@ -197,35 +197,93 @@ def build_rows_worklist(gstructure, D):
     return units, warp_units
 
 
-PIPE_STAGE_FLOATS, PIPE_XBUF, PIPE_RMAX, PIPE_MAXSEG, PIPE_REC = 1408, 192, 128, 4, 32
+# geometry of the pipelined kernel: the same numbers the library was compiled with (include/nengo_b200.h)
+_PIPE = _capi.header_constants("NB2_PIPE_")
+PIPE_STAGE_FLOATS = _PIPE["NB2_PIPE_STAGE_FLOATS"]
+PIPE_STAGES = _PIPE["NB2_PIPE_STAGES"]
+PIPE_CONSUMER_WARPS = _PIPE["NB2_PIPE_CONSUMER_WARPS"]
+PIPE_WARPS_PER_RECORD = _PIPE["NB2_PIPE_WARPS_PER_RECORD"]
+PIPE_CTAS_PER_SM = _PIPE["NB2_PIPE_CTAS_PER_SM"]
+PIPE_RMAX = 128 * PIPE_WARPS_PER_RECORD
+PIPE_MAXSEG, PIPE_REC = 4, 32
 GEMV_PIPE = 3  # persistent producer/consumer kernel (csrc/nb2_gemv_pipe.cu)
-PIPE_CTAS_PER_SM = 2
-PIPE_CONSUMER_WARPS = 8
+PIPE_MIN_CHUNK = 128  # narrowest column chunk worth a record of its own (single-row records)
+
+
+def _pipe_window(n):
+    """Pool floats reserved for a staged copy of ``n`` floats: the copy is the
+    enclosing 16-byte-aligned window of its source (<= 3 floats before, <= 3
+    after), and windows start on 16-byte boundaries of the pool."""
+    return (n + 6 + 3) & ~3
+
+
+def _pipe_cost(R, w, staged_x):
+    return _pipe_window(R * w) + (_pipe_window(w) if staged_x else 0)
 
 
 def _pipe_template(R, terms):
-    """Pack the (term, column chunk) segments of one row range into records.
+    """Pack the terms of one row range of ``R`` rows into records.
 
-    ``terms`` = [(N, s0, contiguous)]; returns a list of records, each a list of
-    (term index, c0, w, aoff_base, xoff).  ``aoff_base`` is 4-aligned; 3 floats of
-    slack follow it so the staged copy can keep the 16-byte phase of its source.
-    """
-    records, cur, used_a, used_x = [], [], 0, 0
-    for ti, (N, s0) in enumerate(terms):
+    ``terms`` = [(N, staged_x)]; returns a list of records, each a list of
+    (term index, c0, w, a_base, x_base) with 4-aligned pool offsets, or None
+    if a whole row of some term does not fit an empty stage (whole rows are
+    required when R > 1 so that every staged copy is one contiguous range;
+    single-row records may cut a row into column chunks)."""
+    C = PIPE_STAGE_FLOATS
+    records, cur, used = [], [], 0
+    for ti, (N, xs) in enumerate(terms):
         c0 = 0
+        w_chunk = None
         while c0 < N:
-            base = (used_a + 3) & ~3
-            w = min(N - c0, (PIPE_STAGE_FLOATS - base - 3) // R, PIPE_XBUF - used_x)
-            if w <= 0 or len(cur) == PIPE_MAXSEG:
+            rem = N - c0
+            if len(cur) < PIPE_MAXSEG and used + _pipe_cost(R, rem, xs) <= C:
+                w = rem
+            elif R == 1 and len(cur) < PIPE_MAXSEG and used + _pipe_cost(1, min(rem, PIPE_MIN_CHUNK), xs) <= C:
+                wmax = ((C - used - 20) // (2 if xs else 1)) & ~3
+                if w_chunk is None:  # equal chunks rather than one full stage and a sliver
+                    n_chunks = -(-rem // max(wmax, 1))
+                    w_chunk = (-(-rem // n_chunks) + 3) & ~3
+                w = min(rem, wmax, w_chunk)
+            elif cur:
                 records.append(cur)
-                cur, used_a, used_x = [], 0, 0
+                cur, used = [], 0
                 continue
-            cur.append((ti, c0, w, base, used_x))
-            used_a = base + 3 + R * w
-            used_x += w
+            else:
+                return None
+            a_base = used
+            x_base = used + _pipe_window(R * w)
+            cur.append((ti, c0, w, a_base, x_base))
+            used += _pipe_cost(R, w, xs)
             c0 += w
     records.append(cur)
     return records
+
+
+def _pipe_rows(m, Ns, staged):
+    """Rows per record for an item of ``m`` rows whose rows are contiguous."""
+    C = PIPE_STAGE_FLOATS
+
+    def largest(group):
+        n = sum(Ns[t] for t in group)
+        x = sum(_pipe_window(Ns[t]) for t in group if staged[t])
+        R = (C - x - 9 * len(group)) // max(n, 1)
+        while R > 0 and sum(_pipe_cost(R, Ns[t], staged[t]) for t in group) > C:
+            R -= 1
+        return R
+
+    nd = len(Ns)
+    groups = [range(t, min(t + PIPE_MAXSEG, nd)) for t in range(0, nd, PIPE_MAXSEG)]
+    R = min(largest(g) for g in groups)
+    if R < 1:  # not even one row of a full group: one term per segment, as many rows as fit
+        R = min(largest([t]) for t in range(nd))
+    R = max(0, min(R, PIPE_RMAX, m))
+    lanes = 32 * PIPE_WARPS_PER_RECORD  # one lane per row: whole multiples keep every lane busy
+    if R >= lanes:
+        R = R // lanes * lanes
+        n_units = -(-m // R)
+        even = -(-(-(-m // n_units)) // lanes) * lanes  # even out the row ranges, still whole multiples
+        R = min(R, even)
+    return R
 
 
 def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
@@ -233,17 +291,22 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
 
     Record layout (32 int32): [0] flags (1 = first of its chain, 2 = last),
     [1] rows, [2] Y_in element index of the first row, [3] Y element index,
-    [4] item id, [5] segment count, then per segment 6 ints at 8 + 6q:
-    A element index of (first row, first column), columns, A row stride,
-    X element index, X stride, (x offset << 16 | a offset) in the stage buffers.
-    Returns ``(records, ranges, warp_units)``; tiny items go to the warp kernel.
+    [4] item id, [5] segment count, [6] 0, [7] bytes of the staged Y_in window
+    (0 = none), then per segment 6 ints at 8 + 6q:
+    A element index of the staged window (multiple of 4), its bytes, X element
+    index of the staged window (or of the first column when X is read from
+    global memory), its bytes (or minus the X stride), columns,
+    (x offset << 16 | a offset) of the first payload element in the stage pool.
+    Returns ``(records, ranges, warp_units, fallback_rows)``; tiny items go to
+    the warp kernel, items whose rows are not contiguous and too narrow for
+    single-row records to the CTA kernel.
     """
     n_items = gstructure.shape[0]
     n_dots = gstructure[:, 4 * D + 2].astype(np.int64) if n_items else np.zeros(0, np.int64)
     M = gstructure[:, 4 * D + 3].astype(np.int64) if n_items else np.zeros(0, np.int64)
     recs = []
     chain_start = []  # record index where each chain starts
-    warp_rows = []
+    warp_rows, fallback_rows = [], []
     for row in range(n_items):
         m, nd = int(M[row]), int(n_dots[row])
         if m == 0:
@@ -258,33 +321,57 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
         astarts = [int(v) for v in g[1 * D:1 * D + nd]]
         xstarts = [int(v) for v in g[0:nd]]
         xstr = [int(v) for v in xstrides[row, :nd]] if nd else []
-        R = (PIPE_STAGE_FLOATS - 8 * max(nd, 1)) // max(row_floats, 1)
-        R = max(R, min(m, 8))
-        R = max(1, min(R, PIPE_RMAX, m))
+        if any(s < 0 for s in xstr):
+            fallback_rows.append(row)
+            continue
+        staged = [s == 1 for s in xstr]
+        contiguous = all(s0 == N for s0, N in zip(s0s, Ns))
+        if contiguous or nd == 0:
+            R = _pipe_rows(m, Ns, staged) if nd else min(m, PIPE_RMAX)
+            R = max(R, 1)
+        elif min(Ns) >= PIPE_MIN_CHUNK:
+            R = 1
+        else:
+            fallback_rows.append(row)
+            continue
+        template = _pipe_template(R, list(zip(Ns, staged)))
+        if template is None:
+            R = 1
+            template = _pipe_template(R, list(zip(Ns, staged)))
         n_units = -(-m // R)
-        R = -(-m // n_units)
-        template = _pipe_template(R, list(zip(Ns, s0s)))
         y_in0, y0, bb = int(g[4 * D + 0]), int(g[4 * D + 1]), int(g[4 * D + 4])
         n_rec = len(template)
         block = np.zeros((n_units, n_rec, PIPE_REC), dtype=np.int64)
         r0 = np.arange(n_units, dtype=np.int64) * R
         rows_u = np.minimum(R, m - r0)
         for k, segs in enumerate(template):
-            block[:, k, 0] = (1 if k == 0 else 0) | (2 if k == n_rec - 1 else 0)
+            last = k == n_rec - 1
+            block[:, k, 0] = (1 if k == 0 else 0) | (2 if last else 0)
             block[:, k, 1] = rows_u
             block[:, k, 2] = y_in0 + r0
             block[:, k, 3] = y0 + r0
             block[:, k, 4] = bb
             block[:, k, 5] = len(segs)
-            for q, (ti, c0, w, base, xoff) in enumerate(segs):
+            if last:
+                yi = y_in0 + r0
+                block[:, k, 7] = 4 * ((((yi & 3) + rows_u + 3) & ~3))
+            for q, (ti, c0, w, a_base, x_base) in enumerate(segs):
                 gidx = astarts[ti] + r0 * s0s[ti] + c0
+                n_a = (rows_u - 1) * w + w if s0s[ti] == Ns[ti] and w == Ns[ti] else w  # R == 1 otherwise
                 o = 8 + 6 * q
-                block[:, k, o + 0] = gidx
-                block[:, k, o + 1] = w
-                block[:, k, o + 2] = s0s[ti]
-                block[:, k, o + 3] = xstarts[ti] + c0 * xstr[ti]
-                block[:, k, o + 4] = xstr[ti]
-                block[:, k, o + 5] = (xoff << 16) | (base + (gidx & 3))
+                block[:, k, o + 0] = gidx & ~3
+                block[:, k, o + 1] = 4 * (((gidx & 3) + n_a + 3) & ~3)
+                xs = xstarts[ti] + c0 * xstr[ti]
+                if staged[ti]:
+                    block[:, k, o + 2] = xs & ~3
+                    block[:, k, o + 3] = 4 * (((xs & 3) + w + 3) & ~3)
+                    xoff = x_base + (xs & 3)
+                else:
+                    block[:, k, o + 2] = xs
+                    block[:, k, o + 3] = -xstr[ti]
+                    xoff = 0
+                block[:, k, o + 4] = w
+                block[:, k, o + 5] = (xoff << 16) | (a_base + (gidx & 3))
         base_index = sum(b.shape[0] for b in recs)
         flat = block.reshape(n_units * n_rec, PIPE_REC)
         chain_start.extend((base_index + np.arange(n_units) * n_rec).tolist())
@@ -293,16 +380,17 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
     if warp_rows:
         warp_units[:, 0] = warp_rows
         warp_units[:, 2] = M[warp_rows]
+    fallback_rows = np.asarray(fallback_rows, dtype=np.int64)
     if not recs:
-        return np.zeros((0, PIPE_REC), np.int32), np.zeros((0, 2), np.int32), warp_units
+        return np.zeros((0, PIPE_REC), np.int32), np.zeros((0, 2), np.int32), warp_units, fallback_rows
     records = np.concatenate(recs, axis=0)
-    assert records.max() < 2 ** 31
+    assert records.max() < 2 ** 31 and records.min() >= -2 ** 31
     records = records.astype(np.int32)
-    # cost of a record = staged floats + a fixed overhead; chains are never split
+    # cost of a record = staged bytes / 4 + a fixed overhead; chains are never split
     nseg = records[:, 5].astype(np.int64)
     cost = np.full(len(records), 256, dtype=np.int64)
     for q in range(PIPE_MAXSEG):
-        cost += np.where(q < nseg, records[:, 1].astype(np.int64) * records[:, 8 + 6 * q + 1], 0)
+        cost += np.where(q < nseg, records[:, 8 + 6 * q + 1].astype(np.int64) // 4, 0)
     chain_start = np.asarray(chain_start, dtype=np.int64)
     chain_len = np.diff(np.concatenate([chain_start, [len(records)]]))
     csum = np.concatenate([[0], np.cumsum(cost)])
@@ -312,9 +400,9 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
     cut = np.unique(np.concatenate([[0], np.searchsorted(chain_cost_end, targets, side="left") + 1,
                                     [len(chain_start)]]))
     cut = cut[cut <= len(chain_start)]
-    # Within a CTA, record i is consumed by warp i % NW: deal the CTA's chains to the
-    # warps round-robin and interleave the per-warp sequences (padding with empty records).
-    NW = PIPE_CONSUMER_WARPS
+    # Within a CTA, record i is consumed by warp group i % NW: deal the CTA's chains to the
+    # groups round-robin and interleave the per-group sequences (padding with empty records).
+    NW = PIPE_CONSUMER_WARPS // PIPE_WARPS_PER_RECORD
     out_blocks, ranges, pos = [], [], 0
     for c0, c1 in zip(cut[:-1], cut[1:]):
         lens = chain_len[c0:c1]
@@ -334,7 +422,7 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
         ranges.append((pos, pos + len(block)))
         pos += len(block)
     records = np.concatenate(out_blocks, axis=0)
-    return records, np.asarray(ranges, dtype=np.int32), warp_units
+    return records, np.asarray(ranges, dtype=np.int32), warp_units, fallback_rows
 
 
 class gemv_prog:
@@ -472,8 +560,13 @@ class gemv_prog:
         cta_kind = self.cta_kind
         if cta_kind == GEMV_PIPE:
             n_ctas_max = PIPE_CTAS_PER_SM * getattr(queue.device, "sm_count", 148)
-            records, ranges, warp_units = build_pipe_records(table, xstrides, D, n_ctas_max)
+            records, ranges, warp_units, fallback = build_pipe_records(table, xstrides, D, n_ctas_max)
             cta_units = np.zeros((0, 4), dtype=np.int32)
+            if len(fallback):  # layouts the bulk copies cannot stage: the plain CTA kernel takes them
+                cta_kind = _capi.GEMV_CTA
+                cta_all, warp_all = build_worklist(table, D)
+                cta_units = cta_all[np.isin(cta_all[:, 0], fallback)]
+                warp_units = np.concatenate([warp_units, warp_all[np.isin(warp_all[:, 0], fallback)]], axis=0)
         elif cta_kind == GEMV_ROWS:
             cta_units, warp_units = build_rows_worklist(table, D)
             records = ranges = np.zeros((0, 2), dtype=np.int32)

@@ -169,37 +169,66 @@ def test_copy_elementwise_reset_slicedcopy_tables_match_reference(golden_tables)
 
 
 def _emulate_pipe_records(records, ranges, A, X, Yin, alpha, beta, gamma):
-    """Host emulation of what nb2_gemv_pipelined does with its work records."""
+    """Host emulation of what nb2_gemv_pipelined does with its work records: the
+    producer's bulk copies of 16-byte-aligned windows into the stage pool, then
+    the consumer's reads from the pool."""
     Y = Yin.copy()
     assert ranges[0, 0] == 0 and ranges[-1, 1] == len(records)
     assert np.array_equal(ranges[1:, 0], ranges[:-1, 1])
-    NW = cura_gemv.PIPE_CONSUMER_WARPS
+    NW = cura_gemv.PIPE_CONSUMER_WARPS // cura_gemv.PIPE_WARPS_PER_RECORD  # warp groups
+    C = cura_gemv.PIPE_STAGE_FLOATS
+
+    def readable(buf, lo, nbytes):  # buffers are readable up to the next 16-byte boundary
+        assert lo % 4 == 0 and nbytes % 16 == 0 and nbytes > 0
+        n = nbytes // 4
+        assert lo + n <= (len(buf) + 3) // 4 * 4
+        out = np.full(n, np.nan)
+        m = min(n, len(buf) - lo)
+        out[:m] = buf[lo:lo + m]
+        return out
+
     for b, e in ranges:
-        for warp in range(NW):  # record i of a CTA range belongs to consumer warp i % NW
+        for warp in range(NW):  # record i of a CTA range belongs to warp group i % NW
             acc = None
             for rec in records[b + warp:e:NW]:
-                flags, R, y_in, y, bb, nseg = rec[:6]
+                flags, R, y_in, y, bb, nseg, logG, yin_bytes = rec[:8]
                 if R == 0:
-                    assert flags == 0 and nseg == 0  # padding record
+                    assert flags == 0 and nseg == 0 and yin_bytes == 0  # padding record
                     continue
                 assert 1 <= R <= cura_gemv.PIPE_RMAX and 0 <= nseg <= cura_gemv.PIPE_MAXSEG
+                assert logG == 0
                 if flags & 1:
                     acc = np.zeros(R, dtype=np.float64)
                 assert acc is not None and len(acc) == R, "a chain stays within one warp"
-                used = []
+                pool = np.full(C, np.nan)
+                filled = np.zeros(C, dtype=bool)
+                segs = []
                 for q in range(nseg):
-                    gidx, w, s0, xstart, xstride, packed = rec[8 + 6 * q: 14 + 6 * q]
+                    a_win, a_bytes, x_idx, x_bytes, w, packed = (int(v) for v in rec[8 + 6 * q: 14 + 6 * q])
                     aoff, xoff = packed & 0xFFFF, packed >> 16
-                    assert aoff % 4 == gidx % 4  # staged copy keeps the 16-byte phase of its source
-                    assert aoff + R * w <= cura_gemv.PIPE_STAGE_FLOATS and xoff + w <= cura_gemv.PIPE_XBUF
-                    used.append((aoff, aoff + R * w))
-                    rows = gidx + np.arange(R)[:, None] * s0 + np.arange(w)[None, :]
-                    acc += A[rows].astype(np.float64) @ X[xstart + np.arange(w) * xstride].astype(np.float64)
-                used.sort()
-                assert all(a1 <= b0 for (_, a1), (b0, _) in zip(used, used[1:]))  # segments do not overlap
+                    dst = aoff & ~3
+                    assert dst + a_bytes // 4 <= C and not filled[dst:dst + a_bytes // 4].any()
+                    pool[dst:dst + a_bytes // 4] = readable(A, a_win, a_bytes)
+                    filled[dst:dst + a_bytes // 4] = True
+                    if x_bytes > 0:
+                        dst = xoff & ~3
+                        assert dst + x_bytes // 4 <= C and not filled[dst:dst + x_bytes // 4].any()
+                        pool[dst:dst + x_bytes // 4] = readable(X, x_idx, x_bytes)
+                        filled[dst:dst + x_bytes // 4] = True
+                    segs.append((aoff, xoff, w, x_idx, x_bytes))
+                for aoff, xoff, w, x_idx, x_bytes in segs:
+                    a = pool[aoff:aoff + R * w].reshape(R, w)
+                    x = pool[xoff:xoff + w] if x_bytes > 0 else X[x_idx + np.arange(w) * (-x_bytes)]
+                    assert not np.isnan(a).any() and not np.isnan(x).any()
+                    acc += a @ x.astype(np.float64)
                 if flags & 2:
-                    Y[y:y + R] = gamma + beta * Yin[y_in:y_in + R] + alpha * acc
+                    assert yin_bytes > 0
+                    yin = readable(Yin, y_in & ~3, yin_bytes)[(y_in & 3):(y_in & 3) + R]
+                    assert yin_bytes // 4 <= cura_gemv.PIPE_RMAX + 8 and np.array_equal(yin, Yin[y_in:y_in + R])
+                    Y[y:y + R] = gamma + beta * yin + alpha * acc
                     acc = None
+                else:
+                    assert yin_bytes == 0
     return Y
 
 
@@ -218,7 +247,8 @@ def test_pipe_records_cover_the_product(case):
         X_js = A_js
     prog = cura_gemv.gemv_geometry(HostQueue(), 0.5, A, A_js, X, X_js, 0.1, Y)
     table, xstrides, D, _, _ = prog.gstructure_table(range(len(Y)))
-    records, ranges, warp = cura_gemv.build_pipe_records(table, xstrides, D, n_ctas_max=444)
+    records, ranges, warp, fallback = cura_gemv.build_pipe_records(table, xstrides, D, n_ctas_max=444)
+    assert len(fallback) == 0
     assert records.dtype == np.int32 and records.shape[1] == 32
     got = _emulate_pipe_records(records, ranges, A.buf, X.buf, Y.buf, 0.5, 0.1, 0.0)
     from oracle import kernels as K
