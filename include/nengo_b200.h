@@ -91,26 +91,22 @@ int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, int gstride, 
                     double gamma, const float* alphas, const float* betas, const float* gammas,
                     int* status);
 
-/* The main GEMV path: persistent CTAs, producer lanes + consumer warps over a
- * ring of shared-memory stages fed by 1-D bulk async copies
- * (cp.async.bulk) only.  Same math and reference counterparts as
- * nb2_gemv_ragged.  `records`: n_records x 32 int32 work records (layout
- * documented in nengo_ocl_b200/cura_gemv.py:build_pipe_records); `ranges`:
- * n_ctas x 2 int32 [begin, end) record ranges, one per CTA; record i of a range
- * uses stage i % NB2_PIPE_STAGES and is consumed by warp group
- * i % (NB2_PIPE_CONSUMER_WARPS / NB2_PIPE_WARPS_PER_RECORD) (chains are
- * interleaved accordingly).
+/* The main GEMV path: persistent CTAs whose warps each own one shared-memory
+ * stage fed by 1-D bulk async copies (cp.async.bulk) only.  Same math and
+ * reference counterparts as nb2_gemv_ragged.  `records`: n_records x 32 int32
+ * work records (layout documented in
+ * nengo_ocl_b200/cura_gemv.py:build_pipe_records); `ranges`: n_ctas x 2 int32
+ * [begin, end) record ranges, one per CTA; record i of a range is worked on by
+ * warp i % NB2_PIPE_WARPS (chains are interleaved accordingly).
  * `records`, `A`, `X` and `Yin` must be 16-byte aligned and readable up to the
  * next 16-byte boundary past their last element (any nb2_malloc buffer is):
  * unaligned sources are staged as their enclosing 16-byte-aligned window. */
 #ifndef NB2_PIPE_STAGE_FLOATS
-#define NB2_PIPE_STAGE_FLOATS 3200      /* floats of one stage's pool */
-#define NB2_PIPE_STAGES 16              /* stages per CTA */
-#define NB2_PIPE_CONSUMER_WARPS 16      /* consumer warps per CTA */
-#define NB2_PIPE_WARPS_PER_RECORD 1     /* consumer warps that share one record */
+#define NB2_PIPE_STAGE_FLOATS 4300 /* floats of one stage's pool */
+#define NB2_PIPE_WARPS 12          /* warps per CTA, one stage each */
 #define NB2_PIPE_CTAS_PER_SM 1
 #endif
-#define NB2_PIPE_RMAX (128 * NB2_PIPE_WARPS_PER_RECORD) /* rows per record */
+#define NB2_PIPE_RMAX 128 /* rows per record */
 int nb2_gemv_pipelined(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
                        const float* A, const float* X, const float* Yin, float* Y, double alpha,
                        double beta, double gamma, const float* alphas, const float* betas,

@@ -4,28 +4,28 @@
 //
 // Same math as the reference's four OpenCL GEMV variants (nengo_ocl/
 // clra_gemv.py:264-1175).  The kernel is bandwidth-bound (0.5 flop/byte), so
-// the design is about keeping HBM busy with as few instructions per byte as
-// possible:
+// the design is about keeping as many bytes in flight per SM as shared memory
+// allows, with as few instructions per byte as possible:
 //
 //  * The host cuts every output item into work records of roughly equal bytes
 //    (<= NB2_PIPE_STAGE_FLOATS staged floats, <= 4 terms or column chunks,
 //    whole rows whenever a row fits).  Records of one row range form a chain
 //    (several records when an item has many terms or very long rows).
-//  * Persistent CTAs own contiguous ranges of records, balanced by bytes, so
-//    neighbouring CTAs stream neighbouring memory.
-//  * Inside a CTA a ring of shared-memory stages connects producer lanes and
-//    consumer warp groups.  Record i of the CTA uses stage i % STAGES, is
-//    issued by the one producer lane that owns this stage and consumed by
-//    warp group i % GROUPS.  A producer lane waits until its stage is free and
-//    issues nothing but 1-D bulk async copies (cp.async.bulk, completion
-//    counted in bytes on the stage's mbarrier): one copy per matrix segment,
-//    one per gathered X segment, one for the Y_in rows, and the NEXT record of
-//    this stage (so the lane reads its work from shared memory and holds no
-//    record in registers).  Sources that do not start or end on a 16-byte
-//    boundary are copied as the enclosing 16-byte-aligned window and indexed
-//    from the remainder, so there are no per-element copies at all.
-//  * Consumers map one lane to one output row (up to 4 rows per lane, 32 lanes
-//    apart) and walk the row's columns linearly: the x value of a column is one
+//  * Persistent CTAs (one per SM) own contiguous ranges of records, balanced
+//    by bytes, so neighbouring CTAs stream neighbouring memory.
+//  * Every warp of a CTA owns one shared-memory stage and the records
+//    i = warp, warp + WARPS, ... of the CTA's range.  Lane 0 fills the stage
+//    with nothing but 1-D bulk async copies (cp.async.bulk, completion counted
+//    in bytes on the stage's mbarrier): one copy per matrix segment, one per
+//    gathered X segment, one for the Y_in rows, and the NEXT record of this
+//    warp (so the work description is read from shared memory and never held
+//    in registers).  Sources that do not start or end on a 16-byte boundary
+//    are copied as the enclosing 16-byte-aligned window and indexed from the
+//    remainder, so there are no per-element copies at all.  While one warp
+//    waits for its copies the others compute: the 12 stages of a CTA keep
+//    about 200 KB in flight per SM.
+//  * The warp maps one lane to one output row (up to 4 rows per lane, 32 lanes
+//    apart) and walks the row's columns linearly: the x value of a column is one
 //    broadcast shared-memory load for the whole warp, row elements are loaded
 //    with immediate offsets, the running sums stay in registers across all
 //    segments and records of a chain, and the epilogue needs no reduction.
@@ -34,36 +34,28 @@
 //    starts at column l mod w).  There is no scratch buffer and no second
 //    reduction kernel.
 //
-// Every mbarrier wait is bounded by the global timer; on timeout the CTA
-// records NB2_ERR_TIMEOUT in the status word, stops issuing, waits (bounded)
-// for the copies it has in flight and exits.
+// Every mbarrier wait is bounded by the global timer; on timeout the warp
+// records NB2_ERR_TIMEOUT in the status word and leaves.
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
 
-#define PIPE_STAGES NB2_PIPE_STAGES
-#define PIPE_NC NB2_PIPE_CONSUMER_WARPS   // consumer warps
-#define PIPE_W NB2_PIPE_WARPS_PER_RECORD  // warps that share one record (each takes a row range)
-#define PIPE_GROUPS (PIPE_NC / PIPE_W)    // record i belongs to warp group i % GROUPS
-#ifndef PIPE_NP
-#define PIPE_NP 2  // producer warps
-#endif
-#define PIPE_LB (PIPE_STAGES / PIPE_NP)  // active lanes per producer warp, one stage each
+#define PIPE_NW NB2_PIPE_WARPS  // warps per CTA = stages per CTA; record i belongs to warp i % NW
 #define PIPE_ROWS_PER_THREAD 4
-#define PIPE_THREADS (32 * (PIPE_NC + PIPE_NP))
+#define PIPE_THREADS (32 * PIPE_NW)
 #define PIPE_A NB2_PIPE_STAGE_FLOATS  // staged floats per stage (matrix rows and x segments share the pool)
 #define PIPE_R NB2_PIPE_RMAX          // max rows per record
 #define PIPE_REC 32                   // ints per record
 #define PIPE_MAXSEG 4
+#ifndef PIPE_UNROLL
+#define PIPE_UNROLL 8
+#endif
+constexpr int kPipeUnroll = PIPE_UNROLL;
 #define PIPE_WAIT_NS 1000000000ull  // limit of one barrier wait
-#define PIPE_SUSPEND_NS 20000u      // a waiting thread is suspended by the hardware for up to this long per poll
+#ifndef PIPE_SUSPEND_NS
+#define PIPE_SUSPEND_NS 20000u  // a waiting thread is suspended by the hardware for up to this long per poll
+#endif
 
-// Stage s is always filled by the same producer lane and (STAGES a multiple of
-// GROUPS) always drained by the same warp group, so a waiter can only wait for
-// phase r of a barrier after it has itself seen phase r-1: parity waits can
-// never be a whole round behind.
-static_assert(PIPE_NC % PIPE_W == 0 && PIPE_STAGES % PIPE_GROUPS == 0, "each stage must belong to one warp group");
-static_assert(PIPE_STAGES % PIPE_NP == 0 && PIPE_LB <= 32, "each stage must belong to one producer lane");
-static_assert(PIPE_R == 32 * PIPE_ROWS_PER_THREAD * PIPE_W, "rows per record = 4 rows per lane in every warp");
+static_assert(PIPE_R == 32 * PIPE_ROWS_PER_THREAD, "rows per record = 4 rows per lane");
 static_assert(PIPE_THREADS <= 1024, "CTA size");
 
 struct PipeParams {
@@ -83,7 +75,7 @@ struct PipeParams {
 struct __align__(128) PipeStage {
   float buf[PIPE_A];
   float yin[PIPE_R + 8];
-  int rec[2][PIPE_REC];  // record of round m in slot m & 1
+  int rec[3][PIPE_REC];  // record of round m in slot m % 3
 };
 
 __device__ __forceinline__ uint32_t pipe_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -104,13 +96,12 @@ __device__ __forceinline__ bool mbar_try(unsigned long long* bar, uint32_t parit
   return done != 0;
 }
 
-// Bounded parity wait.  Returns false on timeout or when another warp of the CTA gave up.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, const volatile int* abort_flag) {
+// Bounded parity wait.  Returns false on timeout.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
   unsigned long long t0 = 0;
   for (int spins = 0;; ++spins) {
     if (mbar_try(bar, parity)) return true;
     if ((spins & 3) == 3) {
-      if (*abort_flag) return false;
       const unsigned long long t = pipe_timer();
       if (t0 == 0) t0 = t;
       else if (t - t0 > PIPE_WAIT_NS) return false;
@@ -160,7 +151,7 @@ __device__ __forceinline__ void pipe_segment(const float* __restrict__ a, const 
       if (cc == w) cc = 0;
     }
   } else {
-#pragma unroll 4
+#pragma unroll kPipeUnroll
     for (int c = 0; c < w; ++c) {
       const float xv = MODE == 0 ? x[c] : __ldg(x + (size_t)c * xstride);
       acc[0] = fmaf(a0[c], xv, acc[0]);
@@ -179,134 +170,112 @@ __device__ __forceinline__ void pipe_segment_mode(const float* a, const float* x
   else pipe_segment<NR, 0>(a, xs, 1, w, lane, roff, acc);
 }
 
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// Lane 0 of a warp: fill the warp's stage for round m (record index i of the CTA's range).
+// The record itself is already in st.rec[m % 3] and the warp's next record in the slot after
+// it: the matrix windows of that next record are prefetched into L2 now, one whole round
+// before they are copied, so that more bytes are in flight than the stages alone can hold.
+// The record two rounds ahead rides along with this round's copies.
+__device__ __forceinline__ void pipe_issue(const PipeParams& p, PipeStage& st, unsigned long long* full,
+                                           const int4* rp, int i, int m, int n) {
+  const int slot = m % 3;
+  const int* r = st.rec[slot];
+  const int nseg = r[5];
+  const int yin_bytes = r[7];
+  const bool more = i + 2 * PIPE_NW < n;
+  uint32_t tx = (uint32_t)yin_bytes + (more ? PIPE_REC * 4u : 0u);
+  int4 sg[PIPE_MAXSEG];  // window index and bytes of A and X
+  int offs[PIPE_MAXSEG];
+#pragma unroll
+  for (int q = 0; q < PIPE_MAXSEG; ++q) {
+    if (q < nseg) {
+      const int2 lo = *reinterpret_cast<const int2*>(r + 8 + 6 * q);
+      const int2 hi = *reinterpret_cast<const int2*>(r + 8 + 6 * q + 2);
+      sg[q] = make_int4(lo.x, lo.y, hi.x, hi.y);
+      offs[q] = r[8 + 6 * q + 5];
+      tx += (uint32_t)lo.y + (uint32_t)max(hi.y, 0);
+    }
+  }
+  // the stage was read through the generic proxy; order those reads before the async-proxy writes
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
+#pragma unroll
+  for (int q = 0; q < PIPE_MAXSEG; ++q) {
+    if (q < nseg) {
+      bulk_copy(st.buf + ((offs[q] & 0xffff) & ~3), p.A + sg[q].x, (uint32_t)sg[q].y, full);
+      if (sg[q].w > 0) bulk_copy(st.buf + ((offs[q] >> 16) & ~3), p.X + sg[q].z, (uint32_t)sg[q].w, full);
+    }
+  }
+  if (yin_bytes > 0) bulk_copy(st.yin, p.Yin + (r[2] & ~3), (uint32_t)yin_bytes, full);
+  if (more) bulk_copy(st.rec[(m + 2) % 3], rp + (size_t)(i + 2 * PIPE_NW) * 8, PIPE_REC * 4u, full);
+  if (i + PIPE_NW < n) {
+    const int* rn = st.rec[(m + 1) % 3];
+    const int nn = rn[5];
+#pragma unroll
+    for (int q = 0; q < PIPE_MAXSEG; ++q) {
+      if (q < nn) {
+        const int2 lo = *reinterpret_cast<const int2*>(rn + 8 + 6 * q);
+        l2_prefetch(p.A + lo.x, (uint32_t)lo.y);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(PIPE_THREADS, NB2_PIPE_CTAS_PER_SM) nb2_gemv_pipe_kernel(const PipeParams p) {
   extern __shared__ __align__(128) unsigned char pipe_raw[];
   PipeStage* stages = reinterpret_cast<PipeStage*>(pipe_raw);
-  __shared__ __align__(8) unsigned long long full_bar[PIPE_STAGES];
-  __shared__ __align__(8) unsigned long long empty_bar[PIPE_STAGES];
-  __shared__ int s_abort;
+  __shared__ __align__(8) unsigned long long full_bar[PIPE_NW];
 
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
   const int2 range = p.ranges[blockIdx.x];
   const int n = range.y - range.x;
+  if (wid >= n) return;  // (no CTA-wide barrier below: every warp works on its own stage)
 
-  if (tid == 0) {
-    for (int s = 0; s < PIPE_STAGES; ++s) {
-      // full: the producer lane's expect_tx arrival; the copies complete the byte count
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&full_bar[s])), "r"(1));
-      // empty: one arrival per consumer warp of the group that owned the record
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(&empty_bar[s])), "r"(PIPE_W));
-    }
-    s_abort = 0;
+  PipeStage& st = stages[wid];
+  unsigned long long* full = &full_bar[wid];
+  const int4* rp = reinterpret_cast<const int4*>(p.records + (size_t)range.x * PIPE_REC);
+  if (lane == 0) {
+    // the copies complete the byte count; the single arrival is lane 0's expect_tx
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(full)), "r"(1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // the first two records of this warp come straight from global memory
+    int4* dst = reinterpret_cast<int4*>(st.rec[0]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = __ldg(rp + (size_t)wid * 8 + j);
+    if (wid + PIPE_NW < n) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[8 + j] = __ldg(rp + (size_t)(wid + PIPE_NW) * 8 + j);
+    }
+    pipe_issue(p, st, full, rp, wid, 0, n);
   }
-  __syncthreads();
+  __syncwarp();
 
-  const int wid = tid >> 5;
-  if (wid >= PIPE_NC) {
-    // ======================= producer lanes =======================
-    if (lane >= PIPE_LB) return;
-    const int s = (wid - PIPE_NC) * PIPE_LB + lane;  // this lane's stage
-    if (s >= n) return;
-    PipeStage& st = stages[s];
-    unsigned long long* full = &full_bar[s];
-    const int4* rp = reinterpret_cast<const int4*>(p.records + (size_t)range.x * PIPE_REC);
-    {  // the first record of this stage comes straight from global memory
-      int4* dst = reinterpret_cast<int4*>(st.rec[0]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) dst[j] = __ldg(rp + (size_t)s * 8 + j);
-    }
-    int issued = -1;  // last round this lane issued
-    bool ok = true;
-    for (int m = 0, i = s; i < n; ++m, i += PIPE_STAGES) {
-      if (m > 0 && !mbar_wait(&empty_bar[s], (uint32_t)((m - 1) & 1), &s_abort)) {
-        ok = false;
-        break;
-      }
-      // (for m > 0 the record landed with the copies of round m - 1, which the consumers have drained)
-      const int* r = st.rec[m & 1];
-      const int nseg = r[5];
-      const int yin_bytes = r[7];
-      const bool more = i + PIPE_STAGES < n;
-      uint32_t tx = (uint32_t)yin_bytes + (more ? PIPE_REC * 4u : 0u);
-      int4 sg[PIPE_MAXSEG];  // window index and bytes of A and X
-      int offs[PIPE_MAXSEG];
-#pragma unroll
-      for (int q = 0; q < PIPE_MAXSEG; ++q) {
-        if (q < nseg) {
-          const int2 lo = *reinterpret_cast<const int2*>(r + 8 + 6 * q);
-          const int2 hi = *reinterpret_cast<const int2*>(r + 8 + 6 * q + 2);
-          sg[q] = make_int4(lo.x, lo.y, hi.x, hi.y);
-          offs[q] = r[8 + 6 * q + 5];
-          tx += (uint32_t)lo.y + (uint32_t)max(hi.y, 0);
-        }
-      }
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx)
-                   : "memory");
-#pragma unroll
-      for (int q = 0; q < PIPE_MAXSEG; ++q) {
-        if (q < nseg) {
-          bulk_copy(st.buf + ((offs[q] & 0xffff) & ~3), p.A + sg[q].x, (uint32_t)sg[q].y, full);
-          if (sg[q].w > 0) bulk_copy(st.buf + ((offs[q] >> 16) & ~3), p.X + sg[q].z, (uint32_t)sg[q].w, full);
-        }
-      }
-      if (yin_bytes > 0) bulk_copy(st.yin, p.Yin + (r[2] & ~3), (uint32_t)yin_bytes, full);
-      if (more) bulk_copy(st.rec[(m + 1) & 1], rp + (size_t)(i + PIPE_STAGES) * 8, PIPE_REC * 4u, full);
-      issued = m;
-    }
-    if (!ok && !*(volatile int*)&s_abort) {
-      s_abort = 1;
-      if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
-    }
-    // copies of the last issued round may still be in flight if the consumers gave up: a
-    // lane does not leave before its own copies have landed (bounded)
-    if (issued >= 0) {
-      const unsigned long long t0 = pipe_timer();
-      while (!mbar_try(full, (uint32_t)(issued & 1)) && pipe_timer() - t0 < PIPE_WAIT_NS) {
-      }
-    }
-    return;
-  }
-
-  // ========================= consumer warps =========================
-  // Record i of the CTA's list belongs to warp group i % GROUPS (the host
-  // interleaves the chains accordingly); warp v of the group takes the rows
-  // [v * RW, (v + 1) * RW) of the record, RW = ceil(R / W), lane l the rows
-  // l, l + 32, l + 64, l + 96 of that range.  R is fixed along a chain, so the
-  // sums stay in registers.
-  const int group = wid % PIPE_GROUPS;
-  const int v = wid / PIPE_GROUPS;
+  // Lane l takes the rows l, l + 32, l + 64, l + 96 of the record.  The row count is
+  // fixed along a chain, so the sums stay in registers.
   float acc[PIPE_ROWS_PER_THREAD] = {0.0f, 0.0f, 0.0f, 0.0f};
-  for (int i = group; i < n; i += PIPE_GROUPS) {
-    const int s = i % PIPE_STAGES;
-    const int m = i / PIPE_STAGES;
-    if (!mbar_wait(&full_bar[s], (uint32_t)(m & 1), &s_abort)) {
-      if (lane == 0 && !*(volatile int*)&s_abort) {
-        s_abort = 1;
-        if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
-      }
-      break;
+  for (int m = 0, i = wid; i < n; ++m, i += PIPE_NW) {
+    if (!mbar_wait(full, (uint32_t)(m & 1))) {
+      if (lane == 0 && p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
+      return;
     }
-    const PipeStage& st = stages[s];
-    const int* rec = st.rec[m & 1];
+    const int* rec = st.rec[m % 3];
     const int4 h0 = *reinterpret_cast<const int4*>(rec);      // flags, rows, y_in, y
     const int4 h1 = *reinterpret_cast<const int4*>(rec + 4);  // item, segments, -, yin bytes
     const int flags = h0.x, R = h0.y, nseg = h1.y;
-    const int RW = PIPE_W == 1 ? R : (R + PIPE_W - 1) / PIPE_W;
-    const int rbase = v * RW;
-    const int rows = min(RW, R - rbase);  // rows of this warp (may be <= 0)
     if (flags & 1) {
 #pragma unroll
       for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) acc[j] = 0.0f;
     }
-#ifndef PIPE_EXP_NOMATH
-    if (rows > 0) {
+    if (R > 0) {
       // lanes beyond the last row re-read it; their sums are discarded
       int roff[PIPE_ROWS_PER_THREAD];
 #pragma unroll
-      for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) roff[j] = rbase + min(lane + 32 * j, rows - 1);
-      const int NR = (rows + 31) >> 5;
+      for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) roff[j] = min(lane + 32 * j, R - 1);
+      const int NR = (R + 31) >> 5;
       for (int q = 0; q < nseg; ++q) {
         const int2 xf = *reinterpret_cast<const int2*>(rec + 8 + 6 * q + 2);  // x index, x bytes / -stride
         const int2 wf = *reinterpret_cast<const int2*>(rec + 8 + 6 * q + 4);  // columns, offsets
@@ -317,28 +286,25 @@ __global__ void __launch_bounds__(PIPE_THREADS, NB2_PIPE_CTAS_PER_SM) nb2_gemv_p
         else if (NR == 2) pipe_segment_mode<2>(a, xs, xg, -xf.y, wf.x, lane, roff, acc);
         else pipe_segment_mode<4>(a, xs, xg, -xf.y, wf.x, lane, roff, acc);
       }
-    }
-#endif
-    if ((flags & 2) && rows > 0) {
-      const int y_in = h0.z + rbase, y = h0.w + rbase, bb = h1.x;
-      const bool staged = h1.w > 0;
+      if (flags & 2) {
+        const int y_in = h0.z, y = h0.w, bb = h1.x;
+        const bool staged = h1.w > 0;
 #pragma unroll
-      for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) {
-        const int r = lane + 32 * j;
-        if (r < rows) {
-          const float yin = staged ? st.yin[(h0.z & 3) + rbase + r] : p.Yin[y_in + r];
-          p.Y[y + r] = pipe_epilogue(p, bb, yin, acc[j]);
+        for (int j = 0; j < PIPE_ROWS_PER_THREAD; ++j) {
+          const int r = lane + 32 * j;
+          if (r < R) {
+            const float yin = staged ? st.yin[(y_in & 3) + r] : p.Yin[y_in + r];
+            p.Y[y + r] = pipe_epilogue(p, bb, yin, acc[j]);
+          }
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) {
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pipe_smem(&empty_bar[s])) : "memory");
-    }
+    __syncwarp();  // every lane is done with the stage
+    if (lane == 0 && i + PIPE_NW < n) pipe_issue(p, st, full, rp, i + PIPE_NW, m + 1, n);
   }
 }
 
-static const size_t kPipeSmem = sizeof(PipeStage) * PIPE_STAGES;
+static const size_t kPipeSmem = sizeof(PipeStage) * PIPE_NW;
 
 extern "C" int nb2_gemv_pipelined(void* stream, const int* records, int n_records, const int* ranges,
                                   int n_ctas, const float* A, const float* X, const float* Yin, float* Y,

@@ -200,9 +200,8 @@ def build_rows_worklist(gstructure, D):
 # geometry of the pipelined kernel: the same numbers the library was compiled with (include/nengo_b200.h)
 _PIPE = _capi.header_constants("NB2_PIPE_")
 PIPE_STAGE_FLOATS = _PIPE["NB2_PIPE_STAGE_FLOATS"]
-PIPE_STAGES = _PIPE["NB2_PIPE_STAGES"]
-PIPE_CONSUMER_WARPS = _PIPE["NB2_PIPE_CONSUMER_WARPS"]
-PIPE_WARPS_PER_RECORD = _PIPE["NB2_PIPE_WARPS_PER_RECORD"]
+PIPE_CONSUMER_WARPS = _PIPE["NB2_PIPE_WARPS"]  # warps per CTA, one stage each
+PIPE_WARPS_PER_RECORD = 1
 PIPE_CTAS_PER_SM = _PIPE["NB2_PIPE_CTAS_PER_SM"]
 PIPE_RMAX = 128 * PIPE_WARPS_PER_RECORD
 PIPE_MAXSEG, PIPE_REC = 4, 32
@@ -297,9 +296,9 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
     index of the staged window (or of the first column when X is read from
     global memory), its bytes (or minus the X stride), columns,
     (x offset << 16 | a offset) of the first payload element in the stage pool.
-    Returns ``(records, ranges, warp_units, fallback_rows)``; tiny items go to
-    the warp kernel, items whose rows are not contiguous and too narrow for
-    single-row records to the CTA kernel.
+    Returns ``(records, ranges, warp_units, fallback_rows)``; tiny items with very
+    many terms go to the warp kernel, items whose rows are not contiguous and too
+    narrow for single-row records to the CTA kernel.
     """
     n_items = gstructure.shape[0]
     n_dots = gstructure[:, 4 * D + 2].astype(np.int64) if n_items else np.zeros(0, np.int64)
@@ -314,13 +313,13 @@ def build_pipe_records(gstructure, xstrides, D, n_ctas_max):
         g = gstructure[row]
         Ns = [int(v) for v in g[3 * D:3 * D + nd]]
         row_floats = sum(Ns)
-        if m <= 32 and m * row_floats <= 1024 and nd <= 64:
-            warp_rows.append(row)
-            continue
         s0s = [int(v) for v in g[2 * D:2 * D + nd]]
         astarts = [int(v) for v in g[1 * D:1 * D + nd]]
         xstarts = [int(v) for v in g[0:nd]]
         xstr = [int(v) for v in xstrides[row, :nd]] if nd else []
+        if nd > 4 * PIPE_MAXSEG and m <= 32 and m * row_floats <= 1024 and nd <= 64:
+            warp_rows.append(row)  # a long chain of tiny segments: one warp walks the terms directly
+            continue
         if any(s < 0 for s in xstr):
             fallback_rows.append(row)
             continue
