@@ -183,6 +183,39 @@ def gemv_microbench(queue, capi, reps=20, n_outputs=4096):
             "status": int(plan.status.get()[0])}
 
 
+def small_model_rates(ctx, capi, which=("c1", "c3", "c4")):
+    """Configurations 1, 3 and 4 (L2-resident models): simulated steps/s through the public
+    API (``run_steps``: graph replay + probe drains), timed after a 10-step warm-up as the
+    reference's benchmark scripts do (examples/benchmark_circconv.py:87-93)."""
+    from nengo_ocl_b200 import Simulator, synth
+
+    makers = {
+        "c1": ("two ensembles, 2 x 100 LIF, 10000 steps", lambda: synth.two_ensemble_model(seed=0), 10000),
+        "c3": ("circular convolution D=256, 516 x 200 LIF, 1000 steps",
+               lambda: synth.circular_convolution_model(seed=4), 1000),
+        "c4": ("Watts-Strogatz 4096 x 50 LIF, 32768 edges, 1000 steps",
+               lambda: synth.watts_strogatz_model(seed=2), 1000),
+    }
+    out = {}
+    for key in which:
+        label, make, steps = makers[key]
+        t0 = time.perf_counter()
+        mdl = make()
+        sim = Simulator(None, model=mdl, context=ctx)
+        build_s = time.perf_counter() - t0
+        sim.run_steps(10)
+        capi.call("nb2_device_sync")
+        t0 = time.perf_counter()
+        sim.run_steps(steps)
+        capi.call("nb2_device_sync")
+        dt_s = time.perf_counter() - t0
+        out[key] = {"workload": label, "steps_per_s": steps / dt_s, "neuron_updates_per_s": mdl.n_neurons * steps / dt_s,
+                    "plans_per_step": len(sim._plans), "launches_per_step": sim._plans.launches_per_step,
+                    "us_per_step": 1e6 * dt_s / steps, "build_s": round(build_s, 2)}
+        sim.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -194,6 +227,7 @@ def main():
     ap.add_argument("--gemv-only", action="store_true", help="run only the GEMV microbenchmark (for profiling)")
     ap.add_argument("--gemv-outputs", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-small", action="store_true", help="skip the steps/s of configurations 1, 3 and 4")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -337,6 +371,8 @@ def main():
     if rank == 0 and not args.no_gemv:
         line["gemv"] = gemv_microbench(queue, _capi)
         line["gemv"]["frac"] = line["gemv"]["achieved_gbs"] / peak
+    if rank == 0 and not args.no_small and world == 1:
+        line["small_models"] = small_model_rates(ctx, _capi)
     if rank == 0 and not args.no_cpu and world == 1:
         n_ens = 512
         rate, s_per_step, nn = cpu_oracle_rate(n_ens, 40)

@@ -32,6 +32,9 @@
 #include "../../include/nengo_b200.h"
 
 #define FUSED_THREADS 256
+#ifndef FUSED_MIN_BLOCKS
+#define FUSED_MIN_BLOCKS 3  // CTAs per SM the register budget is sized for
+#endif
 #define FUSED_RCH 16                         // decoder rows per pass
 #define FUSED_MAX_N NB2_FUSED_MAX_NEURONS    // neurons per ensemble (spikes staged in smem)
 #define FUSED_MAX_X NB2_FUSED_MAX_INPUT      // total encoder columns per ensemble
@@ -66,7 +69,7 @@ __device__ __forceinline__ float fused_lif(float J, float& V, float& W, float ta
 
 // TPE = threads per ensemble (32 or 256); NEMAX = staged neurons per ensemble
 template <int TPE, int NEMAX>
-__global__ void __launch_bounds__(FUSED_THREADS, 3)
+__global__ void __launch_bounds__(FUSED_THREADS, FUSED_MIN_BLOCKS)
 nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* __restrict__ ens_table,
                          const int* __restrict__ term_table, const int* __restrict__ conn_table,
                          float* data, float dt, float dt_inv) {
@@ -106,6 +109,17 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
       xoff += d;
     }
   }
+#ifdef FUSED_L2_PREFETCH
+  // start the decoders (and PES traces) of this ensemble on their way into L2 while phase 1 runs
+  if (active && t < e[E_NCONN]) {
+    const int* c = conn_table + (size_t)(e[E_CONN0] + t) * C_STRIDE;
+    const size_t bytes = (size_t)c[C_D] * n * sizeof(float);
+    const float* Wd = data + c[C_W];
+    if ((((uintptr_t)Wd | bytes) & 15) == 0) {
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Wd), "r"((uint32_t)bytes) : "memory");
+    }
+  }
+#endif
   group_sync();
 
   // ---- phase 1: J = bias + enc . x ; LIF ----

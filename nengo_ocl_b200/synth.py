@@ -258,6 +258,81 @@ def watts_strogatz_model(seed=2, n_ensembles=4096, n_neurons=50, k=4, p=0.1, syn
     return nb.model
 
 
+# ---- configuration 3: circular convolution through product ensembles ------------
+def circular_convolution_model(seed=4, dimensions=256, n_neurons=200, synapse=0.005, dt=0.001, n_templates=8):
+    """c = a (*) b computed in the Fourier domain by 2-d product ensembles.
+
+    Both inputs are seeded unit vectors held constant.  A real DFT of each
+    input (``dimensions // 2 + 1`` complex bins) is formed by dense transforms;
+    every complex product (ar + i ai)(br + i bi) takes four real products, each
+    computed by one ensemble of ``n_neurons`` LIF neurons representing the pair
+    of factors (4 * (D/2 + 1) ensembles, 516 for D = 256); a third dense
+    transform combines the products and applies the inverse real DFT.  All
+    three connections carry a lowpass synapse.  (A construction of the same
+    shapes as a nengo circular-convolution network; the ensemble count of the
+    library network is not reproduced from it.)"""
+    nb = NetBuilder(dt=dt, seed=seed, label="circular convolution")
+    rng = nb.rng
+    D = int(dimensions)
+    nbins = D // 2 + 1
+    a = rng.standard_normal(D)
+    b = rng.standard_normal(D)
+    a /= np.linalg.norm(a)
+    b /= np.linalg.norm(b)
+    # real DFT as a matrix: rows (re_0 .. re_{nb-1}, im_0 .. im_{nb-1}); unit vectors give O(1) bins
+    k = np.arange(nbins)[:, None] * np.arange(D)[None, :]
+    F = np.concatenate([np.cos(2 * np.pi * k / D), -np.sin(2 * np.pi * k / D)], axis=0)  # (2 nbins, D)
+    re, im = np.arange(nbins), nbins + np.arange(nbins)
+    # product p = 4 * bin + {0: ar*br, 1: ai*bi, 2: ar*bi, 3: ai*br}
+    rows_a = np.stack([re, im, re, im], axis=1).reshape(-1)
+    rows_b = np.stack([re, im, im, re], axis=1).reshape(-1)
+    n_prod = 4 * nbins
+    Ta, Tb = F[rows_a], F[rows_b]
+    sa = nb.node_const(a, label="a")
+    sb = nb.node_const(b, label="b")
+    fa = m.Signal(np.zeros(n_prod), name="A.factors")
+    fb = m.Signal(np.zeros(n_prod), name="B.factors")
+    for src, T, dst, label in ((sa, Ta, fa, "a->factors"), (sb, Tb, fb, "b->factors")):
+        w = m.Signal(T, name="%s.weights" % label, readonly=True)
+        weighted = m.Signal(np.zeros(n_prod), name="%s.weighted" % label)
+        nb.model.add_op(m.Reset(weighted))
+        nb.model.add_op(m.DotInc(w, src, weighted, tag="%s.transform" % label))
+        nb.synapse(weighted, synapse, label, out=dst)
+    templates, decoders, ens = [], [], []
+    products = m.Signal(np.zeros(n_prod), name="products")
+    for p_i in range(n_prod):
+        t = templates[p_i % n_templates] if p_i >= n_templates else None
+        e = nb.ensemble(n_neurons, 2, label="prod%d" % p_i, radius=np.sqrt(2.0), params_from=t)
+        if t is None:
+            templates.append(e)
+            decoders.append(nb.solve_decoders(e, function=lambda x: x[0] * x[1]))
+        ens.append(e)
+        nb.model.add_op(m.Copy(fa[p_i:p_i + 1], e.sig_in[0:1], inc=True))
+        nb.model.add_op(m.Copy(fb[p_i:p_i + 1], e.sig_in[1:2], inc=True))
+        nb.connect_decoded(e, None, decoders[p_i % n_templates], synapse=synapse, label="prod%d.out" % p_i,
+                           out_signal=products[p_i:p_i + 1])
+    # combine: Re = ar br - ai bi, Im = ar bi + ai br; inverse real DFT
+    C = np.zeros((2 * nbins, n_prod))
+    for bin_ in range(nbins):
+        C[bin_, 4 * bin_ + 0], C[bin_, 4 * bin_ + 1] = 1.0, -1.0
+        C[nbins + bin_, 4 * bin_ + 2], C[nbins + bin_, 4 * bin_ + 3] = 1.0, 1.0
+    wgt = np.full(nbins, 2.0)
+    wgt[0] = 1.0
+    if D % 2 == 0:
+        wgt[-1] = 1.0
+    kk = np.arange(D)[:, None] * np.arange(nbins)[None, :]
+    Finv = np.concatenate([wgt * np.cos(2 * np.pi * kk / D), -wgt * np.sin(2 * np.pi * kk / D)], axis=1) / D
+    out = m.Signal(np.zeros(D), name="c.in")
+    nb.model.add_op(m.Reset(out))
+    w = m.Signal(Finv @ C, name="products->c.weights", readonly=True)
+    nb.model.add_op(m.DotInc(w, products, out, tag="products->c.transform"))
+    probe = nb.probe(out, synapse=0.01, label="c")
+    exact = np.fft.irfft(np.fft.rfft(a) * np.fft.rfft(b), n=D)
+    nb.model.info = dict(probes=[probe], ensembles=nb.ensembles, connections=nb.connections, a=a, b=b,
+                         exact=exact, n_products=n_prod)
+    return nb.model
+
+
 # ---- configuration 5: large PES learning model -----------------------------------
 def pes_learning_model(seed=3, n_ensembles=4096, n_neurons=1024, dimensions=16, learning_rate=1e-4,
                        synapse=0.01, pre_synapse=0.005, dt=0.001, sim_time=0.5, n_templates=8, n_probes=4,

@@ -180,9 +180,14 @@ def odd_pes(seed=3):
     return small_pes(seed=seed, n_ensembles=5, n_neurons=301, dimensions=3, n_templates=2)
 
 
+def small_cc(seed=4):
+    # circular convolution: dense transforms in, 2-d product ensembles, dense transform out
+    return synth.circular_convolution_model(seed=seed, dimensions=16, n_neurons=64, n_templates=3)
+
+
 @pytest.mark.parametrize("fuse", [False, True])
-@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes],
-                         ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3"])
+@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes, small_cc],
+                         ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3", "circular_convolution"])
 def test_scaled_configs_match_oracle_per_step(make, fuse):
     mdl = make()
     ora = OracleSimulator(mdl)
@@ -198,12 +203,16 @@ def test_scaled_configs_match_oracle_per_step(make, fuse):
     skip.update(s for g in sim.fused_groups for s in g["unstored"])
     assert bool(sim.fused_groups) == fuse
     sigs = [s for s in state_signals(mdl) if s not in skip]
+    # A different float32 summation order can move a spike by one step; that neuron's state then
+    # differs for a few steps.  In the circular convolution every product feeds all outputs through
+    # the dense output transform, so one moved spike touches every element downstream of it.
+    bad_fraction = 1e-2 if make is small_cc else 2e-3
     with sim:
         worst = 0.0
         for step in range(100):
             sim.step()
             ora.step()
-            worst = max(worst, compare_signals(sim, ora, sigs, max_bad_fraction=2e-3))
+            worst = max(worst, compare_signals(sim, ora, sigs, max_bad_fraction=bad_fraction))
         for c in mdl.info["connections"]:
             if "delta" in c and fused_pes:
                 got = np.asarray(sim.signals[c["weights"]])
