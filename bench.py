@@ -64,32 +64,40 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.device = device
+        self.t_first = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.perf_counter()  # the tool takes a moment to start: wait for its first sample
+            while not self.rows and time.perf_counter() - t0 < 3.0 and self.proc.poll() is None:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
+        self.t_first = time.perf_counter()
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.perf_counter()] + [c.strip() for c in line.split(",")])
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            self.t_last = time.perf_counter()
+            time.sleep(0.05)
             self.proc.terminate()
             self.thread.join(timeout=2)
 
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for stamp, *r in self.rows:
+            if stamp < self.t_first or stamp > getattr(self, "t_last", stamp) + 0.03:
+                continue  # sampled before the GPU was under load
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -228,6 +236,7 @@ def main():
     ap.add_argument("--gemv-outputs", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-small", action="store_true", help="skip the steps/s of configurations 1, 3 and 4")
+    ap.add_argument("--small-only", default=None, help="run only these small configurations, e.g. c3,c4 (for profiling)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -264,6 +273,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.small_only:
+        print(json.dumps({"small_models": small_model_rates(ctx, _capi, tuple(args.small_only.split(",")))}), flush=True)
+        return
     if args.gemv_only:
         from nengo_ocl_b200.runtime import CommandQueue
 
@@ -302,19 +314,20 @@ def main():
         pass
     barrier()
     _capi.call("nb2_device_sync")
-    with ClockSampler(local_rank) as clocks:
-        done, total_ms = 0, 0.0
-        while done < K:
-            b = min(B, K - done)
-            sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
-            _capi.call("nb2_stream_sync", queue.stream)
-            ev.start(queue.stream)
-            plans.enqueue_n_times(b)
-            total_ms += ev.stop_ms(queue.stream)
-            sim._probe()               # drain outside the timed region
-            done += b
-        barrier()
-        _capi.call("nb2_device_sync")
+    clocks = ClockSampler(local_rank)
+    clocks.__enter__()
+    done, total_ms = 0, 0.0
+    while done < K:
+        b = min(B, K - done)
+        sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
+        _capi.call("nb2_stream_sync", queue.stream)
+        ev.start(queue.stream)
+        plans.enqueue_n_times(b)
+        total_ms += ev.stop_ms(queue.stream)
+        sim._probe()               # drain outside the timed region
+        done += b
+    barrier()
+    _capi.call("nb2_device_sync")
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / K
     value = world * n_neurons * K / (total_ms / 1e3)
@@ -350,6 +363,7 @@ def main():
     sim.run_steps(K)
     _capi.call("nb2_device_sync")
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks.__exit__(None, None, None)  # sampled over the device-timed, per-kernel and end-to-end regions
     probe_bytes = sum(4 * int(mdl.sig[p]["in"].size) for p in mdl.probes) + 4 * len(mdl.probes) / B + 8.0 / B
     e2e = {"value": world * n_neurons * K / e2e_s, "unit": "neuron-updates/s",
            "h2d_bytes_per_step": int(sim.h2d_bytes_per_step), "d2h_bytes_per_step": int(round(probe_bytes)),

@@ -109,17 +109,6 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
       xoff += d;
     }
   }
-#ifdef FUSED_L2_PREFETCH
-  // start the decoders (and PES traces) of this ensemble on their way into L2 while phase 1 runs
-  if (active && t < e[E_NCONN]) {
-    const int* c = conn_table + (size_t)(e[E_CONN0] + t) * C_STRIDE;
-    const size_t bytes = (size_t)c[C_D] * n * sizeof(float);
-    const float* Wd = data + c[C_W];
-    if ((((uintptr_t)Wd | bytes) & 15) == 0) {
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Wd), "r"((uint32_t)bytes) : "memory");
-    }
-  }
-#endif
   group_sync();
 
   // ---- phase 1: J = bias + enc . x ; LIF ----
