@@ -222,6 +222,26 @@ int nb2_ensemble_step(void* stream, int n_large, const int* large_ids, int n_sma
                       const int* ens_table, const int* term_table, const int* conn_table, float* data,
                       double dt);
 
+/* The same fused step for large populations as a bulk-copy pipeline (persistent
+ * CTAs, one shared-memory stage per warp, cp.async.bulk + mbarrier).  `records`:
+ * n_records x 32 int32 work records and `ranges`: n_ctas x 2 int32 [begin, end)
+ * record ranges, one per CTA, as built by
+ * nengo_ocl_b200/fusion.py:stream_records; the three tables are those of
+ * nb2_ensemble_step.  Only ensembles whose arrays start on multiples of 4 floats,
+ * with n % 4 == 0, n <= NB2_STREAM_MAX_NEURONS, total encoder width <=
+ * NB2_STREAM_MAX_INPUT and at most one PES connection may be streamed.
+ * `status` (may be NULL) receives NB2_ERR_TIMEOUT if a bounded wait gave up. */
+#ifndef NB2_STREAM_STAGE_FLOATS
+#define NB2_STREAM_STAGE_FLOATS 4096 /* floats of one stage */
+#define NB2_STREAM_WARPS 12          /* warps per CTA, one stage each */
+#endif
+#define NB2_STREAM_SLOTS 3           /* ensembles in flight per CTA (spikes + PES trace in shared memory) */
+#define NB2_STREAM_MAX_NEURONS 1024
+#define NB2_STREAM_MAX_INPUT 64
+int nb2_ensemble_stream(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
+                        const int* ens_table, const int* term_table, const int* conn_table, float* data,
+                        double dt, int* status);
+
 /* ---- multi-GPU exchange of decoded signals ---------------------------------
  * No counterpart in the reference (single device, simulator.py:215-219).  Every
  * rank holds a replica of one exchange signal of world*seg floats and owns

@@ -28,6 +28,7 @@ UNITS = [
     ("nb2_neurons.cu", ["-fmad=false"]),
     ("nb2_direct.cu", ["-fmad=false"]),
     ("nb2_fused.cu", ["-fmad=false"]),
+    ("nb2_fused_stream.cu", ["-fmad=false"]),
     ("nb2_exchange.cu", []),
 ]
 

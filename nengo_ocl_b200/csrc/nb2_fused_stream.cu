@@ -1,0 +1,342 @@
+// Streamed fused ensemble step for large populations: the same operator
+// sequence as nb2_fused.cu (encoder GEMV + LIF + decoder GEMV + lowpass synapse
+// + PES decoder update in one kernel per time step; reference counterparts
+// listed there), organised as a bulk-copy pipeline so that every SM always has
+// about 200 KB of loads in flight.
+//
+//  * The host cuts every ensemble into work records: E records (up to 128
+//    neurons: their encoder rows, bias, voltage, refractory time and PES
+//    activity trace) and D records (up to 4 rows of one decoder matrix).  A CTA
+//    (one per SM, persistent) owns a list of whole ensembles; its records are
+//    ordered E(0), E(1), D(0), E(2), D(1), ... so that the spikes a D record
+//    needs were produced a round earlier.
+//  * Every warp owns one shared-memory stage and the records i = warp,
+//    warp + WARPS, ... .  Lane 0 fills the stage with 1-D bulk async copies
+//    (cp.async.bulk, completion counted in bytes on the stage's mbarrier); all
+//    sources are 16-byte aligned by construction (the host only streams
+//    ensembles whose arrays start on multiples of 4 floats).  The warp's next
+//    record rides along with the copies.
+//  * E record: one lane per neuron (4 neurons per lane); J = bias + enc . x with
+//    the staged rows walked diagonally (shared-memory banks), LIF update in the
+//    operation order of the reference kernel (this file is compiled with
+//    -fmad=false, dot products use explicit fmaf), V / W / spikes / new
+//    activity trace written straight to global memory, spikes and the OLD trace
+//    kept in a per-ensemble slot of shared memory for the D records.
+//  * D record: lanes over groups of 4 neurons; decoded = W . s accumulated per
+//    row, the PES update w += (alpha * err) * trace applied to the same element
+//    and written straight back, one shuffle reduction per row, then the synapse.
+//  * Slots are handed from E to D records and back through two counters per slot
+//    in shared memory; a record only ever waits for records that precede it in
+//    the CTA's list, so the lowest unfinished record can always run.
+//
+// Every wait (mbarrier, counters) is bounded by the global timer; on timeout
+// the warp records NB2_ERR_TIMEOUT in the status word, raises the CTA's abort
+// flag and leaves.
+#include "nb2_common.cuh"
+#include "nb2_pipe.cuh"
+#include "nb2_fused_common.cuh"
+#include "../../include/nengo_b200.h"
+
+#define ST_NW NB2_STREAM_WARPS
+#define ST_THREADS (32 * ST_NW)
+#define ST_A NB2_STREAM_STAGE_FLOATS
+#define ST_X NB2_STREAM_MAX_INPUT
+#define ST_N NB2_STREAM_MAX_NEURONS
+#define ST_SLOTS NB2_STREAM_SLOTS
+#define ST_REC 32
+#define ST_MAXCOPY 8
+#define ST_ROWS 4  // decoder rows per D record, neurons per lane in an E record
+
+struct StreamParams {
+  const int* records;  // [n_records][32]
+  const int2* ranges;  // per CTA: [begin, end) record indices
+  const int* ens_table;
+  const int* term_table;
+  const int* conn_table;
+  float* data;
+  float dt, dt_inv;
+  int* status;
+};
+
+struct __align__(128) StreamStage {
+  float buf[ST_A];
+  float x[ST_X];
+  int rec[2][ST_REC];  // record of round m in slot m & 1
+};
+
+struct __align__(16) StreamSlot {
+  float spk[ST_N];
+  float pfo[ST_N];
+};
+
+// record words
+enum { R_TYPE = 0, R_ENS, R_SLOT, R_A, R_B, R_NCOPY, R_TARGET, R_C, R_COPY0 = 8 };
+
+// Lane 0: fill the stage for round m (record index i); the record is in st.rec[m & 1].
+__device__ __forceinline__ void stream_issue(const StreamParams& p, StreamStage& st, unsigned long long* full,
+                                             const int4* rp, int i, int m, int n) {
+  const int* r = st.rec[m & 1];
+  const int ncopy = r[R_NCOPY];
+  const bool more = i + ST_NW < n;
+  uint32_t tx = more ? ST_REC * 4u : 0u;
+  for (int q = 0; q < ncopy; ++q) tx += (uint32_t)r[R_COPY0 + 3 * q + 1];
+  // the stage was read through the generic proxy; order those reads before the async-proxy writes
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
+  for (int q = 0; q < ncopy; ++q)
+    bulk_copy(st.buf + r[R_COPY0 + 3 * q + 2], p.data + r[R_COPY0 + 3 * q], (uint32_t)r[R_COPY0 + 3 * q + 1], full);
+  if (more) bulk_copy(st.rec[(m + 1) & 1], rp + (size_t)(i + ST_NW) * 8, ST_REC * 4u, full);
+}
+
+// All lanes: stage the input vectors of an E record's ensemble (read from global memory, L2-hot).
+__device__ __forceinline__ void stream_stage_x(const StreamParams& p, StreamStage& st, const int* r, int lane) {
+  if (r[R_TYPE] != 1) return;
+  const int* e = p.ens_table + (size_t)r[R_ENS] * E_STRIDE;
+  const int n_terms = __ldg(e + E_NTERMS);
+  const int* terms = p.term_table + (size_t)__ldg(e + E_TERM0) * T_STRIDE;
+  int xoff = 0;
+  for (int k = 0; k < n_terms; ++k) {
+    const int d = __ldg(terms + k * T_STRIDE + T_D);
+    const float* x = p.data + __ldg(terms + k * T_STRIDE + T_X);
+    const int xs = __ldg(terms + k * T_STRIDE + T_XS);
+    for (int c = lane; c < d; c += 32) st.x[xoff + c] = x[(size_t)c * xs];
+    xoff += d;
+  }
+}
+
+// Lane 0 polls a counter of the CTA; the whole warp gets the answer.
+__device__ __forceinline__ bool stream_wait_count(const volatile int* ctr, int target, volatile int* abort_flag,
+                                                  int lane) {
+  int ok = 1;
+  if (lane == 0 && *ctr < target) {
+    const unsigned long long t0 = pipe_timer();
+    for (int spins = 0; *ctr < target; ++spins) {
+      __nanosleep(100);
+      if ((spins & 15) == 15 && (*abort_flag || pipe_timer() - t0 > PIPE_WAIT_NS)) {
+        ok = 0;
+        break;
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __threadfence_block();  // the other warps' shared-memory writes before their count
+  return ok != 0;
+}
+
+__global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(const StreamParams p) {
+  extern __shared__ __align__(128) unsigned char stream_raw[];
+  StreamStage* stages = reinterpret_cast<StreamStage*>(stream_raw);
+  StreamSlot* slots = reinterpret_cast<StreamSlot*>(stream_raw + sizeof(StreamStage) * ST_NW);
+  __shared__ __align__(8) unsigned long long full_bar[ST_NW];
+  __shared__ int e_done[ST_SLOTS];  // E records finished per slot (cumulative)
+  __shared__ int d_done[ST_SLOTS];  // D records finished per slot (cumulative)
+  __shared__ int s_abort;
+
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int2 range = p.ranges[blockIdx.x];
+  const int n = range.y - range.x;
+  if (threadIdx.x < ST_SLOTS) e_done[threadIdx.x] = d_done[threadIdx.x] = 0;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  if (wid >= n) return;
+
+  StreamStage& st = stages[wid];
+  unsigned long long* full = &full_bar[wid];
+  const int4* rp = reinterpret_cast<const int4*>(p.records + (size_t)range.x * ST_REC);
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem(full)), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    int4* dst = reinterpret_cast<int4*>(st.rec[0]);  // the first record comes straight from global memory
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = __ldg(rp + (size_t)wid * 8 + j);
+    stream_issue(p, st, full, rp, wid, 0, n);
+  }
+  __syncwarp();
+  stream_stage_x(p, st, st.rec[0], lane);
+  __syncwarp();
+
+  float* const data = p.data;
+  for (int m = 0, i = wid; i < n; ++m, i += ST_NW) {
+    bool ok = mbar_wait(full, (uint32_t)(m & 1));
+    const int* rec = st.rec[m & 1];
+    const int4 h0 = *reinterpret_cast<const int4*>(rec);      // type, ensemble, slot, a
+    const int4 h1 = *reinterpret_cast<const int4*>(rec + 4);  // b, copies, target, c
+    const int* e = p.ens_table + (size_t)h0.y * E_STRIDE;
+    StreamSlot& slot = slots[h0.z];
+    if (ok && h0.x == 1) {
+      // ---------------- E record: neurons [i0, i0 + ne) ----------------
+      const int i0 = h0.w, ne = h1.x, pf_conn = h1.w;
+      const int n_terms = __ldg(e + E_NTERMS);
+      const int* terms = p.term_table + (size_t)__ldg(e + E_TERM0) * T_STRIDE;
+      const float tau = bits(__ldg(e + E_TAU)), ref = bits(__ldg(e + E_REF)), amp = bits(__ldg(e + E_AMP));
+      const int eV = __ldg(e + E_V), eW = __ldg(e + E_W), eS = __ldg(e + E_S);
+      float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
+      int roff[ST_ROWS];
+#pragma unroll
+      for (int j = 0; j < ST_ROWS; ++j) roff[j] = min(lane + 32 * j, ne - 1);
+      const int NR = (ne + 31) >> 5;
+      int xoff = 0;
+      for (int k = 0; k < n_terms; ++k) {
+        const int d = __ldg(terms + k * T_STRIDE + T_D);
+        const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
+        if (NR == 1) pipe_segment_mode<1>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+        else if (NR == 2) pipe_segment_mode<2>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+        else pipe_segment_mode<4>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+        xoff += d;
+      }
+      const float* s_bias = st.buf + rec[R_COPY0 + 3 * n_terms + 2];
+      const float* s_V = st.buf + rec[R_COPY0 + 3 * (n_terms + 1) + 2];
+      const float* s_W = st.buf + rec[R_COPY0 + 3 * (n_terms + 2) + 2];
+      const float* s_pf = st.buf + rec[R_COPY0 + 3 * (n_terms + 3) + 2];  // (only read when pf_conn >= 0)
+      float pb0 = 0.0f, pa0 = 0.0f;
+      int gpf = 0;
+      if (pf_conn >= 0) {
+        const int* c = p.conn_table + (size_t)pf_conn * C_STRIDE;
+        pb0 = bits(__ldg(c + C_PFB0));
+        pa0 = bits(__ldg(c + C_PFA0));
+        gpf = __ldg(c + C_PF);
+      }
+      // the slot's previous ensemble must have been decoded completely
+      ok = stream_wait_count(&d_done[h0.z], h1.z, &s_abort, lane);
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < ST_ROWS; ++j) {
+          const int r = lane + 32 * j;
+          if (r < ne) {
+            const float J = s_bias[r] + acc[j];
+            float v = s_V[r], w = s_W[r];
+            const float s = fused_lif(J, v, w, tau, ref, amp, p.dt, p.dt_inv);
+            data[eV + i0 + r] = v;
+            data[eW + i0 + r] = w;
+            if (eS >= 0) data[eS + i0 + r] = s;
+            slot.spk[i0 + r] = s;
+            if (pf_conn >= 0) {
+              const float pf = s_pf[r];
+              slot.pfo[i0 + r] = pf;
+              data[gpf + i0 + r] = pb0 * s - pa0 * pf;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicAdd(&e_done[h0.z], 1);
+        }
+      }
+    } else if (ok && h0.x == 2) {
+      // ---------------- D record: rows [r0, r0 + nr) of one decoder matrix ----------------
+      const int* c = p.conn_table + (size_t)h0.w * C_STRIDE;
+      const int r0 = h1.x, nr = h1.w;
+      const int n_e = __ldg(e + E_N);
+      const int n4 = n_e >> 2;
+      const bool pes = __ldg(c + C_PES) != 0;
+      float ae[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (pes) {
+        // alpha * error, formed once per row as in `alpha * aa * xx` (left to right)
+        const float alpha = bits(__ldg(c + C_ALPHA));
+        const float* err = data + __ldg(c + C_ERR) + r0;
+#pragma unroll
+        for (int r = 0; r < ST_ROWS; ++r)
+          if (r < nr) ae[r] = alpha * err[r];
+      }
+      float4* Wd = reinterpret_cast<float4*>(data + __ldg(c + C_W)) + (size_t)r0 * n4;
+      const float4* sw = reinterpret_cast<const float4*>(st.buf);
+      const float4* spk4 = reinterpret_cast<const float4*>(slot.spk);
+      const float4* pfo4 = reinterpret_cast<const float4*>(slot.pfo);
+      // every E record of this ensemble must have delivered its spikes
+      ok = stream_wait_count(&e_done[h0.z], h1.z, &s_abort, lane);
+      if (ok) {
+        float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int i4 = lane; i4 < n4; i4 += 32) {
+          const float4 s4 = spk4[i4];
+          float4 p4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (pes) p4 = pfo4[i4];
+#pragma unroll
+          for (int r = 0; r < ST_ROWS; ++r) {
+            if (r < nr) {
+              const float4 w4 = sw[r * n4 + i4];
+              float a = acc[r];
+              a = fmaf(w4.x, s4.x, a);
+              a = fmaf(w4.y, s4.y, a);
+              a = fmaf(w4.z, s4.z, a);
+              a = fmaf(w4.w, s4.w, a);
+              acc[r] = a;
+              if (pes) {
+                float4 o;
+                o.x = w4.x + ae[r] * p4.x;
+                o.y = w4.y + ae[r] * p4.y;
+                o.z = w4.z + ae[r] * p4.z;
+                o.w = w4.w + ae[r] * p4.w;
+                Wd[(size_t)r * n4 + i4] = o;
+              }
+            }
+          }
+        }
+        // fixed-order reduction over the lanes (xor tree)
+#pragma unroll
+        for (int r = 0; r < ST_ROWS; ++r)
+          for (int off = 16; off > 0; off >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+        if (lane < nr) {
+          float total = acc[0];
+          if (lane == 1) total = acc[1];
+          if (lane == 2) total = acc[2];
+          if (lane == 3) total = acc[3];
+          data[__ldg(c + C_WEIGHTED) + r0 + lane] = total;
+          const int filt = __ldg(c + C_FILT);
+          if (filt >= 0) {
+            float* y = data + filt + r0 + lane;
+            // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
+            const int a0 = __ldg(c + C_A0);
+            if (a0 == 0) *y = bits(__ldg(c + C_B0)) * total;
+            else *y = bits(__ldg(c + C_B0)) * total - bits(a0) * *y;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicAdd(&d_done[h0.z], 1);
+        }
+      }
+    }
+    if (!ok) {
+      if (lane == 0) {
+        s_abort = 1;
+        if (p.status) atomicExch(p.status, NB2_ERR_TIMEOUT);
+      }
+      return;
+    }
+    __syncwarp();  // every lane is done with the stage
+    if (i + ST_NW < n) {
+      if (lane == 0) stream_issue(p, st, full, rp, i + ST_NW, m + 1, n);
+      __syncwarp();
+      stream_stage_x(p, st, st.rec[(m + 1) & 1], lane);
+    }
+  }
+}
+
+static const size_t kStreamSmem = sizeof(StreamStage) * ST_NW + sizeof(StreamSlot) * ST_SLOTS;
+
+extern "C" int nb2_ensemble_stream(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
+                                   const int* ens_table, const int* term_table, const int* conn_table, float* data,
+                                   double dt, int* status) {
+  if (n_records == 0 || n_ctas == 0) return NB2_OK;
+  NB2_REQUIRE(records && ranges && ens_table && term_table && conn_table && data, "null pointer");
+  NB2_REQUIRE(dt > 0, "dt");
+  NB2_REQUIRE((((uintptr_t)records | (uintptr_t)data) & 15) == 0, "records and data must be 16-byte aligned");
+  static bool optin[64] = {};
+  int dev = 0;
+  NB2_CUDA(cudaGetDevice(&dev));
+  if (dev >= 64 || !optin[dev]) {
+    NB2_CUDA(cudaFuncSetAttribute(nb2_ensemble_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kStreamSmem));
+    if (dev < 64) optin[dev] = true;
+  }
+  StreamParams p;
+  p.records = records; p.ranges = reinterpret_cast<const int2*>(ranges);
+  p.ens_table = ens_table; p.term_table = term_table; p.conn_table = conn_table;
+  p.data = data; p.dt = (float)dt; p.dt_inv = (float)(1.0 / dt); p.status = status;
+  nb2_ensemble_stream_kernel<<<n_ctas, ST_THREADS, kStreamSmem, nb2_stream(stream)>>>(p);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}

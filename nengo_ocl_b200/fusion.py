@@ -39,7 +39,7 @@ from nengo_ocl_b200 import _capi
 from nengo_ocl_b200.model import Operator
 from nengo_ocl_b200.operators import MultiDotInc
 from nengo_ocl_b200.plan import Plan
-from nengo_ocl_b200.runtime import to_device
+from nengo_ocl_b200.runtime import to_device, zeros
 
 MAX_NEURONS, SMALL_NEURONS, MAX_INPUT = 4096, 256, 512
 
@@ -304,14 +304,138 @@ def fused_bytes_per_step(members):
     return total
 
 
+# ---- streamed kernel for large populations (csrc/nb2_fused_stream.cu) ---------------
+_STREAM = _capi.header_constants("NB2_STREAM_")
+STREAM_STAGE_FLOATS = _STREAM["NB2_STREAM_STAGE_FLOATS"]
+STREAM_WARPS = _STREAM["NB2_STREAM_WARPS"]
+STREAM_SLOTS = _STREAM["NB2_STREAM_SLOTS"]
+STREAM_MAX_NEURONS = _STREAM["NB2_STREAM_MAX_NEURONS"]
+STREAM_MAX_INPUT = _STREAM["NB2_STREAM_MAX_INPUT"]
+STREAM_MIN_NEURONS = 256
+STREAM_REC, STREAM_ROWS, STREAM_CHUNK = 32, 4, 128
+
+
+def streamable(ens, terms, conns):
+    """Rows of the ensemble table that ``nb2_ensemble_stream`` can take."""
+    out = []
+    for i, row in enumerate(ens):
+        n, nt, t0, nc, c0 = int(row[0]), int(row[6]), int(row[7]), int(row[8]), int(row[9])
+        d_total = int(terms[t0:t0 + nt, 1].sum()) if nt else 0
+        pes = int(conns[c0:c0 + nc, 6].sum()) if nc else 0
+        ok = (row[13] & 1) and STREAM_MIN_NEURONS <= n <= STREAM_MAX_NEURONS and nt <= 4 and pes <= 1
+        ok = ok and d_total <= STREAM_MAX_INPUT and 4 * (d_total + 4) <= STREAM_STAGE_FLOATS
+        ok = ok and (nt == 0 or bool(np.all(terms[t0:t0 + nt, 1] % 4 == 0)))
+        if ok:
+            out.append(i)
+    return np.asarray(out, dtype=np.int32)
+
+
+def stream_records(ens, terms, conns, rows, n_ctas_max):
+    """Work records and per-CTA record ranges of ``nb2_ensemble_stream``.
+
+    Record layout (32 int32): [0] type (1 = E: a block of neurons, 2 = D: rows of
+    one decoder matrix), [1] ensemble table row, [2] shared-memory slot, [5] number
+    of copies, [6] the count of finished records of the other type in this slot
+    that the record waits for, then per copy 3 ints at 8 + 3q: element index in the
+    signal buffer, bytes, float offset in the stage.  E: [3] first neuron, [4]
+    neurons, [7] connection table row of the PES connection or -1; copies = encoder
+    rows of every term, bias, voltage, refractory time [, PES activity trace].
+    D: [3] connection table row, [4] first row, [7] rows; one copy.
+    Ensembles are dealt to CTAs in contiguous runs balanced by bytes; the records
+    of a CTA are ordered E(0), E(1), D(0), E(2), D(1), ..., D(last).
+    """
+    rows = [int(r) for r in rows]
+    per_ens = []
+    for r in rows:
+        row = ens[r]
+        n, nt, t0, nc, c0 = int(row[0]), int(row[6]), int(row[7]), int(row[8]), int(row[9])
+        ds = [int(terms[t0 + k, 1]) for k in range(nt)]
+        pes_conn = next((c0 + k for k in range(nc) if conns[c0 + k, 6]), -1)
+        per_neuron = sum(ds) + 3 + (1 if pes_conn >= 0 else 0)
+        ne_max = min(STREAM_CHUNK, (STREAM_STAGE_FLOATS // per_neuron) & ~3)
+        n_chunks = -(-n // ne_max)
+        ne_even = (-(-n // n_chunks) + 3) & ~3
+        E, D = [], []
+        for i0 in range(0, n, ne_even):
+            ne = min(ne_even, n - i0)
+            rec = np.zeros(STREAM_REC, dtype=np.int64)
+            rec[0], rec[1], rec[3], rec[4], rec[7] = 1, r, i0, ne, pes_conn
+            copies, off = [], 0
+            for k, d in enumerate(ds):
+                copies.append((int(terms[t0 + k, 0]) + i0 * d, 4 * ne * d, off))
+                off += ne * d
+            vecs = [int(row[5]), int(row[2]), int(row[3])] + ([int(conns[pes_conn, 8])] if pes_conn >= 0 else [])
+            for start in vecs:
+                copies.append((start + i0, 4 * ne, off))
+                off += ne
+            assert off <= STREAM_STAGE_FLOATS and len(copies) <= 8
+            rec[5] = len(copies)
+            for q, cp in enumerate(copies):
+                rec[8 + 3 * q:11 + 3 * q] = cp
+            E.append(rec)
+        nr_max = max(1, min(STREAM_ROWS, STREAM_STAGE_FLOATS // n))
+        for k in range(nc):
+            d_c = int(conns[c0 + k, 1])
+            for r0 in range(0, d_c, nr_max):
+                nr = min(nr_max, d_c - r0)
+                rec = np.zeros(STREAM_REC, dtype=np.int64)
+                rec[0], rec[1], rec[3], rec[4], rec[5], rec[7] = 2, r, c0 + k, r0, 1, nr
+                rec[8:11] = (int(conns[c0 + k, 0]) + r0 * n, 4 * nr * n, 0)
+                D.append(rec)
+        nbytes = 4 * n * (sum(ds) + 5) + sum(4 * int(conns[c0 + k, 1]) * n * (2 if conns[c0 + k, 6] else 1)
+                                              for k in range(nc))
+        per_ens.append((E, D, nbytes))
+    if not per_ens:
+        return np.zeros((0, STREAM_REC), np.int32), np.zeros((0, 2), np.int32)
+    cost = np.array([b for _, _, b in per_ens], dtype=np.float64)
+    n_ctas = int(min(len(per_ens), n_ctas_max))
+    csum = np.cumsum(cost)
+    cut = np.unique(np.concatenate([[0], np.searchsorted(csum, csum[-1] * np.arange(1, n_ctas) / n_ctas) + 1,
+                                    [len(per_ens)]]))
+    cut = cut[cut <= len(per_ens)]
+    blocks, ranges, pos = [], [], 0
+    for a, b in zip(cut[:-1], cut[1:]):
+        mine = per_ens[a:b]
+        e_cum = [0] * STREAM_SLOTS
+        d_cum = [0] * STREAM_SLOTS
+        seq = []
+        for g, (E, D, _) in enumerate(mine):
+            slot = g % STREAM_SLOTS
+            for rec in E:
+                rec[2], rec[6] = slot, d_cum[slot]  # the slot's previous ensemble must be decoded
+            e_cum[slot] += len(E)
+            for rec in D:
+                rec[2], rec[6] = slot, e_cum[slot]  # all spikes of this ensemble must be there
+            d_cum[slot] += len(D)
+        for g, (E, D, _) in enumerate(mine):  # E(g) goes before D(g - 1)
+            seq.extend(E)
+            if g > 0:
+                seq.extend(mine[g - 1][1])
+        seq.extend(mine[-1][1])
+        block = np.asarray(seq, dtype=np.int64).reshape(-1, STREAM_REC)
+        blocks.append(block)
+        ranges.append((pos, pos + len(block)))
+        pos += len(block)
+    records = np.concatenate(blocks, axis=0)
+    assert records.max() < 2 ** 31
+    return records.astype(np.int32), np.asarray(ranges, dtype=np.int32)
+
+
 def plan_fused_ensembles(sim, ops):
     (fused,) = ops
     members = fused.members
     queue = sim.queue
     ens, terms, conns = fused_tables(sim, members)
     n_all = np.array([mem["n"] for mem in members])
-    small = np.flatnonzero(n_all <= SMALL_NEURONS // 2).astype(np.int32)
-    large = np.flatnonzero(n_all > SMALL_NEURONS // 2).astype(np.int32)
+    streamed = streamable(ens, terms, conns) if getattr(sim, "stream_ensembles", True) else np.zeros(0, np.int32)
+    rest = np.setdiff1d(np.arange(len(members)), streamed)
+    small = rest[n_all[rest] <= SMALL_NEURONS // 2].astype(np.int32)
+    large = rest[n_all[rest] > SMALL_NEURONS // 2].astype(np.int32)
+    n_ctas_max = getattr(queue.device, "sm_count", 148)
+    records, ranges = stream_records(ens, terms, conns, streamed, n_ctas_max)
+    d_records = to_device(queue, records) if len(records) else None
+    d_ranges = to_device(queue, ranges) if len(ranges) else None
+    status = zeros(queue, (1,), np.int32)
     d_ens, d_terms, d_conns = to_device(queue, ens), to_device(queue, terms), to_device(queue, conns)
     if len(terms) == 0:
         d_terms = to_device(queue, np.zeros((1, 4), np.int32))
@@ -321,17 +445,26 @@ def plan_fused_ensembles(sim, ops):
     d_large = to_device(queue, large) if len(large) else None
     data = sim.all_data.cl_buf
     fn, check, dt = _capi.lib().nb2_ensemble_step, _capi.check, float(sim.model.dt)
+    fn_stream = _capi.lib().nb2_ensemble_stream
     p = lambda a: None if a is None else a.ptr
     args = (len(large), p(d_large), len(small), p(d_small), d_ens.ptr, d_terms.ptr, d_conns.ptr, data.ptr, dt)
+    stream_args = (p(d_records), len(records), p(d_ranges), len(ranges), d_ens.ptr, d_terms.ptr, d_conns.ptr,
+                   data.ptr, dt, status.ptr)
+    n_rest, n_streamed = len(large) + len(small), len(streamed)
 
     def launch(stream):
-        check(fn(stream, *args))
+        if n_streamed:
+            check(fn_stream(stream, *stream_args))
+        if n_rest:
+            check(fn(stream, *args))
 
     plan = Plan(queue, launch, (256, max(len(large), 1) + (len(small) + 7) // 8), lsize=(256, 1),
-                n_launches=int(len(large) > 0) + int(len(small) > 0), name="fused_ensemble_step",
-                tag="%d ensembles" % len(members))
-    plan.full_args = (d_ens, d_terms, d_conns, d_small, d_large, data)
-    plan.tables = dict(ens=ens, terms=terms, conns=conns, small=small, large=large)
+                n_launches=int(len(large) > 0) + int(len(small) > 0) + int(n_streamed > 0),
+                name="fused_ensemble_step", tag="%d ensembles" % len(members))
+    plan.full_args = (d_ens, d_terms, d_conns, d_small, d_large, d_records, d_ranges, status, data)
+    plan.tables = dict(ens=ens, terms=terms, conns=conns, small=small, large=large, streamed=streamed,
+                       records=records, ranges=ranges)
+    plan.status = status
     plan.bw_per_call = fused_bytes_per_step(members)
     n_neurons = int(n_all.sum())
     plan.flops_per_call = sum(2 * mem["n"] * sum(A.shape[1] for A, _ in mem["enc_terms"])

@@ -262,3 +262,82 @@ def test_pipe_records_cover_the_product(case):
         else:
             assert np.allclose(got[lo:lo + len(vals[i])], vals[i], rtol=1e-6, atol=1e-6)
     assert len(ranges) <= 444
+
+
+def test_stream_records_cover_every_ensemble_once():
+    """Work records of the streamed fused kernel: every neuron is in exactly one E
+    record and every decoder row in exactly one D record, copies are 16-byte
+    aligned and fit a stage, and in list order no record waits for a later one."""
+    from nengo_ocl_b200 import fusion
+
+    rng = np.random.RandomState(0)
+    ens, terms, conns, pos = [], [], [], 0
+
+    def alloc(n):
+        nonlocal pos
+        start = pos
+        pos += (n + 3) // 4 * 4
+        return start
+
+    for n, ds, dcs in [(1024, [16], [(16, True)]), (512, [8, 4], [(3, False), (16, True)]), (260, [], [(5, False)]),
+                       (1024, [16], []), (300, [12], [(2, True)])] * 3 + [(200, [4], [(1, False)]),
+                                                                          (1024, [16, 16, 16, 16, 4], [(1, False)])]:
+        row = [n, -1, alloc(n), alloc(n), alloc(n) if rng.rand() < 0.5 else -1, alloc(n), len(ds), len(terms), len(dcs),
+               len(conns), 0, 0, 0, 1, 0, 0]
+        for d in ds:
+            terms.append([alloc(n * d), d, alloc(d), 1])
+        for d_c, pes in dcs:
+            conns.append([alloc(d_c * n), d_c, alloc(d_c), alloc(d_c), 0, 0, int(pes), alloc(d_c), alloc(n), 0, 0, 0,
+                          0, 0, 0, 0])
+        ens.append(row)
+    ens = np.asarray(ens, np.int32)
+    terms = np.asarray(terms, np.int32).reshape(-1, 4)
+    conns = np.asarray(conns, np.int32).reshape(-1, 16)
+    rows = fusion.streamable(ens, terms, conns)
+    assert set(rows) == set(range(15))  # not the 200-neuron one, not the one with five encoder terms
+    records, ranges = fusion.stream_records(ens, terms, conns, rows, n_ctas_max=4)
+    assert records.shape[1] == 32 and ranges[0, 0] == 0 and ranges[-1, 1] == len(records) and len(ranges) <= 4
+    neurons = {int(r): np.zeros(ens[r, 0], int) for r in rows}
+    dec_rows = {}
+    seen_ens = set()
+    for b, e in ranges:
+        e_done = [0] * fusion.STREAM_SLOTS
+        d_done = [0] * fusion.STREAM_SLOTS
+        mine = set()
+        for rec in records[b:e]:
+            kind, r, slot, ncopy, target = int(rec[0]), int(rec[1]), int(rec[2]), int(rec[5]), int(rec[6])
+            mine.add(r)
+            used = np.zeros(fusion.STREAM_STAGE_FLOATS, bool)
+            for q in range(ncopy):
+                idx, nbytes, off = (int(v) for v in rec[8 + 3 * q:11 + 3 * q])
+                assert idx % 4 == 0 and nbytes % 16 == 0 and nbytes > 0 and off % 4 == 0
+                assert off + nbytes // 4 <= fusion.STREAM_STAGE_FLOATS and not used[off:off + nbytes // 4].any()
+                assert idx + nbytes // 4 <= pos
+                used[off:off + nbytes // 4] = True
+            n = int(ens[r, 0])
+            if kind == 1:
+                assert d_done[slot] >= target, "an E record would wait for a later D record"
+                i0, ne = int(rec[3]), int(rec[4])
+                assert 0 < ne <= 128 and ne % 4 == 0 and i0 + ne <= n
+                neurons[r][i0:i0 + ne] += 1
+                nt, t0 = int(ens[r, 6]), int(ens[r, 7])
+                assert ncopy == nt + 3 + (rec[7] >= 0)
+                for k in range(nt):
+                    assert rec[8 + 3 * k] == terms[t0 + k, 0] + i0 * terms[t0 + k, 1]
+                assert rec[8 + 3 * nt] == ens[r, 5] + i0 and rec[8 + 3 * (nt + 1)] == ens[r, 2] + i0
+                if rec[7] >= 0:
+                    assert conns[rec[7], 6] == 1 and rec[8 + 3 * (nt + 3)] == conns[rec[7], 8] + i0
+                e_done[slot] += 1
+            else:
+                assert kind == 2 and e_done[slot] >= target, "a D record would wait for a later E record"
+                c, r0, nr = int(rec[3]), int(rec[4]), int(rec[7])
+                assert int(ens[r, 9]) <= c < int(ens[r, 9]) + int(ens[r, 8]) and 0 < nr <= 4 and nr * n <= 4096
+                dec_rows.setdefault(c, np.zeros(conns[c, 1], int))[r0:r0 + nr] += 1
+                assert rec[8] == conns[c, 0] + r0 * n and rec[9] == 4 * nr * n
+                d_done[slot] += 1
+        assert not (mine & seen_ens), "an ensemble belongs to one CTA"
+        seen_ens |= mine
+    assert all((v == 1).all() for v in neurons.values())
+    for r in rows:
+        for c in range(int(ens[r, 9]), int(ens[r, 9]) + int(ens[r, 8])):
+            assert (dec_rows[c] == 1).all()
