@@ -4,7 +4,7 @@
 // listed there), organised as a bulk-copy pipeline so that every SM always has
 // about 200 KB of loads in flight.
 //
-//  * The host cuts every ensemble into work records: E records (up to 128
+//  * The host cuts every ensemble into work records: E records (up to 192
 //    neurons: their encoder rows, bias, voltage, refractory time and PES
 //    activity trace) and D records (up to 4 rows of one decoder matrix).  A CTA
 //    (one per SM, persistent) owns a list of whole ensembles; its records are
@@ -171,20 +171,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       const int* terms = p.term_table + (size_t)__ldg(e + E_TERM0) * T_STRIDE;
       const float tau = bits(__ldg(e + E_TAU)), ref = bits(__ldg(e + E_REF)), amp = bits(__ldg(e + E_AMP));
       const int eV = __ldg(e + E_V), eW = __ldg(e + E_W), eS = __ldg(e + E_S);
-      float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
-      int roff[ST_ROWS];
-#pragma unroll
-      for (int j = 0; j < ST_ROWS; ++j) roff[j] = min(lane + 32 * j, ne - 1);
-      const int NR = (ne + 31) >> 5;
-      int xoff = 0;
-      for (int k = 0; k < n_terms; ++k) {
-        const int d = __ldg(terms + k * T_STRIDE + T_D);
-        const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
-        if (NR == 1) pipe_segment_mode<1>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
-        else if (NR == 2) pipe_segment_mode<2>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
-        else pipe_segment_mode<4>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
-        xoff += d;
-      }
       const float* s_bias = st.buf + rec[R_COPY0 + 3 * n_terms + 2];
       const float* s_V = st.buf + rec[R_COPY0 + 3 * (n_terms + 1) + 2];
       const float* s_W = st.buf + rec[R_COPY0 + 3 * (n_terms + 2) + 2];
@@ -199,11 +185,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       }
       // the slot's previous ensemble must have been decoded completely
       ok = stream_wait_count(&d_done[h0.z], h1.z, &s_abort, lane);
-      if (ok) {
+      // blocks of 128 neurons: 4 per lane
+      for (int base = 0; ok && base < ne; base += 32 * ST_ROWS) {
+        const int nb = min(32 * ST_ROWS, ne - base);
+        float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int roff[ST_ROWS];
+#pragma unroll
+        for (int j = 0; j < ST_ROWS; ++j) roff[j] = base + min(lane + 32 * j, nb - 1);
+        const int NR = (nb + 31) >> 5;
+        int xoff = 0;
+        for (int k = 0; k < n_terms; ++k) {
+          const int d = __ldg(terms + k * T_STRIDE + T_D);
+          const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
+          if (NR == 1) pipe_segment_mode<1>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+          else if (NR == 2) pipe_segment_mode<2>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+          else pipe_segment_mode<4>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+          xoff += d;
+        }
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
-          const int r = lane + 32 * j;
-          if (r < ne) {
+          const int r = base + lane + 32 * j;
+          if (lane + 32 * j < nb) {
             const float J = s_bias[r] + acc[j];
             float v = s_V[r], w = s_W[r];
             const float s = fused_lif(J, v, w, tau, ref, amp, p.dt, p.dt_inv);
@@ -218,6 +220,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
             }
           }
         }
+      }
+      if (ok) {
         __syncwarp();
         if (lane == 0) {
           __threadfence_block();

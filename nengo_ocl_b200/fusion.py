@@ -312,7 +312,7 @@ STREAM_SLOTS = _STREAM["NB2_STREAM_SLOTS"]
 STREAM_MAX_NEURONS = _STREAM["NB2_STREAM_MAX_NEURONS"]
 STREAM_MAX_INPUT = _STREAM["NB2_STREAM_MAX_INPUT"]
 STREAM_MIN_NEURONS = 256
-STREAM_REC, STREAM_ROWS, STREAM_CHUNK = 32, 4, 128
+STREAM_REC, STREAM_ROWS, STREAM_CHUNK = 32, 4, 192
 
 
 def streamable(ens, terms, conns):

@@ -318,7 +318,7 @@ def test_stream_records_cover_every_ensemble_once():
             if kind == 1:
                 assert d_done[slot] >= target, "an E record would wait for a later D record"
                 i0, ne = int(rec[3]), int(rec[4])
-                assert 0 < ne <= 128 and ne % 4 == 0 and i0 + ne <= n
+                assert 0 < ne <= 192 and ne % 4 == 0 and i0 + ne <= n
                 neurons[r][i0:i0 + ne] += 1
                 nt, t0 = int(ens[r, 6]), int(ens[r, 7])
                 assert ncopy == nt + 3 + (rec[7] >= 0)
