@@ -39,9 +39,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FULL = dict(n_ensembles=4096, n_neurons=1024, dimensions=16)
-# dram__bytes_read.sum + dram__bytes_write.sum of one nb2_ensemble_step_kernel launch on 1024 ensembles
+# dram__bytes_read.sum + dram__bytes_write.sum of one nb2_ensemble_stream_kernel launch on 1024 ensembles
 # (profiles/fused_ensemble_step_pes_model.md), per ensemble
-NCU_DRAM_BYTES_PER_ENSEMBLE = (126.66e6 + 32.0e6) / 1024
+NCU_DRAM_BYTES_PER_ENSEMBLE = (128.93e6 + 28.14e6) / 1024
 WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
 
 
@@ -348,7 +348,10 @@ def main():
     fused_ms = float(np.mean(times))
     peak, peak_src = measured_peak_gbs()
     achieved = fused_plan.bw_per_call / fused_ms / 1e6
-    roofline = {"bound": "hbm", "kernel": "nb2_ensemble_step_kernel", "achieved": achieved, "peak": peak,
+    streamed = len(fused_plan.tables["streamed"])
+    roofline = {"bound": "hbm",
+                "kernel": "nb2_ensemble_stream_kernel" if streamed else "nb2_ensemble_step_kernel",
+                "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": int(NCU_DRAM_BYTES_PER_ENSEMBLE * args.ensembles),
                 "traffic_note": "dram read+write of the 1024-ensemble ncu capture scaled by ensemble count; lower "
