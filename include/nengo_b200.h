@@ -232,10 +232,12 @@ int nb2_ensemble_step(void* stream, int n_large, const int* large_ids, int n_sma
  * NB2_STREAM_MAX_INPUT and at most one PES connection may be streamed.
  * `status` (may be NULL) receives NB2_ERR_TIMEOUT if a bounded wait gave up. */
 #ifndef NB2_STREAM_STAGE_FLOATS
-#define NB2_STREAM_STAGE_FLOATS 4096 /* floats of one stage */
-#define NB2_STREAM_WARPS 12          /* warps per CTA, one stage each */
+#define NB2_STREAM_STAGE_FLOATS 2048 /* floats of one stage */
+#define NB2_STREAM_WARPS 20          /* warps per CTA, one stage each */
 #endif
-#define NB2_STREAM_SLOTS 3           /* ensembles in flight per CTA (spikes + PES trace in shared memory) */
+#ifndef NB2_STREAM_SLOTS
+#define NB2_STREAM_SLOTS 3 /* ensembles in flight per CTA (spikes + PES trace in shared memory) */
+#endif
 #define NB2_STREAM_MAX_NEURONS 1024
 #define NB2_STREAM_MAX_INPUT 64
 int nb2_ensemble_stream(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,

@@ -4,9 +4,10 @@
 // listed there), organised as a bulk-copy pipeline so that every SM always has
 // about 200 KB of loads in flight.
 //
-//  * The host cuts every ensemble into work records: E records (up to 192
+//  * The host cuts every ensemble into work records: E records (a block of
 //    neurons: their encoder rows, bias, voltage, refractory time and PES
-//    activity trace) and D records (up to 4 rows of one decoder matrix).  A CTA
+//    activity trace) and D records (a few rows of one decoder matrix), each
+//    at most one stage (8 KB) of data.  A CTA
 //    (one per SM, persistent) owns a list of whole ensembles; its records are
 //    ordered E(0), E(1), D(0), E(2), D(1), ... so that the spikes a D record
 //    needs were produced a round earlier.
