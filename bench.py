@@ -296,7 +296,8 @@ def main():
         from nengo_ocl_b200.exchange import TorchComm
 
         exchange = (mdl.info["exchange"], TorchComm())
-    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True, exchange=exchange)
+    # probes are drained (and the next window of the error tables uploaded) every 256 steps
+    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True, exchange=exchange, n_prealloc_probes=256)
     build_s = time.perf_counter() - t_build
     plans = sim._plans
     fused = [p for p in plans if p.name == "fused_ensemble_step"]
@@ -378,7 +379,7 @@ def main():
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "ensembles_per_gpu": args.ensembles, "neurons_per_gpu": n_neurons,
                    "l2": "working set per step (~0.9 GB) exceeds the 126 MB L2", "build_s": round(build_s, 1),
-                   "plans_per_step": len(plans), "graph_unroll": plans.unroll,
+                   "plans_per_step": len(plans), "graph_unroll": plans.unroll, "steps_per_probe_drain": B,
                    "parallelism": "ensemble blocks, 1 rank per GPU, per-step peer push of decoded signals"
                                   if world > 1 else "single GPU",
                    "exchange_bytes_per_step_per_gpu": 4 * mdl.info["segment"][1] * (world - 1)},

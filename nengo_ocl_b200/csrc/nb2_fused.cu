@@ -172,6 +172,47 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
   const int n_conn = active ? e[E_NCONN] : 0;
   for (int ci = 0; ci < n_conn; ++ci) {
     const int* c = conn_table + (size_t)(e[E_CONN0] + ci) * C_STRIDE;
+    // A run of single-row connections without PES (e.g. scalar edges of a recurrent graph):
+    // decode up to FUSED_RCH of them in one pass, one row each, instead of one pass per connection.
+    int run = 0;
+    while (ci + run < n_conn && run < FUSED_RCH && c[run * C_STRIDE + C_D] == 1 && c[run * C_STRIDE + C_PES] == 0)
+      ++run;
+    if (run >= 2) {
+      float acc[FUSED_RCH];
+      int woff[FUSED_RCH];
+#pragma unroll
+      for (int r = 0; r < FUSED_RCH; ++r) {
+        acc[r] = 0.0f;
+        woff[r] = c[(r < run ? r : 0) * C_STRIDE + C_W];
+      }
+      for (int i = t; i < n; i += TPE) {
+        const float s = s_spk[grp][i];
+#pragma unroll
+        for (int r = 0; r < FUSED_RCH; ++r)
+          if (r < run) acc[r] = fmaf(data[woff[r] + i], s, acc[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < FUSED_RCH; ++r) {
+        float v = acc[r];
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) s_red[grp][wig][r] = v;
+      }
+      group_sync();
+      if (t < run) {
+        const int* cr = c + t * C_STRIDE;
+        float total = 0.0f;
+        for (int w = 0; w < WARPS; ++w) total += s_red[grp][w][t];
+        data[cr[C_WEIGHTED]] = total;
+        if (cr[C_FILT] >= 0) {
+          float* y = data + cr[C_FILT];
+          if (cr[C_A0] == 0) *y = bits(cr[C_B0]) * total;
+          else *y = bits(cr[C_B0]) * total - bits(cr[C_A0]) * *y;
+        }
+      }
+      group_sync();
+      ci += run - 1;
+      continue;
+    }
     const int d_c = active ? c[C_D] : 0;
     float* Wd = data + c[C_W];
     const bool pes = active && c[C_PES] != 0;
