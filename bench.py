@@ -67,10 +67,13 @@ class ClockSampler:
         self.t_first = None
 
     def __enter__(self):
+        if self.device is None:  # only rank 0 samples: many pollers slow the driver down
+            self.t_first = time.perf_counter()
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
             t0 = time.perf_counter()  # the tool takes a moment to start: wait for its first sample
@@ -191,6 +194,38 @@ def gemv_microbench(queue, capi, reps=20, n_outputs=4096):
             "status": int(plan.status.get()[0])}
 
 
+def spmv_microbench(queue, capi, n=1 << 20, fan_out=64, reps=10):
+    """Sparse neuron-to-neuron transform of the reference's own Watts-Strogatz benchmark
+    (examples/benchmark_wattsstrogatz.py): y = A x with about fan_out nonzeros per row,
+    CSR and ELLPACK, bytes as the reference accounts them (clra_gemv.py:1553-1563)."""
+    from nengo_ocl_b200 import cura_spmv, synth
+    from nengo_ocl_b200.curaggedarray import CUDARaggedArray
+    from nengo_ocl_b200.raggedarray import RaggedArray
+
+    rng = np.random.RandomState(2)
+    hA = cura_spmv.HostSparseMatrix(synth.watts_strogatz_adjacency(n, fan_out, 0.1, rng))
+    X = CUDARaggedArray(queue, RaggedArray([rng.normal(size=(n, 1))], dtype=np.float32))
+    Y = CUDARaggedArray(queue, RaggedArray([np.zeros((n, 1))], dtype=np.float32))
+    out = {"workload": "Watts-Strogatz adjacency %d x %d, %d nonzeros" % (n, n, hA.csr.nnz)}
+    ev = Events(capi)
+    for algorithm in ("CSR", "ELLPACK"):
+        prog = cura_spmv.plan_sparse_dot_inc(queue, hA, X, Y, inc=False, algorithm=algorithm)
+        plan = prog.plans[0]
+        for _ in range(3):
+            plan()
+        times, batch = [], 5  # back-to-back calls; the matrix (>= 0.5 GB) is far larger than L2
+        for _ in range(reps):
+            ev.start(queue.stream)
+            for _ in range(batch):
+                plan.kern(queue.stream)
+            times.append(ev.stop_ms(queue.stream) / batch)
+        ms = float(np.median(times))
+        out[algorithm.lower()] = {"bytes_per_call": int(plan.bw_per_call), "ms_per_call": ms,
+                                  "achieved_gbs": plan.bw_per_call / ms / 1e6, "kernel": plan.name}
+        del prog, plan
+    return out
+
+
 def small_model_rates(ctx, capi, which=("c1", "c3", "c4")):
     """Configurations 1, 3 and 4 (L2-resident models): simulated steps/s through the public
     API (``run_steps``: graph replay + probe drains), timed after a 10-step warm-up as the
@@ -236,6 +271,8 @@ def main():
     ap.add_argument("--gemv-outputs", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-small", action="store_true", help="skip the steps/s of configurations 1, 3 and 4")
+    ap.add_argument("--no-spmv", action="store_true", help="skip the sparse-transform microbenchmark")
+    ap.add_argument("--spmv-only", action="store_true", help="run only the sparse-transform microbenchmark")
     ap.add_argument("--small-only", default=None, help="run only these small configurations, e.g. c3,c4 (for profiling)")
     args = ap.parse_args()
 
@@ -276,6 +313,15 @@ def main():
     if args.small_only:
         print(json.dumps({"small_models": small_model_rates(ctx, _capi, tuple(args.small_only.split(",")))}), flush=True)
         return
+    if args.spmv_only:
+        from nengo_ocl_b200.runtime import CommandQueue
+
+        peak, _ = measured_peak_gbs()
+        out = spmv_microbench(CommandQueue(ctx), _capi)
+        for k in ("csr", "ellpack"):
+            out[k]["frac"] = out[k]["achieved_gbs"] / peak
+        print(json.dumps({"spmv": out}), flush=True)
+        return
     if args.gemv_only:
         from nengo_ocl_b200.runtime import CommandQueue
 
@@ -315,7 +361,7 @@ def main():
         pass
     barrier()
     _capi.call("nb2_device_sync")
-    clocks = ClockSampler(local_rank)
+    clocks = ClockSampler(local_rank if rank == 0 else None)
     clocks.__enter__()
     done, total_ms = 0, 0.0
     while done < K:
@@ -389,6 +435,10 @@ def main():
     if rank == 0 and not args.no_gemv:
         line["gemv"] = gemv_microbench(queue, _capi)
         line["gemv"]["frac"] = line["gemv"]["achieved_gbs"] / peak
+    if rank == 0 and not args.no_spmv and world == 1:
+        line["spmv"] = spmv_microbench(queue, _capi)
+        for k in ("csr", "ellpack"):
+            line["spmv"][k]["frac"] = line["spmv"][k]["achieved_gbs"] / peak
     if rank == 0 and not args.no_small and world == 1:
         line["small_models"] = small_model_rates(ctx, _capi)
     if rank == 0 and not args.no_cpu and world == 1:

@@ -112,6 +112,18 @@ int nb2_gemv_pipelined(void* stream, const int* records, int n_records, const in
                        double beta, double gamma, const float* alphas, const float* betas,
                        const float* gammas, int* status);
 
+/* ---- sparse transforms (clra_gemv.py:1242-1997) ---------------------------
+ * y (+)= A x for one sparse matrix; x and y are contiguous vectors.
+ * nb2_spmv_csr: spmv_csr_impl :1570-1646; `lanes_log2` (0..5) lanes share a row.
+ * nb2_spmv_ell: spmv_ellpack_impl :1649-1755 and spmv_ellpacktwostep_impl
+ * :1758-1916 (no scratch buffer, one launch); `rowlens` bounds every row;
+ * `row_major` = 1: entry (row, k) at row * width + k (one warp per row),
+ * 0: at k * n_rows + row (one thread per row, for narrow matrices). */
+int nb2_spmv_csr(void* stream, const int* indices, const int* indptr, const float* data, int n_rows,
+                 int lanes_log2, const float* x, float* y, int inc);
+int nb2_spmv_ell(void* stream, const int* columns, const float* entries, const int* rowlens, int n_rows,
+                 int width, int row_major, const float* x, float* y, int inc);
+
 /* ---- elementwise family (clra_nonlinearities.py) -------------------------
  * All index tables have the layout the reference's plan functions upload. */
 /* plan_timeupdate :113-144 */

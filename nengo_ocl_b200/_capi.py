@@ -83,6 +83,8 @@ _SIGNATURES = {
     "nb2_probes": [_P, c_int, c_int] + [_P] * 11,
     "nb2_presentinput": [_P, c_int, c_int, _P, c_double] + [_P] * 9,
     "nb2_neurons": [_P, c_int, c_int, c_int, _P, POINTER(nb2_neuron_args)],
+    "nb2_spmv_csr": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int],
+    "nb2_spmv_ell": [_P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int],
     "nb2_ensemble_stream": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, _P],
     "nb2_exchange_wait": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_double],
     "nb2_exchange_push": [_P, _P, _P, _P, _P, c_int, c_int, c_int],

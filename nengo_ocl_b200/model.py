@@ -29,7 +29,15 @@ class Signal:
 
     def __init__(self, initial_value=None, shape=None, name=None, base=None, readonly=False,
                  elemoffset=0, elemstrides=None):
-        if base is None:
+        if base is None and hasattr(initial_value, "tocsr"):
+            # a sparse matrix (scipy.sparse): kept as it is, outside the packed dense store
+            self.sparse = True
+            self._initial_value = initial_value.tocsr()
+            self.shape = tuple(int(v) for v in initial_value.shape)
+            self._base = None
+            self.elemoffset = 0
+            self.elemstrides = (self.shape[1], 1)
+        elif base is None:
             if initial_value is None:
                 initial_value = np.zeros(shape if shape is not None else ())
             initial_value = np.array(initial_value, dtype=np.float64)
@@ -196,6 +204,17 @@ class DotInc(Operator):
 
     def __init__(self, A, X, Y, tag=None):
         super().__init__(tag)
+        self.A, self.X, self.Y = A, X, Y
+        self.incs = [Y]
+        self.reads = [A, X]
+
+
+class SparseDotInc(Operator):
+    """``Y += A . X`` with a sparse matrix signal ``A``"""
+
+    def __init__(self, A, X, Y, tag=None):
+        super().__init__(tag)
+        assert A.sparse and not A.is_view
         self.A, self.X, self.Y = A, X, Y
         self.incs = [Y]
         self.reads = [A, X]

@@ -230,6 +230,12 @@ class Simulator:
         all_signals = stable_unique(sig for op in all_operators for sig in op.all_signals)
         all_signals += [self.model.sig[p]["in"] for p in self.model.probes
                         if self.model.sig[p]["in"] not in set(all_signals)]
+        # sparse signals stay on the host as matrices (reference simulator.py:281-329): each
+        # sparse product uploads its own device form
+        sparse_signals = [s for s in all_signals if getattr(s, "sparse", False)]
+        if any(s.is_view for s in sparse_signals):
+            raise NotImplementedError("Sparse signal views not yet supported")
+        all_signals = [s for s in all_signals if not getattr(s, "sparse", False)]
         all_bases = stable_unique(sig.base for sig in all_signals)
         sigdict = {}
         for op in all_operators:
@@ -237,8 +243,11 @@ class Simulator:
         for base in all_bases:
             if base not in sigdict:
                 sigdict[base] = np.array(base.initial_value, dtype=np.float64)
-        if any(getattr(s, "sparse", False) for s in all_signals):
-            raise NotImplementedError("sparse signals are not supported")
+        self.sparse_data = {}
+        if sparse_signals:
+            from nengo_ocl_b200.cura_spmv import HostSparseMatrix
+
+            self.sparse_data = {s: HostSparseMatrix(s.initial_value) for s in stable_unique(sparse_signals)}
         self.base_reshapes = {}
         dense = []
         for base in all_bases:
@@ -604,6 +613,22 @@ class Simulator:
             Yinds = self.RaggedArray(yinds, dtype=np.int32)
             incs = np.array([op.inc for op in ops], dtype=np.int32)
             plans.append(plan_slicedcopy(self.queue, X, Y, Xinds, Yinds, incs))
+        return plans
+
+    def _plan_SparseDotInc(self, ops):
+        """One plan per sparse product (reference simulator.py:877-892); the algorithm is
+        chosen by ``plan_sparse_dot_inc`` (environment variable ``NENGO_OCL_SPMV_ALGORITHM``
+        or the footprint heuristic).  The product increments its target, as the operator
+        says; the reference plans it in "set" mode, which gives the same values whenever the
+        target was reset in the same step and this is the only product into it."""
+        from nengo_ocl_b200.cura_spmv import plan_sparse_dot_inc
+
+        plans = []
+        for op in ops:
+            A = self.sparse_data[op.A]
+            X = self.all_data[[self.sidx[op.X]]]
+            Y = self.all_data[[self.sidx[op.Y]]]
+            plans += plan_sparse_dot_inc(self.queue, A, X, Y, inc=True, tag=op.tag).plans
         return plans
 
     def _plan_ElementwiseInc(self, ops):

@@ -258,6 +258,46 @@ def watts_strogatz_model(seed=2, n_ensembles=4096, n_neurons=50, k=4, p=0.1, syn
     return nb.model
 
 
+# ---- sparse recurrent population (the reference's own Watts-Strogatz benchmark) ------
+def watts_strogatz_adjacency(n, fan_out, rewire, rng, scale=None):
+    """Sparse (n, n) float32 weights: column j feeds the rows j +- 1 .. fan_out / 2 of
+    a ring; every edge is moved to a random row with probability ``rewire``
+    (duplicates are summed); weights U(-1, 1) * scale."""
+    import scipy.sparse as sp
+
+    half = max(fan_out // 2, 1)
+    offs = np.concatenate([np.arange(-half, 0), np.arange(1, half + 1)])
+    cols = np.repeat(np.arange(n), len(offs))
+    rows = (cols + np.tile(offs, n)) % n
+    moved = rng.uniform(size=rows.size) < rewire
+    rows = np.where(moved, rng.randint(n, size=rows.size), rows)
+    scale = 1.0 / len(offs) if scale is None else scale
+    vals = (rng.uniform(-1, 1, size=rows.size) * scale).astype(np.float32)
+    mat = sp.coo_matrix((vals, (rows, cols)), shape=(n, n)).tocsr()
+    mat.sum_duplicates()
+    return mat
+
+
+def sparse_recurrent_model(seed=9, n_neurons=2000, fan_out=50, rewire=0.1, synapse=0.1, probe_synapse=0.03,
+                           dt=0.001, tau_ref=0.001):
+    """One population with a sparse neuron-to-neuron recurrent connection (the
+    shape of examples/benchmark_wattsstrogatz.py:69-87 of the reference): the
+    spikes go through a sparse matrix, a lowpass synapse and back into the input
+    currents; the filtered spikes are probed."""
+    nb = NetBuilder(dt=dt, seed=seed, label="sparse recurrent")
+    ens = nb.ensemble(n_neurons, 1, label="ens", neuron_type=m.LIF(tau_ref=tau_ref))
+    W = m.Signal(watts_strogatz_adjacency(n_neurons, fan_out, rewire, nb.rng), name="recurrent.weights",
+                 readonly=True)
+    weighted = m.Signal(np.zeros(n_neurons), name="recurrent.weighted")
+    nb.model.add_op(m.Reset(weighted))
+    nb.model.add_op(m.SparseDotInc(W, ens.sig_out, weighted, tag="recurrent.sparse"))
+    filtered = nb.synapse(weighted, synapse, "recurrent")
+    nb.model.add_op(m.Copy(filtered, ens.sig_J, inc=True))
+    probe = nb.probe(ens.sig_out, synapse=probe_synapse, label="ens.neurons")
+    nb.model.info = dict(probes=[probe], ensembles=nb.ensembles, connections=[], weights=W)
+    return nb.model
+
+
 # ---- configuration 3: circular convolution through product ensembles ------------
 def circular_convolution_model(seed=4, dimensions=256, n_neurons=200, synapse=0.005, dt=0.001, n_templates=8):
     """c = a (*) b computed in the Fourier domain by 2-d product ensembles.

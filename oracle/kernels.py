@@ -352,3 +352,41 @@ def sigmoid(J, ref):
     e = np.exp(-J.astype(np.float64)).astype(np.float32)
     mid = f32(1) / (ref * (f32(1) + e))
     return np.where(J < f32(-88), f32(0), np.where(J > f32(15), f32(1) / ref, mid)).astype(np.float32)
+
+
+def spmv_csr(indices, indptr, data, x, y, inc=False):
+    """``sparsedot_inc`` (clra_gemv.py:1591-1617): one row per work-item,
+    ``y[row]`` (zeroed first unless ``inc``) accumulates ``A_data[k] * x[A_indices[k]]``
+    in storage order, every operation rounded to float32.  Returns the new y."""
+    indices, indptr = np.asarray(indices), np.asarray(indptr)
+    data, x = _f(data), _f(x).reshape(-1)
+    out = _f(y).reshape(-1).copy()
+    for row in range(len(indptr) - 1):
+        acc = out[row] if inc else f32(0)
+        for k in range(int(indptr[row]), int(indptr[row + 1])):
+            acc = f32(acc + f32(data[k] * x[indices[k]]))
+        out[row] = acc
+    return out.reshape(np.shape(y))
+
+
+def spmv_ell(columns, entries, x, y, inc=False):
+    """``sparsedot_inc`` in ELLPACK form (clra_gemv.py:1666-1716): every padded
+    entry of a row contributes ``entry * x[column]`` (padding is 0 * x[0]); the
+    work-group reduces the products pairwise, halving the stride each time.
+    Returns the new y."""
+    columns, entries = np.asarray(columns), _f(entries)
+    x = _f(x).reshape(-1)
+    out = _f(y).reshape(-1).copy()
+    n_rows, width = columns.shape
+    wg = 1
+    while wg < max(width, 1):
+        wg *= 2
+    for row in range(n_rows):
+        prod = np.zeros(wg, dtype=np.float32)
+        prod[:width] = entries[row] * x[columns[row]]
+        off = wg // 2
+        while off > 0:
+            prod[:off] = prod[:off] + prod[off:2 * off]
+            off //= 2
+        out[row] = f32(out[row] + prod[0]) if inc else prod[0]
+    return out.reshape(np.shape(y))

@@ -68,7 +68,10 @@ class OracleSimulator:
             for sig in op.all_signals:
                 b = sig.base
                 if b not in self.signals:
-                    self.signals[b] = np.array(b.initial_value, dtype=np.float32, order="C")
+                    if getattr(b, "sparse", False):
+                        self.signals[b] = b.initial_value.astype(np.float32).tocsr()
+                    else:
+                        self.signals[b] = np.array(b.initial_value, dtype=np.float32, order="C")
         for p in model.probes:
             b = model.sig[p]["in"].base
             if b not in self.signals:
@@ -174,6 +177,13 @@ class OracleSimulator:
     def _do__DotGroup(self, op):
         y = self.view(op.Y)
         y[...] = y + self._dot_terms(op.group).reshape(y.shape)
+
+    def _do_SparseDotInc(self, op):
+        # the reference's CSR kernel in increment mode (clra_gemv.py:1591-1617)
+        A = self.signals[op.A]
+        y = self.view(op.Y)
+        y[...] = K.spmv_csr(A.indices, A.indptr, A.data, self.view(op.X).reshape(-1), y.reshape(-1),
+                            inc=True).reshape(y.shape)
 
     def _do_ElementwiseInc(self, op):
         A, X, Y = self.view(op.A), self.view(op.X), self.view(op.Y)

@@ -275,6 +275,56 @@ def main(reference_root, write_fixtures=True):
     kernels["linearfilter/xs"] = np.array(xs_seq)
     kernels["linearfilter/ys"] = np.array(ys_seq)
 
+    # ---------------- sparse transforms: host tables, heuristic, CSR kernel ----------------
+    import scipy.sparse as sp
+
+    HSM = mods["utils"].HostSparseMatrix
+    srng = np.random.RandomState(77)
+    sparse_cases = {
+        "small": sp.random(7, 5, density=0.4, random_state=srng, format="csr", dtype=np.float32),
+        "empty_rows": sp.csr_matrix(np.array([[0, 0, 0], [1.5, 0, -2.0], [0, 0, 0], [0, 3.0, 0]], dtype=np.float32)),
+        "all_zero": sp.csr_matrix((4, 6), dtype=np.float32),
+        "wide_row": sp.vstack([sp.random(1, 300, density=0.9, random_state=srng, dtype=np.float32),
+                               sp.random(40, 300, density=0.02, random_state=srng, dtype=np.float32)]).tocsr(),
+        "banded": sp.diags([srng.normal(size=199), srng.normal(size=200), srng.normal(size=199)], [-1, 0, 1],
+                           format="csr", dtype=np.float32),
+    }
+    for tag, mat in sparse_cases.items():
+        hA = HSM(mat)
+        key = "sparse/" + tag
+        tables[key + "/dense"] = np.asarray(mat.todense(), dtype=np.float32)
+        ell = gemv.plan_ellpack.scipy2elldata(hA)
+        for name in ("columns", "entries", "rowlens"):
+            tables["%s/ell_%s" % (key, name)] = np.asarray(getattr(ell, name))
+        tables[key + "/ell_width_nnz"] = np.array([ell.ellwidth, ell.nnz])
+        csr = gemv.plan_csr.scipy2csrdata(hA)
+        for name in ("indices", "indptr", "data"):
+            tables["%s/csr_%s" % (key, name)] = np.asarray(getattr(csr, name))
+        tables[key + "/heuristic"] = np.array(gemv.spmv_algorithm_heuristic(queue, hA))
+        # the reference's CSR kernel, set and increment mode
+        x = srng.normal(size=(mat.shape[1], 1)).astype(np.float32)
+        y0 = srng.normal(size=(mat.shape[0], 1)).astype(np.float32)
+        kernels[key + "/x"], kernels[key + "/y0"] = x, y0
+        for inc in (False, True):
+            clX, clY = CLRA(queue, ra([x])), CLRA(queue, ra([y0]))
+            plan, _, progs = capture(lambda: gemv.spmv_csr_impl(
+                queue, refstubs.to_device(queue, csr.indices if csr.indices.size else np.zeros(1, np.int32)),
+                refstubs.to_device(queue, csr.indptr),
+                refstubs.to_device(queue, csr.data if csr.data.size else np.zeros(1, np.float32)), clX, clY, inc=inc))
+            refkernels.run_plan(plan, progs[-1], "sparsedot_inc")
+            kernels["%s/y_%s" % (key, "inc" if inc else "set")] = clY.cl_buf._arr.copy()
+    # footprint heuristic on a device with little memory (the three branches)
+    class SmallDevice:
+        global_mem_size = 0
+
+    class SmallQueue:
+        device = SmallDevice()
+
+    big = HSM(sparse_cases["wide_row"])
+    for mem, tag in ((10 ** 3, "hard"), (3 * 10 ** 4, "mid"), (10 ** 9, "soft")):
+        SmallDevice.global_mem_size = mem
+        tables["sparse/heuristic_%s" % tag] = np.array(gemv.spmv_algorithm_heuristic(SmallQueue(), big))
+
     if write_fixtures:
         np.savez_compressed(os.path.join(HERE, "tables.npz"), **tables)
         np.savez_compressed(os.path.join(HERE, "kernels.npz"), **kernels)
