@@ -226,7 +226,7 @@ def spmv_microbench(queue, capi, n=1 << 20, fan_out=64, reps=10):
     return out
 
 
-def small_model_rates(ctx, capi, which=("c1", "c3", "c4")):
+def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse")):
     """Configurations 1, 3 and 4 (L2-resident models): simulated steps/s through the public
     API (``run_steps``: graph replay + probe drains), timed after a 10-step warm-up as the
     reference's benchmark scripts do (examples/benchmark_circconv.py:87-93)."""
@@ -238,6 +238,9 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4")):
                lambda: synth.circular_convolution_model(seed=4), 1000),
         "c4": ("Watts-Strogatz 4096 x 50 LIF, 32768 edges, 1000 steps",
                lambda: synth.watts_strogatz_model(seed=2), 1000),
+        # the reference's own Watts-Strogatz benchmark shape: one population, sparse neuron-to-neuron weights
+        "ws_sparse": ("sparse recurrent population, 204800 LIF, fan-out 50 (10.2 M nonzeros), 1000 steps",
+                      lambda: synth.sparse_recurrent_model(seed=9, n_neurons=204800, fan_out=50), 1000),
     }
     out = {}
     for key in which:

@@ -8,13 +8,14 @@
 // streams of (column, value) pairs read exactly once, i.e. HBM-bound at
 // 8 bytes per nonzero plus the gathered x values (served by L2):
 //
-//  * CSR: 2^k lanes per row (k chosen by the host from the mean row length) so
-//    that a warp's loads of `data` and `indices` are contiguous; partial sums
+//  * CSR: 2^k lanes per row (k chosen by the host from the mean row length:
+//    about 8 nonzeros per lane, several rows per warp) so that a warp's loads
+//    of `data` and `indices` cover whole sectors and many are in flight; partial sums
 //    meet in a shuffle reduction.  No scratch buffer, one launch.
-//  * ELLPACK, narrow (width <= 32): the host stores the padded arrays column-
+//  * ELLPACK, many rows or narrow: the host stores the padded arrays column-
 //    major (entry (row, k) at k * n_rows + row), one thread per row, so every
 //    load instruction of a warp is one contiguous line.
-//  * ELLPACK, wide: row-major as the reference stores it, one warp per row.
+//  * ELLPACK, few wide rows: row-major as the reference stores it, one warp per row.
 //    Row lengths bound every loop, so padding is never read.
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(SPMV_THREADS) nb2_spmv_csr_kernel(const int* _
   float sum = 0.0f;
   if (row < n_rows) {
     const int end = __ldg(indptr + row + 1);
+#pragma unroll 8
     for (int k = __ldg(indptr + row) + g; k < end; k += G)
       sum = fmaf(__ldcs(data + k), __ldg(x + __ldcs(indices + k)), sum);
   }
@@ -50,7 +52,7 @@ __global__ void __launch_bounds__(SPMV_THREADS) nb2_spmv_ell_cm_kernel(const int
   if (row >= n_rows) return;
   const int len = __ldg(rowlens + row);
   float sum = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
   for (int k = 0; k < len; ++k) {
     const size_t at = (size_t)k * n_rows + row;
     sum = fmaf(__ldcs(entries + at), __ldg(x + __ldcs(columns + at)), sum);

@@ -30,7 +30,8 @@ except ImportError:  # pragma: no cover
 ell_matdata = namedtuple("ell_matdata", ["columns", "entries", "rowlens", "ellwidth", "nnz", "shape"])
 csr_matdata = namedtuple("csr_matdata", ["indices", "indptr", "data", "nnz", "shape"])
 
-ELL_COLUMN_MAJOR_WIDTH = 32  # widest matrix stored column-major on the device
+ELL_COLUMN_MAJOR_WIDTH = 32  # widest matrix with few rows that is stored column-major on the device
+ELL_COLUMN_MAJOR_ROWS = 4096  # from this many rows on, one thread per row fills the GPU at any width
 
 
 class HostSparseMatrix:
@@ -96,8 +97,10 @@ class spmv_prog:
         assert self.X.dtype == self.Y.dtype == np.float32
 
     def _xy(self):
-        x = self.X.cl_buf.ptr + 4 * int(self.X.starts[0])
-        y = self.Y.cl_buf.ptr + 4 * int(self.Y.starts[0])
+        import ctypes
+
+        x = ctypes.c_void_p(self.X.cl_buf.data + 4 * int(self.X.starts[0]))
+        y = ctypes.c_void_p(self.Y.cl_buf.data + 4 * int(self.Y.starts[0]))
         return x, y
 
 
@@ -137,7 +140,7 @@ class plan_ellpack(spmv_prog):
 
     def to_device(self):
         h = self.hAstruct
-        self.row_major = h.columns.shape[1] > ELL_COLUMN_MAJOR_WIDTH
+        self.row_major = h.columns.shape[1] > ELL_COLUMN_MAJOR_WIDTH and h.shape[0] < ELL_COLUMN_MAJOR_ROWS
         lay = (lambda a: np.ascontiguousarray(a)) if self.row_major else (lambda a: np.ascontiguousarray(a.T))
         self.dAstruct = ell_matdata(to_device(self.queue, lay(h.columns)), to_device(self.queue, lay(h.entries)),
                                     to_device(self.queue, h.rowlens), h.ellwidth, h.nnz, h.shape)
@@ -225,9 +228,10 @@ class plan_csr(spmv_prog):
 
     @staticmethod
     def lanes_log2(nnz, n_rows):
-        """Lanes that share a row: the power of two nearest below the mean row length (at most 32)."""
+        """Lanes that share a row: about 8 nonzeros per lane, so that a warp works on several
+        rows at once and every lane has several independent loads in flight (at most 32 lanes)."""
         mean = nnz / max(n_rows, 1)
-        return int(np.clip(np.floor(np.log2(max(mean, 1.0))), 0, 5))
+        return int(np.clip(np.floor(np.log2(max(mean / 8.0, 1.0))), 0, 5))
 
     def choose_plans(self):
         d, h = self.dAstruct, self.hAstruct

@@ -167,7 +167,8 @@ class Operator:
         for sig in self.all_signals:
             base = sig.base
             if base not in signals:
-                signals[base] = np.array(base.initial_value, dtype=np.float64)
+                signals[base] = (base.initial_value if base.sparse
+                                 else np.array(base.initial_value, dtype=np.float64))
 
     def __repr__(self):
         return "<%s%s at 0x%x>" % (type(self).__name__, " %s" % self.tag if self.tag else "", id(self))

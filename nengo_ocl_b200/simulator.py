@@ -378,6 +378,8 @@ class Simulator:
                 return len(sim.all_bases)
 
             def __getitem__(_, item):
+                if getattr(item, "sparse", False):  # kept on the host, constant
+                    return sim.sparse_data[item].matrix
                 raw = sim.all_data[sim.sidx[item]]
                 if item.ndim == 0:
                     return raw[0, 0]

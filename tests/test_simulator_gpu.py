@@ -39,7 +39,7 @@ def state_signals(model):
     sigs = []
     for op in model.operators:
         for s in op.all_signals:
-            if s.base not in sigs:
+            if s.base not in sigs and not s.base.sparse:  # (sparse matrices are constants on the host)
                 sigs.append(s.base)
     return sigs
 
