@@ -360,8 +360,6 @@ def main():
     plans.call_n_times(min(W, sim._max_steps_between_probes))
     sim._probe()
     B = sim._max_steps_between_probes
-    for st in sim._input_streams:  # make the whole window resident for the device-only timing
-        pass
     barrier()
     _capi.call("nb2_device_sync")
     clocks = ClockSampler(local_rank if rank == 0 else None)

@@ -187,7 +187,7 @@ class CUDARaggedArray:
 
     def __setitem__(self, item, new_value):
         if isinstance(item, slice) or is_iterable(item):
-            raise NotImplementedError("TODO")
+            raise NotImplementedError("assigning to several items at once is not supported")
         item = int(item)
         m, n = int(self.shape0s[item]), int(self.shape1s[item])
         sm, sn = int(self.stride0s[item]), int(self.stride1s[item])

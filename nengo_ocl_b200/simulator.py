@@ -305,6 +305,7 @@ class Simulator:
             wait, push = self._exchange.plans()
             plans = wait + plans + push
         self._plans = Plans(plans, self.profiling, unroll=graph_unroll)
+        self._status_plans = [p for p in plans if getattr(p, "status", None) is not None]
         self.rng = None
         self._n_steps = 0
         self._time = 0.0
@@ -501,6 +502,9 @@ class Simulator:
             self._upload_inputs(B)
             self._plans.call_n_times(B)
             self._probe()
+            for plan in self._status_plans:  # bounded waits inside the pipelined kernels
+                if int(plan.status.get()[0]) != 0:
+                    raise RuntimeError("kernel %s gave up a bounded wait (NB2_ERR_TIMEOUT)" % plan.name)
             if self._exchange is not None and self._exchange.status() != 0:
                 raise RuntimeError("multi-GPU exchange: a peer did not publish its step within %.1f s"
                                    % self._exchange.timeout_s)
