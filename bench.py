@@ -369,6 +369,7 @@ def main():
         b = min(B, K - done)
         sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
         _capi.call("nb2_stream_sync", queue.stream)
+        barrier()                  # (a rank that starts early would time its wait for the others' uploads)
         ev.start(queue.stream)
         plans.enqueue_n_times(b)
         total_ms += ev.stop_ms(queue.stream)

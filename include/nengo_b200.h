@@ -252,9 +252,25 @@ int nb2_ensemble_step(void* stream, int n_large, const int* large_ids, int n_sma
 #endif
 #define NB2_STREAM_MAX_NEURONS 1024
 #define NB2_STREAM_MAX_INPUT 64
+/* Optional push of the step's decoded values to the other GPUs, folded into
+ * nb2_ensemble_stream (the counterpart of nb2_exchange_push): CTA b stores the
+ * run cta_runs[b] = {first element in the signal buffer, length} (its share of
+ * this rank's segment [x_lo, x_hi) of the exchange signal, which starts at
+ * element x_base and has world * seg floats) into every peer's staging buffer
+ * when it is done; the last CTA publishes the step in the peers' flag words.
+ * `peer_staging`, `peer_flags`: device arrays of `world` pointers; `ctl`: the
+ * control block shared with nb2_exchange_wait. */
+typedef struct nb2_exchange_desc {
+  float* const* peer_staging;
+  int* const* peer_flags;
+  int* ctl;
+  const int* cta_runs; /* n_ctas x 2 */
+  int x_base, x_lo, x_hi;
+  int rank, world, seg;
+} nb2_exchange_desc;
 int nb2_ensemble_stream(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
                         const int* ens_table, const int* term_table, const int* conn_table, float* data,
-                        double dt, int* status);
+                        double dt, int* status, const nb2_exchange_desc* xch /* NULL: none */);
 
 /* ---- multi-GPU exchange of decoded signals ---------------------------------
  * No counterpart in the reference (single device, simulator.py:215-219).  Every

@@ -85,7 +85,7 @@ _SIGNATURES = {
     "nb2_neurons": [_P, c_int, c_int, c_int, _P, POINTER(nb2_neuron_args)],
     "nb2_spmv_csr": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int],
     "nb2_spmv_ell": [_P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int],
-    "nb2_ensemble_stream": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, _P],
+    "nb2_ensemble_stream": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, _P, _P],
     "nb2_exchange_wait": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_double],
     "nb2_exchange_push": [_P, _P, _P, _P, _P, c_int, c_int, c_int],
     "nb2_gather_sum": [_P, c_int, _P, _P, _P],
@@ -102,6 +102,14 @@ def declared_symbols():
         text = f.read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(nb2_[a-z0-9_]+)\s*\(", text)))
+
+
+class ExchangeDesc(ctypes.Structure):
+    """``nb2_exchange_desc``"""
+
+    _fields_ = [("peer_staging", c_void_p), ("peer_flags", c_void_p), ("ctl", c_void_p), ("cta_runs", c_void_p),
+                ("x_base", c_int), ("x_lo", c_int), ("x_hi", c_int),
+                ("rank", c_int), ("world", c_int), ("seg", c_int)]
 
 
 def header_constants(prefix):

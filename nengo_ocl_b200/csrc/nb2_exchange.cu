@@ -18,28 +18,10 @@
 // control block, stops waiting and lets the kernel finish, so the context stays
 // usable and the host can report the failure.
 #include "nb2_common.cuh"
+#include "nb2_exchange_common.cuh"
 #include "../../include/nengo_b200.h"
 
 #define EXCH_THREADS 256
-
-// control block (ints) in local device memory
-enum { X_EPOCH = 0, X_DONE_BLOCKS, X_STATUS, X_WORDS = 8 };
-
-__device__ __forceinline__ unsigned long long nb2_globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
 // Before step epoch+1: wait until every peer published `epoch`, then copy the
 // peers' staged segments (parity epoch & 1) into the local replica.

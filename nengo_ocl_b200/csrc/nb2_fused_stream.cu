@@ -10,7 +10,7 @@
 //    at most one stage (8 KB) of data.  A CTA
 //    (one per SM, persistent) owns a list of whole ensembles; its records are
 //    ordered E(0), E(1), D(0), E(2), D(1), ... so that the spikes a D record
-//    needs were produced a round earlier.
+//    needs were produced one pass over the warps earlier.
 //  * Every warp owns one shared-memory stage and the records i = warp,
 //    warp + WARPS, ... .  Lane 0 fills the stage with 1-D bulk async copies
 //    (cp.async.bulk, completion counted in bytes on the stage's mbarrier); all
@@ -30,12 +30,22 @@
 //    in shared memory; a record only ever waits for records that precede it in
 //    the CTA's list, so the lowest unfinished record can always run.
 //
+//  * Multi-GPU: when the model is sharded, the decoded (filtered) values of a
+//    CTA's ensembles are one contiguous run of this rank's segment of the
+//    exchange signal; the CTA's last warp stores that run into every peer's
+//    staging buffer (plain peer stores over NVLink, whole lines; no multicast)
+//    as soon as the CTA is done, and the last CTA of the grid publishes the
+//    step number in the peers' flag words (st.release.sys).  The compute step
+//    and its push are one kernel; the peers' nb2_exchange_wait is the other
+//    half.
+//
 // Every wait (mbarrier, counters) is bounded by the global timer; on timeout
 // the warp records NB2_ERR_TIMEOUT in the status word, raises the CTA's abort
 // flag and leaves.
 #include "nb2_common.cuh"
 #include "nb2_pipe.cuh"
 #include "nb2_fused_common.cuh"
+#include "nb2_exchange_common.cuh"
 #include "../../include/nengo_b200.h"
 
 #define ST_NW NB2_STREAM_WARPS
@@ -57,12 +67,13 @@ struct StreamParams {
   float* data;
   float dt, dt_inv;
   int* status;
+  nb2_exchange_desc x;  // x.peer_staging == NULL: no exchange
 };
 
 struct __align__(128) StreamStage {
   float buf[ST_A];
   float x[ST_X];
-  int rec[2][ST_REC];  // record of round m in slot m & 1
+  int rec[2][ST_REC];  // record of turn m in slot m & 1
 };
 
 struct __align__(16) StreamSlot {
@@ -73,7 +84,7 @@ struct __align__(16) StreamSlot {
 // record words
 enum { R_TYPE = 0, R_ENS, R_SLOT, R_A, R_B, R_NCOPY, R_TARGET, R_C, R_COPY0 = 8 };
 
-// Lane 0: fill the stage for round m (record index i); the record is in st.rec[m & 1].
+// Lane 0: fill the stage for turn m (record index i); the record is in st.rec[m & 1].
 __device__ __forceinline__ void stream_issue(const StreamParams& p, StreamStage& st, unsigned long long* full,
                                              const int4* rp, int i, int m, int n) {
   const int* r = st.rec[m & 1];
@@ -132,15 +143,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
   __shared__ int e_done[ST_SLOTS];  // E records finished per slot (cumulative)
   __shared__ int d_done[ST_SLOTS];  // D records finished per slot (cumulative)
   __shared__ int s_abort;
+  __shared__ int warps_left;  // warps of this CTA that still work (exchange push only)
 
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int2 range = p.ranges[blockIdx.x];
   const int n = range.y - range.x;
   if (threadIdx.x < ST_SLOTS) e_done[threadIdx.x] = d_done[threadIdx.x] = 0;
-  if (threadIdx.x == 0) s_abort = 0;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    warps_left = min(ST_NW, n);
+  }
   __syncthreads();
   if (wid >= n) return;
+  // exchange push: this step's values go into the staging half of parity (epoch + 1) & 1
+  const bool xpush = p.x.peer_staging != nullptr;
+  const int epoch = xpush ? p.x.ctl[X_EPOCH] : 0;
+  const size_t xoff = (size_t)((epoch + 1) & 1) * p.x.world * p.x.seg;
 
   StreamStage& st = stages[wid];
   unsigned long long* full = &full_bar[wid];
@@ -290,11 +309,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           data[__ldg(c + C_WEIGHTED) + r0 + lane] = total;
           const int filt = __ldg(c + C_FILT);
           if (filt >= 0) {
-            float* y = data + filt + r0 + lane;
+            const int yi = filt + r0 + lane;
             // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
             const int a0 = __ldg(c + C_A0);
-            if (a0 == 0) *y = bits(__ldg(c + C_B0)) * total;
-            else *y = bits(__ldg(c + C_B0)) * total - bits(a0) * *y;
+            float out = bits(__ldg(c + C_B0)) * total;
+            if (a0 != 0) out = out - bits(a0) * data[yi];
+            data[yi] = out;
           }
         }
         __syncwarp();
@@ -318,13 +338,49 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       stream_stage_x(p, st, st.rec[(m + 1) & 1], lane);
     }
   }
+  if (xpush) {
+    // The decoded values of this CTA's ensembles form one contiguous run of this rank's
+    // segment (the host checked): its last warp stores the run into every peer's staging
+    // buffer with whole-line stores (per-value peer stores would be one NVLink packet each),
+    // and the last CTA of the grid publishes the step number to every peer.
+    __threadfence();  // this warp's results before its count
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) last = atomicSub(&warps_left, 1) == 1;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence();  // the other warps' results after their counts
+      const int2 run = reinterpret_cast<const int2*>(p.x.cta_runs)[blockIdx.x];  // first element (in the signal buffer), length
+      const float* src = data + run.x;
+      const size_t dst0 = xoff + (size_t)(run.x - p.x.x_base);
+      for (int q = 0; q < p.x.world; ++q) {
+        if (q == p.x.rank) continue;
+        float* dst = p.x.peer_staging[q] + dst0;
+        if (((run.x | run.y | (int)(dst0 & 3)) & 3) == 0) {
+          for (int i = lane; i < (run.y >> 2); i += 32)
+            reinterpret_cast<float4*>(dst)[i] = __ldcg(reinterpret_cast<const float4*>(src) + i);
+        } else {
+          for (int i = lane; i < run.y; i += 32) dst[i] = __ldcg(src + i);
+        }
+      }
+      __threadfence_system();  // the peer stores before the flags
+      __syncwarp();
+      if (lane == 0 && atomicAdd(p.x.ctl + X_DONE_BLOCKS, 1) + 1 == (int)gridDim.x) {
+        p.x.ctl[X_DONE_BLOCKS] = 0;
+        __threadfence_system();
+        for (int q = 0; q < p.x.world; ++q)
+          if (q != p.x.rank) st_release_sys(p.x.peer_flags[q] + p.x.rank, epoch + 1);
+        p.x.ctl[X_EPOCH] = epoch + 1;
+      }
+    }
+  }
 }
 
 static const size_t kStreamSmem = sizeof(StreamStage) * ST_NW + sizeof(StreamSlot) * ST_SLOTS;
 
 extern "C" int nb2_ensemble_stream(void* stream, const int* records, int n_records, const int* ranges, int n_ctas,
                                    const int* ens_table, const int* term_table, const int* conn_table, float* data,
-                                   double dt, int* status) {
+                                   double dt, int* status, const nb2_exchange_desc* xch) {
   if (n_records == 0 || n_ctas == 0) return NB2_OK;
   NB2_REQUIRE(records && ranges && ens_table && term_table && conn_table && data, "null pointer");
   NB2_REQUIRE(dt > 0, "dt");
@@ -341,6 +397,14 @@ extern "C" int nb2_ensemble_stream(void* stream, const int* records, int n_recor
   p.records = records; p.ranges = reinterpret_cast<const int2*>(ranges);
   p.ens_table = ens_table; p.term_table = term_table; p.conn_table = conn_table;
   p.data = data; p.dt = (float)dt; p.dt_inv = (float)(1.0 / dt); p.status = status;
+  if (xch != NULL && xch->world > 1) {
+    NB2_REQUIRE(xch->peer_staging && xch->peer_flags && xch->ctl && xch->cta_runs, "exchange descriptor");
+    NB2_REQUIRE(xch->rank >= 0 && xch->rank < xch->world && xch->seg > 0 && xch->x_lo <= xch->x_hi,
+                "exchange descriptor");
+    p.x = *xch;
+  } else {
+    p.x = nb2_exchange_desc();
+  }
   nb2_ensemble_stream_kernel<<<n_ctas, ST_THREADS, kStreamSmem, nb2_stream(stream)>>>(p);
   NB2_LAUNCH_CHECK();
   return NB2_OK;

@@ -67,7 +67,7 @@ struct PipeParams {
 struct __align__(128) PipeStage {
   float buf[PIPE_A];
   float yin[PIPE_R + 8];
-  int rec[3][PIPE_REC];  // record of round m in slot m % 3
+  int rec[3][PIPE_REC];  // record of turn m in slot m % 3
 };
 
 __device__ __forceinline__ float pipe_epilogue(const PipeParams& p, int bb, float yin, float sum) {
@@ -80,11 +80,11 @@ __device__ __forceinline__ float pipe_epilogue(const PipeParams& p, int bb, floa
   return (float)((double)pre + p.alpha * (double)sum);
 }
 
-// Lane 0 of a warp: fill the warp's stage for round m (record index i of the CTA's range).
+// Lane 0 of a warp: fill the warp's stage for turn m (record index i of the CTA's range).
 // The record itself is already in st.rec[m % 3] and the warp's next record in the slot after
-// it: the matrix windows of that next record are prefetched into L2 now, one whole round
+// it: the matrix windows of that next record are prefetched into L2 now, one whole turn
 // before they are copied, so that more bytes are in flight than the stages alone can hold.
-// The record two rounds ahead rides along with this round's copies.
+// The record two turns ahead rides along with the copies of this turn.
 __device__ __forceinline__ void pipe_issue(const PipeParams& p, PipeStage& st, unsigned long long* full,
                                            const int4* rp, int i, int m, int n) {
   const int slot = m % 3;

@@ -86,6 +86,7 @@ class Exchange:
         self.flags = zeros(queue, (max(self.world, 1),), np.int32)
         self.staging = zeros(queue, (2 * self.world * self.seg,), np.float32)
         self._opened = []
+        self.fused_push = False
         self.peer_staging = self.peer_flags = None
         if self.world > 1:
             self._connect()
@@ -114,8 +115,22 @@ class Exchange:
         self.comm.barrier()
 
     # -- plans ------------------------------------------------------------------
+    def descriptor(self, x_base, cta_runs):
+        """``nb2_exchange_desc`` for a compute kernel that pushes this rank's segment
+        itself (``x_base``: element index of the exchange signal in the signal buffer;
+        ``cta_runs``: device array, per CTA the run it pushes).  After this call
+        ``plans()`` leaves the separate push kernel out."""
+        assert self.world > 1
+        self.fused_push = True
+        self._cta_runs = cta_runs  # keep alive
+        lo = int(x_base) + self.rank * self.seg
+        return _capi.ExchangeDesc(self.peer_staging.ptr.value, self.peer_flags.ptr.value, self.ctl.ptr.value,
+                                  cta_runs.ptr.value, int(x_base), lo, lo + self.seg, self.rank, self.world,
+                                  self.seg)
+
     def plans(self):
-        """(wait plan, push plan); empty lists for a single rank."""
+        """(wait plan, push plan); empty lists for a single rank, no push plan when the
+        push is folded into the compute kernel."""
         if self.world == 1:
             return [], []
         lib, check = _capi.lib(), _capi.check
@@ -137,7 +152,7 @@ class Exchange:
         pp = Plan(self.queue, push, (256, 1), name="exchange_push", tag="%d peers" % (self.world - 1),
                   bw_per_call=nbytes + 4 * self.seg)
         pw.full_args = pp.full_args = (self.ctl, self.flags, self.staging, self.peer_staging, self.peer_flags)
-        return [pw], [pp]
+        return [pw], ([] if self.fused_push else [pp])
 
     def status(self):
         """0, or NB2_ERR_TIMEOUT if a wait gave up since the last reset."""

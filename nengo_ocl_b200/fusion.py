@@ -421,6 +421,37 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
     return records.astype(np.int32), np.asarray(ranges, dtype=np.int32)
 
 
+def stream_push_runs(ens, conns, records, ranges, lo, hi):
+    """Per CTA of the streamed kernel, the run {first element, length} of the signal-
+    buffer range [lo, hi) that the filtered outputs of its ensembles' connections
+    fill, or None unless every CTA's outputs in that range are one contiguous run
+    and the runs tile the range (then the kernel can push the range to the other
+    GPUs itself, each CTA its own run)."""
+    runs = np.zeros((len(ranges), 2), dtype=np.int32)
+    covered = np.zeros(max(hi - lo, 0), dtype=bool)
+    for b, (r0, r1) in enumerate(ranges):
+        spans = []
+        for r in np.unique(records[r0:r1, 1]):
+            c0, nc = int(ens[r, 9]), int(ens[r, 8])
+            for crow in conns[c0:c0 + nc]:
+                if crow[3] >= 0:
+                    a, e = max(int(crow[3]), lo), min(int(crow[3]) + int(crow[1]), hi)
+                    if a < e:
+                        spans.append((a, e))
+        if not spans:
+            runs[b] = (lo, 0)
+            continue
+        spans.sort()
+        if any(e0 != a1 for (_, e0), (a1, _) in zip(spans, spans[1:])):
+            return None  # gaps or overlaps inside one CTA's outputs
+        first, last = spans[0][0], spans[-1][1]
+        if covered[first - lo:last - lo].any():
+            return None
+        covered[first - lo:last - lo] = True
+        runs[b] = (first, last - first)
+    return runs if hi > lo and covered.all() else None
+
+
 def plan_fused_ensembles(sim, ops):
     (fused,) = ops
     members = fused.members
@@ -448,8 +479,20 @@ def plan_fused_ensembles(sim, ops):
     fn_stream = _capi.lib().nb2_ensemble_stream
     p = lambda a: None if a is None else a.ptr
     args = (len(large), p(d_large), len(small), p(d_small), d_ens.ptr, d_terms.ptr, d_conns.ptr, data.ptr, dt)
+    # Multi-GPU: if every element of this rank's segment of the exchange signal is the filtered
+    # output of a streamed connection, the streamed kernel pushes it to the peers itself.
+    xdesc = None
+    exch = getattr(sim, "_exchange", None)
+    if exch is not None and exch.world > 1 and len(streamed):
+        lo = sim._exchange_start + exch.rank * exch.seg
+        runs = stream_push_runs(ens, conns, records, ranges, lo, lo + exch.seg)
+        if runs is not None:
+            d_runs = to_device(queue, runs)
+            xdesc = exch.descriptor(sim._exchange_start, d_runs)
+    import ctypes
+
     stream_args = (p(d_records), len(records), p(d_ranges), len(ranges), d_ens.ptr, d_terms.ptr, d_conns.ptr,
-                   data.ptr, dt, status.ptr)
+                   data.ptr, dt, status.ptr, ctypes.byref(xdesc) if xdesc is not None else None)
     n_rest, n_streamed = len(large) + len(small), len(streamed)
 
     def launch(stream):
@@ -461,7 +504,8 @@ def plan_fused_ensembles(sim, ops):
     plan = Plan(queue, launch, (256, max(len(large), 1) + (len(small) + 7) // 8), lsize=(256, 1),
                 n_launches=int(len(large) > 0) + int(len(small) > 0) + int(n_streamed > 0),
                 name="fused_ensemble_step", tag="%d ensembles" % len(members))
-    plan.full_args = (d_ens, d_terms, d_conns, d_small, d_large, d_records, d_ranges, status, data)
+    plan.full_args = (d_ens, d_terms, d_conns, d_small, d_large, d_records, d_ranges, status, data, xdesc)
+    plan.fused_push = xdesc is not None
     plan.tables = dict(ens=ens, terms=terms, conns=conns, small=small, large=large, streamed=streamed,
                        records=records, ranges=ranges)
     plan.status = status

@@ -284,6 +284,18 @@ class Simulator:
         self._python_rngs = {}
         self._device_state_to_reset = []
         self.fused_groups = []
+        # multi-GPU: the exchange buffers exist before planning, so that a compute kernel can take
+        # the push of its own results
+        self._exchange = None
+        self._exchange_start = None
+        if exchange is not None:
+            from nengo_ocl_b200.exchange import Exchange
+
+            sig, comm = exchange
+            assert sig.size % comm.world == 0 and not sig.is_view
+            self._exchange_start = int(self.all_data.starts[self.sidx[sig]])
+            self._exchange = Exchange(self.queue, comm, self.all_data.cl_buf.data + 4 * self._exchange_start,
+                                      sig.size // comm.world)
         plans = []
         groups = list(op_groups)
         if self.fuse:
@@ -293,15 +305,7 @@ class Simulator:
         for op_type, op_list in groups:
             plans.extend(self._plan_op_group(op_type, op_list))
         plans.extend(self._plan_probes())
-        self._exchange = None
-        if exchange is not None:
-            from nengo_ocl_b200.exchange import Exchange
-
-            sig, comm = exchange
-            assert sig.size % comm.world == 0 and not sig.is_view
-            start = int(self.all_data.starts[self.sidx[sig]])
-            self._exchange = Exchange(self.queue, comm, self.all_data.cl_buf.data + 4 * start,
-                                      sig.size // comm.world)
+        if self._exchange is not None:
             wait, push = self._exchange.plans()
             plans = wait + plans + push
         self._plans = Plans(plans, self.profiling, unroll=graph_unroll)

@@ -333,4 +333,6 @@ def main(reference_root, write_fixtures=True):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/nengo-ocl")
+    main(sys.argv[1])

@@ -90,3 +90,26 @@ def test_shard_structure():
     assert labels == sorted(c["label"] for c in full.info["connections"])
     with pytest.raises(AssertionError):
         synth.pes_learning_shard(rank=0, world=3, **KW)
+
+
+def test_stream_push_runs():
+    """The streamed kernel may push a rank's segment only if every CTA's outputs are one run
+    and the runs tile the segment."""
+    from nengo_ocl_b200 import fusion
+
+    ens = np.zeros((3, 16), np.int32)
+    conns = np.zeros((4, 16), np.int32)
+    # ensemble r has connection r (ensemble 2 has two): conn table row = [W, d, weighted, filtered, ...]
+    ens[:, 8], ens[:, 9] = [1, 1, 2], [0, 1, 2]
+    conns[:, 1] = 4
+    conns[:, 3] = [100, 104, 108, -1]  # the last connection has no synapse output
+    rec = lambda rows: np.array([[1, r] + [0] * 30 for r in rows], np.int32)
+    two_ctas = (rec([0, 0, 1, 2]), np.array([[0, 3], [3, 4]], np.int32))  # CTA 0: ensembles 0, 1; CTA 1: 2
+    runs = fusion.stream_push_runs(ens, conns, *two_ctas, 100, 112)
+    assert runs.tolist() == [[100, 8], [108, 4]]
+    assert fusion.stream_push_runs(ens, conns, *two_ctas, 100, 116) is None  # 112..115 unwritten
+    assert fusion.stream_push_runs(ens, conns, rec([0, 2]), np.array([[0, 2]], np.int32), 100, 112) is None  # gap
+    assert fusion.stream_push_runs(ens, conns, rec([1]), np.array([[0, 1]], np.int32), 104, 108).tolist() == [[104, 4]]
+    # a CTA whose ensembles write outside the segment pushes nothing
+    runs = fusion.stream_push_runs(ens, conns, *two_ctas, 100, 108)
+    assert runs.tolist() == [[100, 8], [100, 0]]
