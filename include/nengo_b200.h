@@ -160,6 +160,12 @@ int nb2_probes(void* stream, int n_probes, int block_size, float* countdowns, in
                const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
                const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
                float* Y);
+/* plan_probes for large probes: `chunks` CTAs share one probe; `arrive`: n_probes ints of
+ * scratch, zero before the first launch (the kernel leaves them zero). */
+int nb2_probes_wide(void* stream, int n_probes, int chunks, float* countdowns, int* bufpositions,
+                    const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
+                    const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
+                    float* Y, int* arrive);
 /* plan_presentinput :1678-1759; pres_t may be NULL (table indexed by step);
  * Sstride0s may be NULL (table rows packed, as in the reference) or give the
  * row stride of every table (tables that are column blocks of one buffer) */

@@ -319,6 +319,70 @@ extern "C" int nb2_probes(void* stream, int n_probes, int block_size, float* cou
   return NB2_OK;
 }
 
+// Large probes (a whole population's spikes): `chunks` CTAs share one probe.  Every CTA
+// reads the probe's counters before it copies its part; the counters may only advance when
+// all of them have done so, so the CTAs count their arrivals in `arrive[n]` (zero between
+// launches) and the last one advances the counters and clears the count.
+#define PROBE_THREADS 256
+__global__ void __launch_bounds__(PROBE_THREADS) nb2_probes_wide_kernel(
+    float* countdowns, int* bufpositions, const float* __restrict__ periods, const int* __restrict__ Xstarts,
+    const int* __restrict__ Xshape0s, const int* __restrict__ Xshape1s, const int* __restrict__ Xstride0s,
+    const int* __restrict__ Xstride1s, const float* X, const int* __restrict__ Ystarts, float* Y, int* arrive) {
+  const int n = blockIdx.y;
+  const float countdown = countdowns[n];
+  const int bufpos = bufpositions[n];
+  if (countdown <= 0.0f) {
+    const int ni = Xshape0s[n];
+    const int nj = Xshape1s[n];
+    const int n_dims = ni * nj;
+    const int sti = Xstride0s[n];
+    const int stj = Xstride1s[n];
+    const float* x = X + Xstarts[n];
+    float* y = Y + Ystarts[n] + (size_t)bufpos * n_dims;
+    for (int ij = blockIdx.x * PROBE_THREADS + threadIdx.x; ij < n_dims; ij += gridDim.x * PROBE_THREADS) {
+      const int i = ij / nj;
+      const int j = ij - i * nj;
+      y[ij] = x[i * sti + j * stj];
+    }
+  }
+  __syncthreads();  // every thread of this CTA has read the counters
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(arrive + n, 1) + 1 == (int)gridDim.x) {
+      arrive[n] = 0;
+      if (countdown <= 0.0f) {
+        countdowns[n] = countdown + periods[n] - 1.0f;
+        bufpositions[n] = bufpos + 1;
+      } else {
+        countdowns[n] = countdown - 1.0f;
+      }
+    }
+  }
+}
+
+static int nb2_probes_wide_launch(void* stream, int n_probes, int chunks, float* countdowns, int* bufpositions,
+                                  const float* periods, const int* Xstarts, const int* Xshape0s,
+                                  const int* Xshape1s, const int* Xstride0s, const int* Xstride1s, const float* X,
+                                  const int* Ystarts, float* Y, int* arrive) {
+  NB2_REQUIRE(chunks >= 1 && chunks <= 65535 && n_probes <= 65535, "chunks / n_probes");
+  NB2_REQUIRE(countdowns && bufpositions && periods && Xstarts && Xshape0s && Xshape1s && Xstride0s &&
+                  Xstride1s && X && Ystarts && Y && arrive,
+              "null pointer");
+  nb2_probes_wide_kernel<<<dim3(chunks, n_probes), PROBE_THREADS, 0, nb2_stream(stream)>>>(
+      countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
+extern "C" int nb2_probes_wide(void* stream, int n_probes, int chunks, float* countdowns, int* bufpositions,
+                               const float* periods, const int* Xstarts, const int* Xshape0s,
+                               const int* Xshape1s, const int* Xstride0s, const int* Xstride1s, const float* X,
+                               const int* Ystarts, float* Y, int* arrive) {
+  if (n_probes == 0) return NB2_OK;
+  return nb2_probes_wide_launch(stream, n_probes, chunks, countdowns, bufpositions, periods, Xstarts, Xshape0s,
+                                Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive);
+}
+
 // ---- plan_presentinput (:1694-1730) -----------------------------------------
 __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float dt,
                                         const int* __restrict__ Yshape0s,

@@ -339,6 +339,9 @@ def plan_linearfilter(queue, X, Y, A, B, Xbuf, Ybuf, tag=None):
     return [plan]
 
 
+PROBE_WIDE_ELEMENTS = 4096  # probes larger than this are copied by several CTAs
+
+
 def plan_probes(queue, periods, X, Y, tag=None):
     """Sample ``X[i]`` into row ``bufpositions[i]`` of ``Y[i]`` every ``periods[i]`` steps."""
     assert len(X) == len(Y)
@@ -354,16 +357,27 @@ def plan_probes(queue, periods, X, Y, tag=None):
     cl_countdowns = to_device(queue, periods - 1)
     cl_bufpositions = to_device(queue, np.zeros(N, dtype="int32"))
     max_len = int(min(max(X.shape0s), get_mwgs(queue)))
-    fn, check = _capi.lib().nb2_probes, _capi.check
-    args = (N, max_len, cl_countdowns.ptr, cl_bufpositions.ptr, cl_periods.ptr, X.cl_starts.ptr,
-            X.cl_shape0s.ptr, X.cl_shape1s.ptr, X.cl_stride0s.ptr, X.cl_stride1s.ptr, X.cl_buf.ptr,
-            Y.cl_starts.ptr, Y.cl_buf.ptr)
+    check = _capi.check
+    tables = (cl_countdowns.ptr, cl_bufpositions.ptr, cl_periods.ptr, X.cl_starts.ptr,
+              X.cl_shape0s.ptr, X.cl_shape1s.ptr, X.cl_stride0s.ptr, X.cl_stride1s.ptr, X.cl_buf.ptr,
+              Y.cl_starts.ptr, Y.cl_buf.ptr)
+    largest = int(max(X.shape0s * X.shape1s))
+    cl_arrive = None
+    if largest > PROBE_WIDE_ELEMENTS:
+        # a probe of a whole population: several CTAs per probe (one CTA would copy it serially)
+        chunks = int(min(-(-largest // PROBE_WIDE_ELEMENTS), 128))
+        cl_arrive = to_device(queue, np.zeros(N, dtype="int32"))
+        fn = _capi.lib().nb2_probes_wide
+        args = (N, chunks) + tables + (cl_arrive.ptr,)
+    else:
+        fn = _capi.lib().nb2_probes
+        args = (N, max_len) + tables
 
     def launch(stream):
         check(fn(stream, *args))
 
     plan = Plan(queue, launch, (max_len, N), lsize=(max_len, 1), name="cl_probes", tag=tag)
-    plan.full_args = (cl_countdowns, cl_bufpositions, cl_periods, X, Y)
+    plan.full_args = (cl_countdowns, cl_bufpositions, cl_periods, X, Y, cl_arrive)
     plan.cl_bufpositions = cl_bufpositions
     plan.cl_countdowns = cl_countdowns
     plan.periods = periods

@@ -233,3 +233,29 @@ def test_probes_timeupdate_presentinput(queue, rng):
     assert np.array_equal(pplan.cl_bufpositions.get(), pos)
     assert pos.tolist() == [6, 3, 6, 2]
     assert np.array_equal(Y.cl_buf.get(), Yh.buf)
+
+
+def test_probes_of_large_signals(queue, rng):
+    """Probes larger than one CTA's share go through the several-CTAs-per-probe kernel; a
+    small probe, a strided view and different periods ride along."""
+    big = nl.PROBE_WIDE_ELEMENTS * 3 + 17
+    sig = RA([rng.normal(size=(big, 1)), rng.normal(size=(5, 1)), rng.normal(size=(300, 40))])
+    sig.add_views([sig.starts[2] + 3], [300], [1], [40], [1])  # a column of the matrix
+    X = CLRA(queue, sig)
+    n_pre = 5
+    periods = [1, 2, 3, 1]
+    Y = CLRA(queue, RA([np.zeros((n_pre, int(s))) for s in sig.sizes]))
+    pplan = nl.plan_probes(queue, periods, X, Y)
+    assert pplan.full_args[-1] is not None  # the arrival counters of the wide kernel
+    cd = np.asarray(periods, np.float32) - 1
+    pos = np.zeros(4, np.int32)
+    Yh = RA([np.zeros((n_pre, int(s))) for s in sig.sizes])
+    for i in range(5):
+        X[1] = np.full((5, 1), float(i))  # the probed signal changes between samples
+        sig[1] = np.full((5, 1), float(i))
+        pplan()
+        K.probes(cd, pos, np.asarray(periods, np.float32), sig, Yh)
+    assert np.array_equal(pplan.cl_bufpositions.get(), pos) and pos.tolist() == [5, 2, 1, 5]
+    assert np.array_equal(pplan.cl_countdowns.get(), cd)
+    assert np.array_equal(pplan.full_args[-1].get(), np.zeros(4, np.int32))  # counters are left clear
+    assert np.array_equal(Y.cl_buf.get(), Yh.buf)
