@@ -166,6 +166,14 @@ int nb2_probes_wide(void* stream, int n_probes, int chunks, float* countdowns, i
                     const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
                     const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
                     float* Y, int* arrive);
+/* nb2_probes_wide without any allocation (no reference counterpart): the arrival
+ * counters live in a device array of the library (NB2_PROBES_STATIC_MAX probes at
+ * most; more are rejected).  Launches that use it must not overlap in time. */
+#define NB2_PROBES_STATIC_MAX 4096
+int nb2_probes_wide_noalloc(void* stream, int n_probes, int chunks, float* countdowns, int* bufpositions,
+                            const float* periods, const int* Xstarts, const int* Xshape0s,
+                            const int* Xshape1s, const int* Xstride0s, const int* Xstride1s,
+                            const float* X, const int* Ystarts, float* Y);
 /* plan_presentinput :1678-1759; pres_t may be NULL (table indexed by step);
  * Sstride0s may be NULL (table rows packed, as in the reference) or give the
  * row stride of every table (tables that are column blocks of one buffer) */

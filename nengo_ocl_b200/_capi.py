@@ -82,6 +82,7 @@ _SIGNATURES = {
     "nb2_linearfilter": [_P, c_int, c_int, c_int] + [_P] * 23,
     "nb2_probes": [_P, c_int, c_int] + [_P] * 11,
     "nb2_probes_wide": [_P, c_int, c_int] + [_P] * 12,
+    "nb2_probes_wide_noalloc": [_P, c_int, c_int] + [_P] * 11,
     "nb2_presentinput": [_P, c_int, c_int, _P, c_double] + [_P] * 9,
     "nb2_neurons": [_P, c_int, c_int, c_int, _P, POINTER(nb2_neuron_args)],
     "nb2_spmv_csr": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int],

@@ -383,6 +383,30 @@ extern "C" int nb2_probes_wide(void* stream, int n_probes, int chunks, float* co
                                 Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive);
 }
 
+// The same launch with the arrival counters in a device array of this library instead of
+// caller memory: nothing is allocated, by the caller or here.  The array is zero at load
+// time and every launch leaves it zero; its address is looked up once per device.
+static __device__ __align__(256) int g_probe_arrive[NB2_PROBES_STATIC_MAX];
+
+extern "C" int nb2_probes_wide_noalloc(void* stream, int n_probes, int chunks, float* countdowns,
+                                       int* bufpositions, const float* periods, const int* Xstarts,
+                                       const int* Xshape0s, const int* Xshape1s, const int* Xstride0s,
+                                       const int* Xstride1s, const float* X, const int* Ystarts, float* Y) {
+  if (n_probes == 0) return NB2_OK;
+  NB2_REQUIRE(n_probes <= NB2_PROBES_STATIC_MAX, "more probes than the static arrival counters cover");
+  static int* arrive_of_device[64] = {};
+  int dev = 0;
+  NB2_CUDA(cudaGetDevice(&dev));
+  NB2_REQUIRE(dev >= 0 && dev < 64, "device ordinal");
+  if (arrive_of_device[dev] == NULL) {
+    void* sym = NULL;
+    NB2_CUDA(cudaGetSymbolAddress(&sym, g_probe_arrive));
+    arrive_of_device[dev] = static_cast<int*>(sym);
+  }
+  return nb2_probes_wide_launch(stream, n_probes, chunks, countdowns, bufpositions, periods, Xstarts, Xshape0s,
+                                Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive_of_device[dev]);
+}
+
 // ---- plan_presentinput (:1694-1730) -----------------------------------------
 __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float dt,
                                         const int* __restrict__ Yshape0s,
