@@ -147,6 +147,20 @@ int nb2_elementwise_inc(void* stream, int n_blocks, int outer, int inc, const fl
                         const int* Xshape0s, const int* Xshape1s, const int* Xstride0s,
                         const int* Xstarts, const float* X, const int* Yshape0s,
                         const int* Yshape1s, const int* Ystride0s, const int* Ystarts, float* Y);
+/* plan_bcm :2082-2169, plan_oja :2172-2277, plan_voja :2280-2405: weight deltas of the
+ * unsupervised learning rules, one thread per delta element; `aux` = theta (vector) for
+ * BCM, the weights for Oja, the scaled encoders for Voja; `betas` only for Oja, the
+ * learning signal and `scale` only for Voja (NULL otherwise). */
+#define NB2_RULE_BCM 0
+#define NB2_RULE_OJA 1
+#define NB2_RULE_VOJA 2
+int nb2_learning_delta(void* stream, int rule, int n_items, int max_size, const int* shape0s,
+                       const int* shape1s, const int* pre_stride0s, const int* pre_starts, const float* pre,
+                       const int* post_stride0s, const int* post_starts, const float* post,
+                       const int* aux_stride0s, const int* aux_starts, const float* aux,
+                       const int* delta_stride0s, const int* delta_starts, float* delta, const float* alphas,
+                       const float* betas, const int* learn_starts, const float* learn,
+                       const int* scale_stride0s, const int* scale_starts, const float* scale);
 /* plan_linearfilter :577-803 (+ linearfilter_inc ring-position kernel when uses_buf) */
 int nb2_linearfilter(void* stream, int n_blocks, int block_size, int uses_buf, const int* offsets,
                      const int* shape0s, const int* shape1s, const int* Xstride0s,

@@ -80,6 +80,7 @@ _SIGNATURES = {
     "nb2_slicedcopy": [_P, c_int, c_int] + [_P] * 12,
     "nb2_elementwise_inc": [_P, c_int, c_int, c_int] + [_P] * 17,
     "nb2_linearfilter": [_P, c_int, c_int, c_int] + [_P] * 23,
+    "nb2_learning_delta": [_P, c_int, c_int, c_int] + [_P] * 21,
     "nb2_probes": [_P, c_int, c_int] + [_P] * 11,
     "nb2_probes_wide": [_P, c_int, c_int] + [_P] * 12,
     "nb2_probes_wide_noalloc": [_P, c_int, c_int] + [_P] * 11,

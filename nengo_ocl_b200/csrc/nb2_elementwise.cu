@@ -271,6 +271,88 @@ extern "C" int nb2_linearfilter(void* stream, int n_blocks, int block_size, int 
   return NB2_OK;
 }
 
+// ---- weight deltas of the unsupervised learning rules --------------------------
+// plan_bcm (clra_nonlinearities.py:2082-2169), plan_oja (:2172-2277), plan_voja
+// (:2280-2405): one thread per element (i, j) of delta item k,
+//   BCM : delta = alpha * post_i * (post_i - theta_i) * pre_j
+//   Oja : delta = alpha * post_i * (pre_j - beta * w_ij * post_i)
+//   Voja: delta = alpha * learn * post_i * (scale_i * pre_j - enc_ij)
+// evaluated left to right as in the reference kernels (this file is compiled
+// with -fmad=false).  `aux` is theta (a vector), the weights or the encoders.
+struct LearnArgs {
+  const int *shape0s, *shape1s;
+  const int *pre_stride0s, *pre_starts;
+  const float* pre;
+  const int *post_stride0s, *post_starts;
+  const float* post;
+  const int *aux_stride0s, *aux_starts;
+  const float* aux;
+  const int *delta_stride0s, *delta_starts;
+  float* delta;
+  const float *alphas, *betas;
+  const int* learn_starts;
+  const float* learn;
+  const int *scale_stride0s, *scale_starts;
+  const float* scale;
+};
+
+template <int RULE>
+__global__ void nb2_learning_delta_kernel(const LearnArgs a) {
+  const int ij = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  const int shape0 = a.shape0s[k];
+  const int shape1 = a.shape1s[k];
+  const int i = ij / shape1;
+  const int j = ij - i * shape1;
+  if (i >= shape0) return;
+  const float pre = a.pre[a.pre_starts[k] + j * a.pre_stride0s[k]];
+  const float post = a.post[a.post_starts[k] + i * a.post_stride0s[k]];
+  const float alpha = a.alphas[k];
+  float out;
+  if (RULE == NB2_RULE_BCM) {
+    const float theta = a.aux[a.aux_starts[k] + i * a.aux_stride0s[k]];
+    out = alpha * post * (post - theta) * pre;
+  } else if (RULE == NB2_RULE_OJA) {
+    const float weight = a.aux[a.aux_starts[k] + i * a.aux_stride0s[k] + j];
+    out = alpha * post * (pre - a.betas[k] * weight * post);
+  } else {
+    const float enc = a.aux[a.aux_starts[k] + i * a.aux_stride0s[k] + j];
+    const float learn = a.learn[a.learn_starts[k]];
+    const float scale = a.scale[a.scale_starts[k] + i * a.scale_stride0s[k]];
+    out = alpha * learn * post * (scale * pre - enc);
+  }
+  a.delta[a.delta_starts[k] + i * a.delta_stride0s[k] + j] = out;
+}
+
+extern "C" int nb2_learning_delta(void* stream, int rule, int n_items, int max_size, const int* shape0s,
+                                  const int* shape1s, const int* pre_stride0s, const int* pre_starts,
+                                  const float* pre, const int* post_stride0s, const int* post_starts,
+                                  const float* post, const int* aux_stride0s, const int* aux_starts,
+                                  const float* aux, const int* delta_stride0s, const int* delta_starts,
+                                  float* delta, const float* alphas, const float* betas, const int* learn_starts,
+                                  const float* learn, const int* scale_stride0s, const int* scale_starts,
+                                  const float* scale) {
+  if (n_items == 0 || max_size == 0) return NB2_OK;
+  NB2_REQUIRE(rule == NB2_RULE_BCM || rule == NB2_RULE_OJA || rule == NB2_RULE_VOJA, "rule");
+  NB2_REQUIRE(n_items > 0 && n_items <= 65535 && max_size > 0, "n_items / max_size");
+  NB2_REQUIRE(shape0s && shape1s && pre_stride0s && pre_starts && pre && post_stride0s && post_starts && post &&
+                  aux_stride0s && aux_starts && aux && delta_stride0s && delta_starts && delta && alphas,
+              "null pointer");
+  NB2_REQUIRE(rule != NB2_RULE_OJA || betas, "Oja needs betas");
+  NB2_REQUIRE(rule != NB2_RULE_VOJA || (learn_starts && learn && scale_stride0s && scale_starts && scale),
+              "Voja needs the learning signal and the scale");
+  LearnArgs a = {shape0s, shape1s, pre_stride0s, pre_starts, pre, post_stride0s, post_starts, post,
+                 aux_stride0s, aux_starts, aux, delta_stride0s, delta_starts, delta, alphas, betas,
+                 learn_starts, learn, scale_stride0s, scale_starts, scale};
+  const dim3 grid((max_size + 255) / 256, n_items);
+  cudaStream_t s = nb2_stream(stream);
+  if (rule == NB2_RULE_BCM) nb2_learning_delta_kernel<NB2_RULE_BCM><<<grid, 256, 0, s>>>(a);
+  else if (rule == NB2_RULE_OJA) nb2_learning_delta_kernel<NB2_RULE_OJA><<<grid, 256, 0, s>>>(a);
+  else nb2_learning_delta_kernel<NB2_RULE_VOJA><<<grid, 256, 0, s>>>(a);
+  NB2_LAUNCH_CHECK();
+  return NB2_OK;
+}
+
 // ---- plan_probes (:831-902) -------------------------------------------------
 __global__ void nb2_probes_kernel(float* countdowns, int* bufpositions,
                                   const float* __restrict__ periods, const int* __restrict__ Xstarts,

@@ -339,6 +339,82 @@ def plan_linearfilter(queue, X, Y, A, B, Xbuf, Ybuf, tag=None):
     return [plan]
 
 
+def _plan_learning_delta(queue, rule, name, pre, post, aux, delta, alpha, beta=None, learn=None, scale=None,
+                         flops_per_element=4, tag=None):
+    """Common launch of plan_bcm / plan_oja / plan_voja (``nb2_learning_delta``)."""
+    N = len(pre)
+    p = lambda a: None if a is None else a.ptr
+    fn, check = _capi.lib().nb2_learning_delta, _capi.check
+    max_size = int(delta.sizes.max()) if N else 0
+    args = (rule, N, max_size, delta.cl_shape0s.ptr, delta.cl_shape1s.ptr,
+            pre.cl_stride0s.ptr, pre.cl_starts.ptr, pre.cl_buf.ptr,
+            post.cl_stride0s.ptr, post.cl_starts.ptr, post.cl_buf.ptr,
+            aux.cl_stride0s.ptr, aux.cl_starts.ptr, aux.cl_buf.ptr,
+            delta.cl_stride0s.ptr, delta.cl_starts.ptr, delta.cl_buf.ptr, alpha.ptr, p(beta),
+            None if learn is None else learn.cl_starts.ptr, None if learn is None else learn.cl_buf.ptr,
+            None if scale is None else scale.cl_stride0s.ptr, None if scale is None else scale.cl_starts.ptr,
+            None if scale is None else scale.cl_buf.ptr)
+
+    def launch(stream):
+        check(fn(stream, *args))
+
+    plan = Plan(queue, launch, (max_size, N), lsize=None, name=name, tag=tag)
+    plan.full_args = (pre, post, aux, delta, alpha, beta, learn, scale)
+    plan.flops_per_call = flops_per_element * int(delta.sizes.sum())
+    plan.bw_per_call = sum(a.nbytes for a in (pre, post, aux, delta, alpha, beta, learn, scale) if a is not None)
+    plan.description = _describe(delta)
+    return plan
+
+
+def plan_bcm(queue, pre, post, theta, delta, alpha, tag=None):
+    """``delta = alpha * post * (post - theta) * pre`` (outer product over post x pre)."""
+    assert len(pre) == len(post) == len(theta) == len(delta) == alpha.size
+    for arr in (pre, post, theta):  # vectors
+        assert (arr.shape1s == 1).all()
+    for arr in (delta,):  # matrices
+        assert (arr.stride1s == 1).all()
+    assert (post.shape0s == delta.shape0s).all()
+    assert (pre.shape0s == delta.shape1s).all()
+    assert (post.shape0s == theta.shape0s).all()
+    assert pre.ctype == post.ctype == theta.ctype == delta.ctype
+    return _plan_learning_delta(queue, 0, "cl_bcm", pre, post, theta, delta, alpha, flops_per_element=4, tag=tag)
+
+
+def plan_oja(queue, pre, post, weights, delta, alpha, beta, tag=None):
+    """``delta = alpha * post * (pre - beta * weights * post)``"""
+    assert len(pre) == len(post) == len(weights) == len(delta) == alpha.size == beta.size
+    for arr in (pre, post):  # vectors
+        assert (arr.shape1s == 1).all()
+    for arr in (delta, weights):  # matrices
+        assert (arr.stride1s == 1).all()
+    assert (post.shape0s == weights.shape0s).all()
+    assert (pre.shape0s == weights.shape1s).all()
+    assert (weights.shape0s == delta.shape0s).all()
+    assert (weights.shape1s == delta.shape1s).all()
+    assert pre.ctype == post.ctype == weights.ctype == delta.ctype
+    return _plan_learning_delta(queue, 1, "cl_oja", pre, post, weights, delta, alpha, beta=beta,
+                                flops_per_element=5, tag=tag)
+
+
+def plan_voja(queue, pre, post, enc, delta, learn, scale, alpha, tag=None):
+    """``delta = alpha * learn * post * (scale * pre - enc)``"""
+    assert len(pre) == len(post) == len(enc) == len(delta) == len(learn) == alpha.size == len(scale)
+    for arr in (learn,):  # scalars
+        assert (arr.shape0s == 1).all()
+        assert (arr.shape1s == 1).all()
+    for arr in (pre, post, scale):  # vectors
+        assert (arr.shape1s == 1).all()
+    for arr in (enc, delta):  # matrices
+        assert (arr.stride1s == 1).all()
+    assert (post.shape0s == enc.shape0s).all()
+    assert (pre.shape0s == enc.shape1s).all()
+    assert (enc.shape0s == delta.shape0s).all()
+    assert (enc.shape1s == delta.shape1s).all()
+    assert pre.ctype == post.ctype == enc.ctype == delta.ctype == learn.ctype == scale.ctype
+    return _plan_learning_delta(queue, 2, "cl_voja", pre, post, enc, delta, alpha, learn=learn, scale=scale,
+                                flops_per_element=5, tag=tag)
+
+
 PROBE_WIDE_ELEMENTS = 4096  # probes larger than this are copied by several CTAs
 
 

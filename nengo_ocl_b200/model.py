@@ -261,6 +261,42 @@ class SimPES(Operator):
         self.updates = [delta]
 
 
+class SimBCM(Operator):
+    """``delta = learning_rate * dt * post * (post - theta) * pre`` (outer product)"""
+
+    def __init__(self, pre_filtered, post_filtered, theta, delta, learning_rate, tag=None):
+        super().__init__(tag)
+        self.pre_filtered, self.post_filtered, self.theta, self.delta = pre_filtered, post_filtered, theta, delta
+        self.learning_rate = float(learning_rate)
+        self.reads = [pre_filtered, post_filtered, theta]
+        self.updates = [delta]
+
+
+class SimOja(Operator):
+    """``delta = learning_rate * dt * post * (pre - beta * weights * post)``"""
+
+    def __init__(self, pre_filtered, post_filtered, weights, delta, learning_rate, beta, tag=None):
+        super().__init__(tag)
+        self.pre_filtered, self.post_filtered, self.weights, self.delta = pre_filtered, post_filtered, weights, delta
+        self.learning_rate, self.beta = float(learning_rate), float(beta)
+        self.reads = [pre_filtered, post_filtered, weights]
+        self.updates = [delta]
+
+
+class SimVoja(Operator):
+    """``delta = learning_rate * dt * learning_signal * post * (scale * pre_decoded - scaled_encoders)``"""
+
+    def __init__(self, pre_decoded, post_filtered, scaled_encoders, delta, scale, learning_signal, learning_rate,
+                 tag=None):
+        super().__init__(tag)
+        self.pre_decoded, self.post_filtered, self.scaled_encoders = pre_decoded, post_filtered, scaled_encoders
+        self.delta, self.learning_signal = delta, learning_signal
+        self.scale = np.asarray(scale, dtype=np.float64)
+        self.learning_rate = float(learning_rate)
+        self.reads = [pre_decoded, post_filtered, scaled_encoders, learning_signal]
+        self.updates = [delta]
+
+
 class SimPyFunc(Operator):
     def __init__(self, output, fn, t, x, tag=None):
         super().__init__(tag)

@@ -28,12 +28,14 @@ from nengo_ocl_b200 import _capi
 from nengo_ocl_b200.ast_conversion import DeviceFunction
 from nengo_ocl_b200.cura_gemv import plan_block_gemv
 from nengo_ocl_b200.cura_nonlinearities import (
+    plan_bcm,
     plan_copy,
     plan_direct,
     plan_elementwise_inc,
     plan_lif,
     plan_lif_rate,
     plan_linearfilter,
+    plan_oja,
     plan_presentinput,
     plan_probes,
     plan_rectified_linear,
@@ -42,6 +44,7 @@ from nengo_ocl_b200.cura_nonlinearities import (
     plan_slicedcopy,
     plan_spiking_rectified_linear,
     plan_timeupdate,
+    plan_voja,
 )
 from nengo_ocl_b200.curaggedarray import CUDARaggedArray, to_device
 from nengo_ocl_b200.operators import MultiDotInc, simplify_operators
@@ -933,6 +936,36 @@ class Simulator:
         delta = self.all_data[[self.sidx[op.delta] for op in ops]]
         alpha = np.array([-op.learning_rate * self.model.dt / op.pre_filtered.shape[0] for op in ops])
         return [plan_elementwise_inc(self.queue, error, pre, delta, alpha=alpha, outer=True, inc=False)]
+
+    def _plan_SimBCM(self, ops):
+        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
+        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
+        theta = self.all_data[[self.sidx[op.theta] for op in ops]]
+        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
+        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
+        return [plan_bcm(self.queue, pre, post, theta, delta, alpha)]
+
+    def _plan_SimOja(self, ops):
+        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
+        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
+        weights = self.all_data[[self.sidx[op.weights] for op in ops]]
+        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
+        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
+        beta = self.Array([op.beta for op in ops])
+        return [plan_oja(self.queue, pre, post, weights, delta, alpha, beta)]
+
+    def _plan_SimRLS(self, ops):
+        raise NotImplementedError("RLS learning rule not yet supported")
+
+    def _plan_SimVoja(self, ops):
+        pre = self.all_data[[self.sidx[op.pre_decoded] for op in ops]]
+        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
+        encoders = self.all_data[[self.sidx[op.scaled_encoders] for op in ops]]
+        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
+        learning_signal = self.all_data[[self.sidx[op.learning_signal] for op in ops]]
+        scale = self.RaggedArray([np.asarray(op.scale).reshape(-1, 1) for op in ops], dtype=np.float32)
+        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
+        return [plan_voja(self.queue, pre, post, encoders, delta, learning_signal, scale, alpha)]
 
     # ---- reporting ---------------------------------------------------------------
     def print_plans(self):

@@ -390,3 +390,30 @@ def spmv_ell(columns, entries, x, y, inc=False):
             off //= 2
         out[row] = f32(out[row] + prod[0]) if inc else prod[0]
     return out.reshape(np.shape(y))
+
+
+def _outer_terms(pre, post):
+    return _f(post).reshape(-1, 1), _f(pre).reshape(1, -1)
+
+
+def bcm(pre, post, theta, alpha):
+    """``bcm`` (clra_nonlinearities.py:2126-2129): ``alpha * post * (post - theta) * pre``,
+    multiplied left to right in float32; returns the (post, pre) delta matrix."""
+    po, pr = _outer_terms(pre, post)
+    th = _f(theta).reshape(-1, 1)
+    return (((f32(alpha) * po) * (po - th)) * pr).astype(np.float32)
+
+
+def oja(pre, post, weights, alpha, beta):
+    """``oja`` (clra_nonlinearities.py:2232-2235): ``alpha * post * (pre - beta * weights * post)``."""
+    po, pr = _outer_terms(pre, post)
+    w = _f(weights)
+    inner = pr - ((f32(beta) * w) * po)
+    return ((f32(alpha) * po) * inner).astype(np.float32)
+
+
+def voja(pre, post, enc, learn, scale, alpha):
+    """``voja`` (clra_nonlinearities.py:2356-2359): ``alpha * learn * post * (scale * pre - enc)``."""
+    po, pr = _outer_terms(pre, post)
+    sc = _f(scale).reshape(-1, 1)
+    return (((f32(alpha) * f32(learn)) * po) * (sc * pr - _f(enc))).astype(np.float32)

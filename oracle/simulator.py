@@ -280,6 +280,19 @@ class OracleSimulator:
         alpha = f32(-op.learning_rate * self.dt / pre.shape[0])
         delta[...] = ((alpha * err)[:, None] * pre[None, :]).astype(np.float32)
 
+    def _do_SimBCM(self, op):
+        self.view(op.delta)[...] = K.bcm(self.view(op.pre_filtered), self.view(op.post_filtered),
+                                         self.view(op.theta), op.learning_rate * self.dt)
+
+    def _do_SimOja(self, op):
+        self.view(op.delta)[...] = K.oja(self.view(op.pre_filtered), self.view(op.post_filtered),
+                                         self.view(op.weights), op.learning_rate * self.dt, op.beta)
+
+    def _do_SimVoja(self, op):
+        self.view(op.delta)[...] = K.voja(self.view(op.pre_decoded), self.view(op.post_filtered),
+                                          self.view(op.scaled_encoders), self.view(op.learning_signal).reshape(-1)[0],
+                                          op.scale, op.learning_rate * self.dt)
+
     def _do_SimPyFunc(self, op):
         args = []
         if op.t is not None:

@@ -275,6 +275,39 @@ def main(reference_root, write_fixtures=True):
     kernels["linearfilter/xs"] = np.array(xs_seq)
     kernels["linearfilter/ys"] = np.array(ys_seq)
 
+    # ---------------- learning-rule deltas: bcm, oja, voja kernels ----------------
+    lrng = np.random.RandomState(31)
+    shapes = [(5, 3), (1, 7), (12, 12)]  # (post, pre)
+    pre_h = ra([lrng.normal(size=(n, 1)) for _, n in shapes])
+    post_h = ra([lrng.normal(size=(m_, 1)) for m_, _ in shapes])
+    theta_h = ra([lrng.normal(size=(m_, 1)) for m_, _ in shapes])
+    mat_h = ra([lrng.normal(size=sh) for sh in shapes])
+    scale_h = ra([lrng.uniform(0.5, 2, size=(m_, 1)) for m_, _ in shapes])
+    learn_h = ra([lrng.normal(size=(1, 1)) for _ in shapes])
+    alpha_h = lrng.uniform(-1, 1, size=3).astype(np.float32)
+    beta_h = lrng.uniform(0, 2, size=3).astype(np.float32)
+    for name, arr in (("pre", pre_h), ("post", post_h), ("theta", theta_h), ("mat", mat_h), ("scale", scale_h),
+                      ("learn", learn_h)):
+        kernels["learning/%s_buf" % name] = arr.buf.copy()
+    kernels["learning/alpha"], kernels["learning/beta"] = alpha_h, beta_h
+    kernels["learning/shapes"] = np.array(shapes)
+    dev = lambda a: CLRA(queue, a)
+    dalpha, dbeta = refstubs.to_device(queue, alpha_h), refstubs.to_device(queue, beta_h)
+    delta = dev(ra([np.zeros(sh) for sh in shapes]))
+    plan, _, progs = capture(lambda: nl.plan_bcm(queue, dev(pre_h), dev(post_h), dev(theta_h), delta, dalpha))
+    refkernels.run_plan(plan, progs[-1], "bcm")
+    kernels["learning/bcm_delta"] = delta.cl_buf._arr.copy()
+    tables["learning/bcm_gsize"] = np.array(plan.gsize)
+    delta = dev(ra([np.zeros(sh) for sh in shapes]))
+    plan, _, progs = capture(lambda: nl.plan_oja(queue, dev(pre_h), dev(post_h), dev(mat_h), delta, dalpha, dbeta))
+    refkernels.run_plan(plan, progs[-1], "oja")
+    kernels["learning/oja_delta"] = delta.cl_buf._arr.copy()
+    delta = dev(ra([np.zeros(sh) for sh in shapes]))
+    plan, _, progs = capture(lambda: nl.plan_voja(queue, dev(pre_h), dev(post_h), dev(mat_h), delta, dev(learn_h),
+                                                  dev(scale_h), dalpha))
+    refkernels.run_plan(plan, progs[-1], "voja")
+    kernels["learning/voja_delta"] = delta.cl_buf._arr.copy()
+
     # ---------------- sparse transforms: host tables, heuristic, CSR kernel ----------------
     import scipy.sparse as sp
 

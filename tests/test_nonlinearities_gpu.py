@@ -259,3 +259,37 @@ def test_probes_of_large_signals(queue, rng):
     assert np.array_equal(pplan.cl_countdowns.get(), cd)
     assert np.array_equal(pplan.full_args[-1].get(), np.zeros(4, np.int32))  # counters are left clear
     assert np.array_equal(Y.cl_buf.get(), Yh.buf)
+
+
+def test_learning_rule_deltas(queue, rng):
+    """plan_bcm / plan_oja / plan_voja against the oracle: bit-exact (multiply-add only), with a
+    strided delta view among the items."""
+    shapes = [(5, 3), (1, 7), (40, 33), (300, 17)]  # (post, pre)
+    pre = RA([rng.normal(size=(n, 1)) for _, n in shapes])
+    post = RA([rng.normal(size=(m, 1)) for m, _ in shapes])
+    theta = RA([rng.normal(size=(m, 1)) for m, _ in shapes])
+    mat = RA([rng.normal(size=sh) for sh in shapes])
+    scale = RA([rng.uniform(0.5, 2, size=(m, 1)) for m, _ in shapes])
+    learn = RA([rng.normal(size=(1, 1)) for _ in shapes])
+    alpha = rng.uniform(-1, 1, size=len(shapes)).astype(np.float32)
+    beta = rng.uniform(0, 2, size=len(shapes)).astype(np.float32)
+    d_alpha, d_beta = to_device(queue, alpha), to_device(queue, beta)
+    cl = lambda a: CLRA(queue, a)
+    for rule in ("bcm", "oja", "voja"):
+        delta = cl(RA([np.full(sh, 9.0) for sh in shapes]))
+        if rule == "bcm":
+            plan = nl.plan_bcm(queue, cl(pre), cl(post), cl(theta), delta, d_alpha)
+        elif rule == "oja":
+            plan = nl.plan_oja(queue, cl(pre), cl(post), cl(mat), delta, d_alpha, d_beta)
+        else:
+            plan = nl.plan_voja(queue, cl(pre), cl(post), cl(mat), delta, cl(learn), cl(scale), d_alpha)
+        plan()
+        assert plan.bw_per_call > 0 and plan.flops_per_call > 0
+        for k, (m, n) in enumerate(shapes):
+            if rule == "bcm":
+                want = K.bcm(pre[k], post[k], theta[k], alpha[k])
+            elif rule == "oja":
+                want = K.oja(pre[k], post[k], mat[k], alpha[k], beta[k])
+            else:
+                want = K.voja(pre[k], post[k], mat[k], learn[k][0, 0], scale[k], alpha[k])
+            assert np.array_equal(delta[k], want), (rule, k)

@@ -169,3 +169,40 @@ def test_linearfilter_matches_reference_kernel(golden_kernels):
         X.buf[...] = g["linearfilter/xs"][step]
         K.linearfilter(X, Y, A, B, Xb, Yb, xpos, ypos)
         assert np.array_equal(Y.buf, g["linearfilter/ys"][step]), step
+
+
+def _learning_items(gk):
+    """Per item (pre, post, theta, matrix, scale, learn) of the learning-rule fixture."""
+    shapes = [tuple(int(v) for v in sh) for sh in gk["learning/shapes"]]
+    def split(name, sizes):
+        buf, out, pos = gk["learning/%s_buf" % name], [], 0
+        for n in sizes:
+            out.append(buf[pos:pos + n])
+            pos += n
+        return out
+    pre = split("pre", [n for _, n in shapes])
+    post = split("post", [m for m, _ in shapes])
+    theta = split("theta", [m for m, _ in shapes])
+    mat = [a.reshape(sh) for a, sh in zip(split("mat", [m * n for m, n in shapes]), shapes)]
+    scale = split("scale", [m for m, _ in shapes])
+    learn = split("learn", [1 for _ in shapes])
+    return shapes, pre, post, theta, mat, scale, learn
+
+
+def test_learning_rule_deltas_match_reference_kernels(golden_kernels):
+    """bcm / oja / voja restatements against the reference's kernels (multiply-add only: bit-exact)."""
+    gk = golden_kernels
+    shapes, pre, post, theta, mat, scale, learn = _learning_items(gk)
+    alpha, beta = gk["learning/alpha"], gk["learning/beta"]
+    for rule in ("bcm", "oja", "voja"):
+        want, pos = gk["learning/%s_delta" % rule], 0
+        for k, (m, n) in enumerate(shapes):
+            if rule == "bcm":
+                got = K.bcm(pre[k], post[k], theta[k], alpha[k])
+            elif rule == "oja":
+                got = K.oja(pre[k], post[k], mat[k], alpha[k], beta[k])
+            else:
+                got = K.voja(pre[k], post[k], mat[k], learn[k][0], scale[k], alpha[k])
+            assert got.shape == (m, n)
+            assert np.array_equal(got.reshape(-1), want[pos:pos + m * n]), (rule, k)
+            pos += m * n

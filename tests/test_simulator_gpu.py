@@ -185,15 +185,49 @@ def small_cc(seed=4):
     return synth.circular_convolution_model(seed=seed, dimensions=16, n_neurons=64, n_templates=3)
 
 
+def mixed_streamed(seed=11):
+    """Large populations of several shapes for the streamed fused kernel: neuron counts that
+    are not multiples of 32, a second encoder term, connections with and without synapse and
+    PES, narrow decoders, probed spikes."""
+    nb = synth.NetBuilder(dt=0.001, seed=seed, label="mixed")
+    rng = nb.rng
+    sizes = [256, 260, 512, 1024, 300]
+    drive = nb.node_fn(lambda t: [np.sin(7 * t), np.cos(5 * t), 0.3, -0.2], 4, label="drive")
+    ens = [nb.ensemble(n, 8, label="m%d" % i) for i, n in enumerate(sizes)]
+    for i, e in enumerate(ens):
+        # a second encoder term: the drive goes straight into the neurons
+        W2 = m.Signal(rng.normal(size=(e.n_neurons, 4)) * 0.5, name="m%d.direct" % i, readonly=True)
+        nb.model.add_op(m.DotInc(W2, drive, e.sig_J, tag="m%d.direct" % i))
+    err = m.Signal(np.zeros(8), name="err")
+    nb.model.add_op(m.Reset(err))
+    nb.model.add_op(m.Copy(nb.node_fn(lambda t: 0.2 * np.sin(3 * t) * np.ones(8), 8, label="errsrc"), err, inc=True))
+    for i, e in enumerate(ens):
+        nxt = ens[(i + 1) % len(ens)]
+        dec = nb.solve_decoders(e, n_eval=600)
+        if i % 2 == 0:
+            nb.connect_decoded(e, nxt.sig_in, dec, synapse=0.01, label="c%d" % i,
+                               pes=dict(learning_rate=1e-4, error=err, pre_synapse=0.005))
+        else:
+            nb.connect_decoded(e, nxt.sig_in, dec, synapse=0.005, label="c%d" % i)
+        # a narrow decoded output without synapse (3 rows) into a collector signal
+        out3 = m.Signal(np.zeros(3), name="m%d.out3" % i)
+        nb.model.add_op(m.Reset(out3))
+        nb.connect_decoded(e, out3, dec[:3] * 0.5, synapse=None, label="n%d" % i)
+    probes = [nb.model.add_probe(nb.connections[0]["out"], label="c0.out"),
+              nb.probe(ens[1].sig_out, synapse=0.02, label="m1.spikes")]
+    nb.model.info = dict(probes=probes, ensembles=nb.ensembles, connections=nb.connections)
+    return nb.model
+
+
 def small_sparse(seed=9):
     # one population with a sparse neuron-to-neuron recurrent connection
     return synth.sparse_recurrent_model(seed=seed, n_neurons=300, fan_out=12)
 
 
 @pytest.mark.parametrize("fuse", [False, True])
-@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes, small_cc, small_sparse],
+@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes, small_cc, small_sparse, mixed_streamed],
                          ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3", "circular_convolution",
-                              "sparse_recurrent"])
+                              "sparse_recurrent", "mixed_streamed"])
 def test_scaled_configs_match_oracle_per_step(make, fuse):
     mdl = make()
     ora = OracleSimulator(mdl)
@@ -208,6 +242,9 @@ def test_scaled_configs_match_oracle_per_step(make, fuse):
                 skip.update([c["delta"], c["weights"]])
     skip.update(s for g in sim.fused_groups for s in g["unstored"])
     assert bool(sim.fused_groups) == (fuse and make is not small_sparse)  # (its J has a second writer)
+    if fuse and make in (wide_pes, mixed_streamed):  # these go through the streamed kernel
+        fused_plan = [p for p in sim._plans if p.name == "fused_ensemble_step"][0]
+        assert len(fused_plan.tables["streamed"]) == len(mdl.info["ensembles"])
     sigs = [s for s in state_signals(mdl) if s not in skip]
     # A different float32 summation order can move a spike by one step; that neuron's state then
     # differs for a few steps.  In the circular convolution every product feeds all outputs through
@@ -233,3 +270,44 @@ def test_scaled_configs_match_oracle_per_step(make, fuse):
             got, ref = sim.data[p], np.array(ora.probe_data[p])
             assert got.shape == ref.shape
             assert np.sqrt(np.mean((got - ref) ** 2)) < 1e-3
+
+
+def test_unsupervised_learning_rules_match_oracle():
+    """BCM, Oja and Voja deltas applied to weights / encoders over 30 steps (operator-level model)."""
+    rng = np.random.RandomState(3)
+    mdl = m.Model(dt=0.001)
+    n_pre, n_post, d = 24, 17, 5
+    pre = m.Signal(np.zeros(n_pre), name="pre_filtered")
+    post = m.Signal(np.zeros(n_post), name="post_filtered")
+    mdl.add_op(m.SimPyFunc(pre, lambda t: 40 * np.abs(np.sin(30 * t + np.arange(24))), mdl.time, None))
+    mdl.add_op(m.SimPyFunc(post, lambda t: 30 * np.abs(np.cos(20 * t + np.arange(17))), mdl.time, None))
+    theta = m.Signal(rng.uniform(5, 20, size=n_post), name="theta", readonly=True)
+    tracked = []
+    for rule in ("bcm", "oja"):
+        w = m.Signal(rng.normal(size=(n_post, n_pre)) * 0.1, name="%s.weights" % rule)
+        delta = m.Signal(np.zeros((n_post, n_pre)), name="%s.delta" % rule)
+        if rule == "bcm":
+            mdl.add_op(m.SimBCM(pre, post, theta, delta, learning_rate=1e-3))
+        else:
+            mdl.add_op(m.SimOja(pre, post, w, delta, learning_rate=1e-3, beta=0.7))
+        mdl.add_op(m.Copy(delta, w, inc=True))
+        tracked += [w, delta]
+    dec = m.Signal(np.zeros(d), name="pre_decoded")
+    mdl.add_op(m.SimPyFunc(dec, lambda t: np.sin(9 * t + np.arange(5)), mdl.time, None))
+    learn = m.Signal(np.zeros(1), name="learning_signal")
+    mdl.add_op(m.SimPyFunc(learn, lambda t: 1.0 + 0.5 * np.sin(4 * t), mdl.time, None))
+    enc = m.Signal(rng.normal(size=(n_post, d)), name="scaled_encoders")
+    vdelta = m.Signal(np.zeros((n_post, d)), name="voja.delta")
+    mdl.add_op(m.SimVoja(dec, post, enc, vdelta, scale=rng.uniform(0.5, 2, size=n_post), learning_signal=learn,
+                         learning_rate=1e-2))
+    mdl.add_op(m.Copy(vdelta, enc, inc=True))
+    tracked += [enc, vdelta]
+    mdl.add_probe(enc)
+    ora = OracleSimulator(mdl)
+    with Simulator(None, model=mdl) as sim:
+        for _ in range(30):
+            sim.step()
+            ora.step()
+            for sig in tracked:
+                assert np.allclose(np.asarray(sim.signals[sig]), ora[sig], rtol=1e-5, atol=1e-6), sig
+        assert np.abs(ora[tracked[0]]).max() > 0
