@@ -222,6 +222,29 @@ def find_fusable(sim, operators):
     return members, consumed
 
 
+def fold_resets_into_products(operators):
+    """``Reset(y, v)`` followed only by one merged product ``y += sum A_i x_i`` becomes the
+    product in "set" form, ``y = v + sum A_i x_i`` (beta 0, gamma v): one launch less.
+    The products are changed in place; returns the resets that are no longer needed."""
+    writers = {}
+    for op in operators:
+        for kind in ("sets", "incs", "updates"):
+            for s in getattr(op, kind):
+                writers.setdefault(s.base, []).append((op, kind, s))
+    dropped = set()
+    for base, ws in writers.items():
+        if base.is_view or len(ws) != 2:
+            continue
+        resets = [op for op, kind, s in ws if _is_type(op, "Reset") and s is base]
+        dots = [op for op, kind, s in ws if isinstance(op, MultiDotInc) and kind == "incs" and s is base
+                and op.Y is base and op.Y_in is base and op._signal_beta is None and op._float_beta == 1
+                and op.gamma == 0]
+        if len(resets) == 1 and len(dots) == 1:
+            dots[0]._float_beta, dots[0].gamma, dots[0]._incs_Y = 0.0, float(resets[0].value), False
+            dropped.add(resets[0])
+    return dropped
+
+
 def fuse_ensemble_groups(sim, groups, planner=None):
     """Replace matched operators by one ``FusedEnsembles`` op and re-plan."""
     from nengo_ocl_b200.planners import greedy_planner
@@ -230,9 +253,11 @@ def fuse_ensemble_groups(sim, groups, planner=None):
     operators = sim.operators
     members, consumed = find_fusable(sim, operators)
     gathers, gathered = find_gather_sums([op for op in operators if op not in consumed])
-    if not members and not gathers:
-        return groups
     consumed = set(consumed) | gathered
+    folded = fold_resets_into_products([op for op in operators if op not in consumed])
+    if not members and not gathers and not folded:
+        return groups
+    consumed |= folded
     new_ops = [op for op in operators if op not in consumed] + gathers
     if members:
         new_ops.append(FusedEnsembles(members))
@@ -521,18 +546,28 @@ def plan_fused_ensembles(sim, ops):
 
 # ---- reset + whole-signal increments -> one gather-sum ---------------------------
 class GatherSum(Operator):
-    """``dst = sum(srcs)``: a signal that is reset to zero and then only
-    incremented by whole-signal copies."""
+    """``dst[part] = sum(srcs of part)`` for every part of ``dst``: a signal that is
+    reset to zero and then only incremented by copies into the whole signal or into
+    non-overlapping contiguous slices of it.  ``parts`` = [(offset, size, [srcs])];
+    a part without sources is just zeroed."""
 
-    def __init__(self, dst, srcs, ops):
-        Operator.__init__(self, tag="gather-%d" % len(srcs))
-        self.dst, self.srcs, self.ops = dst, list(srcs), list(ops)
+    def __init__(self, dst, parts, ops):
+        n_src = sum(len(srcs) for _, _, srcs in parts)
+        Operator.__init__(self, tag="gather-%d" % n_src)
+        self.dst, self.parts, self.ops = dst, list(parts), list(ops)
+        self.srcs = [s for _, _, srcs in parts for s in srcs]
         self.sets = [dst]
-        self.reads = list(srcs)
+        self.reads = list(self.srcs)
+
+
+def _contiguous_1d(sig):
+    return sig.ndim <= 1 and (sig.size <= 1 or sig.elemstrides[-1] == 1)
 
 
 def find_gather_sums(operators):
-    """Signals written only by ``Reset(0)`` and un-sliced ``Copy(inc=True)`` ops."""
+    """Signals written only by ``Reset(0)`` and un-indexed ``Copy(inc=True)`` ops whose
+    targets are the signal itself or contiguous slices of it that do not overlap
+    each other partially (several copies into the same slice are summed)."""
     writers = {}
     for op in operators:
         for kind in ("sets", "incs", "updates"):
@@ -541,17 +576,31 @@ def find_gather_sums(operators):
     order = {op: i for i, op in enumerate(operators)}
     gathers, consumed = [], set()
     for base, ws in writers.items():
-        if base.is_view or len(ws) < 2:
+        if base.is_view or len(ws) < 2 or base.ndim > 1:
             continue
         resets = [op for op, kind, s in ws if _is_type(op, "Reset") and s is base and op.value == 0]
-        copies = [op for op, kind, s in ws if _is_type(op, "Copy") and kind == "incs" and s is base
-                  and op.src_slice is None and op.dst_slice is None and op.src.size == base.size
-                  and (op.src.ndim <= 1 and (op.src.size <= 1 or op.src.elemstrides[-1] == 1))]
-        if len(resets) != 1 or len(resets) + len(copies) != len(ws) or base.ndim > 1:
+        copies = [(op, s) for op, kind, s in ws if _is_type(op, "Copy") and kind == "incs"
+                  and op.src_slice is None and op.dst_slice is None and op.src.size == s.size
+                  and _contiguous_1d(op.src) and _contiguous_1d(s)]
+        if len(resets) != 1 or len(resets) + len(copies) != len(ws):
             continue
-        ordered = sorted(copies, key=order.get)  # operator order = summation order
-        gathers.append(GatherSum(base, [op.src for op in ordered], resets + ordered))
-        consumed.update(resets + ordered)
+        by_extent = {}
+        for op, s in sorted(copies, key=lambda c: order[c[0]]):  # operator order = summation order
+            by_extent.setdefault((s.elemoffset, s.size), []).append(op)
+        extents = sorted(by_extent)
+        if any(a0 + an > b0 for (a0, an), (b0, _) in zip(extents, extents[1:])):
+            continue  # partially overlapping targets
+        parts, pos = [], 0
+        for off, size in extents:
+            if off > pos:
+                parts.append((pos, off - pos, []))  # nobody increments this stretch: it is only reset
+            parts.append((off, size, [op.src for op in by_extent[(off, size)]]))
+            pos = off + size
+        if pos < base.size:
+            parts.append((pos, base.size - pos, []))
+        ops_used = resets + [op for op, _ in copies]
+        gathers.append(GatherSum(base, parts, ops_used))
+        consumed.update(ops_used)
     return gathers, consumed
 
 
@@ -561,12 +610,13 @@ def plan_gather_sums(sim, ops):
     blocks, srcs = [], []
     n_bytes = 0
     for op in ops:
-        d0, size = int(starts[sidx[op.dst]]), op.dst.size
-        s0 = [int(starts[sidx[s]]) for s in op.srcs]
-        for off in range(0, size, 256):
-            blocks.append([d0 + off, min(256, size - off), len(srcs), len(s0)])
-            srcs.extend(s + off for s in s0)
-        n_bytes += 4 * size * (len(s0) + 1)
+        d0 = int(starts[sidx[op.dst]])
+        for part_off, size, part_srcs in op.parts:
+            s0 = [int(starts[sidx[s]]) for s in part_srcs]
+            for off in range(0, size, 256):
+                blocks.append([d0 + part_off + off, min(256, size - off), len(srcs), len(s0)])
+                srcs.extend(s + off for s in s0)
+            n_bytes += 4 * size * (len(s0) + 1)
     queue = sim.queue
     d_blocks = to_device(queue, np.asarray(blocks, dtype=np.int32).reshape(-1, 4))
     d_srcs = to_device(queue, np.asarray(srcs + [0], dtype=np.int32))

@@ -575,11 +575,15 @@ class Simulator:
             raise NotImplementedError()
         if vector_bs:
             raise NotImplementedError("signal-valued beta")
-        return self._sig_gemv(
-            constant_bs, lambda op: self._A_views[op], lambda op: self._X_views[op],
-            lambda op: self._YYB_views[op][0], lambda op: self._YYB_views[op][1],
-            beta=[op._float_beta for op in constant_bs], gamma=[op.gamma for op in constant_bs],
-            tag="c-beta-%d" % len(constant_bs))
+        # one plan per (beta, gamma) pair, so that the kernels get scalar scales
+        plans = []
+        for scales in stable_unique((op._float_beta, op.gamma) for op in constant_bs):
+            same = [op for op in constant_bs if (op._float_beta, op.gamma) == scales]
+            plans += self._sig_gemv(
+                same, lambda op: self._A_views[op], lambda op: self._X_views[op],
+                lambda op: self._YYB_views[op][0], lambda op: self._YYB_views[op][1],
+                beta=scales[0], gamma=scales[1], tag="c-beta-%d" % len(same))
+        return plans
 
     def _sig_gemv(self, ops, A_js_fn, X_js_fn, Y_fn, Y_in_fn=None, alpha=1.0, beta=1.0, gamma=0.0, tag=None):
         if len(ops) == 0:
