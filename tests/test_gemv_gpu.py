@@ -162,3 +162,40 @@ def test_idempotent_replay_and_linearity(queue):
     vals, mags = K.gemv_exact(1.0, A, A_js[idx], X, X_js[idx], 0.0, Y[idx])
     for j, i in enumerate(idx):
         assert np.all(np.abs(clY1[i][:, 0] - vals[j]) <= 1e-5 * mags[j] + 1e-7)
+
+
+def test_config2_full_size_properties(queue):
+    """Benchmark configuration 2 at its full size (4096 outputs, 688 MB of matrices), checked by
+    properties that do not need the oracle on every element: the pipelined kernel agrees with the
+    independent row-group kernel on every output, with the float64 value on a sample of items, and
+    is linear in alpha (Y(2a) - Y(0) = 2 (Y(a) - Y(0)))."""
+    A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=4096)
+    clA, clX = CLRA(queue, A), CLRA(queue, X)
+
+    def product(alpha, kind):
+        clY = CLRA(queue, Y)
+        prog = cura_gemv.plan_fused_gemv(queue, alpha, clA, A_js, clX, X_js, 0.1, clY, cta_kind=kind)
+        for plan in prog.plans:
+            plan()
+            assert int(plan.status.get()[0]) == 0
+        return clY.cl_buf.get()
+
+    y_pipe = product(0.5, cura_gemv.GEMV_PIPE)
+    y_rows = product(0.5, cura_gemv.GEMV_ROWS)
+    scale = np.abs(y_pipe).max()
+    assert np.allclose(y_pipe, y_rows, rtol=1e-4, atol=1e-5 * scale)
+    # float64 value of 64 sampled items
+    rng = np.random.RandomState(0)
+    for i in rng.choice(len(Y), size=64, replace=False):
+        exact = 0.1 * Y[i].astype(np.float64)
+        mag = np.abs(exact)
+        for a_j, x_j in zip(A_js[i].ravel(), X_js[i].ravel()):
+            a, x = A[int(a_j)].astype(np.float64), X[int(x_j)].astype(np.float64)
+            exact = exact + 0.5 * (a @ x)
+            mag = mag + 0.5 * (np.abs(a) @ np.abs(x))
+        lo = int(Y.starts[i])
+        got = y_pipe[lo:lo + exact.size]
+        assert np.all(np.abs(got - exact.ravel()) <= 1e-5 * mag.ravel() + 1e-7), i
+    y0 = product(0.0, cura_gemv.GEMV_PIPE)
+    y2 = product(1.0, cura_gemv.GEMV_PIPE)
+    assert np.allclose(y2 - y0, 2 * (y_pipe - y0), rtol=1e-4, atol=1e-5 * scale)

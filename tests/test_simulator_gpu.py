@@ -311,3 +311,32 @@ def test_unsupervised_learning_rules_match_oracle():
             for sig in tracked:
                 assert np.allclose(np.asarray(sim.signals[sig]), ora[sig], rtol=1e-5, atol=1e-6), sig
         assert np.abs(ora[tracked[0]]).max() > 0
+
+
+def test_full_size_pes_model_streamed_equals_unfused():
+    """Benchmark configuration 5 at its full size (4096 x 1024 LIF x 16-d, 825 MB per step):
+    the streamed fused kernel against the independent per-operator kernels on the same model.
+    Decoded outputs agree to float32 round-off apart from the few that a one-step spike shift
+    touches; the PES decoders agree with weights + delta of the unfused run."""
+    mdl = synth.pes_learning_model(seed=3, n_ensembles=4096, n_neurons=1024, dimensions=16, sim_time=0.05)
+    steps = 12
+    outs = {}
+    for fuse in (True, False):
+        with Simulator(None, model=mdl, fuse=fuse) as sim:
+            if fuse:
+                fused_plan = [p for p in sim._plans if p.name == "fused_ensemble_step"][0]
+                assert len(fused_plan.tables["streamed"]) == 4096
+            sim.run_steps(steps)
+            conns = mdl.info["connections"]
+            sample = conns[::64]
+            outs[fuse] = dict(
+                out=np.concatenate([np.asarray(sim.signals[c["out"]]) for c in conns]),
+                w=[np.asarray(sim.signals[c["weights"]]) for c in sample],
+                d=None if fuse else [np.asarray(sim.signals[c["delta"]]) for c in sample])
+    a, b = outs[True]["out"], outs[False]["out"]
+    bad = np.abs(a - b) > 1e-6 + 1e-5 * np.abs(b)
+    assert bad.mean() < 2e-3, bad.mean()
+    assert np.allclose(a, b, rtol=1e-2, atol=1e-4)
+    for wf, wu, du in zip(outs[True]["w"], outs[False]["w"], outs[False]["d"]):
+        close = np.abs(wf - (wu + du)) <= 1e-7 + 1e-5 * np.abs(wu + du)
+        assert close.mean() > 0.95
