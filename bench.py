@@ -17,8 +17,11 @@ Printed JSON (one line, rank 0):
   roofline   the fused ensemble-step kernel: algorithmic bytes per launch over
              its CUDA-event time, against the measured HBM copy bandwidth;
   gemv       the ragged gather-GEMV microbenchmark (configuration 2), GB/s;
+  spmv       sparse transforms (CSR, ELLPACK) on a Watts-Strogatz adjacency, GB/s;
+  small_models  simulated steps/s of configurations 1, 3, 4 and of a sparse
+             recurrent population through ``run_steps``;
   cpu_baseline  the CPU oracle (numpy restatement of the reference's kernels)
-             on a bounded slice of the same workload.
+             on a bounded slice of the same workload, one process per host core.
 ``--impl reference`` times that CPU oracle alone, on the host cores.
 With N > 1 (torchrun, one rank per GPU) every rank simulates its shard of the
 ensembles and the decoded signals are exchanged each step.
@@ -133,28 +136,46 @@ class Events:
         return ms.value
 
 
-def cpu_oracle_rate(n_ensembles, steps, warmup=2):
-    """Neuron updates per second of the CPU oracle on a slice of the workload."""
+def _oracle_worker(job):
+    """One host process of the CPU baseline: a block of ensembles of the workload on the oracle."""
+    seed, n_ensembles, steps, warmup = job
     from nengo_ocl_b200 import synth
     from oracle.simulator import OracleSimulator
 
-    mdl = synth.pes_learning_model(n_ensembles=n_ensembles, n_neurons=FULL["n_neurons"],
-                                   dimensions=FULL["dimensions"], n_templates=min(8, n_ensembles), n_probes=2)
+    mdl = synth.pes_learning_model(seed=seed, n_ensembles=n_ensembles, n_neurons=FULL["n_neurons"],
+                                   dimensions=FULL["dimensions"], n_templates=min(4, n_ensembles), n_probes=2)
     ora = OracleSimulator(mdl)
     ora.run_steps(warmup)
     t0 = time.perf_counter()
     ora.run_steps(steps)
-    dt = time.perf_counter() - t0
-    return mdl.n_neurons * steps / dt, dt / steps, mdl.n_neurons
+    return mdl.n_neurons, time.perf_counter() - t0
+
+
+def cpu_oracle_rate(n_ensembles, steps, warmup=2):
+    """Neuron updates per second of the CPU oracle on a slice of the workload, one process per
+    host core, each with its own block of ensembles (the blocks only meet in the exchange
+    signal, as on several GPUs).  Returns (rate, seconds per step, neurons, processes)."""
+    import multiprocessing as mp
+
+    procs = max(1, min(len(os.sched_getaffinity(0)), n_ensembles // 8))
+    per = n_ensembles // procs
+    jobs = [(3 + i, per, steps, warmup) for i in range(procs)]
+    if procs == 1:
+        results = [_oracle_worker(jobs[0])]
+    else:
+        with mp.get_context("spawn").Pool(procs) as pool:
+            results = pool.map(_oracle_worker, jobs)
+    neurons = sum(n for n, _ in results)
+    slowest = max(t for _, t in results)
+    return neurons * steps / slowest, slowest / steps, neurons, procs
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     n_ens = 512
-    rate, s_per_step, n_neurons = cpu_oracle_rate(n_ens, args.steps, warmup=min(max(args.warmup, 1), 3))
-    cores = len(os.sched_getaffinity(0))
-    sample = "%d of 4096 ensembles (%d neurons), %d steps" % (n_ens, n_neurons, args.steps)
+    rate, s_per_step, n_neurons, cores = cpu_oracle_rate(n_ens, args.steps, warmup=min(max(args.warmup, 1), 3))
+    sample = "%d of 4096 ensembles (%d neurons) in %d processes, %d steps" % (n_ens, n_neurons, cores, args.steps)
     line = {
         "impl": "reference", "metric": "neuron_updates_per_s", "value": rate, "unit": "neuron-updates/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * s_per_step,
@@ -445,9 +466,10 @@ def main():
         line["small_models"] = small_model_rates(ctx, _capi)
     if rank == 0 and not args.no_cpu and world == 1:
         n_ens = 512
-        rate, s_per_step, nn = cpu_oracle_rate(n_ens, 40)
-        line["cpu_baseline"] = {"value": rate, "unit": "neuron-updates/s", "cores": len(os.sched_getaffinity(0)),
-                                "kind": "port", "sample": "%d of 4096 ensembles (%d neurons), 40 steps" % (n_ens, nn)}
+        rate, s_per_step, nn, cores = cpu_oracle_rate(n_ens, 40)
+        line["cpu_baseline"] = {"value": rate, "unit": "neuron-updates/s", "cores": cores, "kind": "port",
+                                "sample": "%d of 4096 ensembles (%d neurons) in %d processes, 40 steps"
+                                          % (n_ens, nn, cores)}
     sim.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
