@@ -44,7 +44,7 @@ sys.path.insert(0, ROOT)
 FULL = dict(n_ensembles=4096, n_neurons=1024, dimensions=16)
 # dram__bytes_read.sum + dram__bytes_write.sum of one nb2_ensemble_stream_kernel launch on 1024 ensembles
 # (profiles/fused_ensemble_step_pes_model.md), per ensemble
-NCU_DRAM_BYTES_PER_ENSEMBLE = (128.93e6 + 28.14e6) / 1024
+NCU_DRAM_BYTES_PER_ENSEMBLE = (129.85e6 + 27.6e6) / 1024
 WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
 
 
