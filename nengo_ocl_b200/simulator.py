@@ -182,6 +182,9 @@ class Simulator:
     """
 
     some_context = None
+    #: large populations go through the streamed fused kernel (``nb2_ensemble_stream``); False keeps
+    #: every fused population in the CTA- or warp-per-ensemble kernel
+    stream_ensembles = True
 
     def Array(self, val, dtype=np.float32):
         return to_device(self.queue, np.asarray(val, dtype=dtype))

@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, fused_push):
     sys.path.insert(0, ROOT)
     os.environ["LOCAL_RANK"] = str(rank)
     import torch.distributed as dist
@@ -35,8 +35,12 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
     mdl = synth.pes_learning_shard(rank=rank, world=world, **KW)
     comm = TorchComm()
+    if not fused_push:
+        Simulator.stream_ensembles = False  # per-ensemble kernel, then the separate nb2_exchange_push
     with Simulator(None, model=mdl, context=create_some_context(rank), exchange=(mdl.info["exchange"], comm)) as sim:
         assert sim.fused_groups
+        assert sim._exchange.fused_push == fused_push
+        assert [p.name for p in sim._plans].count("exchange_push") == (0 if fused_push else 1)
         comm.barrier()
         sim.run_steps(STEPS)
         assert sim._exchange.status() == 0 and sim._exchange.epoch() == STEPS
@@ -51,7 +55,8 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_gpus_match_unsharded_oracle(tmp_path):
+@pytest.mark.parametrize("fused_push", [True, False], ids=["push_in_step_kernel", "separate_push_kernel"])
+def test_two_gpus_match_unsharded_oracle(tmp_path, fused_push):
     from nengo_ocl_b200 import _capi
     import ctypes
 
@@ -65,7 +70,7 @@ def test_two_gpus_match_unsharded_oracle(tmp_path):
     from oracle.simulator import OracleSimulator
 
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), fused_push), nprocs=world, join=True)
     full = synth.pes_learning_shard(rank=0, world=1, **KW)
     ora = OracleSimulator(full)
     ora.run_steps(STEPS)

@@ -132,3 +132,34 @@ def test_function_translation_to_postfix():
         DeviceFunction(lambda x: sorted(x), [3])
     with pytest.raises(NotImplementedError):
         DeviceFunction(lambda t: [t, t], [1], out_dim=3)
+
+
+def test_gather_sum_over_slices_and_reset_folding():
+    """The fusion passes on operator lists: copies into slices of a reset signal become one
+    gather-sum with one part per slice (gaps are only zeroed); a reset followed by one merged
+    product becomes the product in set form."""
+    from nengo_ocl_b200 import fusion
+
+    a = m.Signal(np.zeros(6), name="a")
+    s1, s2, s3 = (m.Signal(np.ones(2) * k, name="s%d" % k) for k in (1, 2, 3))
+    ops = [m.Reset(a), m.Copy(s1, a[0:2], inc=True), m.Copy(s2, a[4:6], inc=True), m.Copy(s3, a[0:2], inc=True)]
+    gathers, consumed = fusion.find_gather_sums(ops)
+    assert len(gathers) == 1 and consumed == set(ops)
+    parts = gathers[0].parts
+    assert [(off, size) for off, size, _ in parts] == [(0, 2), (2, 2), (4, 2)]
+    assert parts[0][2] == [s1, s3] and parts[1][2] == [] and parts[2][2] == [s2]
+    # partially overlapping slices are left alone
+    bad = [m.Reset(a), m.Copy(s1, a[0:2], inc=True), m.Copy(s2, a[1:3], inc=True)]
+    assert fusion.find_gather_sums(bad)[0] == []
+
+    y = m.Signal(np.zeros(3), name="y")
+    A = m.Signal(np.eye(3), name="A", readonly=True)
+    x = m.Signal(np.ones(3), name="x")
+    reset, dot = m.Reset(y, value=0.5), MultiDotInc.convert_to(m.DotInc(A, x, y))
+    dropped = fusion.fold_resets_into_products([reset, dot])
+    assert dropped == {reset}
+    assert dot._float_beta == 0 and dot.gamma == 0.5 and dot.sets == [y] and dot.incs == []
+    # a second writer of y keeps the reset
+    reset2, dot2 = m.Reset(y), MultiDotInc.convert_to(m.DotInc(A, x, y))
+    assert fusion.fold_resets_into_products([reset2, dot2, m.Copy(x, y, inc=True)]) == set()
+    assert dot2._float_beta == 1
