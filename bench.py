@@ -278,7 +278,7 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse")):
         label, make, steps = makers[key]
         t0 = time.perf_counter()
         mdl = make()
-        sim = Simulator(None, model=mdl, context=ctx)
+        sim = Simulator(None, model=mdl, context=ctx, n_prealloc_probes=256)  # probes drained every 256 steps
         build_s = time.perf_counter() - t0
         sim.run_steps(10)
         capi.call("nb2_device_sync")

@@ -155,7 +155,9 @@ int nb2_event_elapsed_ms(void* start, void* stop, float* ms) {
 
 // ---- CUDA graph capture / replay ------------------------------------------
 int nb2_graph_begin(void* stream) {
-  NB2_CUDA(cudaStreamBeginCapture(nb2_stream(stream), cudaStreamCaptureModeThreadLocal));
+  // relaxed: an allocation or a free made by the host while the stream captures (e.g. by a
+  // garbage collector) does not invalidate the capture
+  NB2_CUDA(cudaStreamBeginCapture(nb2_stream(stream), cudaStreamCaptureModeRelaxed));
   return NB2_OK;
 }
 

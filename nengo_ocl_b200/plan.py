@@ -203,16 +203,26 @@ class Plans:
     # -- execution ----------------------------------------------------------
     def _capture(self, plans, repeat):
         q = self.queue
-        _capi.call("nb2_graph_begin", q.stream)
+        # No device array may be released while the stream is capturing (a free is not a
+        # capturable call): keep the garbage collector out of the way until the capture ends.
+        import gc
+
+        gc_was_on = gc.isenabled()
+        gc.disable()
         try:
-            for _ in range(repeat):
-                for p in plans:
-                    p.kern(q.stream)
-        except Exception:
-            _capi.lib().nb2_graph_abort(q.stream)
-            raise
-        g = ctypes.c_void_p()
-        _capi.call("nb2_graph_end", q.stream, ctypes.byref(g))
+            _capi.call("nb2_graph_begin", q.stream)
+            try:
+                for _ in range(repeat):
+                    for p in plans:
+                        p.kern(q.stream)
+            except Exception:
+                _capi.lib().nb2_graph_abort(q.stream)
+                raise
+            g = ctypes.c_void_p()
+            _capi.call("nb2_graph_end", q.stream, ctypes.byref(g))
+        finally:
+            if gc_was_on:
+                gc.enable()
         return _Graph(g.value)
 
     def _build_segments(self):
