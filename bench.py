@@ -278,7 +278,9 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse")):
         label, make, steps = makers[key]
         t0 = time.perf_counter()
         mdl = make()
-        sim = Simulator(None, model=mdl, context=ctx, n_prealloc_probes=256)  # probes drained every 256 steps
+        # probes are drained every 256 steps (every 32 for the population-wide probe of the sparse model,
+        # whose 0.8 MB per step would otherwise fill a 210 MB window)
+        sim = Simulator(None, model=mdl, context=ctx, n_prealloc_probes=32 if key == "ws_sparse" else 256)
         build_s = time.perf_counter() - t0
         sim.run_steps(10)
         capi.call("nb2_device_sync")
