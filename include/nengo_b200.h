@@ -91,6 +91,19 @@ int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, int gstride, 
                     double gamma, const float* alphas, const float* betas, const float* gammas,
                     int* status);
 
+/* plan_block_gemv (clra_gemv.py:861-1175; the variant the reference simulator
+ * plans for every MultiDotInc, simulator.py:803) with that kernel pair's exact
+ * float32 summation order: 128-column tiles, four column-strided partial sums
+ * per tile combined as (s0 + s2) + (s1 + s3), tiles added in order to
+ * beta * Y_in, gamma last; scalar alpha / beta / gamma only (as block_impl,
+ * :863-880).  Same index table as nb2_gemv_ragged.  cta_units / warp_units:
+ * int4 {item row, first row, row count, 0}; row count <= 32 for CTA units,
+ * <= 8 for warp units.  Results are bit-identical to the reference kernels
+ * evaluated without fused multiply-add. */
+int nb2_gemv_block(void* stream, const int* gstructure, int gstride, int D, const int* xstrides,
+                   const int* cta_units, int n_cta, const int* warp_units, int n_warp, const float* A,
+                   const float* X, const float* Yin, float* Y, double alpha, double beta, double gamma);
+
 /* The main GEMV path: persistent CTAs whose warps each own one shared-memory
  * stage fed by 1-D bulk async copies (cp.async.bulk) only.  Same math and
  * reference counterparts as nb2_gemv_ragged.  `records`: n_records x 32 int32

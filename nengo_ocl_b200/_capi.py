@@ -72,6 +72,8 @@ _SIGNATURES = {
     "nb2_ipc_close_handle": [_P],
     "nb2_gemv_ragged": [_P, c_int, _P, c_int, c_int, _P, _P, c_int, _P, _P, _P, _P, c_double, c_double,
                         c_double, _P, _P, _P, _P],
+    "nb2_gemv_block": [_P, _P, c_int, c_int, _P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, c_double,
+                       c_double],
     "nb2_gemv_pipelined": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, c_double, c_double, _P, _P, _P,
                            _P],
     "nb2_timeupdate": [_P, _P, _P, c_double],

@@ -24,6 +24,7 @@ UNITS = [
     ("nb2_runtime.cu", []),
     ("nb2_gemv.cu", []),
     ("nb2_gemv_pipe.cu", []),
+    ("nb2_gemv_block.cu", []),
     ("nb2_spmv.cu", []),
     ("nb2_elementwise.cu", ["-fmad=false"]),
     ("nb2_neurons.cu", ["-fmad=false"]),

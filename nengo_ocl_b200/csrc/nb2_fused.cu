@@ -18,17 +18,21 @@
 // are contiguous, so threads map to consecutive neurons.
 //
 // One thread group per ensemble: a CTA of 256 threads for large populations, a
-// warp for small ones (8 per CTA).  Phase 1: each thread computes J for its
-// neurons (x staged in shared memory, encoder rows read with 128-bit loads when
-// aligned), runs the LIF update (same operation order as the reference kernel;
-// this file is compiled with -fmad=false, dot products use explicit fmaf) and
-// keeps the spikes in shared memory.  Phase 2: for every outgoing connection,
-// 16 decoder rows at a time, each thread accumulates w[r][i] * s[i] over its
-// neurons while applying the PES update to the same element, then the group
-// reduces the 16 partial sums in a fixed order and one thread per row runs the
-// synapse.  All index tables are int32 element offsets into the one packed
-// signal buffer.
+// warp for small ones (8 per CTA).  All dot products are summed in the order of
+// the reference's block GEMV (nb2_blockdot.cuh: tiles of 128 columns, four
+// column-strided partial sums per tile, no fused multiply-add), so J and the
+// decoded values are bit-identical to that kernel.  Phase 1: each thread computes
+// J for its neurons (x staged in shared memory, encoder rows read with 128-bit
+// loads when aligned), runs the LIF update (operation order of the reference
+// kernel, -fmad=false, expm1 / log1p correctly rounded) and keeps the spikes in
+// shared memory.  Phase 2: up to 16 decoder rows at a time (rows of one
+// connection, or one row each of a run of single-row connections); every thread
+// owns one partial sum of one (row, tile), walks it in order and applies the PES
+// update to the same elements; one thread per row then combines the partial sums
+// tile by tile and runs the synapse.  All index tables are int32 element offsets
+// into the one packed signal buffer.
 #include "nb2_common.cuh"
+#include "nb2_blockdot.cuh"
 #include "nb2_fused_common.cuh"
 #include "../../include/nengo_b200.h"
 
@@ -41,6 +45,40 @@
 #define FUSED_MAX_X NB2_FUSED_MAX_INPUT      // total encoder columns per ensemble
 #define FUSED_SMALL_N NB2_FUSED_SMALL_NEURONS
 
+// One encoder row (d columns, contiguous) times x (shared memory), added tile by tile to total.
+__device__ __forceinline__ float fused_row_dot(const float* __restrict__ row, const float* __restrict__ xv, int d,
+                                               bool vec, float total) {
+  for (int c0 = 0; c0 < d; c0 += 128) {
+    const int wt = min(128, d - c0);
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    int c = 0;
+    if (vec) {
+      const float4* row4 = reinterpret_cast<const float4*>(row + c0);
+      const float4* x4 = reinterpret_cast<const float4*>(xv + c0);
+      for (; c + 4 <= wt; c += 4) {
+        const float4 a = __ldg(row4 + (c >> 2));
+        const float4 x = x4[c >> 2];
+        s0 = bd_add(s0, bd_mul(a.x, x.x));
+        s1 = bd_add(s1, bd_mul(a.y, x.y));
+        s2 = bd_add(s2, bd_mul(a.z, x.z));
+        s3 = bd_add(s3, bd_mul(a.w, x.w));
+      }
+    } else {
+      for (; c + 4 <= wt; c += 4) {
+        s0 = bd_add(s0, bd_mul(__ldg(row + c0 + c + 0), xv[c0 + c + 0]));
+        s1 = bd_add(s1, bd_mul(__ldg(row + c0 + c + 1), xv[c0 + c + 1]));
+        s2 = bd_add(s2, bd_mul(__ldg(row + c0 + c + 2), xv[c0 + c + 2]));
+        s3 = bd_add(s3, bd_mul(__ldg(row + c0 + c + 3), xv[c0 + c + 3]));
+      }
+    }
+    if (c < wt) s0 = bd_add(s0, bd_mul(__ldg(row + c0 + c), xv[c0 + c]));
+    if (c + 1 < wt) s1 = bd_add(s1, bd_mul(__ldg(row + c0 + c + 1), xv[c0 + c + 1]));
+    if (c + 2 < wt) s2 = bd_add(s2, bd_mul(__ldg(row + c0 + c + 2), xv[c0 + c + 2]));
+    total = bd_add(total, bd_tile(s0, s1, s2, s3));
+  }
+  return total;
+}
+
 // TPE = threads per ensemble (32 or 256); NEMAX = staged neurons per ensemble
 template <int TPE, int NEMAX>
 __global__ void __launch_bounds__(FUSED_THREADS, FUSED_MIN_BLOCKS)
@@ -48,16 +86,14 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
                          const int* __restrict__ term_table, const int* __restrict__ conn_table,
                          float* data, float dt, float dt_inv) {
   constexpr int GROUPS = FUSED_THREADS / TPE;     // ensembles per CTA
-  constexpr int WARPS = TPE / 32;                 // warps per ensemble
+  constexpr int CHAINS = FUSED_RCH * ((NEMAX + 127) / 128) * 4;  // partial sums of one pass
   __shared__ __align__(16) float s_spk[GROUPS][NEMAX];
   __shared__ __align__(16) float s_x[GROUPS][FUSED_MAX_X];
-  __shared__ float s_red[GROUPS][WARPS][FUSED_RCH];
+  __shared__ float s_chain[GROUPS][CHAINS];
   __shared__ float s_ae[GROUPS][FUSED_RCH];
 
   const int grp = threadIdx.x / TPE;
   const int t = threadIdx.x % TPE;
-  const int lane = threadIdx.x & 31;
-  const int wig = t >> 5;  // warp within group
   const int slot = blockIdx.x * GROUPS + grp;
   const bool active = slot < n_ens;
   const int* e = ens_table + (size_t)(active ? ens_ids[slot] : 0) * E_STRIDE;
@@ -85,80 +121,26 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
   }
   group_sync();
 
-  // ---- phase 1: J = bias + enc . x ; LIF ----
+  // ---- phase 1: J = ((bias + enc_0 . x_0) + enc_1 . x_1) ... ; LIF ----
   if (active) {
     const float tau = bits(e[E_TAU]), ref = bits(e[E_REF]), amp = bits(e[E_AMP]);
+    const float em1_dt = bits(e[E_EM1]);
     const float* bias = data + e[E_BIAS];
     float* V = data + e[E_V];
     float* W = data + e[E_W];
     float* S = e[E_S] >= 0 ? data + e[E_S] : nullptr;
     float* Jout = e[E_J] >= 0 ? data + e[E_J] : nullptr;
-    if (vec) {
-      // four consecutive neurons per thread: 16 independent 128-bit encoder loads in flight
-      const int n4 = n >> 2;
-      for (int i4 = t; i4 < n4; i4 += TPE) {
-        const int i = i4 << 2;
-        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        int xoff = 0;
-        for (int k = 0; k < n_terms; ++k) {
-          const int d4 = terms[k * T_STRIDE + T_D] >> 2;
-          const float4* rows =
-              reinterpret_cast<const float4*>(data + terms[k * T_STRIDE + T_A]) + (size_t)i * d4;
-          const float4* xv = reinterpret_cast<const float4*>(&s_x[grp][xoff]);
-          for (int c = 0; c < d4; ++c) {
-            const float4 x4 = xv[c];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float4 a = __ldg(rows + (size_t)j * d4 + c);
-              sum[j] = fmaf(a.x, x4.x, sum[j]);
-              sum[j] = fmaf(a.y, x4.y, sum[j]);
-              sum[j] = fmaf(a.z, x4.z, sum[j]);
-              sum[j] = fmaf(a.w, x4.w, sum[j]);
-            }
-          }
-          xoff += d4 << 2;
-        }
-        const float4 b4 = *reinterpret_cast<const float4*>(bias + i);
-        float4 v4 = *reinterpret_cast<float4*>(V + i);
-        float4 w4 = *reinterpret_cast<float4*>(W + i);
-        float4 J4, s4;
-        J4.x = b4.x + sum[0]; J4.y = b4.y + sum[1]; J4.z = b4.z + sum[2]; J4.w = b4.w + sum[3];
-        s4.x = fused_lif(J4.x, v4.x, w4.x, tau, ref, amp, dt, dt_inv);
-        s4.y = fused_lif(J4.y, v4.y, w4.y, tau, ref, amp, dt, dt_inv);
-        s4.z = fused_lif(J4.z, v4.z, w4.z, tau, ref, amp, dt, dt_inv);
-        s4.w = fused_lif(J4.w, v4.w, w4.w, tau, ref, amp, dt, dt_inv);
-        *reinterpret_cast<float4*>(V + i) = v4;
-        *reinterpret_cast<float4*>(W + i) = w4;
-        if (S) *reinterpret_cast<float4*>(S + i) = s4;
-        if (Jout) *reinterpret_cast<float4*>(Jout + i) = J4;
-        *reinterpret_cast<float4*>(&s_spk[grp][i]) = s4;
-      }
-    } else
     for (int i = t; i < n; i += TPE) {
-      float sum = 0.0f;
+      float J = bias[i];
       int xoff = 0;
       for (int k = 0; k < n_terms; ++k) {
         const int d = terms[k * T_STRIDE + T_D];
         const int a0 = terms[k * T_STRIDE + T_A];
-        const float* row = data + a0 + (size_t)i * d;
-        const float* xv = &s_x[grp][xoff];
-        if (((d | a0) & 3) == 0) {
-          const float4* row4 = reinterpret_cast<const float4*>(row);
-          for (int c = 0; c < (d >> 2); ++c) {
-            const float4 a = __ldg(row4 + c);
-            sum = fmaf(a.x, xv[4 * c + 0], sum);
-            sum = fmaf(a.y, xv[4 * c + 1], sum);
-            sum = fmaf(a.z, xv[4 * c + 2], sum);
-            sum = fmaf(a.w, xv[4 * c + 3], sum);
-          }
-        } else {
-          for (int c = 0; c < d; ++c) sum = fmaf(__ldg(row + c), xv[c], sum);
-        }
+        J = fused_row_dot(data + a0 + (size_t)i * d, &s_x[grp][xoff], d, vec || ((d | a0 | xoff) & 3) == 0, J);
         xoff += d;
       }
-      const float J = bias[i] + sum;
       float v = V[i], w = W[i];
-      const float s = fused_lif(J, v, w, tau, ref, amp, dt, dt_inv);
+      const float s = fused_lif(J, v, w, tau, ref, amp, dt, dt_inv, em1_dt);
       V[i] = v;
       W[i] = w;
       if (S) S[i] = s;
@@ -170,52 +152,19 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
 
   // ---- phase 2: decode, synapse, PES ----
   const int n_conn = active ? e[E_NCONN] : 0;
-  for (int ci = 0; ci < n_conn; ++ci) {
+  const int ntile = (n + 127) >> 7;
+  const int per_row = ntile * 4;  // partial sums of one row
+  const float* spk = s_spk[grp];
+  for (int ci = 0; ci < n_conn;) {
     const int* c = conn_table + (size_t)(e[E_CONN0] + ci) * C_STRIDE;
-    // A run of single-row connections without PES (e.g. scalar edges of a recurrent graph):
-    // decode up to FUSED_RCH of them in one pass, one row each, instead of one pass per connection.
+    // A run of single-row connections without PES (e.g. the scalar edges of a recurrent graph) is
+    // decoded in one pass, one row each, instead of one pass per connection.
     int run = 0;
     while (ci + run < n_conn && run < FUSED_RCH && c[run * C_STRIDE + C_D] == 1 && c[run * C_STRIDE + C_PES] == 0)
       ++run;
-    if (run >= 2) {
-      float acc[FUSED_RCH];
-      int woff[FUSED_RCH];
-#pragma unroll
-      for (int r = 0; r < FUSED_RCH; ++r) {
-        acc[r] = 0.0f;
-        woff[r] = c[(r < run ? r : 0) * C_STRIDE + C_W];
-      }
-      for (int i = t; i < n; i += TPE) {
-        const float s = s_spk[grp][i];
-#pragma unroll
-        for (int r = 0; r < FUSED_RCH; ++r)
-          if (r < run) acc[r] = fmaf(data[woff[r] + i], s, acc[r]);
-      }
-#pragma unroll
-      for (int r = 0; r < FUSED_RCH; ++r) {
-        float v = acc[r];
-        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        if (lane == 0) s_red[grp][wig][r] = v;
-      }
-      group_sync();
-      if (t < run) {
-        const int* cr = c + t * C_STRIDE;
-        float total = 0.0f;
-        for (int w = 0; w < WARPS; ++w) total += s_red[grp][w][t];
-        data[cr[C_WEIGHTED]] = total;
-        if (cr[C_FILT] >= 0) {
-          float* y = data + cr[C_FILT];
-          if (cr[C_A0] == 0) *y = bits(cr[C_B0]) * total;
-          else *y = bits(cr[C_B0]) * total - bits(cr[C_A0]) * *y;
-        }
-      }
-      group_sync();
-      ci += run - 1;
-      continue;
-    }
-    const int d_c = active ? c[C_D] : 0;
-    float* Wd = data + c[C_W];
-    const bool pes = active && c[C_PES] != 0;
+    const bool single = run >= 2;
+    const int d_c = single ? run : c[C_D];
+    const bool pes = !single && c[C_PES] != 0;
     float* pf = pes ? data + c[C_PF] : nullptr;
     for (int r0 = 0; r0 < d_c; r0 += FUSED_RCH) {
       const int nr = min(FUSED_RCH, d_c - r0);
@@ -224,84 +173,49 @@ nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* 
         if (t < nr) s_ae[grp][t] = bits(c[C_ALPHA]) * data[c[C_ERR] + r0 + t];
         group_sync();
       }
-      float acc[FUSED_RCH];
-#pragma unroll
-      for (int r = 0; r < FUSED_RCH; ++r) acc[r] = 0.0f;
-      if (vec) {
-        // 128-bit loads of 8 decoder rows at a time: all loads of a half-pass are issued
-        // before the (possibly aliasing) PES stores of the same rows
-        const int n4 = n >> 2;
-        for (int i4 = t; i4 < n4; i4 += TPE) {
-          const float4 s4 = *reinterpret_cast<const float4*>(&s_spk[grp][i4 << 2]);
-          float4 p4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (pes) p4 = *reinterpret_cast<const float4*>(pf + (i4 << 2));
-#pragma unroll
-          for (int h = 0; h < FUSED_RCH; h += 8) {
-            float4 wv[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (h + r < nr) wv[r] = *(reinterpret_cast<const float4*>(Wd + (size_t)(r0 + h + r) * n) + i4);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (h + r < nr) {
-                float a = acc[h + r];
-                a = fmaf(wv[r].x, s4.x, a);
-                a = fmaf(wv[r].y, s4.y, a);
-                a = fmaf(wv[r].z, s4.z, a);
-                a = fmaf(wv[r].w, s4.w, a);
-                acc[h + r] = a;
-                if (pes) {
-                  const float ae = s_ae[grp][h + r];
-                  float4 o;
-                  o.x = wv[r].x + ae * p4.x;
-                  o.y = wv[r].y + ae * p4.y;
-                  o.z = wv[r].z + ae * p4.z;
-                  o.w = wv[r].w + ae * p4.w;
-                  *(reinterpret_cast<float4*>(Wd + (size_t)(r0 + h + r) * n) + i4) = o;
-                }
-              }
-            }
+      for (int u = t; u < nr * per_row; u += TPE) {
+        const int r = u / per_row, rem = u - r * per_row;
+        const int tile = rem >> 2, j = rem & 3;
+        float* w = single ? data + c[r * C_STRIDE + C_W] : data + c[C_W] + (size_t)(r0 + r) * n;
+        const int end = min(n, (tile + 1) << 7);
+        float acc = 0.0f;
+        if (pes) {
+          const float ae = s_ae[grp][r];
+#pragma unroll 4
+          for (int i = (tile << 7) + j; i < end; i += 4) {
+            const float wv = w[i];
+            acc = bd_add(acc, bd_mul(wv, spk[i]));
+            w[i] = wv + ae * pf[i];
           }
+        } else {
+#pragma unroll 8
+          for (int i = (tile << 7) + j; i < end; i += 4) acc = bd_add(acc, bd_mul(w[i], spk[i]));
         }
-      } else
-      for (int i = t; i < n; i += TPE) {
-        const float s = s_spk[grp][i];
-        const float p = pes ? pf[i] : 0.0f;
-#pragma unroll
-        for (int r = 0; r < FUSED_RCH; ++r) {
-          if (r < nr) {
-            float* wp = Wd + (size_t)(r0 + r) * n + i;
-            const float w = *wp;
-            acc[r] = fmaf(w, s, acc[r]);
-            if (pes) *wp = w + s_ae[grp][r] * p;
-          }
-        }
-      }
-      // fixed-order reduction: lanes (xor tree), then warps in index order
-#pragma unroll
-      for (int r = 0; r < FUSED_RCH; ++r) {
-        float v = acc[r];
-        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        if (lane == 0) s_red[grp][wig][r] = v;
+        s_chain[grp][u] = acc;
       }
       group_sync();
       if (active && t < nr) {
+        const float* ch = &s_chain[grp][t * per_row];
         float total = 0.0f;
-        for (int w = 0; w < WARPS; ++w) total += s_red[grp][w][t];
-        data[c[C_WEIGHTED] + r0 + t] = total;
-        if (c[C_FILT] >= 0) {
-          float* y = data + c[C_FILT] + r0 + t;
+        for (int tile = 0; tile < ntile; ++tile)
+          total = bd_add(total, bd_tile(ch[4 * tile], ch[4 * tile + 1], ch[4 * tile + 2], ch[4 * tile + 3]));
+        const int* cr = single ? c + t * C_STRIDE : c;
+        const int row = single ? 0 : r0 + t;
+        data[cr[C_WEIGHTED] + row] = total;
+        if (cr[C_FILT] >= 0) {
+          float* y = data + cr[C_FILT] + row;
           // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
-          if (c[C_A0] == 0) *y = bits(c[C_B0]) * total;
-          else *y = bits(c[C_B0]) * total - bits(c[C_A0]) * *y;
+          if (cr[C_A0] == 0) *y = bits(cr[C_B0]) * total;
+          else *y = bits(cr[C_B0]) * total - bits(cr[C_A0]) * *y;
         }
       }
       group_sync();
     }
     if (pes) {
       const float b0 = bits(c[C_PFB0]), a0 = bits(c[C_PFA0]);
-      for (int i = t; i < n; i += TPE) pf[i] = b0 * s_spk[grp][i] - a0 * pf[i];
+      for (int i = t; i < n; i += TPE) pf[i] = b0 * spk[i] - a0 * pf[i];
     }
+    ci += single ? run : 1;
   }
 }
 

@@ -17,15 +17,20 @@
 //    sources are 16-byte aligned by construction (the host only streams
 //    ensembles whose arrays start on multiples of 4 floats).  The warp's next
 //    record rides along with the copies.
-//  * E record: one lane per neuron (4 neurons per lane); J = bias + enc . x with
-//    the staged rows walked diagonally (shared-memory banks), LIF update in the
-//    operation order of the reference kernel (this file is compiled with
-//    -fmad=false, dot products use explicit fmaf), V / W / spikes / new
-//    activity trace written straight to global memory, spikes and the OLD trace
-//    kept in a per-ensemble slot of shared memory for the D records.
-//  * D record: lanes over groups of 4 neurons; decoded = W . s accumulated per
-//    row, the PES update w += (alpha * err) * trace applied to the same element
-//    and written straight back, one shuffle reduction per row, then the synapse.
+//  * All dot products are summed in the order of the reference's block GEMV
+//    (nb2_blockdot.cuh), so J and the decoded values are bit-identical to it.
+//  * E record: one lane per neuron (4 neurons per lane); J = bias + enc . x from
+//    the staged rows (128-bit shared loads, lanes time-skewed against bank
+//    conflicts), LIF update in the operation order of the reference kernel
+//    (this file is compiled with -fmad=false; expm1 / log1p correctly rounded),
+//    V / W / spikes / new activity trace written straight to global memory,
+//    spikes and the OLD trace kept in a per-ensemble slot of shared memory for
+//    the D records.
+//  * D record: a pair of lanes owns the four partial sums of one (row, 128-column
+//    tile) and walks them in order; the PES update w += (alpha * err) * trace is
+//    applied to the same element in the stage, which then goes back to global
+//    memory as one bulk async store; two shuffles form the tile value, the tiles
+//    of a row are added in order, then the synapse.
 //  * Slots are handed from E to D records and back through two counters per slot
 //    in shared memory; a record only ever waits for records that precede it in
 //    the CTA's list, so the lowest unfinished record can always run.
@@ -44,6 +49,7 @@
 // flag and leaves.
 #include "nb2_common.cuh"
 #include "nb2_pipe.cuh"
+#include "nb2_blockdot.cuh"
 #include "nb2_fused_common.cuh"
 #include "nb2_exchange_common.cuh"
 #include "../../include/nengo_b200.h"
@@ -56,7 +62,8 @@
 #define ST_SLOTS NB2_STREAM_SLOTS
 #define ST_REC 32
 #define ST_MAXCOPY 8
-#define ST_ROWS 4  // decoder rows per D record, neurons per lane in an E record
+#define ST_ROWS 4  // neurons per lane in an E record
+#define ST_DITEMS 16  // (row, tile) pairs of a D record: two lanes each
 
 struct StreamParams {
   const int* records;  // [n_records][32]
@@ -92,6 +99,8 @@ __device__ __forceinline__ void stream_issue(const StreamParams& p, StreamStage&
   const bool more = i + ST_NW < n;
   uint32_t tx = more ? ST_REC * 4u : 0u;
   for (int q = 0; q < ncopy; ++q) tx += (uint32_t)r[R_COPY0 + 3 * q + 1];
+  // a PES record's write-back (bulk store out of this stage) must have read the stage
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   // the stage was read through the generic proxy; order those reads before the async-proxy writes
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
@@ -205,30 +214,34 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       }
       // the slot's previous ensemble must have been decoded completely
       ok = stream_wait_count(&d_done[h0.z], h1.z, &s_abort, lane);
+      const float em1_dt = bits(__ldg(e + E_EM1));
       // blocks of 128 neurons: 4 per lane
       for (int base = 0; ok && base < ne; base += 32 * ST_ROWS) {
         const int nb = min(32 * ST_ROWS, ne - base);
-        float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float tot[ST_ROWS];
         int roff[ST_ROWS];
 #pragma unroll
-        for (int j = 0; j < ST_ROWS; ++j) roff[j] = base + min(lane + 32 * j, nb - 1);
+        for (int j = 0; j < ST_ROWS; ++j) {
+          roff[j] = base + min(lane + 32 * j, nb - 1);
+          tot[j] = s_bias[roff[j]];  // J = ((bias + term 0) + term 1) + ...
+        }
         const int NR = (nb + 31) >> 5;
         int xoff = 0;
         for (int k = 0; k < n_terms; ++k) {
           const int d = __ldg(terms + k * T_STRIDE + T_D);
           const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
-          if (NR == 1) pipe_segment_mode<1>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
-          else if (NR == 2) pipe_segment_mode<2>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
-          else pipe_segment_mode<4>(a, st.x + xoff, nullptr, 1, d, lane, roff, acc);
+          if (NR == 1) block_rows_staged4<1>(a, st.x + xoff, d, lane, roff, tot, 1.0);
+          else if (NR == 2) block_rows_staged4<2>(a, st.x + xoff, d, lane, roff, tot, 1.0);
+          else block_rows_staged4<4>(a, st.x + xoff, d, lane, roff, tot, 1.0);
           xoff += d;
         }
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
           const int r = base + lane + 32 * j;
           if (lane + 32 * j < nb) {
-            const float J = s_bias[r] + acc[j];
+            const float J = tot[j];
             float v = s_V[r], w = s_W[r];
-            const float s = fused_lif(J, v, w, tau, ref, amp, p.dt, p.dt_inv);
+            const float s = fused_lif(J, v, w, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
             data[eV + i0 + r] = v;
             data[eW + i0 + r] = w;
             if (eS >= 0) data[eS + i0 + r] = s;
@@ -253,63 +266,78 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       const int* c = p.conn_table + (size_t)h0.w * C_STRIDE;
       const int r0 = h1.x, nr = h1.w;
       const int n_e = __ldg(e + E_N);
-      const int n4 = n_e >> 2;
+      const int ntile = (n_e + 127) >> 7;
       const bool pes = __ldg(c + C_PES) != 0;
-      float ae[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
-      if (pes) {
+      // lanes 2i, 2i + 1 own (row, tile) pair i = row * ntile + tile: the even lane the partial
+      // sums 0 and 1 of the tile, the odd lane 2 and 3 (nr * ntile <= ST_DITEMS by construction)
+      const int item = lane >> 1, jp = lane & 1;
+      const int r = item / ntile, t = item - r * ntile;
+      const bool valid = r < nr;
+      const int len = valid ? min(32, (n_e - (t << 7)) >> 2) : 0;  // groups of 4 columns in the tile
+      // the 16 lanes of a 64-bit shared load read 8 pairs at the same column group otherwise
+      // (tiles are 128 floats apart: same banks): pair i starts i mod 8 iterations late
+      const int skew = item & 7;
+      float ae = 0.0f;
+      if (pes && valid) {
         // alpha * error, formed once per row as in `alpha * aa * xx` (left to right)
-        const float alpha = bits(__ldg(c + C_ALPHA));
-        const float* err = data + __ldg(c + C_ERR) + r0;
-#pragma unroll
-        for (int r = 0; r < ST_ROWS; ++r)
-          if (r < nr) ae[r] = alpha * err[r];
+        ae = bits(__ldg(c + C_ALPHA)) * data[__ldg(c + C_ERR) + r0 + r];
       }
-      float4* Wd = reinterpret_cast<float4*>(data + __ldg(c + C_W)) + (size_t)r0 * n4;
-      const float4* sw = reinterpret_cast<const float4*>(st.buf);
-      const float4* spk4 = reinterpret_cast<const float4*>(slot.spk);
-      const float4* pfo4 = reinterpret_cast<const float4*>(slot.pfo);
+      const int col0 = (t << 7) + 2 * jp;
+      float* wrow = st.buf + (valid ? r * n_e : 0) + col0;
+      const float* srow = slot.spk + col0;
+      const float* prow = slot.pfo + col0;
       // every E record of this ensemble must have delivered its spikes
       ok = stream_wait_count(&e_done[h0.z], h1.z, &s_abort, lane);
       if (ok) {
-        float acc[ST_ROWS] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int i4 = lane; i4 < n4; i4 += 32) {
-          const float4 s4 = spk4[i4];
-          float4 p4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (pes) p4 = pfo4[i4];
-#pragma unroll
-          for (int r = 0; r < ST_ROWS; ++r) {
-            if (r < nr) {
-              const float4 w4 = sw[r * n4 + i4];
-              float a = acc[r];
-              a = fmaf(w4.x, s4.x, a);
-              a = fmaf(w4.y, s4.y, a);
-              a = fmaf(w4.z, s4.z, a);
-              a = fmaf(w4.w, s4.w, a);
-              acc[r] = a;
-              if (pes) {
-                float4 o;
-                o.x = w4.x + ae[r] * p4.x;
-                o.y = w4.y + ae[r] * p4.y;
-                o.z = w4.z + ae[r] * p4.z;
-                o.w = w4.w + ae[r] * p4.w;
-                Wd[(size_t)r * n4 + i4] = o;
-              }
+        float ca = 0.0f, cb = 0.0f;
+        const int kmax = min(32, n_e >> 2) + 7;
+        if (pes) {
+          for (int k = 0; k < kmax; ++k) {
+            const int q = k - skew;
+            if (q >= 0 && q < len) {
+              float2 w2 = *reinterpret_cast<const float2*>(wrow + 4 * q);
+              const float2 s2 = *reinterpret_cast<const float2*>(srow + 4 * q);
+              const float2 p2 = *reinterpret_cast<const float2*>(prow + 4 * q);
+              ca = bd_add(ca, bd_mul(w2.x, s2.x));
+              cb = bd_add(cb, bd_mul(w2.y, s2.y));
+              w2.x = w2.x + ae * p2.x;
+              w2.y = w2.y + ae * p2.y;
+              *reinterpret_cast<float2*>(wrow + 4 * q) = w2;
+            }
+          }
+          // the updated rows go back as one bulk store: writes of all lanes -> async proxy
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            float* Wd = data + __ldg(c + C_W) + (size_t)r0 * n_e;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(Wd),
+                         "r"(pipe_smem(st.buf)), "r"((uint32_t)(nr * n_e * 4))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else {
+          for (int k = 0; k < kmax; ++k) {
+            const int q = k - skew;
+            if (q >= 0 && q < len) {
+              const float2 w2 = *reinterpret_cast<const float2*>(wrow + 4 * q);
+              const float2 s2 = *reinterpret_cast<const float2*>(srow + 4 * q);
+              ca = bd_add(ca, bd_mul(w2.x, s2.x));
+              cb = bd_add(cb, bd_mul(w2.y, s2.y));
             }
           }
         }
-        // fixed-order reduction over the lanes (xor tree)
-#pragma unroll
-        for (int r = 0; r < ST_ROWS; ++r)
-          for (int off = 16; off > 0; off >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
-        if (lane < nr) {
-          float total = acc[0];
-          if (lane == 1) total = acc[1];
-          if (lane == 2) total = acc[2];
-          if (lane == 3) total = acc[3];
-          data[__ldg(c + C_WEIGHTED) + r0 + lane] = total;
+        // tile = (s0 + s2) + (s1 + s3); the tiles of a row are added in order
+        const float xa = bd_add(ca, __shfl_xor_sync(0xffffffffu, ca, 1));
+        const float xb = bd_add(cb, __shfl_xor_sync(0xffffffffu, cb, 1));
+        const float tile = bd_add(xa, xb);
+        const int lane_t0 = 2 * (valid ? r : 0) * ntile;
+        float total = 0.0f;
+        for (int tt = 0; tt < ntile; ++tt) total = bd_add(total, __shfl_sync(0xffffffffu, tile, lane_t0 + 2 * tt));
+        if (valid && t == 0 && jp == 0) {
+          data[__ldg(c + C_WEIGHTED) + r0 + r] = total;
           const int filt = __ldg(c + C_FILT);
           if (filt >= 0) {
-            const int yi = filt + r0 + lane;
+            const int yi = filt + r0 + r;
             // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
             const int a0 = __ldg(c + C_A0);
             float out = bits(__ldg(c + C_B0)) * total;
@@ -338,6 +366,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       stream_stage_x(p, st, st.rec[(m + 1) & 1], lane);
     }
   }
+  // write-backs still in flight out of this warp's stage
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   if (xpush) {
     // The decoded values of this CTA's ensembles form one contiguous run of this rank's
     // segment (the host checked): its last warp stores the run into every peer's staging

@@ -5,9 +5,16 @@
 // variable when gind0 < sizes[gind1].
 //
 // Compiled with -fmad=false so that the LIF update keeps the reference's
-// operation order (no fused multiply-add contraction).
+// operation order (no fused multiply-add contraction).  expm1 / log1p / exp are
+// evaluated in double and rounded once to float (correctly rounded float32
+// results, independent of the math library), like the CPU evaluation of the
+// reference kernels this path is checked against.
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
+
+__device__ __forceinline__ float nb2_expm1_cr(float x) { return (float)expm1((double)x); }
+__device__ __forceinline__ float nb2_log1p_cr(float x) { return (float)log1p((double)x); }
+__device__ __forceinline__ float nb2_exp_cr(float x) { return (float)exp((double)x); }
 
 __device__ __forceinline__ float nb2_var_load(const nb2_var& v, int block, int i) {
   return v.buf ? v.buf[v.starts[block] + i] : v.value;
@@ -26,11 +33,11 @@ __device__ __forceinline__ void nb2_lif_core(float J, float& V, float& W, float&
     W -= dtu;
     const float delta_t = (W > dtu) ? 0.0f : (W < 0.0f) ? dtu : dtu - W;
     float dV;
-    if (adaptive) dV = -expm1f(-delta_t / tau) * (J - Nadapt - V);
-    else dV = -expm1f(-delta_t / tau) * (J - V);
+    if (adaptive) dV = -nb2_expm1_cr(-delta_t / tau) * (J - Nadapt - V);
+    else dV = -nb2_expm1_cr(-delta_t / tau) * (J - V);
     V += dV;
     if (V > V_threshold) {
-      const float t_spike = dtu + tau * log1pf(-(V - V_threshold) / (J - V_threshold));
+      const float t_spike = dtu + tau * nb2_log1p_cr(-(V - V_threshold) / (J - V_threshold));
       W = ref + t_spike;
       V = 0.0f;
       spiked = true;
@@ -83,7 +90,7 @@ __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict
     } else {
       J = fmaxf(J - 1.0f, 0.0f);
     }
-    const float R = amp / (ref + tau * log1pf(1.0f / J));
+    const float R = amp / (ref + tau * nb2_log1p_cr(1.0f / J));
     nb2_var_store(a.S, gind1, gind0, R);
     if (a.adaptive) {
       const float tau_n = nb2_var_load(a.tau_n, gind1, gind0);
@@ -108,7 +115,7 @@ __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict
     // plan_sigmoid (:1267-1268)
     const float J = nb2_var_load(a.J, gind1, gind0);
     const float ref = nb2_var_load(a.ref, gind1, gind0);
-    const float R = J < -88.0f ? 0.0f : J > 15.0f ? 1.0f / ref : 1.0f / (ref * (1.0f + expf(-J)));
+    const float R = J < -88.0f ? 0.0f : J > 15.0f ? 1.0f / ref : 1.0f / (ref * (1.0f + nb2_exp_cr(-J)));
     nb2_var_store(a.S, gind1, gind0, R);
   }
 }

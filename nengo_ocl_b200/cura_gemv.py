@@ -718,10 +718,12 @@ class gemv_prog:
         """``block_impl`` (clra_gemv.py:861-1175) as one single-pass plan.
 
         The reference launches a tile kernel that writes partial sums to a
-        scratch buffer and a second kernel that reduces them; here both collapse
-        into the single-pass kernel, so one plan is returned.  The tile tables are
-        still built (``plan.tile_tables``) because they define the reference's
-        launch geometry and are part of the bit-exact index-plan contract.
+        scratch buffer and a second kernel that reduces them; here one kernel
+        (``nb2_gemv_block``) forms the same tile values in the same order and adds
+        them to the output directly, so results are bit-identical to the pair and
+        one plan is returned.  The tile tables are still built
+        (``plan.tile_tables``) because they define the reference's launch
+        geometry and are part of the bit-exact index-plan contract.
         """
         items = list(items)
         if self.cl_alpha is not None or self.cl_beta is not None or self.cl_gamma is not None:
@@ -731,8 +733,46 @@ class gemv_prog:
         self._check_supported(False)
         tables = self.block_tile_tables(items)
         n_tiles = max(len(tables["gstructure"]), 1)
-        plan = self._device_plan(items, "cura_gemv.block_impl", (4, 32, n_tiles), (4, 32, 1),
-                                 per_item_scales=False)
+        table, xstrides, D, _, stride = self.gstructure_table(items)
+        # work units = the reference's 32-row blocks; blocks of at most 8 rows and 8 tiles per row
+        # (scalar gains, single-row decoders) are taken by one warp each
+        M = table[:, 4 * D + 3].astype(np.int64) if len(table) else np.zeros(0, np.int64)
+        if D > 0 and len(table):
+            n_dots = table[:, 4 * D + 2].astype(np.int64)
+            mask = np.arange(D)[None, :] < n_dots[:, None]
+            tiles_per_row = ((-(-table[:, 3 * D:4 * D].astype(np.int64) // 128)) * mask).sum(axis=1)
+        else:
+            tiles_per_row = np.zeros(len(table), np.int64)
+        n_blocks = -(-M // 32)
+        rows_of = np.repeat(np.arange(len(table)), n_blocks)
+        first = np.arange(int(n_blocks.sum())) - np.repeat(np.cumsum(n_blocks) - n_blocks, n_blocks)
+        units = np.zeros((len(rows_of), 4), dtype=np.int32)
+        units[:, 0], units[:, 1] = rows_of, first * 32
+        units[:, 2] = np.minimum(32, M[rows_of] - first * 32)
+        small = (units[:, 2] <= 8) & (tiles_per_row[rows_of] <= 8)
+        cta_units, warp_units = units[~small], units[small]
+        queue = self.queue
+        d_table = to_device(queue, table)
+        d_xstr = to_device(queue, xstrides[:, :max(D, 1)]) if np.any(xstrides != 1) else None
+        d_cta = to_device(queue, cta_units) if len(cta_units) else None
+        d_warp = to_device(queue, warp_units) if len(warp_units) else None
+        A, X, Y, Y_in = self.A.cl_buf, self.X.cl_buf, self.Y.cl_buf, self.Y_in.cl_buf
+        p = lambda arr: None if arr is None else arr.ptr
+        fn, check = _capi.lib().nb2_gemv_block, _capi.check
+        args = (d_table.ptr, stride, D, p(d_xstr), p(d_cta), len(cta_units), p(d_warp), len(warp_units), A.ptr,
+                X.ptr, Y_in.ptr, Y.ptr, self.float_alpha, self.float_beta, self.float_gamma)
+
+        def launch(stream):
+            check(fn(stream, *args))
+
+        plan = Plan(queue, launch, (4, 32, n_tiles), (4, 32, 1),
+                    n_launches=int(len(cta_units) > 0) + int(len(warp_units) > 0), name="cura_gemv.block_impl",
+                    tag=self.tag, bw_per_call=bw_from_geometry(self.geometry, items),
+                    flops_per_call=flops_from_geometry(self.geometry, items))
+        plan.full_args = (d_table, d_xstr, d_cta, d_warp, A, X, Y, Y_in)
+        plan.gstructure = table
+        plan.worklist = (cta_units, warp_units)
+        plan.description = self.geometry_summary(items) if items else "empty"
         plan.tile_tables = tables
         return [plan]
 

@@ -239,7 +239,9 @@ def fold_resets_into_products(operators):
         dots = [op for op, kind, s in ws if isinstance(op, MultiDotInc) and kind == "incs" and s is base
                 and op.Y is base and op.Y_in is base and op._signal_beta is None and op._float_beta == 1
                 and op.gamma == 0]
-        if len(resets) == 1 and len(dots) == 1:
+        # (only a reset to zero: "0 + terms" is exact, any other value would be added after
+        # the terms instead of before them and round differently)
+        if len(resets) == 1 and len(dots) == 1 and resets[0].value == 0:
             dots[0]._float_beta, dots[0].gamma, dots[0]._incs_Y = 0.0, float(resets[0].value), False
             dropped.add(resets[0])
     return dropped
@@ -282,11 +284,15 @@ def fused_tables(sim, members):
     sidx = sim.sidx
     st = lambda sig: int(starts[sidx[sig]])
     ens, terms, conns = [], [], []
+    dt32 = np.float32(sim.model.dt)
     for mem in members:
         nt = mem["neurons"].neurons
+        # expm1(-dt / tau) of a neuron that integrates over the whole step: the float32 quotient,
+        # evaluated in double and rounded once (what the kernels do for any other interval)
+        em1_dt = np.float32(np.expm1(np.float64(-dt32 / np.float32(nt.tau_rc))))
         row = [mem["n"], -1, st(mem["state"][0]), st(mem["state"][1]), st(mem["out"]) if mem["store_spikes"] else -1,
                st(mem["bias"]), len(mem["enc_terms"]), len(terms), len(mem["conns"]), len(conns),
-               _fbits(nt.tau_rc), _fbits(nt.tau_ref), _fbits(nt.amplitude), 0, 0, 0]
+               _fbits(nt.tau_rc), _fbits(nt.tau_ref), _fbits(nt.amplitude), 0, _fbits(em1_dt), 0]
         for A, X in mem["enc_terms"]:
             xi = sidx[X]
             terms.append([st(A), A.shape[1], st(X), int(sim.all_data.stride0s[xi])])
@@ -337,7 +343,7 @@ STREAM_SLOTS = _STREAM["NB2_STREAM_SLOTS"]
 STREAM_MAX_NEURONS = _STREAM["NB2_STREAM_MAX_NEURONS"]
 STREAM_MAX_INPUT = _STREAM["NB2_STREAM_MAX_INPUT"]
 STREAM_MIN_NEURONS = 256
-STREAM_REC, STREAM_ROWS, STREAM_CHUNK = 32, 4, 192
+STREAM_REC, STREAM_DITEMS, STREAM_CHUNK = 32, 16, 192
 
 
 def streamable(ens, terms, conns):
@@ -398,7 +404,8 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
             for q, cp in enumerate(copies):
                 rec[8 + 3 * q:11 + 3 * q] = cp
             E.append(rec)
-        nr_max = max(1, min(STREAM_ROWS, STREAM_STAGE_FLOATS // n))
+        # a D record holds at most STREAM_DITEMS (row, 128-column tile) pairs: two lanes each
+        nr_max = max(1, min(STREAM_DITEMS // (-(-n // 128)), STREAM_STAGE_FLOATS // n))
         for k in range(nc):
             d_c = int(conns[c0 + k, 1])
             for r0 in range(0, d_c, nr_max):

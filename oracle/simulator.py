@@ -12,12 +12,16 @@ arithmetic follows what the reference launches for that operator type
 (nengo_ocl/simulator.py:746-1345): e.g. all ``DotInc`` into one target are
 summed first and added to the target once (``MultiDotInc``), a lowpass
 ``LinearFilter`` is ``y = b0*x - a0*y``, PES writes
-``delta = alpha * outer(error, pre)``.  Dot products are accumulated in
-float64 and rounded to float32 once (order-independent reference value).
+``delta = alpha * outer(error, pre)``.  Dot products follow the kernel the
+reference simulator plans for every ``MultiDotInc``, ``plan_block_gemv``
+(nengo_ocl/simulator.py:803, clra_gemv.py:1018-1058,1137-1153): float32, four
+column-strided partial sums per 128-column tile combined as
+``(s0 + s2) + (s1 + s3)``, tiles added to the target in order.
 """
 
 import numpy as np
 
+from oracle import cport as C
 from oracle import kernels as K
 
 f32 = np.float32
@@ -157,26 +161,31 @@ class OracleSimulator:
         else:
             dst[...] = src
 
-    def _dot_terms(self, ops):
-        acc = None
+    @staticmethod
+    def _as2d(v):
+        return v.reshape(1, 1) if v.ndim == 0 else v.reshape(v.shape[0], 1) if v.ndim == 1 else v
+
+    def _block_inc(self, y_sig, ops):
+        """``y += sum_i A_i . x_i`` as one multi-term block GEMV with alpha = beta = 1, gamma = 0
+        (MultiDotInc.convert_to / get_views, nengo_ocl/operators.py:50-67,159-191: operands
+        become 2-D, a (1, 1) matrix swaps roles with its vector)."""
+        y = self.view(y_sig)
+        total = np.array(y, dtype=np.float32).reshape(-1)  # 1.0 * y_in
         for op in ops:
             A, X = self.view(op.A), self.view(op.X)
-            if A.ndim == 0 or A.size == 1 and A.ndim < 2:
-                term = A.reshape(()).astype(np.float64) * X.astype(np.float64)
-            elif A.ndim == 1:
-                term = np.atleast_1d(A.astype(np.float64) @ X.astype(np.float64))
-            else:
-                term = A.astype(np.float64) @ X.astype(np.float64)
-            acc = term if acc is None else acc + term
-        return acc.astype(np.float32)
+            X2 = self._as2d(X)
+            A2 = A.reshape(1, A.shape[0]) if (A.ndim == 1 and X.ndim == 1) else self._as2d(A)
+            if A2.shape == (1, 1):
+                A2, X2 = X2, A2
+            assert A2.shape == (total.size, X2.shape[0]) and X2.shape[1] == 1, (A.shape, X.shape, y.shape)
+            C.block_rows(total, A2, X2[:, 0])
+        y[...] = total.reshape(y.shape)  # + 0.0
 
     def _do_DotInc(self, op):
-        y = self.view(op.Y)
-        y[...] = y + self._dot_terms([op]).reshape(y.shape)
+        self._block_inc(op.Y, [op])
 
     def _do__DotGroup(self, op):
-        y = self.view(op.Y)
-        y[...] = y + self._dot_terms(op.group).reshape(y.shape)
+        self._block_inc(op.Y, op.group)
 
     def _do_SparseDotInc(self, op):
         # the reference's CSR kernel in increment mode (clra_gemv.py:1591-1617)

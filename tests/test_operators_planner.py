@@ -155,10 +155,13 @@ def test_gather_sum_over_slices_and_reset_folding():
     y = m.Signal(np.zeros(3), name="y")
     A = m.Signal(np.eye(3), name="A", readonly=True)
     x = m.Signal(np.ones(3), name="x")
-    reset, dot = m.Reset(y, value=0.5), MultiDotInc.convert_to(m.DotInc(A, x, y))
+    reset, dot = m.Reset(y), MultiDotInc.convert_to(m.DotInc(A, x, y))
     dropped = fusion.fold_resets_into_products([reset, dot])
     assert dropped == {reset}
-    assert dot._float_beta == 0 and dot.gamma == 0.5 and dot.sets == [y] and dot.incs == []
+    assert dot._float_beta == 0 and dot.gamma == 0 and dot.sets == [y] and dot.incs == []
+    # a reset to another value stays: "value + terms" and "terms + value" round differently
+    reset_h, dot_h = m.Reset(y, value=0.5), MultiDotInc.convert_to(m.DotInc(A, x, y))
+    assert fusion.fold_resets_into_products([reset_h, dot_h]) == set() and dot_h._float_beta == 1
     # a second writer of y keeps the reset
     reset2, dot2 = m.Reset(y), MultiDotInc.convert_to(m.DotInc(A, x, y))
     assert fusion.fold_resets_into_products([reset2, dot2, m.Copy(x, y, inc=True)]) == set()

@@ -331,7 +331,8 @@ def test_stream_records_cover_every_ensemble_once():
             else:
                 assert kind == 2 and e_done[slot] >= target, "a D record would wait for a later E record"
                 c, r0, nr = int(rec[3]), int(rec[4]), int(rec[7])
-                assert int(ens[r, 9]) <= c < int(ens[r, 9]) + int(ens[r, 8]) and 0 < nr <= 4 and nr * n <= 4096
+                assert int(ens[r, 9]) <= c < int(ens[r, 9]) + int(ens[r, 8]) and 0 < nr and nr * (-(-n // 128)) <= fusion.STREAM_DITEMS
+                assert nr * n <= fusion.STREAM_STAGE_FLOATS
                 dec_rows.setdefault(c, np.zeros(conns[c, 1], int))[r0:r0 + nr] += 1
                 assert rec[8] == conns[c, 0] + r0 * n and rec[9] == 4 * nr * n
                 d_done[slot] += 1
