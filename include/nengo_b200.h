@@ -243,9 +243,13 @@ int nb2_neurons(void* stream, int kind, int n_blocks, int block_size, const int*
 
 /* plan_direct :954-1025: the reference compiles a translated Python function
  * per node; here the translation is a postfix program run by one interpreter
- * kernel.  prog: n_ops int32 pairs {opcode, operand}; consts: float pool.
- * Inputs: up to 2 ragged inputs (starts table + buffer + dim); one output. */
-int nb2_direct(void* stream, int n_items, const int* prog, int n_ops, const float* consts,
+ * kernel.  prog: n_ops int32 pairs {opcode, operand}; consts: double pool (the
+ * program is evaluated in double and results rounded to float when stored, as
+ * the Python function itself computes); max_depth: evaluation-stack depth the
+ * program needs, at most NB2_DIRECT_STACK (csrc/nb2_direct_ops.h) or the call
+ * is rejected.  Inputs: up to 2 ragged inputs (starts table + buffer + dim);
+ * one output. */
+int nb2_direct(void* stream, int n_items, const int* prog, int n_ops, int max_depth, const double* consts,
                int out_dim, const int* in0_starts, const float* in0, const int* in1_starts,
                const float* in1, const int* out_starts, float* out);
 

@@ -30,10 +30,12 @@ OUTPUT_NAME = "OUTPUT__"
 def _load_opcodes():
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "nb2_direct_ops.h")
     with open(path) as f:
-        return {m.group(1): int(m.group(2)) for m in re.finditer(r"#define NB2_OP_(\w+) (\d+)", f.read())}
+        text = f.read()
+    ops = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define NB2_OP_(\w+) (\d+)", text)}
+    return ops, int(re.search(r"#define NB2_DIRECT_STACK (\d+)", text).group(1))
 
 
-OPS = _load_opcodes()
+OPS, MAX_STACK = _load_opcodes()
 
 BINOPS = {ast.Add: "ADD", ast.Sub: "SUB", ast.Mult: "MUL", ast.Div: "DIV", ast.Pow: "POW", ast.Mod: "MOD"}
 CMPOPS = {ast.Lt: "LT", ast.LtE: "LE", ast.Gt: "GT", ast.GtE: "GE", ast.Eq: "EQ", ast.NotEq: "NE"}
@@ -60,6 +62,12 @@ class DeviceFunction:
         self.out_dim = out_dim
         self.translator = _Translator(fn, self.in_dims)
         self.program, self.constants, n_out = self.translator.translate()
+        # the interpreter evaluates on a fixed-size stack: a program that needs more is not run
+        # on the device (the caller then evaluates the function on the host)
+        self.max_depth = stack_depth(self.program)
+        if self.max_depth > MAX_STACK:
+            raise NotImplementedError("expression needs %d stack slots, the device interpreter has %d"
+                                      % (self.max_depth, MAX_STACK))
         if out_dim is not None and n_out != out_dim:
             raise NotImplementedError("function returns %d values, expected %d" % (n_out, out_dim))
         self.out_dim = n_out
@@ -302,6 +310,27 @@ class _Translator(ast.NodeVisitor):
         return self._call(fname, args)
 
 
+_PUSHES = {OPS["CONST"], OPS["IN0"], OPS["IN1"]}
+_UNARY = {OPS[name] for name in ("NEG", "NOT", "SIN", "COS", "TAN", "ASIN", "ACOS", "ATAN", "SINH", "COSH", "TANH",
+                                 "EXP", "EXPM1", "LOG", "LOG2", "LOG10", "LOG1P", "SQRT", "ABS", "FLOOR", "CEIL",
+                                 "ROUND", "SIGN")}
+
+
+def stack_depth(program):
+    """Largest number of values a postfix program holds on the evaluation stack."""
+    depth = deepest = 0
+    for op, _ in program:
+        if op in _PUSHES:
+            depth += 1
+        elif op == OPS["SELECT"]:
+            depth -= 2
+        elif op == OPS["STORE"] or op not in _UNARY:
+            depth -= 1  # a store pops one value, a binary operator replaces two by one
+        deepest = max(deepest, depth)
+    assert depth == 0, "unbalanced program"
+    return deepest
+
+
 def is_translatable(fn, in_dims, out_dim=None):
     try:
         DeviceFunction(fn, in_dims, out_dim)
@@ -310,4 +339,5 @@ def is_translatable(fn, in_dims, out_dim=None):
         return False
 
 
-__all__ = ["DeviceFunction", "OclFunction", "OUTPUT_NAME", "OPS", "FUNCS", "is_translatable", "math"]
+__all__ = ["DeviceFunction", "OclFunction", "OUTPUT_NAME", "OPS", "FUNCS", "MAX_STACK", "stack_depth",
+           "is_translatable", "math"]

@@ -10,13 +10,16 @@
 // Two mappings are provided.
 //  * lane per row (block_rows_*): a lane walks its own rows; the four partial
 //    sums are four registers per row.  Rows staged in shared memory with a pitch
-//    that is a multiple of 4 floats are read with 128-bit loads; lanes whose
-//    rows would fall into the same banks start a few iterations later than
-//    their neighbours ("time skew") instead of walking the columns in a
-//    rotated order, which would change the summation order.
-//  * lane per partial sum (chain_*): for short, wide matrices (decoders) every
-//    lane owns one or two of the 4 partial sums of one (row, tile) and walks
-//    them sequentially; the tile value is formed with two shuffles.
+//    that is a multiple of 4 floats are read with 128-bit loads.  Optionally the
+//    lanes whose rows fall into the same banks start a few iterations later than
+//    their neighbours ("time skew"; walking the columns in a rotated order
+//    instead would change the summation order); measured on the fused step the
+//    skew's extra iterations cost slightly more than the bank conflicts it
+//    removes, so the default is off.
+//  * lane per partial sum: for short, wide matrices (decoders) every lane owns
+//    one or two of the 4 partial sums of one (row, tile) and walks them
+//    sequentially; the tile value is formed with two shuffles (see the D records
+//    of nb2_fused_stream.cu, nb2_fused.cu and nb2_gemv_block.cu).
 #pragma once
 #include "nb2_common.cuh"
 
@@ -40,7 +43,7 @@ __device__ __forceinline__ int bd_gcd8(int v) { return (v & 1) ? 1 : (v & 2) ? 2
 template <int NR>
 __device__ __forceinline__ void block_rows_staged4(const float* __restrict__ a, const float* __restrict__ x, int w,
                                                    int lane, const int (&roff)[4], float (&total)[4],
-                                                   double alpha) {
+                                                   double alpha, bool use_skew = false) {
   const int chunks_row = w >> 2;  // float4 per row
   const float4* x4 = reinterpret_cast<const float4*>(x);
   const float4* a4[4];
@@ -49,7 +52,7 @@ __device__ __forceinline__ void block_rows_staged4(const float* __restrict__ a, 
   // A 128-bit shared load is served 8 lanes at a time; those lanes read rows 8 apart at
   // most, i.e. chunk indices row * chunks_row + q: g = gcd(chunks_row, 8) of them collide
   // unless they are g different q apart.
-  const int g = bd_gcd8(chunks_row);
+  const int g = use_skew ? bd_gcd8(chunks_row) : 1;
   const int skew = ((lane & 7) * g) >> 3;
   for (int c0 = 0; c0 < chunks_row; c0 += 32) {  // one tile = 32 chunks
     const int nch = min(32, chunks_row - c0);
@@ -115,13 +118,4 @@ __device__ __forceinline__ void block_rows_scalar(const float* __restrict__ a, i
     for (int j = 0; j < NR; ++j)
       total[j] = bd_add(total[j], bd_scale(bd_tile(s[j][0], s[j][1], s[j][2], s[j][3]), alpha));
   }
-}
-
-// One partial sum (chain) of one tile of one row, read from global memory:
-// elements first, first + 4, ... < end (element stride 1).
-__device__ __forceinline__ float chain_global(const float* __restrict__ w, const float* __restrict__ s, int first,
-                                              int end) {
-  float acc = 0.0f;
-  for (int i = first; i < end; i += 4) acc = bd_add(acc, bd_mul(w[i], s[i]));
-  return acc;
 }

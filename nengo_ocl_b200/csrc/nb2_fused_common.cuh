@@ -2,6 +2,7 @@
 // nb2_fused_stream.cu).
 #pragma once
 #include "nb2_common.cuh"
+#include "nb2_math.cuh"
 
 // table layouts (ints; floats stored as bit patterns)
 enum { E_N = 0, E_J, E_V, E_W, E_S, E_BIAS, E_NTERMS, E_TERM0, E_NCONN, E_CONN0, E_TAU, E_REF, E_AMP, E_FLAGS, E_EM1, E_STRIDE = 16 };
@@ -9,13 +10,6 @@ enum { T_A = 0, T_D, T_X, T_XS, T_STRIDE = 4 };
 enum { C_W = 0, C_D, C_WEIGHTED, C_FILT, C_B0, C_A0, C_PES, C_ERR, C_PF, C_PFB0, C_PFA0, C_ALPHA, C_STRIDE = 16 };
 
 __device__ __forceinline__ float bits(int v) { return __int_as_float(v); }
-
-// expm1 / log1p of a float argument, correctly rounded to float (evaluated in double and
-// rounded once): the float32 result no longer depends on whose math library computed it, so
-// the neuron state is bit-identical to a CPU evaluation of the reference kernel done the same
-// way.
-__device__ __forceinline__ float nb2_expm1_cr(float x) { return (float)expm1((double)x); }
-__device__ __forceinline__ float nb2_log1p_cr(float x) { return (float)log1p((double)x); }
 
 // LIF step with exact spike-time refractory handling, upsample = 1
 // (clra_nonlinearities.py:1087-1132); returns the output spike value.
@@ -41,4 +35,63 @@ __device__ __forceinline__ float fused_lif(float J, float& V, float& W, float ta
     V = 0.0f;
   }
   return spiked ? amp * dt_inv : 0.0f;
+}
+
+// The same update for four neurons of one lane.  The rare double-precision evaluations (a
+// neuron leaving its refractory period inside the step; a neuron that spikes) are taken out of
+// the per-neuron flow: if any of the four needs one, all four arguments are evaluated together,
+// so the warp pays the latency of one series instead of up to four in sequence.  Values are
+// identical to four calls of fused_lif.
+__device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], float (&W)[4], float (&S)[4],
+                                           float tau, float ref, float amp, float dt, float dt_inv,
+                                           float em1_dt) {
+  float em1[4], arg[4];
+  bool need = false;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    W[j] -= dt;
+    const float delta_t = (W[j] > dt) ? 0.0f : (W[j] < 0.0f) ? dt : dt - W[j];
+    em1[j] = (delta_t == 0.0f) ? 0.0f : em1_dt;
+    arg[j] = 0.0f;
+    if (delta_t != dt && delta_t != 0.0f) {
+      need = true;
+      arg[j] = -delta_t / tau;
+    }
+  }
+  if (need) {
+    float v[4];
+    nb2_expm1_cr4(arg, v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (arg[j] != 0.0f) em1[j] = v[j];
+  }
+  float y[4];
+  bool spiked[4], any = false;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float dV = -em1[j] * (J[j] - V[j]);
+    V[j] += dV;
+    y[j] = 0.0f;
+    spiked[j] = V[j] > 1.0f;
+    if (spiked[j]) {
+      any = true;
+      y[j] = -(V[j] - 1.0f) / (J[j] - 1.0f);
+    } else if (V[j] < 0.0f) {
+      V[j] = 0.0f;
+    }
+  }
+  if (any) {
+    float l[4];
+    nb2_log1p_cr4(y, l);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (spiked[j]) {
+        const float t_spike = dt + tau * l[j];
+        W[j] = ref + t_spike;
+        V[j] = 0.0f;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) S[j] = spiked[j] ? amp * dt_inv : 0.0f;
 }

@@ -6,7 +6,7 @@
 //
 //  * The host cuts every ensemble into work records: E records (a block of
 //    neurons: their encoder rows, bias, voltage, refractory time and PES
-//    activity trace) and D records (a few rows of one decoder matrix), each
+//    activity trace) and D records (a few whole rows of one decoder matrix), each
 //    at most one stage (8 KB) of data.  A CTA
 //    (one per SM, persistent) owns a list of whole ensembles; its records are
 //    ordered E(0), E(1), D(0), E(2), D(1), ... so that the spikes a D record
@@ -20,17 +20,18 @@
 //  * All dot products are summed in the order of the reference's block GEMV
 //    (nb2_blockdot.cuh), so J and the decoded values are bit-identical to it.
 //  * E record: one lane per neuron (4 neurons per lane); J = bias + enc . x from
-//    the staged rows (128-bit shared loads, lanes time-skewed against bank
-//    conflicts), LIF update in the operation order of the reference kernel
+//    the staged rows (128-bit shared loads, columns in order), LIF update in the operation order of the reference kernel
 //    (this file is compiled with -fmad=false; expm1 / log1p correctly rounded),
 //    V / W / spikes / new activity trace written straight to global memory,
 //    spikes and the OLD trace kept in a per-ensemble slot of shared memory for
 //    the D records.
-//  * D record: a pair of lanes owns the four partial sums of one (row, 128-column
-//    tile) and walks them in order; the PES update w += (alpha * err) * trace is
-//    applied to the same element in the stage, which then goes back to global
-//    memory as one bulk async store; two shuffles form the tile value, the tiles
-//    of a row are added in order, then the synapse.
+//  * D record: PES update w += (alpha * err) * trace: elementwise, lanes over
+//    groups of 4 neurons, 128-bit shared loads and 128-bit global stores.
+//    Decode: a pair of lanes owns the four partial sums of one (row, 128-column
+//    tile) and walks them in column order (64-bit shared loads; the pairs start
+//    one iteration apart so that the tiles, 128 floats apart, do not meet in the
+//    same banks); two shuffles form the tile value, the tiles of a row are added
+//    in order, then the synapse.
 //  * Slots are handed from E to D records and back through two counters per slot
 //    in shared memory; a record only ever waits for records that precede it in
 //    the CTA's list, so the lowest unfinished record can always run.
@@ -63,7 +64,7 @@
 #define ST_REC 32
 #define ST_MAXCOPY 8
 #define ST_ROWS 4  // neurons per lane in an E record
-#define ST_DITEMS 16  // (row, tile) pairs of a D record: two lanes each
+#define ST_DITEMS 16  // (row, 128-column tile) pairs of a D record: two lanes each
 
 struct StreamParams {
   const int* records;  // [n_records][32]
@@ -81,32 +82,44 @@ struct __align__(128) StreamStage {
   float buf[ST_A];
   float x[ST_X];
   int rec[2][ST_REC];  // record of turn m in slot m & 1
+  float ae[ST_DITEMS];  // alpha * error of the rows of a D record
 };
 
 struct __align__(16) StreamSlot {
-  float spk[ST_N];
-  float pfo[ST_N];
+  float spk[ST_N];  // spikes of this step
+  float pfo[ST_N];  // PES activity trace before this step's update
 };
 
 // record words
 enum { R_TYPE = 0, R_ENS, R_SLOT, R_A, R_B, R_NCOPY, R_TARGET, R_C, R_COPY0 = 8 };
+// D records: R_A connection, R_B first row, R_C rows
 
-// Lane 0: fill the stage for turn m (record index i); the record is in st.rec[m & 1].
+// All lanes: fill the stage for turn m (record index i); the record is in st.rec[m & 1].
+// Every copy is issued by a lane of its own; the warp's next record rides along.
 __device__ __forceinline__ void stream_issue(const StreamParams& p, StreamStage& st, unsigned long long* full,
-                                             const int4* rp, int i, int m, int n) {
+                                             const int4* rp, int i, int m, int n, int lane) {
   const int* r = st.rec[m & 1];
-  const int ncopy = r[R_NCOPY];
   const bool more = i + ST_NW < n;
-  uint32_t tx = more ? ST_REC * 4u : 0u;
-  for (int q = 0; q < ncopy; ++q) tx += (uint32_t)r[R_COPY0 + 3 * q + 1];
-  // a PES record's write-back (bulk store out of this stage) must have read the stage
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   // the stage was read through the generic proxy; order those reads before the async-proxy writes
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
-  for (int q = 0; q < ncopy; ++q)
-    bulk_copy(st.buf + r[R_COPY0 + 3 * q + 2], p.data + r[R_COPY0 + 3 * q], (uint32_t)r[R_COPY0 + 3 * q + 1], full);
-  if (more) bulk_copy(st.rec[(m + 1) & 1], rp + (size_t)(i + ST_NW) * 8, ST_REC * 4u, full);
+  const float* src = nullptr;
+  float* dst = nullptr;
+  uint32_t bytes = 0;
+  if (lane < r[R_NCOPY]) {
+    src = p.data + r[R_COPY0 + 3 * lane];
+    bytes = (uint32_t)r[R_COPY0 + 3 * lane + 1];
+    dst = st.buf + r[R_COPY0 + 3 * lane + 2];
+  }
+  uint32_t tx = bytes;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, off);
+  if (lane == 0) {
+    tx += more ? ST_REC * 4u : 0u;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
+  }
+  __syncwarp();
+  if (bytes) bulk_copy(dst, src, bytes, full);
+  if (more && lane == 31) bulk_copy(st.rec[(m + 1) & 1], rp + (size_t)(i + ST_NW) * 8, ST_REC * 4u, full);
 }
 
 // All lanes: stage the input vectors of an E record's ensemble (read from global memory, L2-hot).
@@ -179,9 +192,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
     int4* dst = reinterpret_cast<int4*>(st.rec[0]);  // the first record comes straight from global memory
 #pragma unroll
     for (int j = 0; j < 8; ++j) dst[j] = __ldg(rp + (size_t)wid * 8 + j);
-    stream_issue(p, st, full, rp, wid, 0, n);
   }
   __syncwarp();
+  stream_issue(p, st, full, rp, wid, 0, n, lane);
   stream_stage_x(p, st, st.rec[0], lane);
   __syncwarp();
 
@@ -235,21 +248,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           else block_rows_staged4<4>(a, st.x + xoff, d, lane, roff, tot, 1.0);
           xoff += d;
         }
+        // (lanes beyond the last neuron of the block recompute it; nothing of theirs is stored)
+        float Vv[ST_ROWS], Wv[ST_ROWS], Sv[ST_ROWS];
+#pragma unroll
+        for (int j = 0; j < ST_ROWS; ++j) {
+          Vv[j] = s_V[roff[j]];
+          Wv[j] = s_W[roff[j]];
+        }
+        fused_lif4(tot, Vv, Wv, Sv, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
           const int r = base + lane + 32 * j;
-          if (lane + 32 * j < nb) {
-            const float J = tot[j];
-            float v = s_V[r], w = s_W[r];
-            const float s = fused_lif(J, v, w, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
-            data[eV + i0 + r] = v;
-            data[eW + i0 + r] = w;
-            if (eS >= 0) data[eS + i0 + r] = s;
-            slot.spk[i0 + r] = s;
+          const bool mine = lane + 32 * j < nb;
+          if (mine) {
+            data[eV + i0 + r] = Vv[j];
+            data[eW + i0 + r] = Wv[j];
+            if (eS >= 0) data[eS + i0 + r] = Sv[j];
+            slot.spk[i0 + r] = Sv[j];
             if (pf_conn >= 0) {
               const float pf = s_pf[r];
               slot.pfo[i0 + r] = pf;
-              data[gpf + i0 + r] = pb0 * s - pa0 * pf;
+              data[gpf + i0 + r] = pb0 * Sv[j] - pa0 * pf;
             }
           }
         }
@@ -264,63 +283,57 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
     } else if (ok && h0.x == 2) {
       // ---------------- D record: rows [r0, r0 + nr) of one decoder matrix ----------------
       const int* c = p.conn_table + (size_t)h0.w * C_STRIDE;
-      const int r0 = h1.x, nr = h1.w;
+      const int r0 = h1.x, nr = h1.w;  // nr * ntile <= ST_DITEMS by construction
       const int n_e = __ldg(e + E_N);
+      const int n4 = n_e >> 2;
       const int ntile = (n_e + 127) >> 7;
       const bool pes = __ldg(c + C_PES) != 0;
-      // lanes 2i, 2i + 1 own (row, tile) pair i = row * ntile + tile: the even lane the partial
-      // sums 0 and 1 of the tile, the odd lane 2 and 3 (nr * ntile <= ST_DITEMS by construction)
-      const int item = lane >> 1, jp = lane & 1;
-      const int r = item / ntile, t = item - r * ntile;
-      const bool valid = r < nr;
-      const int len = valid ? min(32, (n_e - (t << 7)) >> 2) : 0;  // groups of 4 columns in the tile
-      // the 16 lanes of a 64-bit shared load read 8 pairs at the same column group otherwise
-      // (tiles are 128 floats apart: same banks): pair i starts i mod 8 iterations late
-      const int skew = item & 7;
-      float ae = 0.0f;
-      if (pes && valid) {
-        // alpha * error, formed once per row as in `alpha * aa * xx` (left to right)
-        ae = bits(__ldg(c + C_ALPHA)) * data[__ldg(c + C_ERR) + r0 + r];
-      }
-      const int col0 = (t << 7) + 2 * jp;
-      float* wrow = st.buf + (valid ? r * n_e : 0) + col0;
-      const float* srow = slot.spk + col0;
-      const float* prow = slot.pfo + col0;
       // every E record of this ensemble must have delivered its spikes
       ok = stream_wait_count(&e_done[h0.z], h1.z, &s_abort, lane);
       if (ok) {
-        float ca = 0.0f, cb = 0.0f;
-        const int kmax = min(32, n_e >> 2) + 7;
         if (pes) {
-          for (int k = 0; k < kmax; ++k) {
-            const int q = k - skew;
-            if (q >= 0 && q < len) {
-              float2 w2 = *reinterpret_cast<const float2*>(wrow + 4 * q);
-              const float2 s2 = *reinterpret_cast<const float2*>(srow + 4 * q);
-              const float2 p2 = *reinterpret_cast<const float2*>(prow + 4 * q);
-              ca = bd_add(ca, bd_mul(w2.x, s2.x));
-              cb = bd_add(cb, bd_mul(w2.y, s2.y));
-              w2.x = w2.x + ae * p2.x;
-              w2.y = w2.y + ae * p2.y;
-              *reinterpret_cast<float2*>(wrow + 4 * q) = w2;
+          // w += (alpha * error) * trace, with alpha * error formed once per row as in
+          // `alpha * aa * xx` (left to right); the stage keeps the old values for the decode
+          if (lane < nr) st.ae[lane] = bits(__ldg(c + C_ALPHA)) * data[__ldg(c + C_ERR) + r0 + lane];
+          __syncwarp();
+          float4* Wd = reinterpret_cast<float4*>(data + __ldg(c + C_W)) + (size_t)r0 * n4;
+          const float4* sw = reinterpret_cast<const float4*>(st.buf);
+          const float4* pfo4 = reinterpret_cast<const float4*>(slot.pfo);
+#pragma unroll 4
+          for (int i4 = lane; i4 < n4; i4 += 32) {
+            const float4 p4 = pfo4[i4];
+#pragma unroll 2
+            for (int rr = 0; rr < nr; ++rr) {
+              const float ae = st.ae[rr];
+              const float4 w4 = sw[rr * n4 + i4];
+              float4 o;
+              o.x = w4.x + ae * p4.x;
+              o.y = w4.y + ae * p4.y;
+              o.z = w4.z + ae * p4.z;
+              o.w = w4.w + ae * p4.w;
+              Wd[(size_t)rr * n4 + i4] = o;
             }
           }
-          // the updated rows go back as one bulk store: writes of all lanes -> async proxy
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            float* Wd = data + __ldg(c + C_W) + (size_t)r0 * n_e;
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(Wd),
-                         "r"(pipe_smem(st.buf)), "r"((uint32_t)(nr * n_e * 4))
-                         : "memory");
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-        } else {
+        }
+        // lanes 2 i and 2 i + 1 own pair i = row * ntile + tile: the even lane the partial sums 0
+        // and 1 of the tile (columns 4 q and 4 q + 1, q ascending), the odd lane 2 and 3.  Tiles are
+        // 128 floats apart, i.e. in the same banks: pair i starts i mod 8 iterations late, so the
+        // 16 lanes that a 64-bit shared load serves at a time read 16 different bank pairs.
+        const int item = lane >> 1, jp = lane & 1;
+        const int rr = item / ntile, tt = item - rr * ntile;
+        const bool valid = rr < nr;
+        const int len = valid ? min(32, (n_e - (tt << 7)) >> 2) : 0;
+        const int skew = item & 7;
+        const float* wi = st.buf + (valid ? rr * n_e : 0) + (tt << 7) + 2 * jp - 4 * skew;
+        const float* si = slot.spk + (tt << 7) + 2 * jp - 4 * skew;
+        float ca = 0.0f, cb = 0.0f;
+        {
+          const int kmax = min(32, n4) + 7;
+#pragma unroll 8
           for (int k = 0; k < kmax; ++k) {
-            const int q = k - skew;
-            if (q >= 0 && q < len) {
-              const float2 w2 = *reinterpret_cast<const float2*>(wrow + 4 * q);
-              const float2 s2 = *reinterpret_cast<const float2*>(srow + 4 * q);
+            if (k >= skew && k - skew < len) {
+              const float2 w2 = *reinterpret_cast<const float2*>(wi + 4 * k);
+              const float2 s2 = *reinterpret_cast<const float2*>(si + 4 * k);
               ca = bd_add(ca, bd_mul(w2.x, s2.x));
               cb = bd_add(cb, bd_mul(w2.y, s2.y));
             }
@@ -330,14 +343,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
         const float xa = bd_add(ca, __shfl_xor_sync(0xffffffffu, ca, 1));
         const float xb = bd_add(cb, __shfl_xor_sync(0xffffffffu, cb, 1));
         const float tile = bd_add(xa, xb);
-        const int lane_t0 = 2 * (valid ? r : 0) * ntile;
+        const int lane_t0 = 2 * (valid ? rr : 0) * ntile;
         float total = 0.0f;
-        for (int tt = 0; tt < ntile; ++tt) total = bd_add(total, __shfl_sync(0xffffffffu, tile, lane_t0 + 2 * tt));
-        if (valid && t == 0 && jp == 0) {
-          data[__ldg(c + C_WEIGHTED) + r0 + r] = total;
+        for (int t = 0; t < ntile; ++t) total = bd_add(total, __shfl_sync(0xffffffffu, tile, lane_t0 + 2 * t));
+        if (valid && tt == 0 && jp == 0) {
+          data[__ldg(c + C_WEIGHTED) + r0 + rr] = total;
           const int filt = __ldg(c + C_FILT);
           if (filt >= 0) {
-            const int yi = filt + r0 + r;
+            const int yi = filt + r0 + rr;
             // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
             const int a0 = __ldg(c + C_A0);
             float out = bits(__ldg(c + C_B0)) * total;
@@ -361,13 +374,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
     }
     __syncwarp();  // every lane is done with the stage
     if (i + ST_NW < n) {
-      if (lane == 0) stream_issue(p, st, full, rp, i + ST_NW, m + 1, n);
-      __syncwarp();
+      stream_issue(p, st, full, rp, i + ST_NW, m + 1, n, lane);
       stream_stage_x(p, st, st.rec[(m + 1) & 1], lane);
     }
   }
-  // write-backs still in flight out of this warp's stage
-  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   if (xpush) {
     // The decoded values of this CTA's ensembles form one contiguous run of this rank's
     // segment (the host checked): its last warp stores the run into every peer's staging

@@ -10,11 +10,8 @@
 // results, independent of the math library), like the CPU evaluation of the
 // reference kernels this path is checked against.
 #include "nb2_common.cuh"
+#include "nb2_math.cuh"
 #include "../../include/nengo_b200.h"
-
-__device__ __forceinline__ float nb2_expm1_cr(float x) { return (float)expm1((double)x); }
-__device__ __forceinline__ float nb2_log1p_cr(float x) { return (float)log1p((double)x); }
-__device__ __forceinline__ float nb2_exp_cr(float x) { return (float)exp((double)x); }
 
 __device__ __forceinline__ float nb2_var_load(const nb2_var& v, int block, int i) {
   return v.buf ? v.buf[v.starts[block] + i] : v.value;

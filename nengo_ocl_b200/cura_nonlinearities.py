@@ -479,11 +479,12 @@ def plan_direct(queue, code, init, input_names, inputs, output, tag=None):
         assert (x.stride0s == 1).all()
 
     prog = to_device(queue, np.asarray(code.program, dtype=np.int32).reshape(-1, 2))
-    consts = to_device(queue, np.asarray(list(code.constants) + [0.0], dtype=np.float32))
+    # (the pool travels as raw 64-bit words: device arrays are float32 / int32 typed)
+    consts = to_device(queue, np.asarray(list(code.constants) + [0.0], dtype=np.float64).view(np.int32))
     n_ops = len(code.program)
     ins = list(inputs) + [None, None]
     fn, check = _capi.lib().nb2_direct, _capi.check
-    args = (N, prog.ptr, n_ops, consts.ptr, int(output.shape0s.max()),
+    args = (N, prog.ptr, n_ops, code.max_depth, consts.ptr, int(output.shape0s.max()),
             None if ins[0] is None else ins[0].cl_starts.ptr, None if ins[0] is None else ins[0].cl_buf.ptr,
             None if ins[1] is None else ins[1].cl_starts.ptr, None if ins[1] is None else ins[1].cl_buf.ptr,
             output.cl_starts.ptr, output.cl_buf.ptr)

@@ -354,7 +354,7 @@ def streamable(ens, terms, conns):
         d_total = int(terms[t0:t0 + nt, 1].sum()) if nt else 0
         pes = int(conns[c0:c0 + nc, 6].sum()) if nc else 0
         ok = (row[13] & 1) and STREAM_MIN_NEURONS <= n <= STREAM_MAX_NEURONS and nt <= 4 and pes <= 1
-        ok = ok and d_total <= STREAM_MAX_INPUT and 4 * (d_total + 4) <= STREAM_STAGE_FLOATS
+        ok = ok and d_total <= STREAM_MAX_INPUT and 32 * (d_total + 4) <= STREAM_STAGE_FLOATS
         ok = ok and (nt == 0 or bool(np.all(terms[t0:t0 + nt, 1] % 4 == 0)))
         if ok:
             out.append(i)
@@ -371,7 +371,8 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
     signal buffer, bytes, float offset in the stage.  E: [3] first neuron, [4]
     neurons, [7] connection table row of the PES connection or -1; copies = encoder
     rows of every term, bias, voltage, refractory time [, PES activity trace].
-    D: [3] connection table row, [4] first row, [7] rows; one copy.
+    D: [3] connection table row, [4] first row, [7] rows (rows x 128-column tiles
+    <= 16); one copy.
     Ensembles are dealt to CTAs in contiguous runs balanced by bytes; the records
     of a CTA are ordered E(0), E(1), D(0), E(2), D(1), ..., D(last).
     """
@@ -383,9 +384,10 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
         ds = [int(terms[t0 + k, 1]) for k in range(nt)]
         pes_conn = next((c0 + k for k in range(nc) if conns[c0 + k, 6]), -1)
         per_neuron = sum(ds) + 3 + (1 if pes_conn >= 0 else 0)
-        ne_max = min(STREAM_CHUNK, (STREAM_STAGE_FLOATS // per_neuron) & ~3)
+        # E records start on multiples of 32 neurons (one writer per word of the spike bitmap)
+        ne_max = min(STREAM_CHUNK, (STREAM_STAGE_FLOATS // per_neuron) & ~31)
         n_chunks = -(-n // ne_max)
-        ne_even = (-(-n // n_chunks) + 3) & ~3
+        ne_even = min(ne_max, (-(-n // n_chunks) + 31) & ~31)
         E, D = [], []
         for i0 in range(0, n, ne_even):
             ne = min(ne_even, n - i0)

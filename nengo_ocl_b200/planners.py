@@ -95,10 +95,15 @@ def greedy_planner(operators, dependency_graph=_dependency_graph_fast):
     """Group operators by type in a dependency-respecting order."""
     edges = dependency_graph(operators)
 
+    # Successors are visited in operator-list order, so that operators that become ready together
+    # (e.g. the increments of one signal after its reset) are scheduled in the order the model
+    # lists them: float32 sums of several increments then do not depend on object hashes, as
+    # they do when the successors are walked as a set.
+    position = {op: i for i, op in enumerate(operators)}
     predecessors_of = {op: set() for op in operators}
-    successors_of = {op: set() for op in operators}
+    successors_of = {op: [] for op in operators}
     for op, dests in edges.items():
-        successors_of[op].update(dests)
+        successors_of[op] = sorted(dests, key=position.__getitem__)
         for op2 in dests:
             predecessors_of[op2].add(op)
 

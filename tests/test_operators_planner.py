@@ -134,6 +134,30 @@ def test_function_translation_to_postfix():
         DeviceFunction(lambda t: [t, t], [1], out_dim=3)
 
 
+def test_deep_expression_is_not_sent_to_the_device():
+    """The device interpreter evaluates on a fixed-size stack; the translator computes the depth
+    a program needs and refuses deeper ones (the simulator then runs the function on the host).
+    Checked on the host only: such a program must never reach the kernel."""
+    from nengo_ocl_b200.ast_conversion import DeviceFunction, MAX_STACK, stack_depth
+
+    shallow = DeviceFunction(lambda t, x: [x[0] * x[1], t + 2.5], [1, 2])
+    assert shallow.max_depth == 2 == stack_depth(shallow.program)
+
+    def horner(x):
+        return x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (
+            1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (
+                1 + x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1])))))))))))))))))))
+
+    with pytest.raises(NotImplementedError, match="stack"):
+        DeviceFunction(horner, [2])
+    assert MAX_STACK == 32
+
+    def medium(x):
+        return x[0] * (1 + x[1] * (1 + x[0] * (1 + x[1] * (1 + x[0]))))
+
+    assert DeviceFunction(medium, [2]).max_depth == 9
+
+
 def test_gather_sum_over_slices_and_reset_folding():
     """The fusion passes on operator lists: copies into slices of a reset signal become one
     gather-sum with one part per slice (gaps are only zeroed); a reset followed by one merged
