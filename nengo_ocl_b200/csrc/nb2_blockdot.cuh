@@ -78,44 +78,3 @@ __device__ __forceinline__ void block_rows_staged4(const float* __restrict__ a, 
       total[j] = bd_add(total[j], bd_scale(bd_tile(s[j][0], s[j][1], s[j][2], s[j][3]), alpha));
   }
 }
-
-// Lane per row, scalar loads, any pitch / alignment; x either staged (xs == 1, shared
-// memory) or read from global memory with stride xs.  Columns in ascending order.
-template <int NR, bool XGLOBAL>
-__device__ __forceinline__ void block_rows_scalar(const float* __restrict__ a, int pitch, const float* __restrict__ x,
-                                                  int xs, int w, const int (&roff)[4], float (&total)[4],
-                                                  double alpha) {
-  const float* ar[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) ar[j] = a + (size_t)roff[j < NR ? j : 0] * pitch;
-  for (int c0 = 0; c0 < w; c0 += 128) {
-    const int wt = min(128, w - c0);
-    float s[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-    int c = 0;
-    for (; c + 4 <= wt; c += 4) {
-      float xv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) xv[u] = XGLOBAL ? __ldg(x + (size_t)(c0 + c + u) * xs) : x[c0 + c + u];
-#pragma unroll
-      for (int j = 0; j < NR; ++j) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) s[j][u] = bd_add(s[j][u], bd_mul(ar[j][c0 + c + u], xv[u]));
-      }
-    }
-    for (int u = 0; c + u < wt; ++u) {  // u < 3
-      const float xv = XGLOBAL ? __ldg(x + (size_t)(c0 + c + u) * xs) : x[c0 + c + u];
-#pragma unroll
-      for (int j = 0; j < NR; ++j) {
-        const float p = bd_mul(ar[j][c0 + c + u], xv);
-        if (u == 0) s[j][0] = bd_add(s[j][0], p);
-        else if (u == 1) s[j][1] = bd_add(s[j][1], p);
-        else s[j][2] = bd_add(s[j][2], p);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < NR; ++j)
-      total[j] = bd_add(total[j], bd_scale(bd_tile(s[j][0], s[j][1], s[j][2], s[j][3]), alpha));
-  }
-}

@@ -47,7 +47,7 @@ def lib():
 
 
 def _ptr(a):
-    return a.ctypes.data_as(_F)
+    return ctypes.cast(a.__array_interface__["data"][0], _F)
 
 
 def block_rows(total, A, x, alpha=1.0):
@@ -59,6 +59,22 @@ def block_rows(total, A, x, alpha=1.0):
     isz = 4
     lib().nb2o_block_rows(_ptr(A), A.strides[0] // isz, A.strides[1] // isz, M, N, _ptr(x), x.strides[0] // isz,
                           _ptr(total), total.strides[0] // isz, float(alpha))
+
+
+def block_rows_args(total, A, x, alpha=1.0):
+    """Argument tuple of ``block_rows`` for arrays that stay where they are (a simulator's
+    signals): build once, run every step with ``block_rows_run``."""
+    assert total.dtype == A.dtype == x.dtype == np.float32
+    M, N = A.shape
+    assert total.shape == (M,) and x.shape == (N,)
+    assert not np.shares_memory(total, A) and not np.shares_memory(total, x)
+    lib()
+    return (_ptr(A), A.strides[0] // 4, A.strides[1] // 4, M, N, _ptr(x), x.strides[0] // 4, _ptr(total),
+            total.strides[0] // 4, float(alpha), (total, A, x))  # (the arrays are kept alive)
+
+
+def block_rows_run(args):
+    _lib.nb2o_block_rows(*args[:10])
 
 
 def lif(dt, J, V, W, S, tau, ref, amp):

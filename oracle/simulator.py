@@ -94,6 +94,8 @@ class OracleSimulator:
             merged.append(op)
         self._ops = _toposort(self._merge_view(merged))
         self._filter_state = {}
+        self._views = {}  # signal -> strided view into its base array (the arrays never move)
+        self._prepared = {}  # per-operator constants (2-D operand views, filter coefficients)
         self.probe_data = {p: [] for p in model.probes}
         self.n_steps = 0
 
@@ -111,10 +113,13 @@ class OracleSimulator:
 
     # -- signal access ---------------------------------------------------------
     def view(self, sig):
-        base = self.signals[sig.base].reshape(-1)
-        isz = base.itemsize
-        return np.lib.stride_tricks.as_strided(
-            base[sig.elemoffset:], shape=sig.shape, strides=tuple(s * isz for s in sig.elemstrides))
+        v = self._views.get(sig)
+        if v is None:
+            base = self.signals[sig.base].reshape(-1)
+            isz = base.itemsize
+            v = self._views[sig] = np.lib.stride_tricks.as_strided(
+                base[sig.elemoffset:], shape=sig.shape, strides=tuple(s * isz for s in sig.elemstrides))
+        return v
 
     def __getitem__(self, sig):
         return np.array(self.view(sig))
@@ -170,16 +175,22 @@ class OracleSimulator:
         (MultiDotInc.convert_to / get_views, nengo_ocl/operators.py:50-67,159-191: operands
         become 2-D, a (1, 1) matrix swaps roles with its vector)."""
         y = self.view(y_sig)
-        total = np.array(y, dtype=np.float32).reshape(-1)  # 1.0 * y_in
-        for op in ops:
-            A, X = self.view(op.A), self.view(op.X)
-            X2 = self._as2d(X)
-            A2 = A.reshape(1, A.shape[0]) if (A.ndim == 1 and X.ndim == 1) else self._as2d(A)
-            if A2.shape == (1, 1):
-                A2, X2 = X2, A2
-            assert A2.shape == (total.size, X2.shape[0]) and X2.shape[1] == 1, (A.shape, X.shape, y.shape)
-            C.block_rows(total, A2, X2[:, 0])
-        y[...] = total.reshape(y.shape)  # + 0.0
+        terms = self._prepared.get(id(ops[0]))
+        if terms is None:
+            terms = []
+            for op in ops:
+                A, X = self.view(op.A), self.view(op.X)
+                X2 = self._as2d(X)
+                A2 = A.reshape(1, A.shape[0]) if (A.ndim == 1 and X.ndim == 1) else self._as2d(A)
+                if A2.shape == (1, 1):
+                    A2, X2 = X2, A2
+                assert A2.shape == (y.size, X2.shape[0]) and X2.shape[1] == 1, (A.shape, X.shape, y.shape)
+                # the running value is y itself (1.0 * y_in, + 0.0 at the end): accumulate in place
+                terms.append(C.block_rows_args(y.reshape(-1) if y.ndim != 1 else y, A2, X2[:, 0]))
+            self._prepared[id(ops[0])] = terms
+        run = C.block_rows_run
+        for args in terms:
+            run(args)
 
     def _do_DotInc(self, op):
         self._block_inc(op.Y, [op])
@@ -203,7 +214,11 @@ class OracleSimulator:
         kind = type(nt).__name__
         J = self.view(op.J)
         out = self.view(op.output)
-        if kind in ("LIF", "AdaptiveLIF"):
+        if kind == "LIF" and J.flags.c_contiguous and out.flags.c_contiguous:
+            # the compiled restatement of the same kernel (checked against kernels.lif in the tests)
+            C.lif(self.dt, J, self.view(op.state["voltage"]), self.view(op.state["refractory_time"]), out,
+                  f32(nt.tau_rc), f32(nt.tau_ref), f32(nt.amplitude))
+        elif kind in ("LIF", "AdaptiveLIF"):
             V = self.view(op.state["voltage"])
             W = self.view(op.state["refractory_time"])
             n = J.size
@@ -234,12 +249,16 @@ class OracleSimulator:
 
     def _do_SimProcess(self, op):
         proc = op.process
-        names = [c.__name__ for c in type(proc).__mro__]
+        names = self._prepared.get(type(proc))
+        if names is None:
+            names = self._prepared[type(proc)] = [c.__name__ for c in type(proc).__mro__]
         out = self.view(op.output)
         if "LinearFilter" in names:
-            num, den = proc.discrete_tf(self.dt)
-            b = num.astype(np.float32)
-            a = den.astype(np.float32)
+            coef = self._prepared.get(id(op))
+            if coef is None:
+                num, den = proc.discrete_tf(self.dt)
+                coef = self._prepared[id(op)] = (num.astype(np.float32), den.astype(np.float32))
+            b, a = coef
             x = self.view(op.input)
             na, nb = len(a), len(b)
             if na == 0 and nb == 1:

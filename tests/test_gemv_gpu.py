@@ -30,7 +30,8 @@ def run(queue, planner, alpha, A, A_js, X, X_js, beta, Y, gamma=0.0, kind=None):
     prog = planner(queue, alpha, clA, A_js, clX, X_js, beta, clY, gamma=gamma, cta_kind=kind)
     for plan in prog.plans:
         plan()
-        assert int(plan.status.get()[0]) == 0
+        if getattr(plan, "status", None) is not None:  # (kernels with bounded waits report them here)
+            assert int(plan.status.get()[0]) == 0
     return clY, prog
 
 
@@ -199,3 +200,51 @@ def test_config2_full_size_properties(queue):
     y0 = product(0.0, cura_gemv.GEMV_PIPE)
     y2 = product(1.0, cura_gemv.GEMV_PIPE)
     assert np.allclose(y2 - y0, 2 * (y_pipe - y0), rtol=1e-4, atol=1e-5 * scale)
+
+
+def check_block_exact(queue, alpha, A, A_js, X, X_js, beta, Y, gamma=0.0):
+    """plan_block_gemv against the oracle's restatement of the reference's block kernels
+    (clra_gemv.py:1018-1058,1137-1153): every output bit for bit."""
+    ref = clone(Y)
+    K.gemv_block(alpha, A, A_js, X, X_js, beta, ref, gamma=gamma)
+    clY, prog = run(queue, cura_gemv.plan_block_gemv, alpha, A, A_js, X, X_js, beta, Y, gamma=gamma)
+    for i in range(len(Y)):
+        assert np.array_equal(clY[i], ref[i]), i
+    return prog
+
+
+def test_block_gemv_is_bit_exact(queue):
+    """The planner the simulator uses for every MultiDotInc reproduces the float32 summation
+    order of the reference's block kernels: 128-column tiles, four column-strided partial sums
+    per tile, (s0 + s2) + (s1 + s3), tiles added in order to beta * y_in, gamma last."""
+    # the reference's known-answer case
+    A = RA([[[0.1, 0.2], [0.3, 0.4]], [[0.5, 0.6]]])
+    X = RA([[3, 5]])
+    Y = RA([[0.0], [2, 3]])
+    check_block_exact(queue, 1.0, A, RA([[1], [0]], dtype=np.int32), X, RA([[0], [0]], dtype=np.int32), 1.0, Y)
+    # shape family of the reference tests, alpha = .5, beta = .6, gamma = .7
+    rng = np.random.RandomState(1234)
+    for A_shapes in ([(1, 1)], [(10, 1)], [(2001, 1)], [(10, 1 + ii % 2) for ii in range(20)],
+                     [(2000, ii + 1) for ii in range(100)], [(33, 129), (33, 517), (33, 128)],
+                     [(5, 1030)], [(300, 260)]):
+        A = RA([0.1 + rng.rand(*shp) for shp in A_shapes])
+        X = RA([0.1 + rng.rand(shp[1], 1) for shp in A_shapes])
+        Y = RA([0.1 + rng.rand(A_shapes[0][0], 1)])
+        js = RA([range(len(A_shapes))], dtype=np.int32)
+        check_block_exact(queue, 0.5, A, js, X, js, 0.6, Y, gamma=0.7)
+        check_block_exact(queue, 1.0, A, js, X, js, 1.0, Y)  # the simulator's scales
+        check_block_exact(queue, 1.0, A, js, X, js, 0.0, Y)  # a folded reset
+    # the reference's random test and the scaled benchmark configuration 2
+    rng = np.random.RandomState(3294)
+    k, p_, m_, n_ = 4, 4, 2000, 1000
+    A = RA([rng.normal(size=(m_, n_)) for i in range(k)])
+    X = RA([rng.normal(size=n_) for i in range(k)])
+    Y = RA([rng.normal(size=m_) for i in range(k)])
+    A_js = RA([rng.randint(k, size=p_) for i in range(k)], dtype=np.int32)
+    X_js = RA([rng.randint(k, size=p_) for i in range(k)], dtype=np.int32)
+    check_block_exact(queue, 0.5, A, A_js, X, X_js, 0.1, Y)
+    for align in (False, True):
+        A, A_js, X, X_js, Y = gemv_workload(seed=1, n_outputs=256, align=align)
+        prog = check_block_exact(queue, 0.5, A, A_js, X, X_js, 0.1, Y)
+        cta, warp = prog.plans[0].worklist
+        assert len(cta) and len(warp)  # both kernels ran

@@ -65,13 +65,10 @@ def test_lif_large_populations_vs_oracle(queue):
     v, w, s = K.lif(dt, J.buf, V.buf, W.buf, T.buf, np.float32(2e-3), np.float32(1.0))
     plan()
     assert (s > 0).sum() > 50
-    gs = clOS.cl_buf.get()
-    flips = (gs > 0) != (s > 0)
-    assert flips.mean() < 1e-4  # a 1-ulp voltage difference at threshold may flip a spike
-    ok = ~flips
-    assert np.allclose(clV.cl_buf.get()[ok], v[ok], rtol=1e-5, atol=1e-6)
-    assert np.allclose(clW.cl_buf.get()[ok], w[ok], rtol=1e-5, atol=1e-6)
-    assert np.array_equal(gs[ok], s[ok])
+    # expm1 / log1p are correctly rounded on both sides: voltages, refractory times and spikes are
+    # bit-identical (one element in a million is allowed for the double-rounding corner)
+    gs, gv, gw = clOS.cl_buf.get(), clV.cl_buf.get(), clW.cl_buf.get()
+    assert np.count_nonzero(gs != s) + np.count_nonzero(gv != v) + np.count_nonzero(gw != w) <= 3 * s.size // 1000000
     assert np.array_equal(clJ.cl_buf.get(), J.buf)
 
 

@@ -206,3 +206,41 @@ def test_learning_rule_deltas_match_reference_kernels(golden_kernels):
             assert got.shape == (m, n)
             assert np.array_equal(got.reshape(-1), want[pos:pos + m * n]), (rule, k)
             pos += m * n
+
+
+def test_compiled_oracle_matches_numpy_oracle():
+    """oracle/cport.c (the compiled restatement used for large models and as the timed CPU
+    baseline) against oracle/kernels.py on random data: block GEMV and LIF, bit for bit."""
+    from oracle import cport as C
+    from nengo_ocl_b200.raggedarray import RaggedArray
+
+    rng = np.random.RandomState(5)
+    for M, N in [(1, 1), (7, 3), (16, 1024), (100, 16), (33, 300), (5, 129)]:
+        A = rng.randn(M, N).astype(np.float32)
+        x = rng.randn(N).astype(np.float32)
+        y = rng.randn(M).astype(np.float32)
+        total = y.copy()
+        C.block_rows(total, A, x)
+        RA = lambda arrays, dtype=np.float32: RaggedArray(arrays, dtype=dtype)
+        Y = RA([y.reshape(-1, 1)])
+        K.gemv_block(1.0, RA([A]), RA([[0]], np.int32), RA([x.reshape(-1, 1)]), RA([[0]], np.int32), 1.0, Y)
+        assert np.array_equal(total, Y[0][:, 0])
+        # strided operands (views of larger signals)
+        big = rng.randn(M, 2 * N + 3).astype(np.float32)
+        total = y.copy()
+        C.block_rows(total, big[:, 1:2 * N + 1:2], x)
+        Y2 = RA([y.reshape(-1, 1)])
+        K.gemv_block(1.0, RA([np.ascontiguousarray(big[:, 1:2 * N + 1:2])]), RA([[0]], np.int32),
+                     RA([x.reshape(-1, 1)]), RA([[0]], np.int32), 1.0, Y2)
+        assert np.array_equal(total, Y2[0][:, 0])
+    n = 5000
+    J = rng.uniform(-1, 8, n).astype(np.float32)
+    V = rng.uniform(0, 1, n).astype(np.float32)
+    W = rng.uniform(-0.001, 0.003, n).astype(np.float32)
+    for _ in range(5):
+        v, w, s = K.lif(0.001, J, V, W, np.full(n, 0.02, np.float32), np.full(n, 0.002, np.float32),
+                        np.full(n, 1.0, np.float32))
+        Vc, Wc, Sc = V.copy(), W.copy(), np.zeros(n, np.float32)
+        C.lif(0.001, J, Vc, Wc, Sc, 0.02, 0.002, 1.0)
+        assert np.array_equal(v, Vc) and np.array_equal(w, Wc) and np.array_equal(s, Sc)
+        V, W = v, w

@@ -2,11 +2,19 @@
 oracle on the same seeded model (nengo_ocl/simulator.py is the behaviour being
 matched; cases follow nengo_ocl/tests/test_simulator.py:14-107).
 
-Tolerances: float32 signals agree within rtol 1e-5 / atol 1e-6 per step over
-the first 100 steps; probe traces within 1e-3 RMSE.  A neuron whose voltage
-lands within an ulp of the threshold may spike one step apart in the two
-implementations (different expm1/log1p libraries); such elements are counted
-and bounded instead of compared."""
+The oracle evaluates every operator with the arithmetic of the kernel the
+reference plans for it (dot products: the block GEMV's float32 summation
+order; expm1 / log1p: correctly rounded float32), and the CUDA kernels compute
+in exactly that order, so whole models are compared BIT FOR BIT, every signal,
+every step.  The stated tolerance of the hot path (rtol 1e-5 / atol 1e-6 per
+step over the first 100 steps, probe traces within 1e-3 RMSE) is therefore met
+with no element outside it.  Each test records the counts it measured (see the
+parity section of the test summary).  The only budget allowed is for the
+double-rounding corner of expm1 / log1p (the double-precision value lands
+within 2^-52 of a float32 rounding boundary, probability about 1e-8 per
+evaluation): at most one element in a million may differ.  Sparse transforms
+are the exception: their kernels sum a row in a different order than the
+reference's CSR kernel, and are compared within the tolerance."""
 
 import numpy as np
 import pytest
@@ -21,18 +29,45 @@ pytestmark = pytest.mark.gpu
 RTOL, ATOL = 1e-5, 1e-6
 
 
-def compare_signals(sim, ora, signals, max_bad_fraction=0.0):
-    """Fraction of elements outside tolerance over ``signals``."""
-    bad = total = 0
+class Tally:
+    """Counts over all compared elements of a run."""
+
+    def __init__(self):
+        self.total = self.differ = self.out_of_tol = self.spikes_moved = 0
+
+    def fields(self, **extra):
+        out = dict(elements=self.total, not_bit_identical=self.differ, out_of_tolerance=self.out_of_tol,
+                   spikes_moved=self.spikes_moved)
+        out.update(extra)
+        return out
+
+
+def compare_signals(sim, ora, signals, tally=None, spike_signals=(), exact=True):
+    """Compare ``signals`` between the CUDA simulator and the oracle; returns the
+    tally.  ``exact``: at most one element in a million may differ at all."""
+    tally = Tally() if tally is None else tally
+    differ = out = 0
     for sig in signals:
         got = np.asarray(sim.signals[sig], dtype=np.float32).reshape(-1)
         ref = ora[sig].reshape(-1)
-        err = np.abs(got - ref) > ATOL + RTOL * np.abs(ref)
-        bad += int(err.sum())
-        total += err.size
-    frac = bad / max(total, 1)
-    assert frac <= max_bad_fraction, "%d of %d elements out of tolerance" % (bad, total)
-    return frac
+        neq = got != ref
+        n = int(np.count_nonzero(neq))
+        tally.total += got.size
+        if n:
+            differ += n
+            out += int(np.count_nonzero(np.abs(got - ref) > ATOL + RTOL * np.abs(ref)))
+            if sig in spike_signals:
+                tally.spikes_moved += int(np.count_nonzero((got != 0) != (ref != 0)))
+    tally.differ += differ
+    tally.out_of_tol += out
+    if exact:
+        assert tally.differ <= max(tally.total // 1000000, 0), "%d of %d elements differ (%d out of tolerance)" % (
+            tally.differ, tally.total, tally.out_of_tol)
+    return tally
+
+
+def spike_signals(model):
+    return {op.output for op in model.operators if type(op).__name__ == "SimNeurons"}
 
 
 def state_signals(model):
@@ -45,9 +80,10 @@ def state_signals(model):
 
 
 @pytest.mark.parametrize("fuse", [False, True])
-def test_two_ensemble_model_matches_oracle_per_step(fuse):
+def test_two_ensemble_model_matches_oracle_per_step(fuse, parity_report):
     mdl = synth.two_ensemble_model(seed=0)
     ora = OracleSimulator(mdl)
+    tally = Tally()
     with Simulator(None, model=mdl, fuse=fuse) as sim:
         assert bool(sim.fused_groups) == fuse
         unstored = {s for g in sim.fused_groups for s in g["unstored"]}
@@ -55,9 +91,10 @@ def test_two_ensemble_model_matches_oracle_per_step(fuse):
         for step in range(100):
             sim.step()
             ora.step()
-            compare_signals(sim, ora, sigs)
+            compare_signals(sim, ora, sigs, tally, spike_signals(mdl))
         assert sim.n_steps == 100
         assert abs(sim.time - 0.1) < 1e-6
+    parity_report("two ensembles (fuse=%s), 100 steps" % fuse, **tally.fields())
 
 
 @pytest.mark.parametrize("fuse", [False, True])
@@ -74,8 +111,7 @@ def test_two_ensemble_probe_traces(fuse):
             got = sim.data[p]
             ref = np.array(ora.probe_data[p])
             assert got.shape == ref.shape == (1000, 1)
-            rmse = np.sqrt(np.mean((got - ref) ** 2))
-            assert rmse < 1e-3, rmse
+            assert np.array_equal(got, ref)  # (1e-3 RMSE is the stated bound; the traces are identical)
             # and the network computes what it was built to compute
             assert np.sqrt(np.mean((got[200:, 0] - fn(t[200:] - 0.015)) ** 2)) < 0.12
 
@@ -224,52 +260,98 @@ def small_sparse(seed=9):
     return synth.sparse_recurrent_model(seed=seed, n_neurons=300, fan_out=12)
 
 
-@pytest.mark.parametrize("fuse", [False, True])
-@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes, small_cc, small_sparse, mixed_streamed],
-                         ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3", "circular_convolution",
-                              "sparse_recurrent", "mixed_streamed"])
-def test_scaled_configs_match_oracle_per_step(make, fuse):
-    mdl = make()
+def run_against_oracle(mdl, sim, steps, exact=True, every=1):
+    """Step the CUDA simulator and the oracle side by side; compare every signal the simulator
+    stores (every ``every``-th step and the last one).  With fused PES the delta is applied at
+    the end of the step that computes it and never stored: ``weights`` is then compared with the
+    oracle's ``weights + delta``."""
     ora = OracleSimulator(mdl)
     skip = set()
-    sim = Simulator(None, model=mdl, fuse=fuse)
-    fused_pes = fuse and any(g.get("pes") for g in sim.fused_groups)
+    fused_pes = any(g.get("pes") for g in sim.fused_groups)
+    pes_conns = [c for c in mdl.info.get("connections", []) if "delta" in c]
     if fused_pes:
-        # the fused kernel applies the PES delta at the end of the step it is computed in and
-        # never materialises it (compared separately below)
-        for c in mdl.info["connections"]:
-            if "delta" in c:
-                skip.update([c["delta"], c["weights"]])
+        for c in pes_conns:
+            skip.update([c["delta"], c["weights"]])
     skip.update(s for g in sim.fused_groups for s in g["unstored"])
-    assert bool(sim.fused_groups) == (fuse and make is not small_sparse)  # (its J has a second writer)
+    sigs = [s for s in state_signals(mdl) if s not in skip]
+    spikes = spike_signals(mdl)
+    tally = Tally()
+    for step in range(steps):
+        sim.step()
+        ora.step()
+        if step % every == 0 or step == steps - 1:
+            compare_signals(sim, ora, sigs, tally, spikes, exact=exact)
+    if fused_pes:
+        for c in pes_conns:
+            got = np.asarray(sim.signals[c["weights"]])
+            ref = ora[c["weights"]] + ora[c["delta"]]
+            tally.total += got.size
+            tally.differ += int(np.count_nonzero(got != ref))
+        assert tally.differ <= tally.total // 1000000
+    for p in mdl.probes:
+        got, ref = sim.data[p], np.array(ora.probe_data[p])
+        assert got.shape == ref.shape
+        if exact:
+            assert np.array_equal(got, ref)
+        else:
+            assert np.sqrt(np.mean((got - ref) ** 2)) < 1e-3
+    return tally
+
+
+@pytest.mark.parametrize("fuse", [False, True])
+@pytest.mark.parametrize("make", [small_ws, small_pes, wide_pes, odd_pes, small_cc, mixed_streamed],
+                         ids=["watts_strogatz", "pes", "pes_1024x16", "pes_301x3", "circular_convolution",
+                              "mixed_streamed"])
+def test_scaled_configs_match_oracle_per_step(make, fuse, parity_report):
+    """Every stored signal of the scaled-down benchmark configurations, bit for bit, each of the
+    first 100 steps, through the fused kernels and through the per-operator kernels."""
+    mdl = make()
+    sim = Simulator(None, model=mdl, fuse=fuse)
+    assert bool(sim.fused_groups) == fuse
     if fuse and make in (wide_pes, mixed_streamed):  # these go through the streamed kernel
         fused_plan = [p for p in sim._plans if p.name == "fused_ensemble_step"][0]
         assert len(fused_plan.tables["streamed"]) == len(mdl.info["ensembles"])
-    sigs = [s for s in state_signals(mdl) if s not in skip]
-    # A different float32 summation order can move a spike by one step; that neuron's state then
-    # differs for a few steps.  In the circular convolution every product feeds all outputs through
-    # the dense output transform, so one moved spike touches every element downstream of it.
-    bad_fraction = 1e-2 if make is small_cc else 2e-3
     with sim:
-        worst = 0.0
-        for step in range(100):
-            sim.step()
-            ora.step()
-            worst = max(worst, compare_signals(sim, ora, sigs, max_bad_fraction=bad_fraction))
-        for c in mdl.info["connections"]:
-            if "delta" in c and fused_pes:
-                got = np.asarray(sim.signals[c["weights"]])
-                ref = ora[c["weights"]] + ora[c["delta"]]
-                # decoders integrate the activity trace over all steps, so a neuron whose spike
-                # moved by one step keeps a small offset: most elements agree to float32
-                # round-off, all of them to 1 %
-                close = np.abs(got - ref) <= 1e-7 + 1e-5 * np.abs(ref)
-                assert close.mean() > 0.95
-                assert np.allclose(got, ref, rtol=1e-2, atol=1e-6)
-        for p in mdl.info["probes"]:
-            got, ref = sim.data[p], np.array(ora.probe_data[p])
-            assert got.shape == ref.shape
-            assert np.sqrt(np.mean((got - ref) ** 2)) < 1e-3
+        tally = run_against_oracle(mdl, sim, 100)
+    parity_report("%s (fuse=%s), 100 steps" % (make.__name__, fuse), **tally.fields())
+
+
+def test_sparse_recurrent_model_within_tolerance(parity_report):
+    """Sparse transform (the shape of the reference's own Watts-Strogatz benchmark): the CUDA
+    sparse kernels add the products of a row in a different order than the reference's CSR
+    kernel, so this model is compared within the tolerance; a neuron whose voltage lands within
+    round-off of the threshold may spike one step apart.  The measured counts are recorded."""
+    mdl = small_sparse()
+    with Simulator(None, model=mdl) as sim:
+        assert not sim.fused_groups  # (its J has a second writer)
+        tally = run_against_oracle(mdl, sim, 100, exact=False)
+    assert tally.out_of_tol <= 2e-3 * tally.total
+    parity_report("sparse recurrent, 100 steps", **tally.fields())
+
+
+FULL_SIZE = {
+    # configuration 3: circular convolution, D = 256 -> 516 product ensembles x 200 LIF
+    "circular_convolution_D256": (lambda: synth.circular_convolution_model(seed=4, dimensions=256), 100, 1),
+    # configuration 4: Watts-Strogatz, 4096 ensembles x 50 LIF, 32768 decoded edges
+    "watts_strogatz_4096x50": (lambda: synth.watts_strogatz_model(seed=2), 100, 10),
+    # configuration 5: 4096 ensembles x 1024 LIF x 16-d with PES (825 MB touched per step)
+    "pes_4096x1024x16": (lambda: synth.pes_learning_model(seed=3, sim_time=0.05), 20, 4),
+}
+
+
+@pytest.mark.parametrize("name", list(FULL_SIZE))
+def test_full_size_configs_match_oracle(name, parity_report):
+    """The benchmark configurations at their FULL size against the CPU oracle (the compiled
+    restatement keeps this to about a minute per model): every stored signal bit for bit, on
+    every step for the circular convolution and on every ``every``-th step (and the last one)
+    for the two large models; probes on every step."""
+    make, steps, every = FULL_SIZE[name]
+    mdl = make()
+    sim = Simulator(None, model=mdl)
+    assert sim.fused_groups
+    with sim:
+        tally = run_against_oracle(mdl, sim, steps, every=every)
+    parity_report("%s, %d steps" % (name, steps), **tally.fields(neurons=mdl.n_neurons))
 
 
 def test_unsupervised_learning_rules_match_oracle():
@@ -311,32 +393,3 @@ def test_unsupervised_learning_rules_match_oracle():
             for sig in tracked:
                 assert np.allclose(np.asarray(sim.signals[sig]), ora[sig], rtol=1e-5, atol=1e-6), sig
         assert np.abs(ora[tracked[0]]).max() > 0
-
-
-def test_full_size_pes_model_streamed_equals_unfused():
-    """Benchmark configuration 5 at its full size (4096 x 1024 LIF x 16-d, 825 MB per step):
-    the streamed fused kernel against the independent per-operator kernels on the same model.
-    Decoded outputs agree to float32 round-off apart from the few that a one-step spike shift
-    touches; the PES decoders agree with weights + delta of the unfused run."""
-    mdl = synth.pes_learning_model(seed=3, n_ensembles=4096, n_neurons=1024, dimensions=16, sim_time=0.05)
-    steps = 12
-    outs = {}
-    for fuse in (True, False):
-        with Simulator(None, model=mdl, fuse=fuse) as sim:
-            if fuse:
-                fused_plan = [p for p in sim._plans if p.name == "fused_ensemble_step"][0]
-                assert len(fused_plan.tables["streamed"]) == 4096
-            sim.run_steps(steps)
-            conns = mdl.info["connections"]
-            sample = conns[::64]
-            outs[fuse] = dict(
-                out=np.concatenate([np.asarray(sim.signals[c["out"]]) for c in conns]),
-                w=[np.asarray(sim.signals[c["weights"]]) for c in sample],
-                d=None if fuse else [np.asarray(sim.signals[c["delta"]]) for c in sample])
-    a, b = outs[True]["out"], outs[False]["out"]
-    bad = np.abs(a - b) > 1e-6 + 1e-5 * np.abs(b)
-    assert bad.mean() < 2e-3, bad.mean()
-    assert np.allclose(a, b, rtol=1e-2, atol=1e-4)
-    for wf, wu, du in zip(outs[True]["w"], outs[False]["w"], outs[False]["d"]):
-        close = np.abs(wf - (wu + du)) <= 1e-7 + 1e-5 * np.abs(wu + du)
-        assert close.mean() > 0.95
