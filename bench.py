@@ -20,11 +20,18 @@ Printed JSON (one line, rank 0):
   spmv       sparse transforms (CSR, ELLPACK) on a Watts-Strogatz adjacency, GB/s;
   small_models  simulated steps/s of configurations 1, 3, 4 and of a sparse
              recurrent population through ``run_steps``;
-  cpu_baseline  the CPU oracle (numpy restatement of the reference's kernels)
-             on a bounded slice of the same workload, one process per host core.
-``--impl reference`` times that CPU oracle alone, on the host cores.
+  cpu_baseline  the CPU oracle on a bounded slice of the same workload: the
+             compiled restatement of the reference's kernels (oracle/cport.c, one
+             loop nest per kernel launch, OpenMP over the ragged items, all host
+             cores), with the numpy operator-list interpreter beside it.
+``--impl reference`` times that compiled CPU oracle alone, on the host cores.
 With N > 1 (torchrun, one rank per GPU) every rank simulates its shard of the
-ensembles and the decoded signals are exchanged each step.
+ensembles and the decoded signals are exchanged each step: ``value`` is the
+weak-scaling figure (``--ensembles`` per GPU); the line also carries a
+``strong`` block (configuration 5 as written: 4096 ensembles split over the
+GPUs) and ``parity_checked`` (a small sharded model through the same exchange
+path, compared bit for bit with the unsharded CPU oracle before anything is
+timed).
 """
 
 import argparse
@@ -42,9 +49,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FULL = dict(n_ensembles=4096, n_neurons=1024, dimensions=16)
-# dram__bytes_read.sum + dram__bytes_write.sum of one nb2_ensemble_stream_kernel launch on 1024 ensembles
-# (profiles/fused_ensemble_step_pes_model.md), per ensemble
-NCU_DRAM_BYTES_PER_ENSEMBLE = (129.85e6 + 27.6e6) / 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the fused kernel on the full-size
+# workload (4096 ensembles), from an ncu capture of this file's own default command; None for
+# other sizes (not captured)
+NCU_DRAM_BYTES_FULL_SIZE = None
+REPEATS = 5  # the timed region runs this many times; the median is reported
 WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
 
 
@@ -140,7 +149,8 @@ class Events:
 
 
 def _oracle_worker(job):
-    """One host process of the CPU baseline: a block of ensembles of the workload on the oracle."""
+    """One host process of the interpreter figure: a block of ensembles of the workload on the
+    numpy operator-list interpreter."""
     seed, n_ensembles, steps, warmup = job
     from nengo_ocl_b200 import synth
     from oracle.simulator import OracleSimulator
@@ -160,10 +170,9 @@ def _oracle_worker(job):
     return mdl.n_neurons, time.perf_counter() - t0
 
 
-def cpu_oracle_rate(n_ensembles, steps, warmup=2):
-    """Neuron updates per second of the CPU oracle on a slice of the workload, one process per
-    host core, each with its own block of ensembles (the blocks only meet in the exchange
-    signal, as on several GPUs).  Returns (rate, seconds per step, neurons, processes)."""
+def cpu_interpreter_rate(n_ensembles, steps, warmup=2):
+    """Neuron updates per second of the numpy interpreter on a slice of the workload, one
+    process per host core, each with its own block of ensembles."""
     import multiprocessing as mp
 
     procs = max(1, min(len(os.sched_getaffinity(0)), n_ensembles // 8))
@@ -177,24 +186,51 @@ def cpu_oracle_rate(n_ensembles, steps, warmup=2):
             results = pool.map(_oracle_worker, jobs)
     neurons = sum(n for n, _ in results)
     slowest = max(t for _, t in results)
-    return neurons * steps / slowest, slowest / steps, neurons, procs
+    return {"value": neurons * steps / slowest, "unit": "neuron-updates/s", "processes": procs,
+            "sample": "%d ensembles (%d neurons), %d steps" % (per * procs, neurons, steps)}
+
+
+def cpu_compiled_rate(n_ensembles, steps, warmup=3):
+    """The timed CPU baseline: the compiled restatement of the reference's kernels
+    (oracle/cport.c through oracle/pes_batch.py; gcc -O2 -fopenmp, every kernel of the reference
+    one loop nest, OpenMP threads over the ragged items) on ``n_ensembles`` of the workload's
+    4096 ensembles.  Returns the ``cpu_baseline`` object."""
+    from nengo_ocl_b200 import synth
+    from oracle.pes_batch import PesBatch
+
+    cores = len(os.sched_getaffinity(0))
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    mdl = synth.pes_learning_model(seed=3, n_ensembles=n_ensembles, n_neurons=FULL["n_neurons"],
+                                   dimensions=FULL["dimensions"], n_templates=2, n_probes=2,
+                                   sim_time=max(steps + warmup, 50) * 1e-3)
+    batch = PesBatch(mdl)
+    batch.run_steps(warmup)
+    t0 = time.perf_counter()
+    batch.run_steps(steps)
+    dt_s = time.perf_counter() - t0
+    return {"value": mdl.n_neurons * steps / dt_s, "unit": "neuron-updates/s",
+            "cores": int(os.environ["OMP_NUM_THREADS"]), "kind": "port",
+            "implementation": "C restatement of the reference's kernels (oracle/cport.c), gcc -O2 -fopenmp, "
+                              "one loop nest per kernel launch",
+            "sample": "%d of 4096 ensembles (%d neurons), %d steps, %.1f s" % (n_ensembles, mdl.n_neurons, steps,
+                                                                               dt_s),
+            "ms_per_step_of_sample": 1e3 * dt_s / steps,
+            "host_gbs": batch.bytes_per_step * steps / dt_s / 1e9}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    n_ens = 512
-    rate, s_per_step, n_neurons, cores = cpu_oracle_rate(n_ens, args.steps, warmup=min(max(args.warmup, 1), 3))
-    sample = "%d of 4096 ensembles (%d neurons) in %d processes, %d steps" % (n_ens, n_neurons, cores, args.steps)
+    base = cpu_compiled_rate(512, max(args.steps, 1), warmup=min(max(args.warmup, 1), 3))
     line = {
-        "impl": "reference", "metric": "neuron_updates_per_s", "value": rate, "unit": "neuron-updates/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * s_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": rate, "unit": "neuron-updates/s", "cores": cores, "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": rate, "unit": "neuron-updates/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "steps_per_s_of_sample": 1.0 / s_per_step,
+        "impl": "reference", "metric": "neuron_updates_per_s", "value": base["value"], "unit": "neuron-updates/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["ms_per_step_of_sample"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": base["sample"]},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "neuron-updates/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
@@ -219,9 +255,18 @@ def gemv_microbench(queue, capi, reps=20, n_outputs=4096):
             plan.kern(queue.stream)
         times.append(ev.stop_ms(queue.stream) / batch)
     ms = float(np.median(times))
+    alone = []  # one call at a time on an idle stream (the pipeline fills and drains inside the call)
+    for _ in range(reps):
+        capi.call("nb2_stream_sync", queue.stream)
+        ev.start(queue.stream)
+        plan.kern(queue.stream)
+        alone.append(ev.stop_ms(queue.stream))
+    ms_alone = float(np.median(alone))
     return {"workload": "ragged gather-GEMV, %d outputs x 1-4 terms, M U[1,1024], N U[1,64], seed 1" % n_outputs,
             "bytes_per_call": int(plan.bw_per_call), "ms_per_call": ms,
             "achieved_gbs": plan.bw_per_call / ms / 1e6, "launches_per_call": plan.n_launches,
+            "timing": "5 calls back to back per event pair, as inside a step loop",
+            "isolated_call": {"ms_per_call": ms_alone, "achieved_gbs": plan.bw_per_call / ms_alone / 1e6},
             "status": int(plan.status.get()[0])}
 
 
@@ -368,19 +413,46 @@ def main():
         return
 
     K, W = args.steps, max(args.warmup, 3)
-    t_build = time.perf_counter()
-    # weak scaling: every GPU simulates `--ensembles` ensembles of one network of world * ensembles
-    mdl = synth.pes_learning_shard(seed=3, n_ensembles=args.ensembles * world, rank=rank, world=world,
-                                   n_neurons=FULL["n_neurons"], dimensions=FULL["dimensions"], sim_time=0.5)
-    n_neurons = mdl.n_neurons
-    exchange = None
+    parity_checked = None
     if world > 1:
-        from nengo_ocl_b200.exchange import TorchComm
+        parity_checked = sharded_parity_check(ctx, rank, world, dist)
 
-        exchange = (mdl.info["exchange"], TorchComm())
-    # probes are drained (and the next window of the error tables uploaded) every 256 steps
-    sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True, exchange=exchange, n_prealloc_probes=256)
-    build_s = time.perf_counter() - t_build
+    def build(n_total):
+        """This rank's shard of a PES learning model of ``n_total`` ensembles."""
+        t0 = time.perf_counter()
+        mdl = synth.pes_learning_shard(seed=3, n_ensembles=n_total, rank=rank, world=world,
+                                       n_neurons=FULL["n_neurons"], dimensions=FULL["dimensions"], sim_time=0.5)
+        exchange = None
+        if world > 1:
+            from nengo_ocl_b200.exchange import TorchComm
+
+            exchange = (mdl.info["exchange"], TorchComm())
+        # probes are drained (and the next window of the error tables uploaded) every 256 steps
+        sim = Simulator(None, model=mdl, context=ctx, stream_inputs=True, exchange=exchange, n_prealloc_probes=256)
+        return mdl, sim, time.perf_counter() - t0
+
+    def device_timed(sim, steps):
+        """Milliseconds (max over ranks) of ``steps`` graph-replayed steps, inputs resident."""
+        plans, queue = sim._plans, sim.queue
+        B = sim._max_steps_between_probes
+        done, total_ms = 0, 0.0
+        while done < steps:
+            b = min(B, steps - done)
+            sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
+            _capi.call("nb2_stream_sync", queue.stream)
+            barrier()                  # (a rank that starts early would time its wait for the others' uploads)
+            ev.start(queue.stream)
+            plans.enqueue_n_times(b)
+            total_ms += ev.stop_ms(queue.stream)
+            sim._probe()               # drain outside the timed region
+            done += b
+        barrier()
+        _capi.call("nb2_device_sync")
+        return max_over_ranks(total_ms)
+
+    # weak scaling: every GPU simulates `--ensembles` ensembles of one network of world * ensembles
+    mdl, sim, build_s = build(args.ensembles * world)
+    n_neurons = mdl.n_neurons
     plans = sim._plans
     fused = [p for p in plans if p.name == "fused_ensemble_step"]
     assert fused, "the fused ensemble kernel must be on the path"
@@ -389,35 +461,23 @@ def main():
     ev = Events(_capi)
 
     # ---- value: device-timed, inputs resident ---------------------------------
-    sim._upload_inputs(min(W, sim._max_steps_between_probes))
-    plans.call_n_times(min(W, sim._max_steps_between_probes))
-    sim._probe()
     B = sim._max_steps_between_probes
+    sim._upload_inputs(min(W, B))
+    plans.call_n_times(min(W, B))
+    sim._probe()
     barrier()
     _capi.call("nb2_device_sync")
     clocks = ClockSampler(local_rank if rank == 0 else None)
     clocks.__enter__()
-    done, total_ms = 0, 0.0
-    while done < K:
-        b = min(B, K - done)
-        sim._upload_inputs(b)      # not timed: inputs are resident when the timed region starts
-        _capi.call("nb2_stream_sync", queue.stream)
-        barrier()                  # (a rank that starts early would time its wait for the others' uploads)
-        ev.start(queue.stream)
-        plans.enqueue_n_times(b)
-        total_ms += ev.stop_ms(queue.stream)
-        sim._probe()               # drain outside the timed region
-        done += b
-    barrier()
-    _capi.call("nb2_device_sync")
-    total_ms = max_over_ranks(total_ms)
+    region_ms = [device_timed(sim, K) for _ in range(REPEATS)]
+    total_ms = float(np.median(region_ms))
     ms_per_step = total_ms / K
     value = world * n_neurons * K / (total_ms / 1e3)
     launches = K * plans.launches_per_step
 
     # ---- roofline: the fused kernel, CUDA events around every launch -----------
     times = []
-    for _ in range(min(K, 30)):
+    for _ in range(min(max(K, 10), 30)):
         for p in plans:
             if p is fused_plan:
                 ev.start(queue.stream)
@@ -431,23 +491,30 @@ def main():
     peak, peak_src = measured_peak_gbs()
     achieved = fused_plan.bw_per_call / fused_ms / 1e6
     streamed = len(fused_plan.tables["streamed"])
+    full_size = args.ensembles == FULL["n_ensembles"]
     roofline = {"bound": "hbm",
                 "kernel": "nb2_ensemble_stream_kernel" if streamed else "nb2_ensemble_step_kernel",
                 "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": int(NCU_DRAM_BYTES_PER_ENSEMBLE * args.ensembles),
-                "traffic_note": "dram read+write of the 1024-ensemble ncu capture scaled by ensemble count; lower "
-                                "bound (206 MB per launch there is only 1.6x the L2)",
+                "traffic": NCU_DRAM_BYTES_FULL_SIZE if full_size else None,
+                "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture of this "
+                                "command at full size" if full_size and NCU_DRAM_BYTES_FULL_SIZE else
+                                "not captured at this size",
                 "algorithmic_bytes_per_launch": int(fused_plan.bw_per_call), "ms_per_launch": fused_ms,
-                "share_of_step": fused_ms / ms_per_step}
+                "ms_per_launch_min_max": [float(np.min(times)), float(np.max(times))],
+                "share_of_step": fused_ms / ms_per_step,
+                "whole_step_frac": fused_plan.bw_per_call / ms_per_step / 1e6 / peak}
 
     # ---- e2e: public API, host tables in, probe data out ------------------------
-    barrier()
-    _capi.call("nb2_device_sync")
-    t0 = time.perf_counter()
-    sim.run_steps(K)
-    _capi.call("nb2_device_sync")
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_runs = []
+    for _ in range(REPEATS):
+        barrier()
+        _capi.call("nb2_device_sync")
+        t0 = time.perf_counter()
+        sim.run_steps(K)
+        _capi.call("nb2_device_sync")
+        e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
+    e2e_s = float(np.median(e2e_runs))
     # The timed regions of a short run are over before the sampler has three readings: keep the same
     # steps running (untimed, every rank alike because the ranks step together) until it has.
     for _ in range(40):
@@ -459,41 +526,113 @@ def main():
     probe_bytes = sum(4 * int(mdl.sig[p]["in"].size) for p in mdl.probes) + 4 * len(mdl.probes) / B + 8.0 / B
     e2e = {"value": world * n_neurons * K / e2e_s, "unit": "neuron-updates/s",
            "h2d_bytes_per_step": int(sim.h2d_bytes_per_step), "d2h_bytes_per_step": int(round(probe_bytes)),
-           "steps_per_s": K / e2e_s}
+           "steps_per_s": K / e2e_s, "ms_per_step_min_max": [1e3 * min(e2e_runs) / K, 1e3 * max(e2e_runs) / K]}
 
+    ens_tab = fused_plan.tables["ens"]
     line = {
         "metric": "neuron_updates_per_s", "value": value, "unit": "neuron-updates/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "ensembles_per_gpu": args.ensembles, "neurons_per_gpu": n_neurons,
+                   # an ensemble that no connection targets has a constant-zero input: the simplifier drops
+                   # its encoder product, so it does no encoder work (targets are drawn at random)
+                   "ensembles_with_encoder_input": int(np.count_nonzero(ens_tab[:, 6] > 0)),
+                   "arithmetic": "float32 in the summation order of the reference's block GEMV, no fused "
+                                 "multiply-add; expm1/log1p correctly rounded (bit-identical to the CPU oracle)",
                    "l2": "working set per step (~0.9 GB) exceeds the 126 MB L2", "build_s": round(build_s, 1),
                    "plans_per_step": len(plans), "graph_unroll": plans.unroll, "steps_per_probe_drain": B,
+                   "timed_region": "%d repeats of %d steps, median; min/max in `timing`" % (REPEATS, K),
                    "parallelism": "ensemble blocks, 1 rank per GPU, per-step peer push of decoded signals"
                                   if world > 1 else "single GPU",
                    "exchange_bytes_per_step_per_gpu": 4 * mdl.info["segment"][1] * (world - 1)},
-        "steps_per_s": K / (total_ms / 1e3), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
-        "clocks": clocks.summary(),
+        "steps_per_s": K / (total_ms / 1e3),
+        "timing": {"ms_per_step_median": ms_per_step, "ms_per_step_min": min(region_ms) / K,
+                   "ms_per_step_max": max(region_ms) / K, "repeats": REPEATS},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
     }
+    if parity_checked is not None:
+        line["parity_checked"] = parity_checked
+    sim.close()
+    del sim, mdl, plans, fused_plan
+    if world > 1 and FULL["n_ensembles"] % world == 0:
+        # ---- strong scaling: configuration 5 as written, 4096 ensembles over all GPUs ----
+        mdl_s, sim_s, _ = build(FULL["n_ensembles"])
+        Bs = sim_s._max_steps_between_probes
+        sim_s._upload_inputs(min(W, Bs))
+        sim_s._plans.call_n_times(min(W, Bs))
+        sim_s._probe()
+        strong_ms = float(np.median([device_timed(sim_s, K) for _ in range(REPEATS)]))
+        line["strong"] = {"workload": "%d ensembles in total, %d per GPU" % (FULL["n_ensembles"],
+                                                                           FULL["n_ensembles"] // world),
+                          "n_gpus": world, "ms_per_step": strong_ms / K, "steps_per_s": K / (strong_ms / 1e3),
+                          "neuron_updates_per_s": FULL["n_ensembles"] * FULL["n_neurons"] * K / (strong_ms / 1e3),
+                          "note": "speed-up = this steps_per_s over the steps_per_s of the 1-GPU line"}
+        sim_s.close()
+        del sim_s, mdl_s
     if rank == 0 and not args.no_gemv:
-        line["gemv"] = gemv_microbench(queue, _capi)
+        from nengo_ocl_b200.runtime import CommandQueue
+
+        q2 = CommandQueue(ctx)
+        line["gemv"] = gemv_microbench(q2, _capi)
         line["gemv"]["frac"] = line["gemv"]["achieved_gbs"] / peak
+        line["gemv"]["isolated_call"]["frac"] = line["gemv"]["isolated_call"]["achieved_gbs"] / peak
     if rank == 0 and not args.no_spmv and world == 1:
-        line["spmv"] = spmv_microbench(queue, _capi)
+        from nengo_ocl_b200.runtime import CommandQueue
+
+        line["spmv"] = spmv_microbench(CommandQueue(ctx), _capi)
         for k in ("csr", "ellpack"):
             line["spmv"][k]["frac"] = line["spmv"][k]["achieved_gbs"] / peak
     if rank == 0 and not args.no_small and world == 1:
         line["small_models"] = small_model_rates(ctx, _capi)
     if rank == 0 and not args.no_cpu and world == 1:
-        n_ens = 512
-        rate, s_per_step, nn, cores = cpu_oracle_rate(n_ens, 20)
-        line["cpu_baseline"] = {"value": rate, "unit": "neuron-updates/s", "cores": cores, "kind": "port",
-                                "sample": "%d of 4096 ensembles (%d neurons) in %d processes, 20 steps"
-                                          % (n_ens, nn, cores)}
-    sim.close()
+        line["cpu_baseline"] = cpu_compiled_rate(512, 150)
+        line["cpu_baseline"]["numpy_interpreter"] = cpu_interpreter_rate(256, 10)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def sharded_parity_check(ctx, rank, world, dist, steps=70):
+    """A small sharded model (8 ensembles per rank) through the same fused step and per-step
+    exchange as the benchmark, against the unsharded CPU oracle: every rank compares its own
+    segment of the exchange signal and its probe bit for bit.  Returns True only if every rank
+    agrees with the oracle."""
+    import torch
+
+    from nengo_ocl_b200 import synth
+    from nengo_ocl_b200.exchange import TorchComm
+    from nengo_ocl_b200.simulator import Simulator
+    from oracle.simulator import OracleSimulator
+
+    kw = dict(seed=5, n_ensembles=8 * world, n_neurons=256, dimensions=8, n_templates=2, n_probes=2, sim_time=0.1)
+    mdl = synth.pes_learning_shard(rank=rank, world=world, **kw)
+    ok = True
+    with Simulator(None, model=mdl, context=ctx, exchange=(mdl.info["exchange"], TorchComm())) as sim:
+        sim.run_steps(steps)
+        ok = ok and sim._exchange.status() == 0
+        got = np.asarray(sim.signals[mdl.info["exchange"]])
+        probe = np.asarray(sim.data[mdl.probes[0]])
+        dist.barrier()
+    full = synth.pes_learning_shard(rank=0, world=1, **kw)
+    ora = OracleSimulator(full)
+    rows = []
+    for _ in range(steps):
+        ora.step()
+        rows.append(ora[full.info["exchange"]])
+    ref = rows[-1]
+    seg = ref.size // world
+    own = slice(rank * seg, (rank + 1) * seg)
+    ok = ok and bool(np.array_equal(got[own], ref[own]))
+    # the probe of this rank's first probed connection, every step
+    g = mdl.info["probe_ids"][0]
+    d = kw["dimensions"]
+    ref_probe = np.array([row[g * d:(g + 1) * d] for row in rows])
+    ok = ok and probe.shape == ref_probe.shape and bool(np.array_equal(probe, ref_probe))
+    flag = torch.tensor([1.0 if ok else 0.0], dtype=torch.float64, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item() == 1.0)
 
 
 if __name__ == "__main__":

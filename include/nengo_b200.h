@@ -30,6 +30,14 @@ extern "C" {
  * 128-196 (to_device, to_host, enqueue_copy), plan.py:85-149 (enqueue loop). */
 const char* nb2_last_error(void);
 int nb2_abi_version(void);
+/* Kernels are launched with the programmatic-stream-serialization attribute
+ * (the next kernel of a stream or captured graph is scheduled while the
+ * current one runs and waits, at its first instruction, for everything before
+ * it to complete): the launch gaps of a step's chain of small kernels overlap
+ * with execution, data dependencies are those of an in-order stream.  On by
+ * default; 0 turns it off (also: environment variable NENGO_B200_PDL=0).  No
+ * counterpart in the reference (one OpenCL in-order queue, plan.py:85-91). */
+int nb2_set_programmatic_launch(int enabled);
 int nb2_device_count(int* count);
 int nb2_set_device(int ordinal);
 int nb2_device_info(int ordinal, int* sm_count, int* max_threads_per_block, size_t* global_mem,

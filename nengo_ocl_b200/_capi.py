@@ -41,6 +41,7 @@ _P = c_void_p  # every device / host pointer crosses the boundary as void*
 
 _SIGNATURES = {
     "nb2_abi_version": [],
+    "nb2_set_programmatic_launch": [c_int],
     "nb2_device_count": [POINTER(c_int)],
     "nb2_set_device": [c_int],
     "nb2_device_info": [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_size_t), POINTER(c_size_t),

@@ -44,6 +44,41 @@ void nb2_set_error(const char* fmt, ...);
 
 static inline cudaStream_t nb2_stream(void* s) { return (cudaStream_t)s; }
 
+// ---- programmatic dependent launch -----------------------------------------------------
+// A simulation step is a chain of small dependent launches; most of a tiny kernel's cost is
+// the launch gap before it.  Every kernel of this library is launched with the
+// programmatic-stream-serialization attribute and starts with nb2_pdl_enter(): the next
+// kernel of the stream (or of the captured graph) may be scheduled while this one still runs
+// and then waits, at its first instruction, until every kernel before it has completed and
+// flushed its memory.  The data dependencies are exactly those of an ordinary in-order
+// stream; only the launch latency overlaps.  nb2_set_programmatic_launch(0) (or the
+// environment variable NENGO_B200_PDL=0) turns the attribute off; the device-side
+// instructions are then no-ops.
+extern "C" int nb2_programmatic_launch_enabled();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void nb2_pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t nb2_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = nb2_programmatic_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // B200: 148 SMs. Grid sizes for grid-stride kernels are multiples of this.
 #define NB2_NUM_SMS 148
 

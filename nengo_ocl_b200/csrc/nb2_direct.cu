@@ -21,6 +21,7 @@ __global__ void nb2_direct_kernel(int n_items, const int2* __restrict__ prog, in
                                   const double* __restrict__ consts, const int* __restrict__ in0_starts,
                                   const float* in0, const int* __restrict__ in1_starts, const float* in1,
                                   const int* __restrict__ out_starts, float* out) {
+  nb2_pdl_enter();
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= n_items) return;
   const float* x0 = in0 ? in0 + in0_starts[n] : nullptr;
@@ -100,8 +101,7 @@ extern "C" int nb2_direct(void* stream, int n_items, const int* prog, int n_ops,
   NB2_REQUIRE(max_depth >= 0 && max_depth <= NB2_DIRECT_STACK, "program needs a deeper evaluation stack");
   NB2_REQUIRE((in0 == NULL) == (in0_starts == NULL) && (in1 == NULL) == (in1_starts == NULL),
               "input buffer/starts mismatch");
-  nb2_direct_kernel<<<(n_items + 127) / 128, 128, 0, nb2_stream(stream)>>>(
-      n_items, reinterpret_cast<const int2*>(prog), n_ops, consts, in0_starts, in0, in1_starts, in1,
+  nb2_launch(nb2_direct_kernel, dim3((n_items + 127) / 128), dim3(128), 0, nb2_stream(stream), n_items, reinterpret_cast<const int2*>(prog), n_ops, consts, in0_starts, in0, in1_starts, in1,
       out_starts, out);
   NB2_LAUNCH_CHECK();
   return NB2_OK;

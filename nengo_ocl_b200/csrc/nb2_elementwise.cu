@@ -10,6 +10,7 @@
 
 // ---- plan_timeupdate (clra_nonlinearities.py:119-133) ----------------------
 __global__ void nb2_timeupdate_kernel(float* step, float* time, double dt) {
+  nb2_pdl_enter();
   const float s = step[0] + 1.0f;
   step[0] = s;
   time[0] = (float)(dt * (double)s);  // dt is a double literal in the reference source
@@ -17,7 +18,7 @@ __global__ void nb2_timeupdate_kernel(float* step, float* time, double dt) {
 
 extern "C" int nb2_timeupdate(void* stream, float* step, float* time, double dt) {
   NB2_REQUIRE(step && time, "null pointer");
-  nb2_timeupdate_kernel<<<1, 1, 0, nb2_stream(stream)>>>(step, time, dt);
+  nb2_launch(nb2_timeupdate_kernel, dim3(1), dim3(1), 0, nb2_stream(stream), step, time, dt);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -26,6 +27,7 @@ extern "C" int nb2_timeupdate(void* stream, float* step, float* time, double dt)
 __global__ void nb2_reset_kernel(int n_blocks, const float* __restrict__ values,
                                  const int* __restrict__ sizes, const int* __restrict__ starts,
                                  float* Y) {
+  nb2_pdl_enter();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int n = t >> 4;
   const int i = t & 15;
@@ -37,8 +39,7 @@ extern "C" int nb2_reset(void* stream, int n_blocks, const float* values, const 
   if (n_blocks == 0) return NB2_OK;
   NB2_REQUIRE(values && sizes && starts && Y, "null pointer");
   const long long threads = (long long)n_blocks * 16;
-  nb2_reset_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, nb2_stream(stream)>>>(
-      n_blocks, values, sizes, starts, Y);
+  nb2_launch(nb2_reset_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, nb2_stream(stream), n_blocks, values, sizes, starts, Y);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -50,6 +51,7 @@ __global__ void nb2_copy_kernel(int inc_mode, const int* __restrict__ incdata,
                                 const int* __restrict__ Xstarts, const float* X,
                                 const int* __restrict__ Ystride0s, const int* __restrict__ Ystarts,
                                 float* Y) {
+  nb2_pdl_enter();
   const int n = blockIdx.x;
   const int ij = threadIdx.x + offsets[n];
   const int shape1 = shape1s[n];
@@ -71,7 +73,7 @@ extern "C" int nb2_copy(void* stream, int n_blocks, int inc_mode, const int* inc
   NB2_REQUIRE(offsets && shape0s && shape1s && Xstride0s && Xstarts && X && Ystride0s && Ystarts && Y,
               "null pointer");
   NB2_REQUIRE(inc_mode != 2 || incdata, "incdata required for inc_mode 2");
-  nb2_copy_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(inc_mode, incdata, offsets, shape0s, shape1s,
+  nb2_launch(nb2_copy_kernel, dim3(n_blocks), dim3(256), 0, nb2_stream(stream), inc_mode, incdata, offsets, shape0s, shape1s,
                                                            Xstride0s, Xstarts, X, Ystride0s, Ystarts, Y);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
@@ -88,6 +90,7 @@ __global__ void nb2_slicedcopy_kernel(int n_blocks, int inc_mode, const int* __r
                                       const int* __restrict__ XIdata,
                                       const int* __restrict__ YIstarts,
                                       const int* __restrict__ YIdata) {
+  nb2_pdl_enter();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int n = t >> 4;
   const int i = t & 15;
@@ -112,8 +115,7 @@ extern "C" int nb2_slicedcopy(void* stream, int n_blocks, int inc_mode, const in
               "null pointer");
   NB2_REQUIRE(inc_mode != 2 || incdata, "incdata required for inc_mode 2");
   const long long threads = (long long)n_blocks * 16;
-  nb2_slicedcopy_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, nb2_stream(stream)>>>(
-      n_blocks, inc_mode, incdata, Xstride0s, Xstarts, X, Ystride0s, Ystarts, Y, Isizes, XIstarts, XIdata,
+  nb2_launch(nb2_slicedcopy_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, nb2_stream(stream), n_blocks, inc_mode, incdata, Xstride0s, Xstarts, X, Ystride0s, Ystarts, Y, Isizes, XIstarts, XIdata,
       YIstarts, YIdata);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
@@ -136,6 +138,7 @@ __global__ void nb2_elementwise_inc_kernel(
     const int* __restrict__ Xstride0s, const int* __restrict__ Xstarts, const float* X,
     const int* __restrict__ Yshape0s, const int* __restrict__ Yshape1s,
     const int* __restrict__ Ystride0s, const int* __restrict__ Ystarts, float* Y) {
+  nb2_pdl_enter();
   const int n = blockIdx.x;
   const int ij = threadIdx.x + offsets[n];
   const float* a = A + Astarts[n];
@@ -172,8 +175,7 @@ extern "C" int nb2_elementwise_inc(void* stream, int n_blocks, int outer, int in
   NB2_REQUIRE(offsets && Ashape0s && Ashape1s && Astride0s && Astarts && A && Xshape0s && Xshape1s &&
                   Xstride0s && Xstarts && X && Yshape0s && Yshape1s && Ystride0s && Ystarts && Y,
               "null pointer");
-  nb2_elementwise_inc_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(
-      outer, inc, alphas, offsets, Ashape0s, Ashape1s, Astride0s, Astarts, A, Xshape0s, Xshape1s, Xstride0s,
+  nb2_launch(nb2_elementwise_inc_kernel, dim3(n_blocks), dim3(256), 0, nb2_stream(stream), outer, inc, alphas, offsets, Ashape0s, Ashape1s, Astride0s, Astarts, A, Xshape0s, Xshape1s, Xstride0s,
       Xstarts, X, Yshape0s, Yshape1s, Ystride0s, Ystarts, Y);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
@@ -191,6 +193,7 @@ __global__ void nb2_linearfilter_kernel(
     const float* __restrict__ Bdata, const int* __restrict__ Xbufstarts, float* Xbufdata,
     const int* __restrict__ Ybufstarts, float* Ybufdata, const int* __restrict__ Xbufpos,
     const int* __restrict__ Ybufpos) {
+  nb2_pdl_enter();
   const int k = blockIdx.x;
   const int ij = threadIdx.x + offsets[k];
   const int shape0 = shape0s[k];
@@ -235,6 +238,7 @@ __global__ void nb2_linearfilter_kernel(
 __global__ void nb2_linearfilter_inc_kernel(int n, const int* __restrict__ Ashape0s,
                                             const int* __restrict__ Bshape0s, int* Xbufpos,
                                             int* Ybufpos) {
+  nb2_pdl_enter();
   const int k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k >= n) return;
   const int ix = Xbufpos[k];
@@ -259,12 +263,11 @@ extern "C" int nb2_linearfilter(void* stream, int n_blocks, int block_size, int 
   NB2_REQUIRE(!uses_buf || (Xbufstarts && Xbuf && Ybufstarts && Ybuf && Xbufpos && Ybufpos),
               "ring buffers required when uses_buf");
   cudaStream_t s = nb2_stream(stream);
-  nb2_linearfilter_kernel<<<n_blocks, block_size, 0, s>>>(
-      uses_buf, offsets, shape0s, shape1s, Xstride0s, Xstride1s, Xstarts, X, Ystride0s, Ystride1s, Ystarts, Y,
+  nb2_launch(nb2_linearfilter_kernel, dim3(n_blocks), dim3(block_size), 0, s, uses_buf, offsets, shape0s, shape1s, Xstride0s, Xstride1s, Xstarts, X, Ystride0s, Ystride1s, Ystarts, Y,
       Ashape0s, Astarts, A, Bshape0s, Bstarts, B, Xbufstarts, Xbuf, Ybufstarts, Ybuf, Xbufpos, Ybufpos);
   NB2_LAUNCH_CHECK();
   if (uses_buf) {
-    nb2_linearfilter_inc_kernel<<<(n_blocks + 255) / 256, 256, 0, s>>>(n_blocks, Ashape0s, Bshape0s, Xbufpos,
+    nb2_launch(nb2_linearfilter_inc_kernel, dim3((n_blocks + 255) / 256), dim3(256), 0, s, n_blocks, Ashape0s, Bshape0s, Xbufpos,
                                                                        Ybufpos);
     NB2_LAUNCH_CHECK();
   }
@@ -298,6 +301,7 @@ struct LearnArgs {
 
 template <int RULE>
 __global__ void nb2_learning_delta_kernel(const LearnArgs a) {
+  nb2_pdl_enter();
   const int ij = blockIdx.x * blockDim.x + threadIdx.x;
   const int k = blockIdx.y;
   const int shape0 = a.shape0s[k];
@@ -346,9 +350,9 @@ extern "C" int nb2_learning_delta(void* stream, int rule, int n_items, int max_s
                  learn_starts, learn, scale_stride0s, scale_starts, scale};
   const dim3 grid((max_size + 255) / 256, n_items);
   cudaStream_t s = nb2_stream(stream);
-  if (rule == NB2_RULE_BCM) nb2_learning_delta_kernel<NB2_RULE_BCM><<<grid, 256, 0, s>>>(a);
-  else if (rule == NB2_RULE_OJA) nb2_learning_delta_kernel<NB2_RULE_OJA><<<grid, 256, 0, s>>>(a);
-  else nb2_learning_delta_kernel<NB2_RULE_VOJA><<<grid, 256, 0, s>>>(a);
+  if (rule == NB2_RULE_BCM) nb2_launch(nb2_learning_delta_kernel<NB2_RULE_BCM>, dim3(grid), dim3(256), 0, s, a);
+  else if (rule == NB2_RULE_OJA) nb2_launch(nb2_learning_delta_kernel<NB2_RULE_OJA>, dim3(grid), dim3(256), 0, s, a);
+  else nb2_launch(nb2_learning_delta_kernel<NB2_RULE_VOJA>, dim3(grid), dim3(256), 0, s, a);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -360,6 +364,7 @@ __global__ void nb2_probes_kernel(float* countdowns, int* bufpositions,
                                   const int* __restrict__ Xstride0s,
                                   const int* __restrict__ Xstride1s, const float* X,
                                   const int* __restrict__ Ystarts, float* Y) {
+  nb2_pdl_enter();
   const int n = blockIdx.x;
   const float countdown = countdowns[n];
   const int bufpos = bufpositions[n];
@@ -395,8 +400,7 @@ extern "C" int nb2_probes(void* stream, int n_probes, int block_size, float* cou
   NB2_REQUIRE(countdowns && bufpositions && periods && Xstarts && Xshape0s && Xshape1s && Xstride0s &&
                   Xstride1s && X && Ystarts && Y,
               "null pointer");
-  nb2_probes_kernel<<<n_probes, block_size, 0, nb2_stream(stream)>>>(
-      countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y);
+  nb2_launch(nb2_probes_kernel, dim3(n_probes), dim3(block_size), 0, nb2_stream(stream), countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -410,6 +414,7 @@ __global__ void __launch_bounds__(PROBE_THREADS) nb2_probes_wide_kernel(
     float* countdowns, int* bufpositions, const float* __restrict__ periods, const int* __restrict__ Xstarts,
     const int* __restrict__ Xshape0s, const int* __restrict__ Xshape1s, const int* __restrict__ Xstride0s,
     const int* __restrict__ Xstride1s, const float* X, const int* __restrict__ Ystarts, float* Y, int* arrive) {
+  nb2_pdl_enter();
   const int n = blockIdx.y;
   const float countdown = countdowns[n];
   const int bufpos = bufpositions[n];
@@ -450,8 +455,7 @@ static int nb2_probes_wide_launch(void* stream, int n_probes, int chunks, float*
   NB2_REQUIRE(countdowns && bufpositions && periods && Xstarts && Xshape0s && Xshape1s && Xstride0s &&
                   Xstride1s && X && Ystarts && Y && arrive,
               "null pointer");
-  nb2_probes_wide_kernel<<<dim3(chunks, n_probes), PROBE_THREADS, 0, nb2_stream(stream)>>>(
-      countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive);
+  nb2_launch(nb2_probes_wide_kernel, dim3(dim3(chunks, n_probes)), dim3(PROBE_THREADS), 0, nb2_stream(stream), countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -498,6 +502,7 @@ __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float 
                                         const int* __restrict__ Sstarts,
                                         const int* __restrict__ Sstride0s,
                                         const float* __restrict__ S) {
+  nb2_pdl_enter();
   const int k = blockIdx.x;
   const int m = Yshape0s[k];
   float* y = Y + Ystarts[k];
@@ -518,8 +523,7 @@ extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const
   if (n_items == 0) return NB2_OK;
   NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
   NB2_REQUIRE(Yshape0s && Ystarts && Y && Tstarts && T && Sshape0s && Sstarts && S, "null pointer");
-  nb2_presentinput_kernel<<<n_items, block_size, 0, nb2_stream(stream)>>>(
-      pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S);
+  nb2_launch(nb2_presentinput_kernel, dim3(n_items), dim3(block_size), 0, nb2_stream(stream), pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -534,6 +538,7 @@ extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const
 // src_starts: element offset of every (block, source) pair.
 __global__ void nb2_gather_sum_kernel(const int4* __restrict__ blocks, const int* __restrict__ src_starts,
                                       float* data) {
+  nb2_pdl_enter();
   const int4 b = blocks[blockIdx.x];
   const int i = threadIdx.x;
   if (i >= b.y) return;
@@ -545,7 +550,7 @@ __global__ void nb2_gather_sum_kernel(const int4* __restrict__ blocks, const int
 extern "C" int nb2_gather_sum(void* stream, int n_blocks, const int* blocks, const int* src_starts, float* data) {
   if (n_blocks == 0) return NB2_OK;
   NB2_REQUIRE(blocks && src_starts && data, "null pointer");
-  nb2_gather_sum_kernel<<<n_blocks, 256, 0, nb2_stream(stream)>>>(reinterpret_cast<const int4*>(blocks),
+  nb2_launch(nb2_gather_sum_kernel, dim3(n_blocks), dim3(256), 0, nb2_stream(stream), reinterpret_cast<const int4*>(blocks),
                                                                  src_starts, data);
   NB2_LAUNCH_CHECK();
   return NB2_OK;

@@ -27,6 +27,7 @@
 // peers' staged segments (parity epoch & 1) into the local replica.
 __global__ void nb2_exchange_wait_kernel(int* ctl, const int* flags, const float* staging, float* replica,
                                          int rank, int world, int seg, long long timeout_ns) {
+  nb2_pdl_enter();
   const int epoch = ctl[X_EPOCH];
   if (epoch == 0) return;  // nothing has been exchanged yet: replicas hold the initial values
   __shared__ int s_ok;
@@ -59,6 +60,7 @@ __global__ void nb2_exchange_wait_kernel(int* ctl, const int* flags, const float
 // of parity (epoch+1) & 1, then (last block) publish epoch+1 to every peer.
 __global__ void nb2_exchange_push_kernel(int* ctl, float* const* peer_staging, int* const* peer_flags,
                                          const float* replica, int rank, int world, int seg) {
+  nb2_pdl_enter();
   const int next = ctl[X_EPOCH] + 1;
   const size_t off = (size_t)(next & 1) * world * seg + (size_t)rank * seg;
   const float* src = replica + (size_t)rank * seg;
@@ -90,8 +92,7 @@ extern "C" int nb2_exchange_wait(void* stream, int* ctl, const int* flags, const
   int blocks = (int)((total + EXCH_THREADS * 8 - 1) / (EXCH_THREADS * 8));
   if (blocks > 2 * NB2_NUM_SMS) blocks = 2 * NB2_NUM_SMS;
   if (blocks < 1) blocks = 1;
-  nb2_exchange_wait_kernel<<<blocks, EXCH_THREADS, 0, nb2_stream(stream)>>>(
-      ctl, flags, staging, replica, rank, world, seg, (long long)(timeout_s * 1e9));
+  nb2_launch(nb2_exchange_wait_kernel, dim3(blocks), dim3(EXCH_THREADS), 0, nb2_stream(stream), ctl, flags, staging, replica, rank, world, seg, (long long)(timeout_s * 1e9));
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -104,7 +105,7 @@ extern "C" int nb2_exchange_push(void* stream, int* ctl, float* const* peer_stag
   int blocks = (seg + EXCH_THREADS * 4 - 1) / (EXCH_THREADS * 4);
   if (blocks > NB2_NUM_SMS) blocks = NB2_NUM_SMS;
   if (blocks < 1) blocks = 1;
-  nb2_exchange_push_kernel<<<blocks, EXCH_THREADS, 0, nb2_stream(stream)>>>(ctl, peer_staging, peer_flags,
+  nb2_launch(nb2_exchange_push_kernel, dim3(blocks), dim3(EXCH_THREADS), 0, nb2_stream(stream), ctl, peer_staging, peer_flags,
                                                                             replica, rank, world, seg);
   NB2_LAUNCH_CHECK();
   return NB2_OK;

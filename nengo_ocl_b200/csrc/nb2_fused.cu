@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, FUSED_MIN_BLOCKS)
 nb2_ensemble_step_kernel(int n_ens, const int* __restrict__ ens_ids, const int* __restrict__ ens_table,
                          const int* __restrict__ term_table, const int* __restrict__ conn_table,
                          float* data, float dt, float dt_inv) {
+  nb2_pdl_enter();
   constexpr int GROUPS = FUSED_THREADS / TPE;     // ensembles per CTA
   constexpr int CHAINS = FUSED_RCH * ((NEMAX + 127) / 128) * 4;  // partial sums of one pass
   __shared__ __align__(16) float s_spk[GROUPS][NEMAX];
@@ -229,15 +230,13 @@ extern "C" int nb2_ensemble_step(void* stream, int n_large, const int* large_ids
   const float dt_inv = (float)(1.0 / dt);
   if (n_large > 0) {
     NB2_REQUIRE(large_ids != NULL, "large_ids");
-    nb2_ensemble_step_kernel<256, FUSED_MAX_N><<<n_large, FUSED_THREADS, 0, s>>>(
-        n_large, large_ids, ens_table, term_table, conn_table, data, dtf, dt_inv);
+    nb2_launch(nb2_ensemble_step_kernel<256, FUSED_MAX_N>, dim3(n_large), dim3(FUSED_THREADS), 0, s, n_large, large_ids, ens_table, term_table, conn_table, data, dtf, dt_inv);
     NB2_LAUNCH_CHECK();
   }
   if (n_small > 0) {
     NB2_REQUIRE(small_ids != NULL, "small_ids");
     const int blocks = (n_small + 7) / 8;
-    nb2_ensemble_step_kernel<32, FUSED_SMALL_N><<<blocks, FUSED_THREADS, 0, s>>>(
-        n_small, small_ids, ens_table, term_table, conn_table, data, dtf, dt_inv);
+    nb2_launch(nb2_ensemble_step_kernel<32, FUSED_SMALL_N>, dim3(blocks), dim3(FUSED_THREADS), 0, s, n_small, small_ids, ens_table, term_table, conn_table, data, dtf, dt_inv);
     NB2_LAUNCH_CHECK();
   }
   return NB2_OK;

@@ -158,6 +158,7 @@ __device__ __forceinline__ bool stream_wait_count(const volatile int* ctr, int t
 }
 
 __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(const StreamParams p) {
+  nb2_pdl_enter();
   extern __shared__ __align__(128) unsigned char stream_raw[];
   StreamStage* stages = reinterpret_cast<StreamStage*>(stream_raw);
   StreamSlot* slots = reinterpret_cast<StreamSlot*>(stream_raw + sizeof(StreamStage) * ST_NW);
@@ -445,7 +446,7 @@ extern "C" int nb2_ensemble_stream(void* stream, const int* records, int n_recor
   } else {
     p.x = nb2_exchange_desc();
   }
-  nb2_ensemble_stream_kernel<<<n_ctas, ST_THREADS, kStreamSmem, nb2_stream(stream)>>>(p);
+  nb2_launch(nb2_ensemble_stream_kernel, dim3(n_ctas), dim3(ST_THREADS), kStreamSmem, nb2_stream(stream), p);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

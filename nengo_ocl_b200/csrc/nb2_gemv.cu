@@ -89,6 +89,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 template <int BULK>
 __global__ void __launch_bounds__(GEMV_THREADS)
 nb2_gemv_cta_kernel(const GemvParams p) {
+  nb2_pdl_enter();
   extern __shared__ __align__(128) float smem[];
   float* sA = smem;                       // GEMV_ABUF
   float* sX = sA + GEMV_ABUF;             // GEMV_XBUF
@@ -261,6 +262,7 @@ nb2_gemv_cta_kernel(const GemvParams p) {
 // One warp per unit, at most 32 rows, A read directly from global memory.
 __global__ void __launch_bounds__(GEMV_THREADS)
 nb2_gemv_warp_kernel(const GemvParams p) {
+  nb2_pdl_enter();
   __shared__ float acc[GEMV_WARPS][32];
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
@@ -316,6 +318,7 @@ nb2_gemv_warp_kernel(const GemvParams p) {
 #define ROWS_PER_THREAD 8
 __global__ void __launch_bounds__(GEMV_THREADS)
 nb2_gemv_rows_kernel(const GemvParams p) {
+  nb2_pdl_enter();
   const int tid = threadIdx.x;
   const int4 unit = p.worklist[blockIdx.x];
   const int* __restrict__ g = p.gstructure + (size_t)unit.x * p.gstride;
@@ -410,15 +413,15 @@ extern "C" int nb2_gemv_ragged(void* stream, int kind, const int* gstructure, in
   cudaStream_t s = nb2_stream(stream);
   if (kind == NB2_GEMV_WARP) {
     const int blocks = (n_units + GEMV_WARPS - 1) / GEMV_WARPS;
-    nb2_gemv_warp_kernel<<<blocks, GEMV_THREADS, 0, s>>>(p);
+    nb2_launch(nb2_gemv_warp_kernel, dim3(blocks), dim3(GEMV_THREADS), 0, s, p);
   } else if (kind == NB2_GEMV_CTA_BULK) {
     NB2_CUDA(gemv_optin_smem(1));
-    nb2_gemv_cta_kernel<1><<<n_units, GEMV_THREADS, kGemvSmem, s>>>(p);
+    nb2_launch(nb2_gemv_cta_kernel<1>, dim3(n_units), dim3(GEMV_THREADS), kGemvSmem, s, p);
   } else if (kind == NB2_GEMV_CTA) {
     NB2_CUDA(gemv_optin_smem(0));
-    nb2_gemv_cta_kernel<0><<<n_units, GEMV_THREADS, kGemvSmem, s>>>(p);
+    nb2_launch(nb2_gemv_cta_kernel<0>, dim3(n_units), dim3(GEMV_THREADS), kGemvSmem, s, p);
   } else if (kind == NB2_GEMV_ROWS) {
-    nb2_gemv_rows_kernel<<<n_units, GEMV_THREADS, 0, s>>>(p);
+    nb2_launch(nb2_gemv_rows_kernel, dim3(n_units), dim3(GEMV_THREADS), 0, s, p);
   } else {
     NB2_REQUIRE(false, "unknown gemv kind");
   }

@@ -70,6 +70,7 @@ __device__ __forceinline__ float gb_tile_value(const GemvBlockParams& p, const i
 }
 
 __global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_cta_kernel(const GemvBlockParams p) {
+  nb2_pdl_enter();
   __shared__ float s_tile[GB_ROWS][GB_TMAX + 1];
   __shared__ float s_total[GB_ROWS];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_cta_kernel(const Ge
 }
 
 __global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_warp_kernel(const GemvBlockParams p) {
+  nb2_pdl_enter();
   const int lane = threadIdx.x & 31;
   const int u = blockIdx.x * GB_WARPS + (threadIdx.x >> 5);
   if (u >= p.n_units) return;
@@ -151,14 +153,14 @@ extern "C" int nb2_gemv_block(void* stream, const int* gstructure, int gstride, 
     NB2_REQUIRE(cta_units != NULL, "cta_units");
     p.worklist = reinterpret_cast<const int4*>(cta_units);
     p.n_units = n_cta;
-    nb2_gemv_block_cta_kernel<<<n_cta, GB_THREADS, 0, s>>>(p);
+    nb2_launch(nb2_gemv_block_cta_kernel, dim3(n_cta), dim3(GB_THREADS), 0, s, p);
     NB2_LAUNCH_CHECK();
   }
   if (n_warp > 0) {
     NB2_REQUIRE(warp_units != NULL, "warp_units");
     p.worklist = reinterpret_cast<const int4*>(warp_units);
     p.n_units = n_warp;
-    nb2_gemv_block_warp_kernel<<<(n_warp + GB_WARPS - 1) / GB_WARPS, GB_THREADS, 0, s>>>(p);
+    nb2_launch(nb2_gemv_block_warp_kernel, dim3((n_warp + GB_WARPS - 1) / GB_WARPS), dim3(GB_THREADS), 0, s, p);
     NB2_LAUNCH_CHECK();
   }
   return NB2_OK;

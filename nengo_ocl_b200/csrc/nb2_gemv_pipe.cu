@@ -131,6 +131,7 @@ __device__ __forceinline__ void pipe_issue(const PipeParams& p, PipeStage& st, u
 }
 
 __global__ void __launch_bounds__(PIPE_THREADS, NB2_PIPE_CTAS_PER_SM) nb2_gemv_pipe_kernel(const PipeParams p) {
+  nb2_pdl_enter();
   extern __shared__ __align__(128) unsigned char pipe_raw[];
   PipeStage* stages = reinterpret_cast<PipeStage*>(pipe_raw);
   __shared__ __align__(8) unsigned long long full_bar[PIPE_NW];
@@ -234,7 +235,7 @@ extern "C" int nb2_gemv_pipelined(void* stream, const int* records, int n_record
   p.alpha = alpha; p.beta = beta; p.gamma = gamma;
   p.alphas = alphas; p.betas = betas; p.gammas = gammas;
   p.status = status;
-  nb2_gemv_pipe_kernel<<<n_ctas, PIPE_THREADS, kPipeSmem, nb2_stream(stream)>>>(p);
+  nb2_launch(nb2_gemv_pipe_kernel, dim3(n_ctas), dim3(PIPE_THREADS), kPipeSmem, nb2_stream(stream), p);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

@@ -47,6 +47,7 @@ __device__ __forceinline__ void nb2_lif_core(float J, float& V, float& W, float&
 
 __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict__ sizes,
                                    const nb2_neuron_args a) {
+  nb2_pdl_enter();
   const int gind0 = threadIdx.x;
   const int gind1 = blockIdx.x;
   if (gind1 >= n_blocks || gind0 >= sizes[gind1]) return;
@@ -130,7 +131,7 @@ extern "C" int nb2_neurons(void* stream, int kind, int n_blocks, int block_size,
   if (args->adaptive) NB2_REQUIRE(args->N.buf, "N buffer required");
   nb2_neuron_args a = *args;
   if (a.upsample < 1) a.upsample = 1;
-  nb2_neurons_kernel<<<n_blocks, block_size, 0, nb2_stream(stream)>>>(kind, n_blocks, sizes, a);
+  nb2_launch(nb2_neurons_kernel, dim3(n_blocks), dim3(block_size), 0, nb2_stream(stream), kind, n_blocks, sizes, a);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

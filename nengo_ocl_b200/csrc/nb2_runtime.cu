@@ -6,6 +6,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <stdlib.h>
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
 
@@ -23,6 +24,22 @@ extern "C" {
 const char* nb2_last_error(void) { return g_err; }
 
 int nb2_abi_version(void) { return NB2_ABI_VERSION; }
+
+// -1: not decided yet (first use reads the environment)
+static int g_programmatic_launch = -1;
+
+int nb2_programmatic_launch_enabled() {
+  if (g_programmatic_launch < 0) {
+    const char* env = getenv("NENGO_B200_PDL");
+    g_programmatic_launch = (env != NULL && env[0] == '0') ? 0 : 1;
+  }
+  return g_programmatic_launch;
+}
+
+int nb2_set_programmatic_launch(int enabled) {
+  g_programmatic_launch = enabled ? 1 : 0;
+  return NB2_OK;
+}
 
 int nb2_device_count(int* count) {
   NB2_REQUIRE(count != NULL, "count");

@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(SPMV_THREADS) nb2_spmv_csr_kernel(const int* _
                                                                      const int* __restrict__ indptr,
                                                                      const float* __restrict__ data, int n_rows,
                                                                      const float* __restrict__ x, float* y, int inc) {
+  nb2_pdl_enter();
   constexpr int G = 1 << LOGG;
   const int row = (int)(((size_t)blockIdx.x * SPMV_THREADS + threadIdx.x) >> LOGG);
   const int g = threadIdx.x & (G - 1);
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(SPMV_THREADS) nb2_spmv_ell_cm_kernel(const int
                                                                         const int* __restrict__ rowlens, int n_rows,
                                                                         const float* __restrict__ x, float* y,
                                                                         int inc) {
+  nb2_pdl_enter();
   const int row = blockIdx.x * SPMV_THREADS + threadIdx.x;
   if (row >= n_rows) return;
   const int len = __ldg(rowlens + row);
@@ -66,6 +68,7 @@ __global__ void __launch_bounds__(SPMV_THREADS) nb2_spmv_ell_rm_kernel(const int
                                                                         const int* __restrict__ rowlens, int n_rows,
                                                                         int width, const float* __restrict__ x,
                                                                         float* y, int inc) {
+  nb2_pdl_enter();
   const int row = (int)(((size_t)blockIdx.x * SPMV_THREADS + threadIdx.x) >> 5);
   const int lane = threadIdx.x & 31;
   float sum = 0.0f;
@@ -89,12 +92,12 @@ extern "C" int nb2_spmv_csr(void* stream, const int* indices, const int* indptr,
   const long long threads = (long long)n_rows << lanes_log2;
   const unsigned blocks = (unsigned)((threads + SPMV_THREADS - 1) / SPMV_THREADS);
   switch (lanes_log2) {
-    case 0: nb2_spmv_csr_kernel<0><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
-    case 1: nb2_spmv_csr_kernel<1><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
-    case 2: nb2_spmv_csr_kernel<2><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
-    case 3: nb2_spmv_csr_kernel<3><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
-    case 4: nb2_spmv_csr_kernel<4><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
-    default: nb2_spmv_csr_kernel<5><<<blocks, SPMV_THREADS, 0, s>>>(indices, indptr, data, n_rows, x, y, inc); break;
+    case 0: nb2_launch(nb2_spmv_csr_kernel<0>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
+    case 1: nb2_launch(nb2_spmv_csr_kernel<1>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
+    case 2: nb2_launch(nb2_spmv_csr_kernel<2>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
+    case 3: nb2_launch(nb2_spmv_csr_kernel<3>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
+    case 4: nb2_launch(nb2_spmv_csr_kernel<4>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
+    default: nb2_launch(nb2_spmv_csr_kernel<5>, dim3(blocks), dim3(SPMV_THREADS), 0, s, indices, indptr, data, n_rows, x, y, inc); break;
   }
   NB2_LAUNCH_CHECK();
   return NB2_OK;
@@ -108,10 +111,10 @@ extern "C" int nb2_spmv_ell(void* stream, const int* columns, const float* entri
   cudaStream_t s = nb2_stream(stream);
   if (row_major) {
     const unsigned blocks = (unsigned)(((long long)n_rows * 32 + SPMV_THREADS - 1) / SPMV_THREADS);
-    nb2_spmv_ell_rm_kernel<<<blocks, SPMV_THREADS, 0, s>>>(columns, entries, rowlens, n_rows, width, x, y, inc);
+    nb2_launch(nb2_spmv_ell_rm_kernel, dim3(blocks), dim3(SPMV_THREADS), 0, s, columns, entries, rowlens, n_rows, width, x, y, inc);
   } else {
     const unsigned blocks = (unsigned)((n_rows + SPMV_THREADS - 1) / SPMV_THREADS);
-    nb2_spmv_ell_cm_kernel<<<blocks, SPMV_THREADS, 0, s>>>(columns, entries, rowlens, n_rows, x, y, inc);
+    nb2_launch(nb2_spmv_ell_cm_kernel, dim3(blocks), dim3(SPMV_THREADS), 0, s, columns, entries, rowlens, n_rows, x, y, inc);
   }
   NB2_LAUNCH_CHECK();
   return NB2_OK;

@@ -218,7 +218,28 @@ def find_fusable(sim, operators):
         member["store_spikes"] = any(op not in fused_here for op in out_readers) or any(
             sim.model.sig[p]["in"].base is out for p in sim.model.probes)
         members.append(member)
-        consumed.update(member["ops"])
+    # The fused kernel runs all members concurrently: a member whose encoder input overlaps a
+    # signal that the kernel itself writes (any member's decoded value, filtered value, spikes
+    # or activity trace) could read the old or the new value.  The operator order gives it the
+    # old one (reads come before updates), so such a member stays un-fused.
+    written = {}
+    for mem in members:
+        sigs = [mem["out"]] + list(mem["state"])
+        for c in mem["conns"]:
+            sigs += [c["weighted"]] + ([c["filtered"]] if c["filtered"] is not None else [])
+            sigs += [c["pre_filtered"], c["W"]] if c["pes"] else []
+        for sig in sigs:
+            written.setdefault(sig.base, []).append(_extent(sig))
+    def reads_own_output(mem):
+        for _, X in mem["enc_terms"]:
+            lo, hi = _extent(X)
+            if any(a < hi and b > lo for a, b in written.get(X.base, [])):
+                return True
+        return False
+
+    members = [mem for mem in members if not reads_own_output(mem)]
+    for mem in members:
+        consumed.update(mem["ops"])
     return members, consumed
 
 
@@ -232,6 +253,7 @@ def fold_resets_into_products(operators):
             for s in getattr(op, kind):
                 writers.setdefault(s.base, []).append((op, kind, s))
     dropped = set()
+    changed = []
     for base, ws in writers.items():
         if base.is_view or len(ws) != 2:
             continue
@@ -242,9 +264,17 @@ def fold_resets_into_products(operators):
         # (only a reset to zero: "0 + terms" is exact, any other value would be added after
         # the terms instead of before them and round differently)
         if len(resets) == 1 and len(dots) == 1 and resets[0].value == 0:
+            changed.append((dots[0], dots[0]._float_beta, dots[0].gamma, dots[0]._incs_Y))
             dots[0]._float_beta, dots[0].gamma, dots[0]._incs_Y = 0.0, float(resets[0].value), False
             dropped.add(resets[0])
+    fold_resets_into_products.last_changes = changed
     return dropped
+
+
+def undo_fold(changes):
+    """Put the products changed by ``fold_resets_into_products`` back into increment form."""
+    for dot, beta, gamma, incs in changes:
+        dot._float_beta, dot.gamma, dot._incs_Y = beta, gamma, incs
 
 
 def fuse_ensemble_groups(sim, groups, planner=None):
@@ -266,7 +296,10 @@ def fuse_ensemble_groups(sim, groups, planner=None):
     try:
         new_groups = planner(new_ops)
     except ValueError:
-        return groups  # merging would create a same-step dependency cycle: stay un-fused
+        # merging would create a same-step dependency cycle: stay un-fused, with the products back
+        # in the increment form that the kept groups (and their resets) were planned for
+        undo_fold(getattr(fold_resets_into_products, "last_changes", []))
+        return groups
     sim.operators = new_ops
     sim.fused_groups = [dict(pes=any(c["pes"] for c in mem["conns"]), n=mem["n"],
                              unstored=[mem["J"]] + ([] if mem["store_spikes"] else [mem["out"]])

@@ -126,3 +126,30 @@ void nb2o_pes_step(int n_ens, int n, int d, int dc, double dt, const float* x, c
     for (int i = 0; i < n; ++i) p[i] = pb0 * s[i] - pa0 * p[i];
   }
 }
+
+/* ---- one whole time step of the PES learning model on a batch of ensembles -------
+ * (benchmark configuration 5).  Ensemble e has one decoded connection with a PES rule into
+ * ensemble targets[e]; its error is played back from a table.  Operator order as the reference
+ * schedules it: gather of the inputs (reset + one increment per incoming connection, in
+ * connection order), table playback (plan_presentinput, clra_nonlinearities.py:1710-1728:
+ * row `step % nt`), then the operators of nb2o_pes_step.  err_tables: [ensemble][nt][dc]. */
+void nb2o_pes_model_step(int n_ens, int n, int d, int dc, double dt, int step, int nt, const int* targets,
+                         const float* err_tables, float* x, const float* enc, const float* bias, float* J,
+                         float* V, float* W, float* S, float* dec, float* delta, float* weighted,
+                         float* filtered, float* err, float* pf, float tau, float ref, float amp, float b0,
+                         float a0, float pb0, float pa0, float alpha) {
+  /* plan_reset + plan_copy(inc): inputs = sum of the filtered outputs that target them */
+  memset(x, 0, sizeof(float) * (size_t)n_ens * d);
+  for (int e = 0; e < n_ens; ++e) {
+    float* xt = x + (long)targets[e] * d;
+    const float* f = filtered + (long)e * dc;
+    for (int k = 0; k < d; ++k) xt[k] = xt[k] + f[k];
+  }
+  /* plan_presentinput + reset + copy(inc) into the error signal: 0 + table row */
+  const int ti = step % nt;
+#pragma omp parallel for schedule(static)
+  for (int e = 0; e < n_ens; ++e)
+    for (int k = 0; k < dc; ++k) err[(long)e * dc + k] = 0.0f + err_tables[((long)e * nt + ti) * dc + k];
+  nb2o_pes_step(n_ens, n, d, dc, dt, x, enc, bias, J, V, W, S, dec, delta, weighted, filtered, err, pf, tau, ref,
+                amp, b0, a0, pb0, pa0, alpha);
+}

@@ -190,3 +190,38 @@ def test_gather_sum_over_slices_and_reset_folding():
     reset2, dot2 = m.Reset(y), MultiDotInc.convert_to(m.DotInc(A, x, y))
     assert fusion.fold_resets_into_products([reset2, dot2, m.Copy(x, y, inc=True)]) == set()
     assert dot2._float_beta == 1
+
+
+def test_member_reading_a_fused_output_is_not_fused():
+    """An ensemble whose encoder product reads a signal that the fused kernel writes (here: the
+    filtered output of another ensemble's connection, directly, without an input signal in
+    between) must stay un-fused: inside one kernel it could see the old or the new value."""
+    from types import SimpleNamespace
+
+    from nengo_ocl_b200 import fusion, synth
+    from nengo_ocl_b200.operators import simplify_operators
+
+    nb = synth.NetBuilder(dt=0.001, seed=1)
+    a = nb.ensemble(40, 2, label="a")
+    b = nb.ensemble(40, 2, label="b")
+    conn = nb.connect_decoded(a, None, nb.solve_decoders(a), synapse=0.005, label="a->b")
+    # b's encoders read the filtered value itself (and a constant keeps a's input alive)
+    nb.model.operators = [op for op in nb.model.operators
+                          if not (type(op).__name__ == "DotInc" and op.Y is b.sig_J)]
+    nb.model.add_op(m.DotInc(b.sig_enc, conn["out"], b.sig_J, tag="b.encode"))
+    nb.model.add_op(m.Copy(nb.node_const([0.3, -0.2]), a.sig_in, inc=True))
+    ops = simplify_operators(list(nb.model.operators))
+    ops = MultiDotInc.compress(list(map(MultiDotInc.convert_to, ops)))
+    views = {}
+    for op in ops:
+        if isinstance(op, MultiDotInc):
+            A_views, X_views, *_ = op.get_views()
+            views[op] = (A_views, X_views)
+    sim = SimpleNamespace(_A_views={op: v[0] for op, v in views.items()},
+                          _X_views={op: v[1] for op, v in views.items()},
+                          model=SimpleNamespace(sig={}, probes=[], dt=0.001),
+                          linear_filter_coefficients=lambda op: op.process.discrete_tf(0.001))
+    members, consumed = fusion.find_fusable(sim, ops)
+    fused = {mem["neurons"].J for mem in members}
+    assert a.sig_J in fused and b.sig_J not in fused
+    assert not any(getattr(op, "J", None) is b.sig_J for op in consumed)

@@ -244,3 +244,25 @@ def test_compiled_oracle_matches_numpy_oracle():
         C.lif(0.001, J, Vc, Wc, Sc, 0.02, 0.002, 1.0)
         assert np.array_equal(v, Vc) and np.array_equal(w, Wc) and np.array_equal(s, Sc)
         V, W = v, w
+
+
+def test_compiled_pes_model_step_matches_interpreter():
+    """The compiled whole-step restatement of benchmark configuration 5 (oracle/pes_batch.py:
+    the timed CPU baseline) against the operator-list interpreter, every array, 30 steps."""
+    from nengo_ocl_b200 import synth
+    from oracle.pes_batch import PesBatch
+    from oracle.simulator import OracleSimulator
+
+    mdl = synth.pes_learning_model(seed=3, n_ensembles=12, n_neurons=128, dimensions=4, n_templates=3, n_probes=2,
+                                   sim_time=0.05)
+    ora, batch = OracleSimulator(mdl), PesBatch(mdl)
+    for _ in range(30):
+        ora.step()
+        batch.step()
+    assert np.abs(batch.filtered).max() > 0
+    for i, (c, e) in enumerate(zip(mdl.info["connections"], mdl.info["ensembles"])):
+        for arr, sig in [(batch.filtered[i], c["out"]), (batch.V[i], e.state["voltage"]),
+                         (batch.W[i], e.state["refractory_time"]), (batch.dec[i], c["weights"]),
+                         (batch.delta[i], c["delta"]), (batch.pf[i], c["pre_filtered"]), (batch.x[i], e.sig_in),
+                         (batch.S[i], e.sig_out)]:
+            assert np.array_equal(arr, ora[sig].reshape(arr.shape)), (i, sig.name)
