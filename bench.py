@@ -569,6 +569,25 @@ def main():
                           "note": "speed-up = this steps_per_s over the steps_per_s of the 1-GPU line"}
         sim_s.close()
         del sim_s, mdl_s
+    if not args.no_small:
+        # ---- configuration 4 sharded over the GPUs (strong scaling of a latency-bound model) ----
+        mdl4 = synth.watts_strogatz_shard(seed=2, n_ensembles=4096, rank=rank, world=world)
+        ex4 = None
+        if world > 1:
+            from nengo_ocl_b200.exchange import TorchComm
+
+            ex4 = (mdl4.info["exchange"], TorchComm())
+        sim4 = Simulator(None, model=mdl4, context=ctx, exchange=ex4, n_prealloc_probes=256)
+        sim4._plans.call_n_times(16)
+        sim4._probe()
+        ms4 = float(np.median([device_timed(sim4, 1000) for _ in range(3)]))
+        line["c4_sharded"] = {"workload": "Watts-Strogatz 4096 x 50 LIF, 32768 edges, %d ensembles per GPU, 1000 "
+                                          "steps" % (4096 // world), "n_gpus": world, "us_per_step": ms4,
+                              "steps_per_s": 1e6 / ms4, "launches_per_step": sim4._plans.launches_per_step,
+                              "note": "latency-bound (11.5 MB per step): every step is a full exchange between "
+                                      "the GPUs, so more GPUs need not be faster"}
+        sim4.close()
+        del sim4, mdl4
     if rank == 0 and not args.no_gemv:
         from nengo_ocl_b200.runtime import CommandQueue
 

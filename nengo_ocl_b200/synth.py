@@ -258,6 +258,60 @@ def watts_strogatz_model(seed=2, n_ensembles=4096, n_neurons=50, k=4, p=0.1, syn
     return nb.model
 
 
+def watts_strogatz_shard(seed=2, n_ensembles=4096, rank=0, world=1, n_neurons=50, k=4, p=0.1, synapse=0.01,
+                         dt=0.001, n_templates=16, n_probes=4, max_out=16):
+    """Shard ``rank`` of ``world`` of the Watts-Strogatz network (``n_ensembles`` a multiple of
+    ``world``), in the same way as ``pes_learning_shard``: the whole network is described by
+    seeded draws that do not depend on the rank; a shard instantiates its contiguous block of
+    ensembles, their OUTGOING edges (decoders live with the source ensemble) and the increments
+    of its own ensembles' inputs.  The filtered value of the j-th outgoing edge of ensemble ``s``
+    lives in slot ``s * max_out + j`` of one ``exchange`` signal (identical layout on every rank;
+    unused slots stay zero), so a rank's slots are one contiguous segment and the only cross-rank
+    data per step are the other ranks' segments.  With ``world == 1`` this is the complete model
+    (the unsharded reference of the sharded runs)."""
+    assert n_ensembles % world == 0
+    n_local = n_ensembles // world
+    lo = rank * n_local
+    nb = NetBuilder(dt=dt, seed=seed, label="watts-strogatz shard %d/%d" % (rank, world))
+    trng = np.random.RandomState(seed)
+    scratch = NetBuilder(dt=dt, seed=seed)  # template ensembles are solved outside the shard's model
+    scratch.rng = trng
+    templates = [scratch.ensemble(n_neurons, 1, label="template%d" % t) for t in range(n_templates)]
+    decoders = [scratch.solve_decoders(t) for t in templates]
+    grng = np.random.RandomState(seed + 1)
+    edges = watts_strogatz_edges(n_ensembles, k, p, grng)
+    weights = grng.uniform(-1, 1, size=len(edges))
+    out_index, out_count = [], np.zeros(n_ensembles, dtype=np.int64)
+    for s_, _ in edges:
+        out_index.append(int(out_count[s_]))
+        out_count[s_] += 1
+    assert out_count.max() <= max_out, "an ensemble has more than max_out outgoing edges"
+
+    exchange = m.Signal(np.zeros(n_ensembles * max_out), name="exchange")
+    slot = lambda s_, j: exchange[s_ * max_out + j:s_ * max_out + j + 1]
+    ens = {}
+    for g in range(lo, lo + n_local):
+        ens[g] = nb.ensemble(n_neurons, 1, label="e%d" % g, params_from=templates[g % n_templates])
+    # inputs of local ensembles: every edge (from any rank) that targets them, in edge order
+    for e_i, (s_, d_) in enumerate(edges):
+        if lo <= d_ < lo + n_local:
+            nb.model.add_op(m.Copy(slot(s_, out_index[e_i]), ens[d_].sig_in, inc=True))
+    # outgoing edges of local ensembles
+    for e_i, (s_, d_) in enumerate(edges):
+        if lo <= s_ < lo + n_local:
+            nb.connect_decoded(ens[s_], None, weights[e_i] * decoders[s_ % n_templates], synapse=synapse,
+                               label="e%d->e%d" % (s_, d_), out_signal=slot(s_, out_index[e_i]))
+    if lo == 0:
+        stim = nb.node_fn(lambda t: np.sin(t), 1, label="stim")
+        nb.connect_signal(stim, ens[0].sig_in, synapse=None, label="stim->e0")
+    probe_ids = [lo + int(i) for i in np.linspace(0, n_local - 1, n_probes).astype(int)]
+    probes = [nb.model.add_probe(ens[g].sig_in, label="e%d.in" % g) for g in probe_ids]
+    nb.model.info = dict(probes=probes, probe_ids=probe_ids, ensembles=nb.ensembles, connections=nb.connections,
+                         edges=edges, exchange=exchange, segment=(lo * max_out, n_local * max_out), rank=rank,
+                         world=world)
+    return nb.model
+
+
 # ---- sparse recurrent population (the reference's own Watts-Strogatz benchmark) ------
 def watts_strogatz_adjacency(n, fan_out, rewire, rng, scale=None):
     """Sparse (n, n) float32 weights: column j feeds the rows j +- 1 .. fan_out / 2 of

@@ -15,7 +15,16 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 KW = dict(seed=5, n_ensembles=8, n_neurons=48, dimensions=4, n_templates=2, n_probes=2, sim_time=0.05)
+KW_WS = dict(seed=2, n_ensembles=16, n_neurons=30, k=2, n_templates=3, n_probes=2, max_out=8)
 STEPS = 25
+
+
+def make_shard(kind, rank, world):
+    from nengo_ocl_b200 import synth
+
+    if kind == "pes":
+        return synth.pes_learning_shard(rank=rank, world=world, **KW)
+    return synth.watts_strogatz_shard(rank=rank, world=world, **KW_WS)
 
 
 def _free_port():
@@ -24,7 +33,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, kind):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -37,9 +46,10 @@ def _worker(rank, world, port, out_dir):
     comm = TorchComm()
     assert (comm.rank, comm.world) == (rank, world)
     assert comm.all_gather_object(("r", rank)) == [("r", r) for r in range(world)]
-    mdl = synth.pes_learning_shard(rank=rank, world=world, **KW)
+    mdl = make_shard(kind, rank, world)
     lo, n = mdl.info["segment"]
-    assert (lo // KW["dimensions"], (lo + n) // KW["dimensions"]) == shard_ranges(KW["n_ensembles"], world)[rank]
+    if kind == "pes":
+        assert (lo // KW["dimensions"], (lo + n) // KW["dimensions"]) == shard_ranges(KW["n_ensembles"], world)[rank]
     ora = OracleSimulator(mdl)
     ex = mdl.info["exchange"]
     for _ in range(STEPS):
@@ -54,16 +64,16 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_gloo_ranks_reproduce_the_unsharded_model(tmp_path):
+@pytest.mark.parametrize("kind", ["pes", "watts_strogatz"])
+def test_two_gloo_ranks_reproduce_the_unsharded_model(tmp_path, kind):
     import torch.multiprocessing as mp
 
     sys.path.insert(0, ROOT)
-    from nengo_ocl_b200 import synth
     from oracle.simulator import OracleSimulator
 
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    full = synth.pes_learning_shard(rank=0, world=1, **KW)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), kind), nprocs=world, join=True)
+    full = make_shard(kind, 0, 1)
     ora = OracleSimulator(full)
     ora.run_steps(STEPS)
     ref = ora[full.info["exchange"]]
@@ -71,7 +81,7 @@ def test_two_gloo_ranks_reproduce_the_unsharded_model(tmp_path):
     for r in range(world):
         got = np.load(tmp_path / ("exchange_%d.npy" % r))
         assert np.array_equal(got, ref)
-    # probe 0 of rank 0 is the slot of connection 0, which the full model probes first too
+    # probe 0 of rank 0 is the first probe of the full model too (connection / ensemble 0)
     assert np.array_equal(np.load(tmp_path / "probe_0.npy"), np.array(ora.probe_data[full.probes[0]]))
 
 
