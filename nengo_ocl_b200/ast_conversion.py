@@ -10,7 +10,12 @@ Supported: arithmetic, comparisons, boolean and/or/not, conditional
 expressions, unary minus, constants from closures / globals / default
 arguments, indexing of the vector argument with constant indices, whole-vector
 arithmetic with broadcasting, tuple / list / ``np.array([...])`` results, and
-the math functions in ``FUNCS`` from ``math`` / ``numpy``.  Anything else raises
+every entry of the reference's three function tables (``direct_funcs``,
+``indirect_funcs``, ``vector_funcs`` / ``vector_attr``, ast_conversion.py:62-262):
+the elementary functions in ``FUNCS``, the composite ones in ``COMPOSITES``
+(degrees, hypot, logaddexp, ...) and the reductions over a vector in
+``REDUCTIONS`` (sum, prod, mean, max, min, all, any, len; also as methods,
+``x.sum()``), expanded like the reference expands them.  Anything else raises
 ``NotImplementedError`` (the simulator then falls back to running the function
 on the host, depending on ``if_python_code``).
 """
@@ -50,6 +55,50 @@ FUNCS = {
     "arctan2": ("ATAN2", 2), "atan2": ("ATAN2", 2), "power": ("POW", 2), "pow": ("POW", 2),
     "minimum": ("MIN", 2), "maximum": ("MAX", 2), "min": ("MIN", 2), "max": ("MAX", 2), "fmod": ("MOD", 2),
     "where": ("SELECT", 3),
+    "arccosh": ("ACOSH", 1), "acosh": ("ACOSH", 1), "arcsinh": ("ASINH", 1), "asinh": ("ASINH", 1),
+    "arctanh": ("ATANH", 1), "atanh": ("ATANH", 1), "exp2": ("EXP2", 1), "isinf": ("ISINF", 1),
+    "isnan": ("ISNAN", 1), "isfinite": ("ISFINITE", 1), "erf": ("ERF", 1), "erfc": ("ERFC", 1),
+    "lgamma": ("LGAMMA", 1), "fmax": ("MAX", 2), "fmin": ("MIN", 2), "mod": ("FMOD", 2),
+    "add": ("ADD", 2), "subtract": ("SUB", 2), "multiply": ("MUL", 2), "divide": ("DIV", 2),
+    "true_divide": ("DIV", 2), "equal": ("EQ", 2), "not_equal": ("NE", 2), "greater": ("GT", 2),
+    "greater_equal": ("GE", 2), "less": ("LT", 2), "less_equal": ("LE", 2), "remainder": ("MOD", 2),
+}
+FUNCS["fmod"] = ("FMOD", 2)  # C fmod: the result has the sign of the dividend (math.fmod, np.fmod)
+
+# functions the reference expands into expressions (indirect_funcs, ast_conversion.py:131-195):
+# name -> (arity, builder(translator, *argument values))
+COMPOSITES = {
+    "degrees": (1, lambda t, x: t._apply("MUL", x, t._const(180.0 / math.pi))),
+    "rad2deg": (1, lambda t, x: t._apply("MUL", x, t._const(180.0 / math.pi))),
+    "radians": (1, lambda t, x: t._apply("MUL", x, t._const(math.pi / 180.0))),
+    "deg2rad": (1, lambda t, x: t._apply("MUL", x, t._const(math.pi / 180.0))),
+    "hypot": (2, lambda t, x, y: t._apply("SQRT", t._apply("ADD", t._apply("MUL", x, x), t._apply("MUL", y, y)))),
+    "ldexp": (2, lambda t, x, y: t._apply("MUL", x, t._apply("POW", t._const(2.0), y))),
+    "reciprocal": (1, lambda t, x: t._apply("DIV", t._const(1.0), x)),
+    "signbit": (1, lambda t, x: t._apply("LT", x, t._const(0.0))),
+    "floor_divide": (2, lambda t, x, y: t._apply("FLOOR", t._apply("DIV", x, y))),
+    "logaddexp": (2, lambda t, x, y: t._apply("LOG", t._apply("ADD", t._apply("EXP", x), t._apply("EXP", y)))),
+    "logaddexp2": (2, lambda t, x, y: t._apply("LOG2", t._apply("ADD", t._apply("EXP2", x), t._apply("EXP2", y)))),
+    "gamma": (1, lambda t, x: t._apply("EXP", t._apply("LGAMMA", x))),
+}
+
+
+def _fold(op):
+    """x0 op (x1 op (x2 op ...)): the right-nested expansion of the reference (_recurse_binexp)."""
+    def build(t, elems):
+        out = [elems[-1]]
+        for e in reversed(elems[:-1]):
+            out = t._apply(op, [e], out)
+        return out
+    return build
+
+
+# reductions over the elements of one vector argument (vector_funcs / vector_attr, :198-262)
+REDUCTIONS = {
+    "sum": _fold("ADD"), "prod": _fold("MUL"), "max": _fold("MAX"), "min": _fold("MIN"), "amax": _fold("MAX"),
+    "amin": _fold("MIN"), "all": _fold("AND"), "any": _fold("OR"),
+    "len": lambda t, elems: t._const(len(elems)),
+    "mean": lambda t, elems: t._apply("DIV", _fold("ADD")(t, elems), t._const(len(elems))),
 }
 
 
@@ -97,13 +146,18 @@ class _Translator(ast.NodeVisitor):
             self.tree = None
             self.namespace = {}
             return
-        src = textwrap.dedent(inspect.getsource(fn)).strip()
-        try:
-            tree = ast.parse(src)
-        except SyntaxError:
-            tree = self._parse_embedded_lambda(src)
-        self.tree = tree
-        self.func_node = self._find_function(tree, fn)
+        node = self._lambda_from_file(fn) if getattr(fn, "__name__", "") == "<lambda>" else None
+        if node is not None:
+            tree = ast.Module(body=[ast.Expr(node)], type_ignores=[])
+            self.tree, self.func_node = tree, node
+        else:
+            src = textwrap.dedent(inspect.getsource(fn)).strip()
+            try:
+                tree = ast.parse(src)
+            except SyntaxError:
+                tree = self._parse_embedded_lambda(src)
+            self.tree = tree
+            self.func_node = self._find_function(tree, fn)
         args = self.func_node.args
         self.arg_names = [a.arg for a in args.args]
         if inspect.ismethod(fn):
@@ -116,6 +170,31 @@ class _Translator(ast.NodeVisitor):
             self.namespace[name] = value
         self.arg_names = self.arg_names[: len(in_dims)]
         self.locals = {}
+
+    @staticmethod
+    def _lambda_from_file(fn):
+        """The ``ast.Lambda`` of ``fn`` located in its source file by line number; several lambdas
+        on one line (a table of functions) are told apart by their compiled code."""
+        try:
+            path = inspect.getsourcefile(fn)
+            with open(path) as f:
+                tree = ast.parse(f.read())
+        except (TypeError, OSError, SyntaxError):
+            return None
+        line = fn.__code__.co_firstlineno
+        found = [n for n in ast.walk(tree) if isinstance(n, ast.Lambda) and n.lineno == line]
+        if len(found) == 1:
+            return found[0]
+        # the code object records the columns of its instructions: the lambda whose body spans them
+        cols = [(c0, c1) for l0, _, c0, c1 in fn.__code__.co_positions()
+                if l0 == line and c0 is not None and c1 is not None and c1 > c0]
+        if cols:
+            lo, hi = min(c for c, _ in cols), max(c for _, c in cols)
+            inside = [n for n in found if n.body.lineno == line and n.body.col_offset <= lo
+                      and (n.body.end_lineno > line or hi <= n.body.end_col_offset)]
+            if len(inside) == 1:
+                return inside[0]
+        return None
 
     @staticmethod
     def _parse_embedded_lambda(src):
@@ -207,6 +286,17 @@ class _Translator(ast.NodeVisitor):
         return [[(op, j)] for j in range(self.in_dims[index])]
 
     def _call(self, name, args):
+        # a reduction takes one vector (max / min with several scalars are the binary functions)
+        if name in REDUCTIONS and len(args) == 1 and (len(args[0]) > 1 or name not in FUNCS):
+            out = REDUCTIONS[name](self, args[0])
+            if name in ("all", "any"):  # truth value of the (possibly single) element
+                out = self._apply("NE", out, self._const(0.0))
+            return out
+        if name in COMPOSITES:
+            arity, build = COMPOSITES[name]
+            if len(args) != arity:
+                raise NotImplementedError("%s with %d arguments" % (name, len(args)))
+            return build(self, *args)
         if name not in FUNCS:
             raise NotImplementedError("function %r" % name)
         op, arity = FUNCS[name]
@@ -306,6 +396,11 @@ class _Translator(ast.NodeVisitor):
         fname = node.func.attr if isinstance(node.func, ast.Attribute) else getattr(node.func, "id", None)
         if fname in ("array", "asarray", "float", "float32", "float64"):
             return self.visit(node.args[0])
+        # a reduction as a method of a vector value: x.sum(), (x * x).mean()
+        if (isinstance(node.func, ast.Attribute) and fname in REDUCTIONS and not node.args
+                and not (isinstance(node.func.value, ast.Name) and node.func.value.id in self.namespace
+                         and node.func.value.id not in self.arg_names and node.func.value.id not in self.locals)):
+            return self._call(fname, [self.visit(node.func.value)])
         args = [self.visit(a) for a in node.args]
         return self._call(fname, args)
 
@@ -313,7 +408,8 @@ class _Translator(ast.NodeVisitor):
 _PUSHES = {OPS["CONST"], OPS["IN0"], OPS["IN1"]}
 _UNARY = {OPS[name] for name in ("NEG", "NOT", "SIN", "COS", "TAN", "ASIN", "ACOS", "ATAN", "SINH", "COSH", "TANH",
                                  "EXP", "EXPM1", "LOG", "LOG2", "LOG10", "LOG1P", "SQRT", "ABS", "FLOOR", "CEIL",
-                                 "ROUND", "SIGN")}
+                                 "ROUND", "SIGN", "ACOSH", "ASINH", "ATANH", "EXP2", "ISINF", "ISNAN", "ISFINITE",
+                                 "ERF", "ERFC", "LGAMMA")}
 
 
 def stack_depth(program):

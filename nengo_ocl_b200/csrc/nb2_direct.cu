@@ -80,6 +80,17 @@ __global__ void nb2_direct_kernel(int n_items, const int2* __restrict__ prog, in
       case NB2_OP_CEIL: UN(ceil(a));
       case NB2_OP_ROUND: UN(rint(a));
       case NB2_OP_SIGN: UN(a > 0.0 ? 1.0 : (a < 0.0 ? -1.0 : 0.0));
+      case NB2_OP_ACOSH: UN(acosh(a));
+      case NB2_OP_ASINH: UN(asinh(a));
+      case NB2_OP_ATANH: UN(atanh(a));
+      case NB2_OP_EXP2: UN(exp2(a));
+      case NB2_OP_ISINF: UN(isinf(a) ? 1.0 : 0.0);
+      case NB2_OP_ISNAN: UN(isnan(a) ? 1.0 : 0.0);
+      case NB2_OP_ISFINITE: UN(isfinite(a) ? 1.0 : 0.0);
+      case NB2_OP_ERF: UN(erf(a));
+      case NB2_OP_ERFC: UN(erfc(a));
+      case NB2_OP_LGAMMA: UN(lgamma(a));
+      case NB2_OP_FMOD: BIN(fmod(a, b));
       case NB2_OP_SELECT: {
         double b = POP(); double a = POP(); double c = POP();
         PUSH(c != 0.0 ? a : b);

@@ -30,25 +30,21 @@ __global__ void nb2_exchange_wait_kernel(int* ctl, const int* flags, const float
   nb2_pdl_enter();
   const int epoch = ctl[X_EPOCH];
   if (epoch == 0) return;  // nothing has been exchanged yet: replicas hold the initial values
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    int ok = 1;
+  // thread p watches peer p's flag (the flags live in this GPU's memory; the peers store into
+  // them), so the block waits for the slowest peer, not for the peers one after the other
+  int ok = 1;
+  if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
     const unsigned long long t0 = nb2_globaltimer();
-    for (int p = 0; p < world && ok; ++p) {
-      if (p == rank) continue;
-      while (ld_acquire_sys(flags + p) < epoch) {
-        if ((long long)(nb2_globaltimer() - t0) > timeout_ns) {
-          ok = 0;
-          atomicExch(ctl + X_STATUS, NB2_ERR_TIMEOUT);
-          break;
-        }
-        __nanosleep(200);
+    while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
+      if ((long long)(nb2_globaltimer() - t0) > timeout_ns) {
+        ok = 0;
+        atomicExch(ctl + X_STATUS, NB2_ERR_TIMEOUT);
+        break;
       }
+      __nanosleep(100);
     }
-    s_ok = ok;
   }
-  __syncthreads();
-  if (!s_ok) return;
+  if (!__syncthreads_and(ok)) return;
   const float* src = staging + (size_t)(epoch & 1) * world * seg;
   const size_t total = (size_t)world * seg;
   const size_t lo = (size_t)rank * seg, hi = lo + seg;
@@ -86,7 +82,7 @@ __global__ void nb2_exchange_push_kernel(int* ctl, float* const* peer_staging, i
 extern "C" int nb2_exchange_wait(void* stream, int* ctl, const int* flags, const float* staging,
                                  float* replica, int rank, int world, int seg, double timeout_s) {
   NB2_REQUIRE(ctl && flags && staging && replica, "null pointer");
-  NB2_REQUIRE(world >= 1 && rank >= 0 && rank < world && seg > 0, "rank/world/seg");
+  NB2_REQUIRE(world >= 1 && world <= EXCH_THREADS && rank >= 0 && rank < world && seg > 0, "rank/world/seg");
   if (world == 1) return NB2_OK;
   const long long total = (long long)world * seg;
   int blocks = (int)((total + EXCH_THREADS * 8 - 1) / (EXCH_THREADS * 8));

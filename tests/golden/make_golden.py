@@ -100,6 +100,35 @@ def main(reference_root, write_fixtures=True):
     toref = lambda r: RA.from_buffer(r.buf.copy(), r.starts, r.shape0s, r.shape1s, r.stride0s, r.stride1s)
     gemv_case("config2_k64", toref(hA), toref(hX), toref(hY), toref(hA_js), toref(hX_js), 0.5, 0.1, 0.0)
 
+    # ---------------- the block GEMV executed from the reference's kernel text ----------------
+    # plan_block_gemv (what the reference simulator plans for every MultiDotInc): the tile
+    # kernel has barriers that only separate "fill local memory" from "use it" and a two-level
+    # tree: with work-items run one after the other, every sweep over a work-group completes one more
+    # stage (structure, x, partial sums, tree, output), so five sweeps reproduce it; the reduce
+    # kernel has no barrier.
+    def block_case(tag, A, X, Y, A_js, X_js, alpha, beta, gamma):
+        clA, clX, clY = CLRA(queue, A), CLRA(queue, X), CLRA(queue, Y)
+        kernels["gemv_block/%s/A" % tag] = A.buf.copy()
+        kernels["gemv_block/%s/X" % tag] = X.buf.copy()
+        kernels["gemv_block/%s/Y0" % tag] = Y.buf.copy()
+        prog, _, progs = capture(lambda: gemv.plan_block_gemv(queue, alpha, clA, A_js, clX, X_js, beta, clY,
+                                                              gamma=gamma))
+        texts = [t for t in progs if "__kernel void fn" in t] + [t for t in progs if "__kernel void reduce" in t]
+        refkernels.run_plan_grouped(prog.plans[0], texts[0], "fn", passes=5, group_axis=2)
+        refkernels.run_plan(prog.plans[1], texts[1], "reduce")
+        kernels["gemv_block/%s/Y1" % tag] = clY.cl_buf._arr.copy()
+        kernels["gemv_block/%s/scales" % tag] = np.array([alpha, beta, gamma])
+
+    brng = np.random.RandomState(99)
+    shapes_b = [(40, 300), (40, 129), (40, 7)]  # three terms: 3, 2 and 1 column tiles
+    block_case("three_terms", ra([brng.normal(size=s_) for s_ in shapes_b]),
+               ra([brng.normal(size=(s_[1], 1)) for s_ in shapes_b]), ra([brng.normal(size=(40, 1))]),
+               ra([[0, 1, 2]], np.int32), ra([[0, 1, 2]], np.int32), 1.0, 1.0, 0.0)
+    block_case("scaled", ra([brng.normal(size=(70, 260)), brng.normal(size=(5, 16))]),
+               ra([brng.normal(size=(260, 1)), brng.normal(size=(16, 1))]),
+               ra([brng.normal(size=(70, 1)), brng.normal(size=(5, 1))]),
+               ra([[0], [1]], np.int32), ra([[0], [1]], np.int32), 0.5, 0.6, 0.7)
+
     # ---------------- elementwise / neuron block tables ----------------
     rng = np.random.RandomState(7)
     sizes = [100, 1000, 37, 2049]
@@ -130,6 +159,45 @@ def main(reference_root, write_fixtures=True):
         kernels[key + "/W1"] = clW.cl_buf._arr.copy()
         kernels[key + "/S1"] = clS.cl_buf._arr.copy()
     kernels["lif/sizes"] = np.array(sizes)
+
+    # adaptive LIF (cl_alif): three consecutive steps with the adaptation state carried
+    Na = ra([rng.uniform(0, 0.5, size=n) for n in sizes])
+    clNa = CLRA(queue, Na)
+    for r, c in ((V, clV), (W, clW), (S, clS)):
+        c.cl_buf._arr[...] = r.buf
+    plan, cap, progs = capture(lambda: nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0, N=clNa,
+                                                   tau_n=0.1, inc_n=0.05))
+    kernels["alif/N0"] = Na.buf.copy()
+    for step in range(3):
+        refkernels.run_plan(plan, progs[-1], "cl_alif")
+        for nm, c in (("V", clV), ("W", clW), ("S", clS), ("N", clNa)):
+            kernels["alif/%s%d" % (nm, step + 1)] = c.cl_buf._arr.copy()
+
+    # timeupdate: 5 consecutive calls
+    st = CLRA(queue, ra([np.zeros((1, 1))]))
+    tm = CLRA(queue, ra([np.zeros((1, 1))]))
+    plan, cap, progs = capture(lambda: nl.plan_timeupdate(queue, st, tm, 0.001))
+    seq = []
+    for _ in range(5):
+        refkernels.run_plan(plan, progs[-1], "timeupdate")
+        seq.append([st.cl_buf._arr[0], tm.cl_buf._arr[0]])
+    kernels["timeupdate/step_time"] = np.array(seq, dtype=np.float32)
+
+    # presentinput: table playback by step index and by presentation time
+    prng = np.random.RandomState(21)
+    tabs = ra([prng.normal(size=(7, 3)), prng.normal(size=(4, 1))])
+    Yp = ra([np.zeros((3, 1)), np.zeros((1, 1))])
+    tp = ra([np.zeros((1, 1)), np.zeros((1, 1))])
+    kernels["presentinput/tables"] = tabs.buf.copy()
+    for mode, pres in (("index", None), ("time", refstubs.to_device(queue, np.array([0.003, 0.002], np.float32)))):
+        clYp, cltp, cltabs = CLRA(queue, Yp), CLRA(queue, tp), CLRA(queue, tabs)
+        plan, cap, progs = capture(lambda: nl.plan_presentinput(queue, clYp, cltp, cltabs, 0.001, pres_t=pres))
+        outs = []
+        for step in range(1, 13):
+            cltp.cl_buf._arr[...] = step
+            refkernels.run_plan(plan, progs[-1], "presentinput")
+            outs.append(clYp.cl_buf._arr.copy())
+        kernels["presentinput/%s" % mode] = np.array(outs)
 
     # several consecutive LIF steps on one population (state carried)
     n = 4096

@@ -248,3 +248,17 @@ def test_block_gemv_is_bit_exact(queue):
         prog = check_block_exact(queue, 0.5, A, A_js, X, X_js, 0.1, Y)
         cta, warp = prog.plans[0].worklist
         assert len(cta) and len(warp)  # both kernels ran
+
+
+@pytest.mark.parametrize("tag", ["three_terms", "scaled"])
+def test_block_gemv_matches_reference_kernel_text(queue, golden_kernels, tag):
+    """plan_block_gemv on the GPU against outputs of the reference's own block kernels (tile +
+    reduce, rendered and executed on the CPU; tests/golden/make_golden.py): bit for bit."""
+    import sys, os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_oracle_golden import _block_case
+
+    A, X, Y, J, alpha, beta, gamma = _block_case(golden_kernels, tag)
+    clY, _ = run(queue, cura_gemv.plan_block_gemv, alpha, A, J, X, J, beta, Y, gamma=gamma)
+    assert np.array_equal(clY.cl_buf.get()[:Y.buf.size], golden_kernels["gemv_block/%s/Y1" % tag])

@@ -290,3 +290,54 @@ def test_learning_rule_deltas(queue, rng):
             else:
                 want = K.voja(pre[k], post[k], mat[k], learn[k][0, 0], scale[k], alpha[k])
             assert np.array_equal(delta[k], want), (rule, k)
+
+
+def test_adaptive_lif_matches_reference_kernel(queue, golden_kernels):
+    """cl_alif (clra_nonlinearities.py:1028-1146 with N): three consecutive steps with the
+    adaptation state carried, against outputs of the reference's own rendered kernel and, bit for
+    bit, against the oracle."""
+    g = golden_kernels
+    sizes = [int(s) for s in g["lif/sizes"]]
+    split = lambda buf: RA(np.split(buf, np.cumsum(sizes)[:-1]))
+    key = "lif_up1/"
+    clJ, clV, clW = (CLRA(queue, split(g[key + k])) for k in ("J", "V0", "W0"))
+    clS = CLRA(queue, RA([np.zeros(n) for n in sizes]))
+    clT = CLRA(queue, split(g[key + "tau"]))
+    clN = CLRA(queue, split(g["alif/N0"]))
+    plan = nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0, N=clN, tau_n=0.1, inc_n=0.05)
+    n = sum(sizes)
+    V, W, N = g[key + "V0"], g[key + "W0"], g["alif/N0"]
+    for step in range(1, 4):
+        plan()
+        V, W, S, N = K.lif(1e-3, g[key + "J"], V, W, g[key + "tau"], np.full(n, 2e-3, np.float32),
+                           np.full(n, 1.0, np.float32), N=N, tau_n=np.full(n, 0.1, np.float32),
+                           inc_n=np.full(n, 0.05, np.float32))
+        for got, ref in ((clV, V), (clW, W), (clS, S), (clN, N)):
+            assert np.array_equal(got.cl_buf.get(), ref)
+        assert np.allclose(clV.cl_buf.get(), g["alif/V%d" % step], rtol=1e-4, atol=1e-5)
+        assert np.allclose(clN.cl_buf.get(), g["alif/N%d" % step], rtol=1e-4, atol=1e-6)
+        assert (clS.cl_buf.get() > 0).sum() == (g["alif/S%d" % step] > 0).sum()
+
+
+def test_timeupdate_and_presentinput_match_reference_kernels(queue, golden_kernels):
+    g = golden_kernels
+    step = CLRA(queue, RA([np.zeros((1, 1))]))
+    time = CLRA(queue, RA([np.zeros((1, 1))]))
+    tplan = nl.plan_timeupdate(queue, step, time, 0.001)
+    for want in g["timeupdate/step_time"]:
+        tplan()
+        assert step[0][0, 0] == want[0] and time[0][0, 0] == want[1]
+    tabs = RA([np.zeros((7, 3)), np.zeros((4, 1))])
+    tabs.buf[...] = g["presentinput/tables"]
+    for mode, pres in (("index", None), ("time", np.array([0.003, 0.002], np.float32))):
+        S = CLRA(queue, tabs)
+        Y = CLRA(queue, RA([np.zeros((3, 1)), np.zeros((1, 1))]))
+        t = CLRA(queue, RA([np.zeros((1, 1)), np.zeros((1, 1))]))
+        from nengo_ocl_b200.runtime import to_device
+
+        plan = nl.plan_presentinput(queue, Y, t, S, 0.001, pres_t=None if pres is None else to_device(queue, pres))
+        for i, s_ in enumerate(range(1, 13)):
+            t[0] = np.full((1, 1), float(s_))
+            t[1] = np.full((1, 1), float(s_))
+            plan()
+            assert np.array_equal(Y.cl_buf.get(), g["presentinput/%s" % mode][i]), (mode, s_)

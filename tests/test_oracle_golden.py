@@ -266,3 +266,59 @@ def test_compiled_pes_model_step_matches_interpreter():
                          (batch.delta[i], c["delta"]), (batch.pf[i], c["pre_filtered"]), (batch.x[i], e.sig_in),
                          (batch.S[i], e.sig_out)]:
             assert np.array_equal(arr, ora[sig].reshape(arr.shape)), (i, sig.name)
+
+
+def _block_case(g, tag):
+    shapes = {"three_terms": ([(40, 300), (40, 129), (40, 7)], [(40, 1)], [[0, 1, 2]]),
+              "scaled": ([(70, 260), (5, 16)], [(70, 1), (5, 1)], [[0], [1]])}[tag]
+    A_shapes, Y_shapes, js = shapes
+    A = RaggedArray([np.zeros(s) for s in A_shapes], dtype=np.float32)
+    X = RaggedArray([np.zeros((s[1], 1)) for s in A_shapes], dtype=np.float32)
+    Y = RaggedArray([np.zeros(s) for s in Y_shapes], dtype=np.float32)
+    A.buf[...], X.buf[...], Y.buf[...] = g["gemv_block/%s/A" % tag], g["gemv_block/%s/X" % tag], g["gemv_block/%s/Y0" % tag]
+    J = RaggedArray(js, dtype=np.int32)
+    alpha, beta, gamma = (float(v) for v in g["gemv_block/%s/scales" % tag])
+    return A, X, Y, J, alpha, beta, gamma
+
+
+@pytest.mark.parametrize("tag", ["three_terms", "scaled"])
+def test_block_gemv_oracle_matches_reference_kernel_text(golden_kernels, tag):
+    """oracle.kernels.gemv_block against the reference's own block kernels (tile kernel +
+    reduce kernel, rendered and executed on the CPU): several column tiles per term, several
+    terms, alpha/beta/gamma other than the simulator's; bit for bit."""
+    A, X, Y, J, alpha, beta, gamma = _block_case(golden_kernels, tag)
+    K.gemv_block(alpha, A, J, X, J, beta, Y, gamma=gamma)
+    assert np.array_equal(Y.buf, golden_kernels["gemv_block/%s/Y1" % tag])
+
+
+def test_adaptive_lif_oracle_matches_reference_kernel(golden_kernels):
+    g = golden_kernels
+    V, W, N = g["lif_up1/V0"], g["lif_up1/W0"], g["alif/N0"]
+    J, tau = g["lif_up1/J"], g["lif_up1/tau"]
+    n = J.size
+    for step in range(1, 4):
+        V, W, S, N = K.lif(1e-3, J, V, W, tau, np.full(n, 2e-3, np.float32), np.full(n, 1.0, np.float32), N=N,
+                           tau_n=np.full(n, 0.1, np.float32), inc_n=np.full(n, 0.05, np.float32))
+        # the reference kernel ran with glibc's float expm1 / log1p, the oracle rounds correctly
+        assert np.allclose(V, g["alif/V%d" % step], rtol=1e-5, atol=1e-6)
+        assert np.allclose(W, g["alif/W%d" % step], rtol=1e-5, atol=1e-6)
+        assert np.array_equal(S > 0, g["alif/S%d" % step] > 0)
+        assert np.allclose(N, g["alif/N%d" % step], rtol=1e-6, atol=1e-7)
+        V, W, N = g["alif/V%d" % step], g["alif/W%d" % step], g["alif/N%d" % step]
+
+
+def test_timeupdate_and_presentinput_oracle_match_reference_kernels(golden_kernels):
+    g = golden_kernels
+    RA = lambda arrays, dtype=np.float32: RaggedArray(arrays, dtype=dtype)
+    step, time = RA([np.zeros((1, 1))]), RA([np.zeros((1, 1))])
+    for want in g["timeupdate/step_time"]:
+        K.timeupdate(step, time, 0.001)
+        assert step[0][0, 0] == want[0] and time[0][0, 0] == want[1]
+    tabs = RA([np.zeros((7, 3)), np.zeros((4, 1))])
+    tabs.buf[...] = g["presentinput/tables"]
+    for mode, pres in (("index", None), ("time", np.array([0.003, 0.002], np.float32))):
+        Y = RA([np.zeros((3, 1)), np.zeros((1, 1))])
+        for i, s_ in enumerate(range(1, 13)):
+            t = RA([np.full((1, 1), s_), np.full((1, 1), s_)])
+            K.presentinput(Y, t, tabs, 0.001, pres_t=pres)
+            assert np.array_equal(Y.buf, g["presentinput/%s" % mode][i]), (mode, s_)
