@@ -57,6 +57,14 @@ REPEATS = 5  # the timed region runs this many times; the median is reported
 WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
 
 
+_T0 = time.perf_counter()
+
+
+def note(msg):
+    """Progress on stderr (the JSON line on stdout stays alone)."""
+    print("[bench %6.1f s] %s" % (time.perf_counter() - _T0, msg), file=sys.stderr, flush=True)
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -221,7 +229,10 @@ def cpu_compiled_rate(n_ensembles, steps, warmup=3):
 def run_reference(args, rank):
     if rank != 0:
         return
-    base = cpu_compiled_rate(512, max(args.steps, 1), warmup=min(max(args.warmup, 1), 3))
+    # every "step" of this arm is a bounded sample: 100 simulated steps of 512 of the 4096 ensembles
+    # (about 0.3 s of CPU work on 16 cores), so that any --steps finishes within minutes
+    sample_steps = 100 * max(min(args.steps, 200), 1)
+    base = cpu_compiled_rate(512, sample_steps, warmup=min(max(args.warmup, 1), 3) * 10)
     line = {
         "impl": "reference", "metric": "neuron_updates_per_s", "value": base["value"], "unit": "neuron-updates/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -361,7 +372,6 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        args.steps = min(args.steps, 60)  # bounded sample: about 0.2 s of CPU time per step
         run_reference(args, rank)
         return
 
@@ -452,6 +462,7 @@ def main():
 
     # weak scaling: every GPU simulates `--ensembles` ensembles of one network of world * ensembles
     mdl, sim, build_s = build(args.ensembles * world)
+    note("model + simulator built")
     n_neurons = mdl.n_neurons
     plans = sim._plans
     fused = [p for p in plans if p.name == "fused_ensemble_step"]
@@ -470,6 +481,7 @@ def main():
     clocks = ClockSampler(local_rank if rank == 0 else None)
     clocks.__enter__()
     region_ms = [device_timed(sim, K) for _ in range(REPEATS)]
+    note("device-timed region done")
     total_ms = float(np.median(region_ms))
     ms_per_step = total_ms / K
     value = world * n_neurons * K / (total_ms / 1e3)
@@ -515,6 +527,7 @@ def main():
         _capi.call("nb2_device_sync")
         e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
     e2e_s = float(np.median(e2e_runs))
+    note("end-to-end region done")
     # The timed regions of a short run are over before the sampler has three readings: keep the same
     # steps running (untimed, every rank alike because the ranks step together) until it has.
     for _ in range(40):
@@ -569,6 +582,7 @@ def main():
                           "note": "speed-up = this steps_per_s over the steps_per_s of the 1-GPU line"}
         sim_s.close()
         del sim_s, mdl_s
+    note("main workload closed")
     if not args.no_small:
         # ---- configuration 4 sharded over the GPUs (strong scaling of a latency-bound model) ----
         mdl4 = synth.watts_strogatz_shard(seed=2, n_ensembles=4096, rank=rank, world=world)
@@ -588,6 +602,7 @@ def main():
                                       "the GPUs, so more GPUs need not be faster"}
         sim4.close()
         del sim4, mdl4
+    note("sharded configuration 4 done")
     if rank == 0 and not args.no_gemv:
         from nengo_ocl_b200.runtime import CommandQueue
 
@@ -601,11 +616,14 @@ def main():
         line["spmv"] = spmv_microbench(CommandQueue(ctx), _capi)
         for k in ("csr", "ellpack"):
             line["spmv"][k]["frac"] = line["spmv"][k]["achieved_gbs"] / peak
+    note("microbenchmarks done")
     if rank == 0 and not args.no_small and world == 1:
         line["small_models"] = small_model_rates(ctx, _capi)
+        note("small models done")
     if rank == 0 and not args.no_cpu and world == 1:
-        line["cpu_baseline"] = cpu_compiled_rate(512, 150)
+        line["cpu_baseline"] = cpu_compiled_rate(512, 4000)  # about 10 s of CPU work on 16 cores
         line["cpu_baseline"]["numpy_interpreter"] = cpu_interpreter_rate(256, 10)
+        note("CPU baseline done")
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:

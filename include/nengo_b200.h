@@ -201,9 +201,15 @@ int nb2_probes_wide(void* stream, int n_probes, int chunks, float* countdowns, i
                     const float* periods, const int* Xstarts, const int* Xshape0s, const int* Xshape1s,
                     const int* Xstride0s, const int* Xstride1s, const float* X, const int* Ystarts,
                     float* Y, int* arrive);
-/* nb2_probes_wide without any allocation (no reference counterpart): the arrival
- * counters live in a device array of the library (NB2_PROBES_STATIC_MAX probes at
- * most; more are rejected).  Launches that use it must not overlap in time. */
+/* nb2_probes_wide without any allocation (no reference counterpart): for callers
+ * that cannot allocate device memory at this point (inside a stream capture, or
+ * with a fixed memory budget handed out elsewhere), the arrival counters live in
+ * a 16 KB device array of the library (NB2_PROBES_STATIC_MAX probes at most; more
+ * are rejected with NB2_ERR_ARG).  The first call on a device looks the array's
+ * device address up (once per device, under a lock); make that first call before
+ * any stream capture.  Every call shares the one array: the kernel leaves the
+ * counters zero, but two launches that overlap in time on one GPU (two streams,
+ * two host threads) race on them and must not be issued. */
 #define NB2_PROBES_STATIC_MAX 4096
 int nb2_probes_wide_noalloc(void* stream, int n_probes, int chunks, float* countdowns, int* bufpositions,
                             const float* periods, const int* Xstarts, const int* Xshape0s,

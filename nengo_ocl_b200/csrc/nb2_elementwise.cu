@@ -5,6 +5,7 @@
 // host-side plans are interchangeable.  This translation unit is compiled
 // with -fmad=false: every a*b+c below is a separate multiply and add, as in
 // the CPU restatement the results are checked against.
+#include <mutex>
 #include "nb2_common.cuh"
 #include "../../include/nengo_b200.h"
 
@@ -480,14 +481,22 @@ extern "C" int nb2_probes_wide_noalloc(void* stream, int n_probes, int chunks, f
                                        const int* Xstride1s, const float* X, const int* Ystarts, float* Y) {
   if (n_probes == 0) return NB2_OK;
   NB2_REQUIRE(n_probes <= NB2_PROBES_STATIC_MAX, "more probes than the static arrival counters cover");
+  // Set-up, once per device and with that device current: the array's name is only a host-side
+  // stand-in, the kernel needs its device address.  Done by the first call on a device (under a
+  // lock, so that two host threads cannot both be "first"); that call should come before any
+  // stream capture.
   static int* arrive_of_device[64] = {};
+  static std::mutex setup_lock;
   int dev = 0;
   NB2_CUDA(cudaGetDevice(&dev));
   NB2_REQUIRE(dev >= 0 && dev < 64, "device ordinal");
-  if (arrive_of_device[dev] == NULL) {
-    void* sym = NULL;
-    NB2_CUDA(cudaGetSymbolAddress(&sym, g_probe_arrive));
-    arrive_of_device[dev] = static_cast<int*>(sym);
+  {
+    std::lock_guard<std::mutex> guard(setup_lock);
+    if (arrive_of_device[dev] == NULL) {
+      void* sym = NULL;
+      NB2_CUDA(cudaGetSymbolAddress(&sym, g_probe_arrive));
+      arrive_of_device[dev] = static_cast<int*>(sym);
+    }
   }
   return nb2_probes_wide_launch(stream, n_probes, chunks, countdowns, bufpositions, periods, Xstarts, Xshape0s,
                                 Xshape1s, Xstride0s, Xstride1s, X, Ystarts, Y, arrive_of_device[dev]);

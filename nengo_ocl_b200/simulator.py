@@ -52,7 +52,7 @@ from nengo_ocl_b200.plan import BasePlan, Plans, PythonPlan
 from nengo_ocl_b200.planners import greedy_planner
 from nengo_ocl_b200.raggedarray import RaggedArray
 from nengo_ocl_b200.runtime import CommandQueue, DeviceArray, create_some_context
-from nengo_ocl_b200.utils import groupby, indent, split, stable_unique
+from nengo_ocl_b200.utils import groupby, indent, stable_unique
 
 logger = logging.getLogger(__name__)
 
@@ -537,23 +537,21 @@ class Simulator:
 
     # --- planning ---------------------------------------------------------------
     def _plan_probes(self):
-        plans = []
-        if len(self.model.probes) == 0:
-            self._max_steps_between_probes = self.n_prealloc_probes
-            self._cl_probe_plan = None
-        else:
-            n_prealloc = self.n_prealloc_probes
-            probes = self.model.probes
-            periods = [max(1 if p.sample_every is None else p.sample_every / self.dt, 1) for p in probes]
-            X = self.all_data[[self.sidx[self.model.sig[p]["in"]] for p in probes]]
-            Y = self.RaggedArray([np.zeros((n_prealloc, self.model.sig[p]["in"].size)) for p in probes],
-                                 dtype=np.float32)
-            cl_plan = plan_probes(self.queue, periods, X, Y)
-            self._max_steps_between_probes = n_prealloc * int(min(periods))
-            self._cl_probe_plan = cl_plan
-            plans.append(cl_plan)
+        """One plan that samples every probe into a device ring of ``n_prealloc_probes`` rows; the
+        host drains the rings every ``_max_steps_between_probes`` steps (the slowest ring to fill
+        decides; reference simulator.py:705-731)."""
+        probes = self.model.probes
+        self._cl_probe_plan = None
+        self._max_steps_between_probes = self.n_prealloc_probes
+        if not probes:
+            return []
+        targets = [self.model.sig[p]["in"] for p in probes]
+        periods = [max(1 if p.sample_every is None else p.sample_every / self.dt, 1) for p in probes]
+        rings = self.RaggedArray([np.zeros((self.n_prealloc_probes, sig.size)) for sig in targets], dtype=np.float32)
+        self._cl_probe_plan = plan_probes(self.queue, periods, self._items(targets), rings)
+        self._max_steps_between_probes = self.n_prealloc_probes * int(min(periods))
         assert self._max_steps_between_probes >= 1
-        return plans
+        return [self._cl_probe_plan]
 
     def _plan_op_group(self, op_type, ops):
         return getattr(self, "_plan_" + op_type.__name__)(ops)
@@ -603,35 +601,37 @@ class Simulator:
         return rval.plans
 
     def _plan_TimeUpdate(self, ops):
-        (op,) = ops
-        step = self.all_data[[self.sidx[op.step]]]
-        time = self.all_data[[self.sidx[op.time]]]
+        assert len(ops) == 1, "a model has one clock"
+        step, time = self._gather(ops, "step", "time")
         return [plan_timeupdate(self.queue, step, time, self.model.dt)]
 
     def _plan_Reset(self, ops):
-        targets = self.all_data[[self.sidx[op.dst] for op in ops]]
-        values = self.Array([op.value for op in ops])
-        return [plan_reset(self.queue, targets, values)]
+        return [plan_reset(self.queue, self._gather(ops, "dst"), self.Array([op.value for op in ops]))]
 
     def _plan_Copy(self, ops):
-        copies, ops = split(ops, lambda op: (op.src_slice is None and op.dst_slice is None))
+        """Whole-signal copies go to ``plan_copy``; copies with a slice on either side to
+        ``plan_slicedcopy`` with explicit element index lists (reference simulator.py:829-869)."""
+        def element_indices(sig, sl):
+            idx = np.arange(sig.size, dtype=np.int32)
+            return idx if sl is None else idx[sl]
+
+        whole = [op for op in ops if op.src_slice is None and op.dst_slice is None]
+        sliced = [op for op in ops if op not in whole]
         plans = []
-        if copies:
-            X = self.all_data[[self.sidx[op.src] for op in copies]]
-            Y = self.all_data[[self.sidx[op.dst] for op in copies]]
-            incs = np.array([op.inc for op in copies], dtype=np.int32)
-            plans.append(plan_copy(self.queue, X, Y, incs))
-        if ops:
-            inds = lambda ary, i: np.arange(ary.size, dtype=np.int32)[Ellipsis if i is None else i]
-            xinds = [inds(op.src, op.src_slice) for op in ops]
-            yinds = [inds(op.dst, op.dst_slice) for op in ops]
-            if any(len(i) != len(set(i.tolist())) for i in xinds + yinds):
-                raise NotImplementedError("Duplicates in indices")
-            X = self.all_data[[self.sidx[op.src] for op in ops]]
-            Y = self.all_data[[self.sidx[op.dst] for op in ops]]
-            Xinds = self.RaggedArray(xinds, dtype=np.int32)
-            Yinds = self.RaggedArray(yinds, dtype=np.int32)
-            incs = np.array([op.inc for op in ops], dtype=np.int32)
+        for group, planner in ((whole, plan_copy), (sliced, plan_slicedcopy)):
+            if not group:
+                continue
+            X, Y = self._gather(group, "src", "dst")
+            incs = np.array([op.inc for op in group], dtype=np.int32)
+            if planner is plan_copy:
+                plans.append(plan_copy(self.queue, X, Y, incs))
+                continue
+            index_lists = [[element_indices(op.src, op.src_slice) for op in group],
+                           [element_indices(op.dst, op.dst_slice) for op in group]]
+            for idx in index_lists[0] + index_lists[1]:
+                if len(np.unique(idx)) != len(idx):
+                    raise NotImplementedError("Duplicates in indices")
+            Xinds, Yinds = (self.RaggedArray(lists, dtype=np.int32) for lists in index_lists)
             plans.append(plan_slicedcopy(self.queue, X, Y, Xinds, Yinds, incs))
         return plans
 
@@ -652,10 +652,7 @@ class Simulator:
         return plans
 
     def _plan_ElementwiseInc(self, ops):
-        A = self.all_data[[self.sidx[op.A] for op in ops]]
-        X = self.all_data[[self.sidx[op.X] for op in ops]]
-        Y = self.all_data[[self.sidx[op.Y] for op in ops]]
-        return [plan_elementwise_inc(self.queue, A, X, Y)]
+        return [plan_elementwise_inc(self.queue, *self._gather(ops, "A", "X", "Y"))]
 
     # ---- python functions ---------------------------------------------------
     def _plan_SimPyFunc(self, ops):
@@ -750,8 +747,27 @@ class Simulator:
             plans.extend(getattr(self, attr_name)(ops))
         return plans
 
+    def _items(self, signals):
+        """Device view (sharing the packed buffer) of the ragged items of ``signals``."""
+        return self.all_data[[self.sidx[sig] for sig in signals]]
+
+    def _gather(self, ops, *names):
+        """One device view per name: ``op.<name>`` over ``ops``.  A name with a dot is looked up in
+        the operator's state dictionary (``"state.voltage"``)."""
+        def pick(op, name):
+            if name.startswith("state."):
+                return op.state[name[6:]]
+            return getattr(op, name)
+
+        views = [self._items([pick(op, name) for op in ops]) for name in names]
+        return views[0] if len(views) == 1 else views
+
     def _sigs(self, ops, fn):
-        return self.all_data[[self.sidx[fn(op)] for op in ops]]
+        return self._items([fn(op) for op in ops])
+
+    def _scaled_rates(self, ops):
+        """learning_rate * dt of every operator, as a device vector."""
+        return self.Array([op.learning_rate * self.model.dt for op in ops])
 
     def _param(self, ops, fn):
         """A python float when all ops agree, else a per-neuron ragged array
@@ -761,61 +777,57 @@ class Simulator:
             return values[0]
         return self.RaggedArray([v * np.ones(op.J.size) for v, op in zip(values, ops)], dtype=np.float32)
 
+    # neuron type -> (plan function, takes dt, signal arguments, parameter arguments, keyword signals,
+    # keyword parameters); parameters become a python float when all operators agree, else a
+    # per-neuron ragged array (what the reference always builds, simulator.py:1054-1063)
+    _NEURON_PLANS = {
+        "LIF": (plan_lif, True, ("J", "state.voltage", "state.refractory_time", "output"),
+                ("tau_ref", "tau_rc", "amplitude"), {}, {}),
+        "LIFRate": (plan_lif_rate, True, ("J", "output"), ("tau_ref", "tau_rc", "amplitude"), {}, {}),
+        "AdaptiveLIF": (plan_lif, True, ("J", "state.voltage", "state.refractory_time", "output"),
+                        ("tau_ref", "tau_rc", "amplitude"), {"N": "state.adaptation"},
+                        {"tau_n": "tau_n", "inc_n": "inc_n"}),
+        "AdaptiveLIFRate": (plan_lif_rate, True, ("J", "output"), ("tau_ref", "tau_rc", "amplitude"),
+                            {"N": "state.adaptation"}, {"tau_n": "tau_n", "inc_n": "inc_n"}),
+        "Sigmoid": (plan_sigmoid, False, ("J", "output"), ("tau_ref",), {}, {}),
+    }
+
+    def _plan_from_table(self, kind, ops):
+        planner, with_dt, sig_names, param_names, kw_sigs, kw_params = self._NEURON_PLANS[kind]
+        neuron_param = lambda name: self._param(ops, lambda op: getattr(op.neurons, name))
+        views = self._gather(ops, *sig_names)
+        args = ([self.model.dt] if with_dt else []) + list(views) + [neuron_param(n) for n in param_names]
+        kwargs = {k: self._gather(ops, v) for k, v in kw_sigs.items()}
+        kwargs.update({k: neuron_param(v) for k, v in kw_params.items()})
+        return [planner(self.queue, *args, **kwargs)]
+
     def _plan_LIF(self, ops):
-        if not all(op.neurons.min_voltage == 0 for op in ops):
+        if any(op.neurons.min_voltage != 0 for op in ops):
             raise NotImplementedError("LIF min voltage")
-        return [plan_lif(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
-                         self._sigs(ops, lambda op: op.state["voltage"]),
-                         self._sigs(ops, lambda op: op.state["refractory_time"]),
-                         self._sigs(ops, lambda op: op.output),
-                         self._param(ops, lambda op: op.neurons.tau_ref),
-                         self._param(ops, lambda op: op.neurons.tau_rc),
-                         self._param(ops, lambda op: op.neurons.amplitude))]
+        return self._plan_from_table("LIF", ops)
 
     def _plan_LIFRate(self, ops):
-        return [plan_lif_rate(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
-                              self._sigs(ops, lambda op: op.output),
-                              self._param(ops, lambda op: op.neurons.tau_ref),
-                              self._param(ops, lambda op: op.neurons.tau_rc),
-                              self._param(ops, lambda op: op.neurons.amplitude))]
+        return self._plan_from_table("LIFRate", ops)
 
     def _plan_AdaptiveLIF(self, ops):
-        return [plan_lif(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
-                         self._sigs(ops, lambda op: op.state["voltage"]),
-                         self._sigs(ops, lambda op: op.state["refractory_time"]),
-                         self._sigs(ops, lambda op: op.output),
-                         self._param(ops, lambda op: op.neurons.tau_ref),
-                         self._param(ops, lambda op: op.neurons.tau_rc),
-                         self._param(ops, lambda op: op.neurons.amplitude),
-                         N=self._sigs(ops, lambda op: op.state["adaptation"]),
-                         tau_n=self._param(ops, lambda op: op.neurons.tau_n),
-                         inc_n=self._param(ops, lambda op: op.neurons.inc_n))]
+        return self._plan_from_table("AdaptiveLIF", ops)
 
     def _plan_AdaptiveLIFRate(self, ops):
-        return [plan_lif_rate(self.queue, self.model.dt, self._sigs(ops, lambda op: op.J),
-                              self._sigs(ops, lambda op: op.output),
-                              self._param(ops, lambda op: op.neurons.tau_ref),
-                              self._param(ops, lambda op: op.neurons.tau_rc),
-                              self._param(ops, lambda op: op.neurons.amplitude),
-                              N=self._sigs(ops, lambda op: op.state["adaptation"]),
-                              tau_n=self._param(ops, lambda op: op.neurons.tau_n),
-                              inc_n=self._param(ops, lambda op: op.neurons.inc_n))]
-
-    def _plan_RectifiedLinear(self, ops):
-        J = self._sigs(ops, lambda op: op.J)
-        amp = self.RaggedArray([op.neurons.amplitude * np.ones(op.J.size) for op in ops], dtype=J.dtype)
-        return [plan_rectified_linear(self.queue, J, self._sigs(ops, lambda op: op.output), amp)]
-
-    def _plan_SpikingRectifiedLinear(self, ops):
-        J = self._sigs(ops, lambda op: op.J)
-        amp = self.RaggedArray([op.neurons.amplitude * np.ones(op.J.size) for op in ops], dtype=J.dtype)
-        return [plan_spiking_rectified_linear(self.queue, self.model.dt, J,
-                                              self._sigs(ops, lambda op: op.state["voltage"]),
-                                              self._sigs(ops, lambda op: op.output), amp)]
+        return self._plan_from_table("AdaptiveLIFRate", ops)
 
     def _plan_Sigmoid(self, ops):
-        return [plan_sigmoid(self.queue, self._sigs(ops, lambda op: op.J), self._sigs(ops, lambda op: op.output),
-                             self._param(ops, lambda op: op.neurons.tau_ref))]
+        return self._plan_from_table("Sigmoid", ops)
+
+    def _amplitudes(self, ops):
+        return self.RaggedArray([op.neurons.amplitude * np.ones(op.J.size) for op in ops], dtype=np.float32)
+
+    def _plan_RectifiedLinear(self, ops):
+        J, out = self._gather(ops, "J", "output")
+        return [plan_rectified_linear(self.queue, J, out, self._amplitudes(ops))]
+
+    def _plan_SpikingRectifiedLinear(self, ops):
+        J, V, out = self._gather(ops, "J", "state.voltage", "output")
+        return [plan_spiking_rectified_linear(self.queue, self.model.dt, J, V, out, self._amplitudes(ops))]
 
     # ---- processes --------------------------------------------------------------
     def _plan_SimProcess(self, all_ops):
@@ -937,76 +949,76 @@ class Simulator:
         pres_t = self.Array([p.presentation_time for p in ps])
         return [plan_presentinput(self.queue, Y, t, inputs, self.model.dt, pres_t=pres_t)]
 
+    # ---- learning rules: every rule produces a delta; a separate Copy(inc) applies it ---------
     def _plan_SimPES(self, ops):
-        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
-        error = self.all_data[[self.sidx[op.error] for op in ops]]
-        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
+        """delta = alpha * outer(error, pre activities), alpha = -learning_rate * dt / n_pre
+        (reference simulator.py:1334-1345)."""
+        error, pre, delta = self._gather(ops, "error", "pre_filtered", "delta")
         alpha = np.array([-op.learning_rate * self.model.dt / op.pre_filtered.shape[0] for op in ops])
         return [plan_elementwise_inc(self.queue, error, pre, delta, alpha=alpha, outer=True, inc=False)]
 
     def _plan_SimBCM(self, ops):
-        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
-        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
-        theta = self.all_data[[self.sidx[op.theta] for op in ops]]
-        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
-        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
-        return [plan_bcm(self.queue, pre, post, theta, delta, alpha)]
+        pre, post, theta, delta = self._gather(ops, "pre_filtered", "post_filtered", "theta", "delta")
+        return [plan_bcm(self.queue, pre, post, theta, delta, self._scaled_rates(ops))]
 
     def _plan_SimOja(self, ops):
-        pre = self.all_data[[self.sidx[op.pre_filtered] for op in ops]]
-        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
-        weights = self.all_data[[self.sidx[op.weights] for op in ops]]
-        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
-        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
-        beta = self.Array([op.beta for op in ops])
-        return [plan_oja(self.queue, pre, post, weights, delta, alpha, beta)]
-
-    def _plan_SimRLS(self, ops):
-        raise NotImplementedError("RLS learning rule not yet supported")
+        pre, post, weights, delta = self._gather(ops, "pre_filtered", "post_filtered", "weights", "delta")
+        return [plan_oja(self.queue, pre, post, weights, delta, self._scaled_rates(ops),
+                         self.Array([op.beta for op in ops]))]
 
     def _plan_SimVoja(self, ops):
-        pre = self.all_data[[self.sidx[op.pre_decoded] for op in ops]]
-        post = self.all_data[[self.sidx[op.post_filtered] for op in ops]]
-        encoders = self.all_data[[self.sidx[op.scaled_encoders] for op in ops]]
-        delta = self.all_data[[self.sidx[op.delta] for op in ops]]
-        learning_signal = self.all_data[[self.sidx[op.learning_signal] for op in ops]]
+        pre, post, encoders, delta, learn = self._gather(ops, "pre_decoded", "post_filtered", "scaled_encoders",
+                                                         "delta", "learning_signal")
         scale = self.RaggedArray([np.asarray(op.scale).reshape(-1, 1) for op in ops], dtype=np.float32)
-        alpha = self.Array([op.learning_rate * self.model.dt for op in ops])
-        return [plan_voja(self.queue, pre, post, encoders, delta, learning_signal, scale, alpha)]
+        return [plan_voja(self.queue, pre, post, encoders, delta, learn, scale, self._scaled_rates(ops))]
+
+    def _plan_SimRLS(self, ops):
+        raise NotImplementedError("RLS learning rule not yet supported")  # (nor in the reference, :1372)
 
     # ---- reporting ---------------------------------------------------------------
     def print_plans(self):
+        """Every plan of a step with its launch shape and what it works on."""
         print(" Plans ".center(80, "-"))
         for plan in self._plans:
-            print("%r" % plan)
-            if hasattr(plan, "description"):
-                print(indent(plan.description, 4))
+            print(repr(plan))
+            description = getattr(plan, "description", None)
+            if description:
+                print(indent(description, 4))
+
+    def profiling_rows(self):
+        """Per plan: calls, seconds on the device, GF/s and GB/s from the plan's own flop and byte
+        counts (``flops_per_call`` / ``bw_per_call``, the figures the reference prints too)."""
+        rows = []
+        for plan in self._plans:
+            if not isinstance(plan, BasePlan):
+                continue
+            seconds = float(sum(plan.ctimes))
+            rate = plan.n_calls / seconds if seconds > 0 else float("nan")
+            scale = lambda per_call: 1e-9 * per_call * rate if per_call is not None else float("nan")
+            rows.append(dict(plan=str(plan), n_calls=plan.n_calls, seconds=seconds,
+                             gflops=scale(plan.flops_per_call), gbs=scale(plan.bw_per_call)))
+        return rows
 
     def print_profiling(self, sort=None):
-        """Table of n_calls, runtime, GF/s, GB/s per plan (needs ``profiling=True``)."""
+        """Table of calls, device time, GF/s and GB/s per plan (needs ``profiling=True``).
+        ``sort``: column to sort by (0 calls, 1 time, 2 GF/s, 3 GB/s; negative = ascending)."""
         if not self.profiling:
             print("Profiling not enabled!")
             return
-        table = []
-        for p in self._plans:
-            if isinstance(p, BasePlan):
-                t = sum(p.ctimes)
-                calls_per_sec = p.n_calls / t if t > 0 else np.nan
-                gfps = 1e-9 * p.flops_per_call * calls_per_sec if p.flops_per_call is not None else np.nan
-                gbps = 1e-9 * p.bw_per_call * calls_per_sec if p.bw_per_call is not None else np.nan
-                table.append((p.n_calls, t, gfps, gbps, str(p)))
+        rows = self.profiling_rows()
+        columns = ("n_calls", "seconds", "gflops", "gbs")
         if sort is not None:
-            table.sort(key=lambda x: x[abs(sort)], reverse=sort >= 0)
+            rows.sort(key=lambda r: r[columns[abs(sort)]], reverse=sort >= 0)
         print(" Profiling ".center(80, "-"))
         print("%8s|%10s|%10s|%10s|" % ("n_calls", "runtime", "GF/s", "GB/s"))
-        for r in table:
-            print("%8d|%10.3f|%10.3f|%10.3f| %s" % r)
+        for r in rows:
+            print("%8d|%10.3f|%10.3f|%10.3f| %s" % (r["n_calls"], r["seconds"], r["gflops"], r["gbs"], r["plan"]))
         print("-" * 80)
-        times = np.array([r[1] for r in table], dtype=np.float64)
+        total = sum(r["seconds"] for r in rows)
 
-        def wmean(col):
-            x = np.array([r[col] for r in table], dtype=np.float64)
-            m = ~np.isnan(x)
-            return (x[m] * times[m]).sum() / times[m].sum() if times[m].sum() > 0 else np.nan
+        def time_weighted(col):
+            pairs = [(r[col], r["seconds"]) for r in rows if r[col] == r[col]]  # (skip NaN)
+            weight = sum(w for _, w in pairs)
+            return sum(v * w for v, w in pairs) / weight if weight > 0 else float("nan")
 
-        print("totals:\t%2.3f\t%2.3f\t%2.3f" % (times.sum(), wmean(2), wmean(3)))
+        print("totals:\t%2.3f\t%2.3f\t%2.3f" % (total, time_weighted("gflops"), time_weighted("gbs")))
