@@ -91,8 +91,12 @@ struct __align__(16) StreamSlot {
 };
 
 // record words
-enum { R_TYPE = 0, R_ENS, R_SLOT, R_A, R_B, R_NCOPY, R_TARGET, R_C, R_COPY0 = 8 };
-// D records: R_A connection, R_B first row, R_C rows
+enum { R_TYPE = 0, R_ENS, R_SLOT, R_A, R_B, R_NCOPY, R_TARGET, R_C, R_COPY0 = 8, R_TX = 31 };
+// D records: R_A connection, R_B first row, R_C rows; everything else the record needs is written
+// into it by the host (one shared-memory read instead of a table lookup in global memory):
+enum { RD_NE = 11, RD_PES, RD_ALPHA, RD_ERR, RD_WEIGHTED, RD_FILT, RD_B0, RD_A0 };  // neurons, PES flag, alpha
+// (float bits), element index of the error / decoded / filtered value of the first row (filtered: -1 = none),
+// synapse coefficients (float bits; a0 == 0: pure gain)
 
 // All lanes: fill the stage for turn m (record index i); the record is in st.rec[m & 1].
 // Every copy is issued by a lane of its own; the warp's next record rides along.
@@ -110,11 +114,8 @@ __device__ __forceinline__ void stream_issue(const StreamParams& p, StreamStage&
     bytes = (uint32_t)r[R_COPY0 + 3 * lane + 1];
     dst = st.buf + r[R_COPY0 + 3 * lane + 2];
   }
-  uint32_t tx = bytes;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, off);
   if (lane == 0) {
-    tx += more ? ST_REC * 4u : 0u;
+    const uint32_t tx = (uint32_t)r[R_TX] + (more ? ST_REC * 4u : 0u);  // (the host added up the copies)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pipe_smem(full)), "r"(tx) : "memory");
   }
   __syncwarp();
@@ -136,6 +137,17 @@ __device__ __forceinline__ void stream_stage_x(const StreamParams& p, StreamStag
     for (int c = lane; c < d; c += 32) st.x[xoff + c] = x[(size_t)c * xs];
     xoff += d;
   }
+}
+
+// w + (alpha * error) * trace for 4 neighbouring columns (two roundings per element, as the
+// reference's delta kernel followed by its increment)
+__device__ __forceinline__ float4 pes_update(float4 w, float ae, float4 p) {
+  float4 o;
+  o.x = w.x + ae * p.x;
+  o.y = w.y + ae * p.y;
+  o.z = w.z + ae * p.z;
+  o.w = w.w + ae * p.w;
+  return o;
 }
 
 // Lane 0 polls a counter of the CTA; the whole warp gets the answer.
@@ -239,14 +251,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           roff[j] = base + min(lane + 32 * j, nb - 1);
           tot[j] = s_bias[roff[j]];  // J = ((bias + term 0) + term 1) + ...
         }
-        const int NR = (nb + 31) >> 5;
         int xoff = 0;
         for (int k = 0; k < n_terms; ++k) {
           const int d = __ldg(terms + k * T_STRIDE + T_D);
           const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
-          if (NR == 1) block_rows_staged4<1>(a, st.x + xoff, d, lane, roff, tot, 1.0);
-          else if (NR == 2) block_rows_staged4<2>(a, st.x + xoff, d, lane, roff, tot, 1.0);
-          else block_rows_staged4<4>(a, st.x + xoff, d, lane, roff, tot, 1.0);
+          // (always four rows per lane: a short last block repeats its last neuron, which keeps
+          // the kernel's code small)
+          block_rows_staged4<4>(a, st.x + xoff, d, lane, roff, tot, 1.0);
           xoff += d;
         }
         // (lanes beyond the last neuron of the block recompute it; nothing of theirs is stored)
@@ -257,20 +268,32 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           Wv[j] = s_W[roff[j]];
         }
         fused_lif4(tot, Vv, Wv, Sv, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
+        // row j of this lane is neuron i0 + base + lane + 32 j: every array is walked with immediates
+        const int first = i0 + base + lane;
+        float* gV = data + eV + first;
+        float* gW = data + eW + first;
+        float* gS = eS >= 0 ? data + eS + first : nullptr;
+        float* sspk = slot.spk + first;
+        if (pf_conn >= 0) {
+          const float* spf = s_pf + base + lane;
+          float* spfo = slot.pfo + first;
+          float* gPF = data + gpf + first;
+#pragma unroll
+          for (int j = 0; j < ST_ROWS; ++j) {
+            if (lane + 32 * j < nb) {
+              const float pf = spf[32 * j];
+              spfo[32 * j] = pf;
+              gPF[32 * j] = pb0 * Sv[j] - pa0 * pf;
+            }
+          }
+        }
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
-          const int r = base + lane + 32 * j;
-          const bool mine = lane + 32 * j < nb;
-          if (mine) {
-            data[eV + i0 + r] = Vv[j];
-            data[eW + i0 + r] = Wv[j];
-            if (eS >= 0) data[eS + i0 + r] = Sv[j];
-            slot.spk[i0 + r] = Sv[j];
-            if (pf_conn >= 0) {
-              const float pf = s_pf[r];
-              slot.pfo[i0 + r] = pf;
-              data[gpf + i0 + r] = pb0 * Sv[j] - pa0 * pf;
-            }
+          if (lane + 32 * j < nb) {
+            gV[32 * j] = Vv[j];
+            gW[32 * j] = Wv[j];
+            if (gS) gS[32 * j] = Sv[j];
+            sspk[32 * j] = Sv[j];
           }
         }
       }
@@ -283,36 +306,43 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       }
     } else if (ok && h0.x == 2) {
       // ---------------- D record: rows [r0, r0 + nr) of one decoder matrix ----------------
-      const int* c = p.conn_table + (size_t)h0.w * C_STRIDE;
-      const int r0 = h1.x, nr = h1.w;  // nr * ntile <= ST_DITEMS by construction
-      const int n_e = __ldg(e + E_N);
+      const int nr = h1.w;  // nr * ntile <= ST_DITEMS by construction
+      const int4 k0 = *reinterpret_cast<const int4*>(rec + 8);   // W element index, bytes, 0, neurons
+      const int4 k1 = *reinterpret_cast<const int4*>(rec + 12);  // PES, alpha, error, decoded
+      const int4 k2 = *reinterpret_cast<const int4*>(rec + 16);  // filtered, b0, a0, -
+      const int n_e = k0.w;
       const int n4 = n_e >> 2;
       const int ntile = (n_e + 127) >> 7;
-      const bool pes = __ldg(c + C_PES) != 0;
+      const bool pes = k1.x != 0;
       // every E record of this ensemble must have delivered its spikes
       ok = stream_wait_count(&e_done[h0.z], h1.z, &s_abort, lane);
       if (ok) {
         if (pes) {
           // w += (alpha * error) * trace, with alpha * error formed once per row as in
           // `alpha * aa * xx` (left to right); the stage keeps the old values for the decode
-          if (lane < nr) st.ae[lane] = bits(__ldg(c + C_ALPHA)) * data[__ldg(c + C_ERR) + r0 + lane];
+          if (lane < nr) st.ae[lane] = bits(k1.y) * data[k1.z + lane];
           __syncwarp();
-          float4* Wd = reinterpret_cast<float4*>(data + __ldg(c + C_W)) + (size_t)r0 * n4;
-          const float4* sw = reinterpret_cast<const float4*>(st.buf);
-          const float4* pfo4 = reinterpret_cast<const float4*>(slot.pfo);
-#pragma unroll 4
-          for (int i4 = lane; i4 < n4; i4 += 32) {
-            const float4 p4 = pfo4[i4];
+          // (pointers advance by immediates: the loop body is loads, 8 flops per row and stores)
+          const float4* pf4 = reinterpret_cast<const float4*>(slot.pfo) + lane;
+          const float4* w4p = reinterpret_cast<const float4*>(st.buf) + lane;
+          float4* g4p = reinterpret_cast<float4*>(data + k0.x) + lane;
+          const int iters = (n4 - lane + 31) >> 5;  // this lane's groups of 4 columns
+          if (nr == 2) {
+            const float a0 = st.ae[0], a1 = st.ae[1];
 #pragma unroll 2
+            for (int it = 0; it < iters; ++it) {
+              const float4 p4 = pf4[32 * it];
+              const float4 u = w4p[32 * it], v = w4p[n4 + 32 * it];
+              g4p[32 * it] = pes_update(u, a0, p4);
+              g4p[n4 + 32 * it] = pes_update(v, a1, p4);
+            }
+          } else {
             for (int rr = 0; rr < nr; ++rr) {
-              const float ae = st.ae[rr];
-              const float4 w4 = sw[rr * n4 + i4];
-              float4 o;
-              o.x = w4.x + ae * p4.x;
-              o.y = w4.y + ae * p4.y;
-              o.z = w4.z + ae * p4.z;
-              o.w = w4.w + ae * p4.w;
-              Wd[(size_t)rr * n4 + i4] = o;
+              const float a = st.ae[rr];
+              const float4* wr = w4p + rr * n4;
+              float4* gr = g4p + (size_t)rr * n4;
+#pragma unroll 4
+              for (int it = 0; it < iters; ++it) gr[32 * it] = pes_update(wr[32 * it], a, pf4[32 * it]);
             }
           }
         }
@@ -332,7 +362,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           const int kmax = min(32, n4) + 7;
 #pragma unroll 8
           for (int k = 0; k < kmax; ++k) {
-            if (k >= skew && k - skew < len) {
+            if ((unsigned)(k - skew) < (unsigned)len) {
               const float2 w2 = *reinterpret_cast<const float2*>(wi + 4 * k);
               const float2 s2 = *reinterpret_cast<const float2*>(si + 4 * k);
               ca = bd_add(ca, bd_mul(w2.x, s2.x));
@@ -348,14 +378,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
         float total = 0.0f;
         for (int t = 0; t < ntile; ++t) total = bd_add(total, __shfl_sync(0xffffffffu, tile, lane_t0 + 2 * t));
         if (valid && tt == 0 && jp == 0) {
-          data[__ldg(c + C_WEIGHTED) + r0 + rr] = total;
-          const int filt = __ldg(c + C_FILT);
-          if (filt >= 0) {
-            const int yi = filt + r0 + rr;
+          data[k1.w + rr] = total;
+          if (k2.x >= 0) {
+            const int yi = k2.x + rr;
             // plan_linearfilter fast path (clra_nonlinearities.py:657-660)
-            const int a0 = __ldg(c + C_A0);
-            float out = bits(__ldg(c + C_B0)) * total;
-            if (a0 != 0) out = out - bits(a0) * data[yi];
+            float out = bits(k2.y) * total;
+            if (k2.z != 0) out = out - bits(k2.z) * data[yi];
             data[yi] = out;
           }
         }

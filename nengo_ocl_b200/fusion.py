@@ -405,7 +405,9 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
     neurons, [7] connection table row of the PES connection or -1; copies = encoder
     rows of every term, bias, voltage, refractory time [, PES activity trace].
     D: [3] connection table row, [4] first row, [7] rows (rows x 128-column tiles
-    <= 16); one copy.
+    <= 16); one copy; [11..18] neurons, PES flag, alpha, element index of the first
+    row's error / decoded / filtered value (filtered: -1 = none), synapse b0, a0
+    (float bits).  [31] (both types): total bytes of the copies.
     Ensembles are dealt to CTAs in contiguous runs balanced by bytes; the records
     of a CTA are ordered E(0), E(1), D(0), E(2), D(1), ..., D(last).
     """
@@ -438,6 +440,7 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
             rec[5] = len(copies)
             for q, cp in enumerate(copies):
                 rec[8 + 3 * q:11 + 3 * q] = cp
+            rec[31] = sum(cp[1] for cp in copies)  # bytes the stage's barrier expects
             E.append(rec)
         # a D record holds at most STREAM_DITEMS (row, 128-column tile) pairs: two lanes each
         nr_max = max(1, min(STREAM_DITEMS // (-(-n // 128)), STREAM_STAGE_FLOATS // n))
@@ -448,6 +451,13 @@ def stream_records(ens, terms, conns, rows, n_ctas_max):
                 rec = np.zeros(STREAM_REC, dtype=np.int64)
                 rec[0], rec[1], rec[3], rec[4], rec[5], rec[7] = 2, r, c0 + k, r0, 1, nr
                 rec[8:11] = (int(conns[c0 + k, 0]) + r0 * n, 4 * nr * n, 0)
+                # what the record needs from the connection table, so that the kernel reads it from
+                # shared memory: neurons, PES flag, alpha, error / decoded / filtered element of the
+                # first row, synapse coefficients
+                crow = conns[c0 + k]
+                rec[11:19] = (n, int(crow[6]), int(crow[11]), int(crow[7]) + r0, int(crow[2]) + r0,
+                              int(crow[3]) + r0 if crow[3] >= 0 else -1, int(crow[4]), int(crow[5]))
+                rec[31] = 4 * nr * n
                 D.append(rec)
         nbytes = 4 * n * (sum(ds) + 5) + sum(4 * int(conns[c0 + k, 1]) * n * (2 if conns[c0 + k, 6] else 1)
                                               for k in range(nc))
