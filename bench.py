@@ -313,7 +313,7 @@ def spmv_microbench(queue, capi, n=1 << 20, fan_out=64, reps=10):
     return out
 
 
-def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse")):
+def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse"), steps_override=None):
     """Configurations 1, 3 and 4 (L2-resident models): simulated steps/s through the public
     API (``run_steps``: graph replay + probe drains), timed after a 10-step warm-up as the
     reference's benchmark scripts do (examples/benchmark_circconv.py:87-93)."""
@@ -332,6 +332,7 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse")):
     out = {}
     for key in which:
         label, make, steps = makers[key]
+        steps = steps_override or steps
         t0 = time.perf_counter()
         mdl = make()
         # probes are drained every 256 steps (every 32 for the population-wide probe of the sparse model,
@@ -365,6 +366,7 @@ def main():
     ap.add_argument("--no-small", action="store_true", help="skip the steps/s of configurations 1, 3 and 4")
     ap.add_argument("--no-spmv", action="store_true", help="skip the sparse-transform microbenchmark")
     ap.add_argument("--spmv-only", action="store_true", help="run only the sparse-transform microbenchmark")
+    ap.add_argument("--small-steps", type=int, default=None, help="timed steps of the small configurations (profiling)")
     ap.add_argument("--small-only", default=None, help="run only these small configurations, e.g. c3,c4 (for profiling)")
     args = ap.parse_args()
 
@@ -402,7 +404,7 @@ def main():
         return float(t.item())
 
     if args.small_only:
-        print(json.dumps({"small_models": small_model_rates(ctx, _capi, tuple(args.small_only.split(",")))}), flush=True)
+        print(json.dumps({"small_models": small_model_rates(ctx, _capi, tuple(args.small_only.split(",")), args.small_steps)}), flush=True)
         return
     if args.spmv_only:
         from nengo_ocl_b200.runtime import CommandQueue

@@ -227,8 +227,10 @@ int nb2_presentinput(void* stream, int n_items, int block_size, const float* pre
  * and then one plan_copy(inc) (:217-304) per group of non-overlapping targets.
  * blocks [n_blocks][4] = {dst start, elements (<= 256), first source, n sources};
  * src_starts holds the element offset of every (block, source) pair; sources are
- * added in order starting from zero. */
-int nb2_gather_sum(void* stream, int n_blocks, const int* blocks, const int* src_starts, float* data);
+ * added in order starting from zero.  width: threads per block of the table, a
+ * power of two >= the longest block (256 / width blocks share one CTA). */
+int nb2_gather_sum(void* stream, int n_blocks, int width, const int* blocks, const int* src_starts,
+                   float* data);
 
 /* Neuron models generated by _plan_template (:1286-1483): plan_lif :1028-1146,
  * plan_lif_rate :1149-1197, plan_spiking_rectified_linear :1200-1235,

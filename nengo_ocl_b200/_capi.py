@@ -94,7 +94,7 @@ _SIGNATURES = {
     "nb2_ensemble_stream": [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_double, _P, _P],
     "nb2_exchange_wait": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_double],
     "nb2_exchange_push": [_P, _P, _P, _P, _P, c_int, c_int, c_int],
-    "nb2_gather_sum": [_P, c_int, _P, _P, _P],
+    "nb2_gather_sum": [_P, c_int, c_int, _P, _P, _P],
     "nb2_ensemble_step": [_P, c_int, _P, c_int, _P, _P, _P, _P, _P, c_double],
     "nb2_direct": [_P, c_int, _P, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P],
 }

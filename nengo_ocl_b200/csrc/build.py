@@ -65,10 +65,12 @@ def build(force=False, verbose=False):
         subprocess.run(cmd, check=True)
         rebuilt = True
     if rebuilt or not os.path.exists(LIB) or force:
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ARCH + ["-Xcompiler", "-fPIC"]
+        tmp = LIB + ".tmp"  # link beside the target and rename: a reader never sees a half-written library
+        cmd = [nvcc, "-shared", "-o", tmp] + objs + ARCH + ["-Xcompiler", "-fPIC"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -503,7 +503,7 @@ extern "C" int nb2_probes_wide_noalloc(void* stream, int n_probes, int chunks, f
 }
 
 // ---- plan_presentinput (:1694-1730) -----------------------------------------
-__global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float dt,
+__global__ void nb2_presentinput_kernel(int n_items, int width, const float* __restrict__ pres_t, float dt,
                                         const int* __restrict__ Yshape0s,
                                         const int* __restrict__ Ystarts, float* Y,
                                         const int* __restrict__ Tstarts, const float* T,
@@ -512,7 +512,10 @@ __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float 
                                         const int* __restrict__ Sstride0s,
                                         const float* __restrict__ S) {
   nb2_pdl_enter();
-  const int k = blockIdx.x;
+  // `width` threads per item (a power of two): a CTA takes blockDim.x / width items, so that
+  // many short tables do not cost one nearly empty CTA each
+  const int k = blockIdx.x * (blockDim.x / width) + threadIdx.x / width;
+  if (k >= n_items) return;
   const int m = Yshape0s[k];
   float* y = Y + Ystarts[k];
   const float* s = S + Sstarts[k];
@@ -522,7 +525,7 @@ __global__ void nb2_presentinput_kernel(const float* __restrict__ pres_t, float 
   if (pres_t) ti = (int)(((float)it - 0.5f) * (dt / pres_t[k])) % nt;
   else ti = it % nt;
   const int row = Sstride0s ? Sstride0s[k] : m;  // table rows are packed unless a stride table is given
-  for (int i = threadIdx.x; i < m; i += blockDim.x) y[i] = s[(size_t)row * ti + i];
+  for (int i = threadIdx.x % width; i < m; i += width) y[i] = s[(size_t)row * ti + i];
 }
 
 extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
@@ -532,7 +535,12 @@ extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const
   if (n_items == 0) return NB2_OK;
   NB2_REQUIRE(block_size >= 1 && block_size <= 1024, "block_size");
   NB2_REQUIRE(Yshape0s && Ystarts && Y && Tstarts && T && Sshape0s && Sstarts && S, "null pointer");
-  nb2_launch(nb2_presentinput_kernel, dim3(n_items), dim3(block_size), 0, nb2_stream(stream), pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S);
+  int width = 1;
+  while (width < block_size) width <<= 1;
+  const int threads = width < 256 ? 256 : width;
+  const int per_cta = threads / width;
+  nb2_launch(nb2_presentinput_kernel, dim3((n_items + per_cta - 1) / per_cta), dim3(threads), 0, nb2_stream(stream),
+             n_items, width, pres_t, (float)dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }
@@ -545,22 +553,29 @@ extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const
 // the reset + sequential increments.
 // blocks: [n_blocks][4] = {dst start, element count (<= 256), first source, source count};
 // src_starts: element offset of every (block, source) pair.
-__global__ void nb2_gather_sum_kernel(const int4* __restrict__ blocks, const int* __restrict__ src_starts,
-                                      float* data) {
+__global__ void nb2_gather_sum_kernel(int n_blocks, int width, const int4* __restrict__ blocks,
+                                      const int* __restrict__ src_starts, float* data) {
   nb2_pdl_enter();
-  const int4 b = blocks[blockIdx.x];
-  const int i = threadIdx.x;
+  // `width` threads per table block (a power of two >= the longest block): 256 / width blocks
+  // per CTA, so that thousands of one- or sixteen-element targets fill their CTAs
+  const int k = blockIdx.x * (256 / width) + threadIdx.x / width;
+  if (k >= n_blocks) return;
+  const int4 b = blocks[k];
+  const int i = threadIdx.x % width;
   if (i >= b.y) return;
   float sum = 0.0f;
-  for (int k = 0; k < b.w; ++k) sum += data[src_starts[b.z + k] + i];
+  for (int q = 0; q < b.w; ++q) sum += data[src_starts[b.z + q] + i];
   data[b.x + i] = sum;
 }
 
-extern "C" int nb2_gather_sum(void* stream, int n_blocks, const int* blocks, const int* src_starts, float* data) {
+extern "C" int nb2_gather_sum(void* stream, int n_blocks, int width, const int* blocks, const int* src_starts,
+                              float* data) {
   if (n_blocks == 0) return NB2_OK;
   NB2_REQUIRE(blocks && src_starts && data, "null pointer");
-  nb2_launch(nb2_gather_sum_kernel, dim3(n_blocks), dim3(256), 0, nb2_stream(stream), reinterpret_cast<const int4*>(blocks),
-                                                                 src_starts, data);
+  NB2_REQUIRE(width >= 1 && width <= 256 && (width & (width - 1)) == 0, "width must be a power of two <= 256");
+  const int per_cta = 256 / width;
+  nb2_launch(nb2_gather_sum_kernel, dim3((n_blocks + per_cta - 1) / per_cta), dim3(256), 0, nb2_stream(stream), n_blocks,
+             width, reinterpret_cast<const int4*>(blocks), src_starts, data);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

@@ -67,6 +67,8 @@ class FusedEnsembles(Operator):
                     reads.append(c["error"])
                     updates.extend([c["pre_filtered"], c["W"]])
                     internal.add(c["delta"])
+                    if c.get("error_alias") is not None:
+                        internal.add(c["error_alias"])
                 else:
                     reads.append(c["W"])
         self.sets, self.incs, self.reads, self.updates = sets, incs, reads, updates
@@ -210,6 +212,22 @@ def find_fusable(sim, operators):
                                             pf_b0=coef[0], pf_a0=coef[1],
                                             alpha=-pes_op.learning_rate * sim.model.dt / pf.shape[0])
                                 conn["ops"] += [pes_op, cop, pfw[0][0]]
+                                # An error signal that is only "reset to zero, += one whole signal" and read
+                                # by nothing but this rule is that signal (0 + x = x): the kernel reads the
+                                # source directly and the reset + copy need no launch of their own.
+                                err = pes_op.error
+                                ew = writers.get(err.base, [])
+                                er = [op for op, _ in readers.get(err.base, [])]
+                                e_reset = [op for op, kind, s in ew if _is_type(op, "Reset") and s is err
+                                           and op.value == 0]
+                                e_copy = [op for op, kind, s in ew if _is_type(op, "Copy") and kind == "incs"
+                                          and s is err and op.src_slice is None and op.dst_slice is None
+                                          and op.src.size == err.size and _contiguous_1d(op.src)]
+                                if (not err.is_view and len(ew) == 2 and len(e_reset) == 1 and len(e_copy) == 1
+                                        and er == [pes_op]
+                                        and not any(sim.model.sig[p]["in"].base is err for p in sim.model.probes)):
+                                    conn.update(error=e_copy[0].src, error_alias=err)
+                                    conn["ops"] += [e_reset[0], e_copy[0]]
             if not conn["pes"] and w_writers:
                 continue  # somebody else modifies these weights during the step
             member["conns"].append(conn)
@@ -303,7 +321,9 @@ def fuse_ensemble_groups(sim, groups, planner=None):
     sim.operators = new_ops
     sim.fused_groups = [dict(pes=any(c["pes"] for c in mem["conns"]), n=mem["n"],
                              unstored=[mem["J"]] + ([] if mem["store_spikes"] else [mem["out"]])
-                             + [c["delta"] for c in mem["conns"] if c["pes"]]) for mem in members]
+                             + [c["delta"] for c in mem["conns"] if c["pes"]]
+                             + [c["error_alias"] for c in mem["conns"] if c.get("error_alias") is not None])
+                        for mem in members]
     return new_groups
 
 
@@ -674,12 +694,15 @@ def plan_gather_sums(sim, ops):
     d_srcs = to_device(queue, np.asarray(srcs + [0], dtype=np.int32))
     data = sim.all_data.cl_buf
     fn, check = _capi.lib().nb2_gather_sum, _capi.check
-    args = (len(blocks), d_blocks.ptr, d_srcs.ptr, data.ptr)
+    width = 1  # threads per table block: the next power of two >= the longest block
+    while width < max([b[1] for b in blocks] + [1]):
+        width *= 2
+    args = (len(blocks), width, d_blocks.ptr, d_srcs.ptr, data.ptr)
 
     def launch(stream):
         check(fn(stream, *args))
 
-    plan = Plan(queue, launch, (256, max(len(blocks), 1)), lsize=(256, 1), name="gather_sum",
+    plan = Plan(queue, launch, (256, max(len(blocks) * width // 256, 1)), lsize=(256, 1), name="gather_sum",
                 tag="%d signals" % len(ops))
     plan.full_args = (d_blocks, d_srcs, data)
     plan.bw_per_call = n_bytes
