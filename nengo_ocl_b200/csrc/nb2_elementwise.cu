@@ -7,14 +7,14 @@
 // the CPU restatement the results are checked against.
 #include <mutex>
 #include "nb2_common.cuh"
+#include "nb2_phase_bodies.cuh"
 #include "../../include/nengo_b200.h"
 
 // ---- plan_timeupdate (clra_nonlinearities.py:119-133) ----------------------
 __global__ void nb2_timeupdate_kernel(float* step, float* time, double dt) {
   nb2_pdl_enter();
-  const float s = step[0] + 1.0f;
-  step[0] = s;
-  time[0] = (float)(dt * (double)s);  // dt is a double literal in the reference source
+  const Nb2TimeupdateArgs a = {step, time, dt};
+  nb2_timeupdate_body(a, 0, 0);
 }
 
 extern "C" int nb2_timeupdate(void* stream, float* step, float* time, double dt) {
@@ -370,26 +370,9 @@ __global__ void nb2_probes_kernel(float* countdowns, int* bufpositions,
   const float countdown = countdowns[n];
   const int bufpos = bufpositions[n];
   __syncthreads();  // everyone has read the counters before thread 0 rewrites them
-  if (countdown <= 0.0f) {
-    const int ni = Xshape0s[n];
-    const int nj = Xshape1s[n];
-    const int n_dims = ni * nj;
-    const int sti = Xstride0s[n];
-    const int stj = Xstride1s[n];
-    const float* x = X + Xstarts[n];
-    float* y = Y + Ystarts[n] + bufpos * n_dims;
-    for (int ij = threadIdx.x; ij < n_dims; ij += blockDim.x) {
-      const int i = ij / nj;
-      const int j = ij - i * nj;
-      y[ij] = x[i * sti + j * stj];
-    }
-    if (threadIdx.x == 0) {
-      countdowns[n] = countdown + periods[n] - 1.0f;
-      bufpositions[n] = bufpos + 1;
-    }
-  } else if (threadIdx.x == 0) {
-    countdowns[n] = countdown - 1.0f;
-  }
+  const Nb2ProbesArgs a = {countdowns, bufpositions, periods, Xstarts, Xshape0s, Xshape1s, Xstride0s, Xstride1s, X,
+                           Ystarts, Y};
+  nb2_probes_body(a, n, threadIdx.x, blockDim.x, countdown, bufpos);
 }
 
 extern "C" int nb2_probes(void* stream, int n_probes, int block_size, float* countdowns,
@@ -514,18 +497,8 @@ __global__ void nb2_presentinput_kernel(int n_items, int width, const float* __r
   nb2_pdl_enter();
   // `width` threads per item (a power of two): a CTA takes blockDim.x / width items, so that
   // many short tables do not cost one nearly empty CTA each
-  const int k = blockIdx.x * (blockDim.x / width) + threadIdx.x / width;
-  if (k >= n_items) return;
-  const int m = Yshape0s[k];
-  float* y = Y + Ystarts[k];
-  const float* s = S + Sstarts[k];
-  const int it = (int)T[Tstarts[k]];
-  const int nt = Sshape0s[k];
-  int ti;
-  if (pres_t) ti = (int)(((float)it - 0.5f) * (dt / pres_t[k])) % nt;
-  else ti = it % nt;
-  const int row = Sstride0s ? Sstride0s[k] : m;  // table rows are packed unless a stride table is given
-  for (int i = threadIdx.x % width; i < m; i += width) y[i] = s[(size_t)row * ti + i];
+  const Nb2PresentArgs a = {n_items, width, pres_t, dt, Yshape0s, Ystarts, Y, Tstarts, T, Sshape0s, Sstarts, Sstride0s, S};
+  nb2_presentinput_body(a, blockIdx.x * (blockDim.x / width) + threadIdx.x / width, threadIdx.x % width, width);
 }
 
 extern "C" int nb2_presentinput(void* stream, int n_items, int block_size, const float* pres_t, double dt,
@@ -558,14 +531,8 @@ __global__ void nb2_gather_sum_kernel(int n_blocks, int width, const int4* __res
   nb2_pdl_enter();
   // `width` threads per table block (a power of two >= the longest block): 256 / width blocks
   // per CTA, so that thousands of one- or sixteen-element targets fill their CTAs
-  const int k = blockIdx.x * (256 / width) + threadIdx.x / width;
-  if (k >= n_blocks) return;
-  const int4 b = blocks[k];
-  const int i = threadIdx.x % width;
-  if (i >= b.y) return;
-  float sum = 0.0f;
-  for (int q = 0; q < b.w; ++q) sum += data[src_starts[b.z + q] + i];
-  data[b.x + i] = sum;
+  const Nb2GatherArgs a = {n_blocks, width, blocks, src_starts, data};
+  nb2_gather_sum_body(a, blockIdx.x, threadIdx.x);
 }
 
 extern "C" int nb2_gather_sum(void* stream, int n_blocks, int width, const int* blocks, const int* src_starts,
