@@ -348,6 +348,10 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse"), steps_ov
         out[key] = {"workload": label, "steps_per_s": steps / dt_s, "neuron_updates_per_s": mdl.n_neurons * steps / dt_s,
                     "plans_per_step": len(sim._plans), "launches_per_step": sim._plans.launches_per_step,
                     "us_per_step": 1e6 * dt_s / steps, "build_s": round(build_s, 2)}
+        loop = sim._plans.step_loop
+        # (persistent step loop: the plans run as phases of one cooperative launch per run_steps batch)
+        out[key]["step_loop"] = None if loop is None else {"phases": loop.n_phases, "barriers_per_step": loop.n_barriers,
+                                                           "ctas": loop.grid}
         sim.close()
     return out
 

@@ -350,6 +350,62 @@ int nb2_exchange_wait(void* stream, int* ctl, const int* flags, const float* sta
 int nb2_exchange_push(void* stream, int* ctl, float* const* peer_staging, int* const* peer_flags,
                       const float* replica, int rank, int world, int seg);
 
+/* ---- persistent step loop ---------------------------------------------------
+ * Replaces Plans.call_n_times / enqueue_n_times (nengo_ocl/plan.py:137-149: every
+ * kernel of every plan enqueued n times) for models whose plans all have a phase
+ * form: ONE cooperative launch runs n whole steps.  A loop is built once:
+ * create, one add call per plan in plan order (same arguments as the launch
+ * entry point of that name without the stream; `barrier` != 0 puts a grid-wide
+ * barrier before the phase - required whenever the phase reads or writes what
+ * an earlier phase since the last barrier wrote, or writes what one read,
+ * counting the previous step's phases as earlier), finalize, then run any
+ * number of times.  Results are bit-identical to the separate launches: the
+ * phases execute the same device code.  Ring-buffer filters, wide probes and
+ * the streamed ensemble kernel have no phase form (the add call returns
+ * NB2_ERR_LIMIT or does not exist): such models keep the launch-per-plan path.
+ * finalize: max_ctas > 0 caps the grid (0: as many CTAs as are co-resident, at
+ * most the widest phase).  A grid of ONE CTA (max_ctas == 1, or no phase wider
+ * than one block) runs a variant whose barrier is a CTA barrier and whose loads
+ * stay in that multiprocessor's L1: the form that pays for very small models
+ * (nb2_step_loop_info: total_vblocks = blocks of all phases of one step).  A barrier wait is bounded (about a second); if it
+ * runs out the kernel returns and nb2_step_loop_status reports NB2_ERR_TIMEOUT
+ * (sticky) after synchronising the stream. */
+#define NB2_STEP_LOOP_MAX_PHASES 64
+int nb2_step_loop_create(void** loop);
+int nb2_step_loop_destroy(void* loop);
+int nb2_step_loop_add_timeupdate(void* loop, int barrier, float* step, float* time, double dt);
+int nb2_step_loop_add_gather_sum(void* loop, int barrier, int n_blocks, int width, const int* blocks,
+                                 const int* src_starts, float* data);
+int nb2_step_loop_add_direct(void* loop, int barrier, int n_items, const int* prog, int n_ops, int max_depth,
+                             const double* consts, int out_dim, const int* in0_starts, const float* in0,
+                             const int* in1_starts, const float* in1, const int* out_starts, float* out);
+int nb2_step_loop_add_ensemble_step(void* loop, int barrier, int n_large, const int* large_ids, int n_small,
+                                    const int* small_ids, const int* ens_table, const int* term_table,
+                                    const int* conn_table, float* data, double dt);
+int nb2_step_loop_add_gemv_block(void* loop, int barrier, const int* gstructure, int gstride, int D,
+                                 const int* xstrides, const int* cta_units, int n_cta, const int* warp_units,
+                                 int n_warp, const float* A, const float* X, const float* Yin, float* Y,
+                                 double alpha, double beta, double gamma);
+int nb2_step_loop_add_probes(void* loop, int barrier, int n_probes, int block_size, float* countdowns,
+                             int* bufpositions, const float* periods, const int* Xstarts, const int* Xshape0s,
+                             const int* Xshape1s, const int* Xstride0s, const int* Xstride1s, const float* X,
+                             const int* Ystarts, float* Y);
+int nb2_step_loop_add_linearfilter(void* loop, int barrier, int n_blocks, int block_size, int uses_buf,
+                                   const int* offsets, const int* shape0s, const int* shape1s,
+                                   const int* Xstride0s, const int* Xstride1s, const int* Xstarts, const float* X,
+                                   const int* Ystride0s, const int* Ystride1s, const int* Ystarts, float* Y,
+                                   const int* Ashape0s, const int* Astarts, const float* A, const int* Bshape0s,
+                                   const int* Bstarts, const float* B, const int* Xbufstarts, float* Xbuf,
+                                   const int* Ybufstarts, float* Ybuf, int* Xbufpos, int* Ybufpos);
+int nb2_step_loop_add_presentinput(void* loop, int barrier, int n_items, int block_size, const float* pres_t,
+                                   double dt, const int* Yshape0s, const int* Ystarts, float* Y,
+                                   const int* Tstarts, const float* T, const int* Sshape0s, const int* Sstarts,
+                                   const int* Sstride0s, const float* S);
+int nb2_step_loop_finalize(void* loop, int max_ctas);
+int nb2_step_loop_run(void* loop, void* stream, int n_steps);
+int nb2_step_loop_info(void* loop, int* n_phases, int* n_barriers, int* grid, int* total_vblocks);
+int nb2_step_loop_status(void* loop, void* stream, int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -97,7 +97,18 @@ _SIGNATURES = {
     "nb2_gather_sum": [_P, c_int, c_int, _P, _P, _P],
     "nb2_ensemble_step": [_P, c_int, _P, c_int, _P, _P, _P, _P, _P, c_double],
     "nb2_direct": [_P, c_int, _P, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P],
+    "nb2_step_loop_create": [POINTER(c_void_p)],
+    "nb2_step_loop_destroy": [_P],
+    "nb2_step_loop_finalize": [_P, c_int],
+    "nb2_step_loop_run": [_P, _P, c_int],
+    "nb2_step_loop_info": [_P, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)],
+    "nb2_step_loop_status": [_P, _P, POINTER(c_int)],
 }
+# a phase of the step loop takes (loop, barrier) + the arguments of the launch entry point without the stream
+for _name in ("timeupdate", "gather_sum", "direct", "ensemble_step", "gemv_block", "probes", "linearfilter",
+              "presentinput"):
+    _SIGNATURES["nb2_step_loop_add_" + _name] = [_P, c_int] + _SIGNATURES["nb2_" + _name][1:]
+del _name
 
 _lib = None
 
@@ -158,3 +169,13 @@ def check(status):
 def call(name, *args):
     """Call ``name`` through the C ABI and raise on a negative status."""
     return check(getattr(lib(), name)(*args))
+
+
+def phase(name, *args):
+    """``(loop, barrier) -> None`` that appends the launch ``nb2_<name>(stream, *args)`` as a
+    phase of a persistent step loop (``nb2_step_loop_add_<name>``, csrc/nb2_step_loop.cu)."""
+
+    def add(loop, barrier):
+        call("nb2_step_loop_add_" + name, loop, int(bool(barrier)), *args)
+
+    return add

@@ -32,6 +32,9 @@ UNITS = [
     ("nb2_fused.cu", ["-fmad=false"]),
     ("nb2_fused_stream.cu", ["-fmad=false"]),
     ("nb2_exchange.cu", []),
+    # the persistent step loop reads what other CTAs wrote earlier in the same launch: global loads in L2 only
+    ("nb2_step_loop.cu", ["-fmad=false", "-Xptxas", "-dlcm=cg"]),
+    ("nb2_step_loop_single.cu", ["-fmad=false"]),
 ]
 
 

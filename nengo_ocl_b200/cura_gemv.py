@@ -769,6 +769,7 @@ class gemv_prog:
                     n_launches=int(len(cta_units) > 0) + int(len(warp_units) > 0), name="cura_gemv.block_impl",
                     tag=self.tag, bw_per_call=bw_from_geometry(self.geometry, items),
                     flops_per_call=flops_from_geometry(self.geometry, items))
+        plan.phase = _capi.phase("gemv_block", *args)
         plan.full_args = (d_table, d_xstr, d_cta, d_warp, A, X, Y, Y_in)
         plan.gstructure = table
         plan.worklist = (cta_units, warp_units)

@@ -124,6 +124,7 @@ def plan_timeupdate(queue, step, time, dt):
         check(fn(stream, step_ptr, time_ptr, dt))
 
     plan = Plan(queue, launch, (1,), lsize=None, name="cl_timeupdate")
+    plan.phase = _capi.phase("timeupdate", step_ptr, time_ptr, dt)
     plan.full_args = (step.cl_buf, time.cl_buf)
     return plan
 
@@ -329,6 +330,8 @@ def plan_linearfilter(queue, X, Y, A, B, Xbuf, Ybuf, tag=None):
 
     plan = Plan(queue, launch, (lsize0, max(n, 1)), lsize=(lsize0, 1), n_launches=2 if uses_buf else 1,
                 name="cl_linearfilter", tag=tag)
+    if not uses_buf:
+        plan.phase = _capi.phase("linearfilter", *args)
     plan.full_args = (dev, X.cl_buf, Y.cl_buf, A.cl_buf, B.cl_buf, Xbuf.cl_buf, Ybuf.cl_buf, Xbufpos, Ybufpos)
     plan.tables = dict(tables, sizes=sizes, inds=inds)
     plan.Xbufpos, plan.Ybufpos = Xbufpos, Ybufpos
@@ -453,6 +456,8 @@ def plan_probes(queue, periods, X, Y, tag=None):
         check(fn(stream, *args))
 
     plan = Plan(queue, launch, (max_len, N), lsize=(max_len, 1), name="cl_probes", tag=tag)
+    if cl_arrive is None:
+        plan.phase = _capi.phase("probes", *args)
     plan.full_args = (cl_countdowns, cl_bufpositions, cl_periods, X, Y, cl_arrive)
     plan.cl_bufpositions = cl_bufpositions
     plan.cl_countdowns = cl_countdowns
@@ -493,6 +498,7 @@ def plan_direct(queue, code, init, input_names, inputs, output, tag=None):
         check(fn(stream, *args))
 
     plan = Plan(queue, launch, (max(N, 1),), lsize=None, name="cl_direct", tag=tag)
+    plan.phase = _capi.phase("direct", *args)
     plan.full_args = (prog, consts, inputs, output)
     plan.description = _describe(output)
     return plan
@@ -522,6 +528,7 @@ def plan_presentinput(queue, Y, t, signals, dt, pres_t=None, tag=None):
         check(fn(stream, *args))
 
     plan = Plan(queue, launch, (max_len, N), lsize=(max_len, 1), name="cl_presentinput", tag=tag)
+    plan.phase = _capi.phase("presentinput", *args)
     plan.full_args = (pres_t, Y, t, signals)
     return plan
 

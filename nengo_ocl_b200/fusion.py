@@ -601,6 +601,8 @@ def plan_fused_ensembles(sim, ops):
     plan = Plan(queue, launch, (256, max(len(large), 1) + (len(small) + 7) // 8), lsize=(256, 1),
                 n_launches=int(len(large) > 0) + int(len(small) > 0) + int(n_streamed > 0),
                 name="fused_ensemble_step", tag="%d ensembles" % len(members))
+    if not n_streamed:  # (the streamed kernel owns its CTAs for a whole step: no phase form)
+        plan.phase = _capi.phase("ensemble_step", *args)
     plan.full_args = (d_ens, d_terms, d_conns, d_small, d_large, d_records, d_ranges, status, data, xdesc)
     plan.fused_push = xdesc is not None
     plan.tables = dict(ens=ens, terms=terms, conns=conns, small=small, large=large, streamed=streamed,
@@ -704,6 +706,7 @@ def plan_gather_sums(sim, ops):
 
     plan = Plan(queue, launch, (256, max(len(blocks) * width // 256, 1)), lsize=(256, 1), name="gather_sum",
                 tag="%d signals" % len(ops))
+    plan.phase = _capi.phase("gather_sum", *args)
     plan.full_args = (d_blocks, d_srcs, data)
     plan.bw_per_call = n_bytes
     plan.description = "signals: %d; sources: %d" % (len(ops), len(srcs))

@@ -153,16 +153,123 @@ class _Graph:
             pass
 
 
+def phase_barriers(uses):
+    """Where a persistent step loop needs a grid-wide barrier.
+
+    ``uses``: per phase ``(reads, writes)``, two sets of hashable signal keys, in
+    step order; the list repeats every step.  Phase p needs a barrier before it
+    when it reads or writes something that a phase since the last barrier wrote,
+    or writes something one of them read (the phases of the previous step count:
+    the list is a ring).  Returns one bool per phase."""
+    uses = [(set(r), set(w)) for r, w in uses]
+    flags = [False] * len(uses)
+    read_acc, write_acc = set(), set()
+    quiet_laps = 0
+    # Replay the ring exactly as the kernel runs it (a flagged phase clears what has accumulated)
+    # and flag every conflict met, until two whole laps add nothing.
+    while quiet_laps < 2:
+        added = False
+        for i, (reads, writes) in enumerate(uses):
+            if not flags[i] and (write_acc & (reads | writes) or read_acc & writes):
+                flags[i] = added = True
+            if flags[i]:
+                read_acc, write_acc = set(), set()
+            read_acc |= reads
+            write_acc |= writes
+        quiet_laps = 0 if added else quiet_laps + 1
+    return flags
+
+
+class StepLoop:
+    """All plans of a step as phases of one persistent kernel (csrc/nb2_step_loop.cu):
+    ``run(stream, n)`` simulates n steps with one launch.  No counterpart in the
+    reference, which enqueues every kernel of every step (plan.py:137-149).
+
+    ``max_ctas=1`` selects the single-CTA form (CTA barriers, signals resident in one
+    multiprocessor's L1), which is what pays: measured on a B200, it takes the step of a
+    two-ensemble model well below the launch-per-plan cost, while the multi-CTA form
+    (grid-wide barriers, L2-only loads) is slower than replaying a captured graph for
+    models of hundreds of blocks.  ``build(..., auto=True)`` therefore returns a loop only
+    for models whose whole step is at most ``AUTO_MAX_BLOCKS`` blocks."""
+
+    AUTO_MAX_BLOCKS = 16
+
+    @classmethod
+    def build(cls, plans, barriers, max_ctas=0, auto=False):
+        loop = cls(plans, barriers)
+        if auto:
+            if loop.total_blocks > cls.AUTO_MAX_BLOCKS:
+                loop.close()
+                return None
+            max_ctas = 1
+        loop.finalize(max_ctas)
+        return loop
+
+    def __init__(self, plans, barriers):
+        handle = ctypes.c_void_p()
+        _capi.call("nb2_step_loop_create", ctypes.byref(handle))
+        self.handle = handle
+        self.grid = 0
+        try:
+            for plan, barrier in zip(plans, barriers):
+                plan.phase(handle, barrier)
+            self._info()
+        except Exception:
+            self.close()
+            raise
+
+    def _info(self):
+        a, b, c, d = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _capi.call("nb2_step_loop_info", self.handle, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c),
+                   ctypes.byref(d))
+        self.n_phases, self.n_barriers, self.grid, self.total_blocks = a.value, b.value, c.value, d.value
+
+    def finalize(self, max_ctas=0):
+        try:
+            _capi.call("nb2_step_loop_finalize", self.handle, int(max_ctas))
+            self._info()
+        except Exception:
+            self.close()
+            raise
+
+    def run(self, stream, n):
+        _capi.call("nb2_step_loop_run", self.handle, stream, int(n))
+
+    def status(self, stream):
+        st = ctypes.c_int()
+        _capi.call("nb2_step_loop_status", self.handle, stream, ctypes.byref(st))
+        return st.value
+
+    def close(self):
+        if self.handle is not None:
+            try:
+                _capi.lib().nb2_step_loop_destroy(self.handle)
+            except Exception:
+                pass
+            self.handle = None
+
+    def __del__(self):
+        self.close()
+
+
 class Plans:
     """Ordered plan list = one simulator step; replays it n times."""
 
-    def __init__(self, planlist, profiling, use_graph=True, unroll=1):
+    def __init__(self, planlist, profiling, use_graph=True, unroll=1, step_loop=False, max_ctas=0):
         self.plans = list(planlist)
         self.profiling = profiling
         self.use_graph = use_graph
         self.unroll = max(1, int(unroll))
         self._segments = None  # list of ("graph", _Graph, _Graph_unrolled) / ("python", plan)
         self.kernel_launches = 0  # device kernels issued so far (graph nodes count)
+        # persistent step loop (step_loop: False, True or "auto" = only where it pays): needs every
+        # plan to have a phase form and to declare the signals it touches
+        self.step_loop = None
+        if (step_loop and use_graph and not profiling and self.plans
+                and all(getattr(p, "phase", None) is not None and getattr(p, "signal_use", None) is not None
+                        for p in self.plans)):
+            self.step_loop = StepLoop.build(self.plans, phase_barriers([p.signal_use for p in self.plans]),
+                                            max_ctas, auto=(step_loop == "auto"))
 
     def __call__(self):
         return self.call_n_times(1)
@@ -190,6 +297,14 @@ class Plans:
     def invalidate(self):
         """Drop captured graphs (call after changing the plan list)."""
         self._segments = None
+        if self.step_loop is not None:
+            self.step_loop.close()
+            self.step_loop = None
+
+    def check_status(self):
+        """Raise if the step loop gave up a bounded barrier wait (synchronises the stream)."""
+        if self.step_loop is not None and self.step_loop.status(self.queue.stream) != 0:
+            raise RuntimeError("the persistent step loop gave up waiting at a grid barrier (NB2_ERR_TIMEOUT)")
 
     def call_n_times(self, n):
         self.enqueue_n_times(n)
@@ -267,6 +382,10 @@ class Plans:
                         q.finish()
                         p(profiling=self.profiling)
             self.kernel_launches += n * self.launches_per_step
+            return _Event(q)
+        if self.step_loop is not None:
+            self.step_loop.run(q.stream, n)
+            self.kernel_launches += 1
             return _Event(q)
         if self._segments is None:
             self._build_segments()

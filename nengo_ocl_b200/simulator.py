@@ -179,6 +179,11 @@ class Simulator:
     stream_inputs : bool
         Keep input tables (WhiteSignal) in pinned host memory and upload only the
         rows of the next batch of steps before it runs.
+    step_loop : bool, optional
+        Run all steps of a ``run_steps`` batch as one launch of the persistent step-loop kernel
+        instead of replaying a captured graph.  Default: only for models whose step is a handful
+        of thread blocks (one CTA then runs the whole model out of its L1).  ``"single"`` forces
+        that one-CTA form, ``True`` a grid as wide as the widest plan.
     """
 
     some_context = None
@@ -194,7 +199,7 @@ class Simulator:
 
     def __init__(self, network, dt=0.001, seed=None, model=None, context=None, n_prealloc_probes=32,
                  profiling=None, if_python_code="none", planner=greedy_planner, progress_bar=True, fuse=True,
-                 graph_unroll=8, stream_inputs=False, exchange=None):
+                 graph_unroll=8, stream_inputs=False, exchange=None, step_loop=None):
         self.closed = False
         self.model = None
         if context is None and Simulator.some_context is None:
@@ -309,12 +314,28 @@ class Simulator:
 
             groups = fuse_ensemble_groups(self, groups)
         for op_type, op_list in groups:
-            plans.extend(self._plan_op_group(op_type, op_list))
-        plans.extend(self._plan_probes())
+            group_plans = self._plan_op_group(op_type, op_list)
+            use = self._signal_use(op_list)
+            for plan in group_plans:  # (every plan of a group is charged with the whole group's signals)
+                plan.signal_use = use
+            plans.extend(group_plans)
+        probe_plans = self._plan_probes()
+        for plan in probe_plans:  # reads the probed signals; the rings and counters are its own
+            plan.signal_use = ({self.model.sig[p]["in"].base for p in self.model.probes}, {plan})
+        plans.extend(probe_plans)
         if self._exchange is not None:
             wait, push = self._exchange.plans()
             plans = wait + plans + push
-        self._plans = Plans(plans, self.profiling, unroll=graph_unroll)
+        # A model whose whole step is a handful of blocks runs n steps as ONE launch of a single-CTA
+        # persistent kernel (csrc/nb2_step_loop_single.cu); the others replay a captured graph.
+        # step_loop: None = that rule, True = always use the loop where every plan has a phase form
+        # ("single": on one CTA whatever the size), False = never.  NENGO_B200_STEP_LOOP=0 / 1 overrides the default.
+        if step_loop is None:
+            step_loop = {"0": False, "1": True}.get(os.environ.get("NENGO_B200_STEP_LOOP", ""), "auto")
+        if self._exchange is not None or stream_inputs:
+            step_loop = False
+        self._plans = Plans(plans, self.profiling, unroll=graph_unroll, step_loop=step_loop,
+                            max_ctas=1 if step_loop == "single" else int(os.environ.get("NENGO_B200_STEP_LOOP_CTAS", "0")))
         self._status_plans = [p for p in plans if getattr(p, "status", None) is not None]
         self.rng = None
         self._n_steps = 0
@@ -512,6 +533,7 @@ class Simulator:
             self._upload_inputs(B)
             self._plans.call_n_times(B)
             self._probe()
+            self._plans.check_status()
             for plan in self._status_plans:  # bounded waits inside the pipelined kernels
                 if int(plan.status.get()[0]) != 0:
                     raise RuntimeError("kernel %s gave up a bounded wait (NB2_ERR_TIMEOUT)" % plan.name)
@@ -552,6 +574,17 @@ class Simulator:
         self._max_steps_between_probes = self.n_prealloc_probes * int(min(periods))
         assert self._max_steps_between_probes >= 1
         return [self._cl_probe_plan]
+
+    @staticmethod
+    def _signal_use(ops):
+        """(base signals read, base signals written) by a group of operators."""
+        reads, writes = set(), set()
+        for op in ops:
+            reads.update(s.base for s in list(op.reads) + list(op.incs) + list(op.updates))
+            writes.update(s.base for s in list(op.sets) + list(op.incs) + list(op.updates))
+            for s in getattr(op, "internal", ()):  # signals a fused kernel may still store
+                writes.add(s.base)
+        return reads, writes
 
     def _plan_op_group(self, op_type, ops):
         return getattr(self, "_plan_" + op_type.__name__)(ops)

@@ -225,3 +225,21 @@ def test_member_reading_a_fused_output_is_not_fused():
     fused = {mem["neurons"].J for mem in members}
     assert a.sig_J in fused and b.sig_J not in fused
     assert not any(getattr(op, "J", None) is b.sig_J for op in consumed)
+
+
+def test_step_loop_barriers_follow_the_signal_dependencies():
+    """Grid barriers of the persistent step loop: one before every phase that touches what an
+    earlier phase since the last barrier wrote (or writes what it read), the previous step's
+    phases included."""
+    from nengo_ocl_b200.plan import phase_barriers
+
+    # clock | gather x <- f | ensembles x -> f (state v) | probes f -> ring
+    uses = [(set(), {"t"}), ({"f"}, {"x"}), ({"x", "v"}, {"f", "v"}), ({"f"}, {"ring"})]
+    assert phase_barriers(uses) == [False, False, True, True]
+    # the gather of the next step reads f while the probes only read it: no barrier at the step boundary,
+    # but a phase that overwrites what the last phase of the previous step read needs one
+    uses = [({"a"}, {"b"}), ({"b"}, {"c"}), ({"c"}, {"a"})]
+    assert phase_barriers(uses) == [True, True, True]
+    # independent phases that only rewrite their own outputs: one barrier per step keeps the steps apart
+    assert phase_barriers([(set(), {"a"}), (set(), {"b"})]) == [True, False]
+    assert phase_barriers([({"k"}, {"a"}), ({"k"}, {"b"}), ({"a", "b"}, {"c"})]) == [True, False, True]
