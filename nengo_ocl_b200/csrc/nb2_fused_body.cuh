@@ -12,7 +12,7 @@
 
 #define FUSED_THREADS 256
 #ifndef FUSED_MIN_BLOCKS
-#define FUSED_MIN_BLOCKS 3  // CTAs per SM the register budget is sized for
+#define FUSED_MIN_BLOCKS 4  // CTAs per SM the register budget is sized for (the populations left to these kernels are latency-bound)
 #endif
 #ifndef FUSED_MIN_BLOCKS_SMALL
 #define FUSED_MIN_BLOCKS_SMALL 4  // the warp-per-ensemble variant is latency-bound: more resident warps
@@ -22,6 +22,9 @@
 #define FUSED_MAX_X NB2_FUSED_MAX_INPUT      // total encoder columns per ensemble
 #define FUSED_SMALL_N NB2_FUSED_SMALL_NEURONS
 #define FUSED_CONN_STAGED 16  // connection-table rows per ensemble prefetched into shared memory
+#ifndef FUSED_PREFETCH_BYTES
+#define FUSED_PREFETCH_BYTES 4096  // decoder matrices up to this size are prefetched into L1
+#endif
 #define FUSED_BATCH 4         // neurons per thread whose loads are issued together
 
 template <bool NC> __device__ __forceinline__ float fused_ld(const float* p) { return NC ? __ldg(p) : *p; }
@@ -129,6 +132,17 @@ __device__ __forceinline__ void nb2_ensemble_step_body(void* smem, int vblock, i
   auto conn_row = [&](int i) -> const int* {
     return i < FUSED_CONN_STAGED ? s_conn + i * C_STRIDE : conn_rows + (size_t)i * C_STRIDE;
   };
+  // Small decoder matrices (the many one-row connections of a graph model) are asked into L1 now:
+  // they are needed only after the neuron update, whose latency then hides the fetch.
+  for (int k = 0; k < min(n_conn, FUSED_CONN_STAGED); ++k) {
+    const int* c = s_conn + k * C_STRIDE;
+    const int bytes = c[C_D] * n * 4;
+    if (bytes > FUSED_PREFETCH_BYTES) continue;
+    const char* base = reinterpret_cast<const char*>(data + c[C_W]);
+    for (int off = t * 128; off < bytes + 124; off += TPE * 128)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(base + min(off, bytes - 4)));
+    if (t == TPE - 1 && c[C_FILT] >= 0) asm volatile("prefetch.global.L1 [%0];" ::"l"(data + c[C_FILT]));
+  }
 
   // ---- phase 1: J = ((bias + enc_0 . x_0) + enc_1 . x_1) ... ; LIF ----
   if (active) {

@@ -41,7 +41,7 @@ __device__ __forceinline__ float gb_tile_value(const GemvBlockParams& p, const i
     const int xs = xst ? __ldg(&xst[k]) : 1;
     const float* x = p.X + __ldg(&g[0 * D + k]) + (ptrdiff_t)c0 * xs;
     if (xs == 1) {
-#pragma unroll 8
+#pragma unroll 16
       for (int c = j; c < len; c += 4) acc = bd_add(acc, bd_mul(gb_ld<NC>(a + c), gb_ld<NC>(x + c)));
     } else {
 #pragma unroll 4
