@@ -50,9 +50,11 @@ sys.path.insert(0, ROOT)
 
 FULL = dict(n_ensembles=4096, n_neurons=1024, dimensions=16)
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the fused kernel on the full-size
-# workload (4096 ensembles), from an ncu capture of this file's own default command; None for
-# other sizes (not captured)
-NCU_DRAM_BYTES_FULL_SIZE = None
+# workload (4096 ensembles): 516.99 MB read + 267.53 MB written, from a one-pass ncu capture of
+# `bench.py --steps 16 --warmup 3 --no-gemv --no-cpu --no-small --no-spmv` (profiles/); 0.95 of the
+# algorithmic bytes (a little of the write-back is still in L2 when the next launch reads it).
+# None for other sizes (not captured)
+NCU_DRAM_BYTES_FULL_SIZE = 784520000
 REPEATS = 5  # the timed region runs this many times; the median is reported
 WORKLOAD = "pes-learning 4096 ens x 1024 LIF x 16-d, PES lr 1e-4, lowpass 10 ms, dt 1 ms"
 

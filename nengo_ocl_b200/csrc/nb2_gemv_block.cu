@@ -13,10 +13,10 @@
 // row count <= 32, 0) mirror the reference's 32-row blocks.  Four lanes own the
 // four partial sums of one row of one tile and walk them in order; two shuffles
 // give the tile value.
-//  * nb2_gemv_block_cta_kernel: one CTA (8 warps) per unit.  The (8-row group,
+//  * CTA units (nb2_gemv_block_cta_body): one CTA (8 warps) per unit.  The (8-row group,
 //    tile) pairs of the unit are dealt to the warps; tile values meet in shared
 //    memory and one thread per row adds them in order.
-//  * nb2_gemv_block_warp_kernel: one warp per unit of at most 8 rows and a few
+//  * warp units (nb2_gemv_block_warp_body): one warp per unit of at most 8 rows and a few
 //    tiles (the many tiny products of a model: scalar gains, 1 x n decoders).
 // Matrices are read straight from global memory (these products are small and
 // L2-resident inside a model step; the HBM-bound products of a model run in the
@@ -24,15 +24,14 @@
 #include "nb2_gemv_block_body.cuh"
 #include "../../include/nengo_b200.h"
 
-__global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_cta_kernel(const GemvBlockParams p) {
+// One launch for both kinds of unit: the first n_cta blocks take a 32-row unit each, the blocks
+// after them eight warp units each.
+__global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_kernel(const GemvBlockParams pc, const GemvBlockParams pw,
+                                                                    int n_cta) {
   nb2_pdl_enter();
   __shared__ __align__(16) unsigned char smem[sizeof(GemvBlockSmem)];
-  nb2_gemv_block_cta_body<true>(smem, p, blockIdx.x);
-}
-
-__global__ void __launch_bounds__(GB_THREADS) nb2_gemv_block_warp_kernel(const GemvBlockParams p) {
-  nb2_pdl_enter();
-  nb2_gemv_block_warp_body<true>(p, blockIdx.x);
+  if ((int)blockIdx.x < n_cta) nb2_gemv_block_cta_body<true>(smem, pc, blockIdx.x);
+  else nb2_gemv_block_warp_body<true>(pw, blockIdx.x - n_cta);
 }
 
 extern "C" int nb2_gemv_block(void* stream, const int* gstructure, int gstride, int D, const int* xstrides,
@@ -47,19 +46,14 @@ extern "C" int nb2_gemv_block(void* stream, const int* gstructure, int gstride, 
   p.A = A; p.X = X; p.Yin = Yin; p.Y = Y;
   p.alpha = alpha; p.beta = beta; p.gamma = gamma;
   cudaStream_t s = nb2_stream(stream);
-  if (n_cta > 0) {
-    NB2_REQUIRE(cta_units != NULL, "cta_units");
-    p.worklist = reinterpret_cast<const int4*>(cta_units);
-    p.n_units = n_cta;
-    nb2_launch(nb2_gemv_block_cta_kernel, dim3(n_cta), dim3(GB_THREADS), 0, s, p);
-    NB2_LAUNCH_CHECK();
-  }
-  if (n_warp > 0) {
-    NB2_REQUIRE(warp_units != NULL, "warp_units");
-    p.worklist = reinterpret_cast<const int4*>(warp_units);
-    p.n_units = n_warp;
-    nb2_launch(nb2_gemv_block_warp_kernel, dim3((n_warp + GB_WARPS - 1) / GB_WARPS), dim3(GB_THREADS), 0, s, p);
-    NB2_LAUNCH_CHECK();
-  }
+  NB2_REQUIRE((n_cta == 0 || cta_units != NULL) && (n_warp == 0 || warp_units != NULL), "units");
+  GemvBlockParams pc = p, pw = p;
+  pc.worklist = reinterpret_cast<const int4*>(cta_units);
+  pc.n_units = n_cta;
+  pw.worklist = reinterpret_cast<const int4*>(warp_units);
+  pw.n_units = n_warp;
+  const int warp_blocks = (n_warp + GB_WARPS - 1) / GB_WARPS;
+  nb2_launch(nb2_gemv_block_kernel, dim3(n_cta + warp_blocks), dim3(GB_THREADS), 0, s, pc, pw, n_cta);
+  NB2_LAUNCH_CHECK();
   return NB2_OK;
 }

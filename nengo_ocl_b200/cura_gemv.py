@@ -766,7 +766,7 @@ class gemv_prog:
             check(fn(stream, *args))
 
         plan = Plan(queue, launch, (4, 32, n_tiles), (4, 32, 1),
-                    n_launches=int(len(cta_units) > 0) + int(len(warp_units) > 0), name="cura_gemv.block_impl",
+                    n_launches=1, name="cura_gemv.block_impl",
                     tag=self.tag, bw_per_call=bw_from_geometry(self.geometry, items),
                     flops_per_call=flops_from_geometry(self.geometry, items))
         plan.phase = _capi.phase("gemv_block", *args)

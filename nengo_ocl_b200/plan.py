@@ -153,21 +153,22 @@ class _Graph:
             pass
 
 
-def phase_barriers(uses):
+def phase_barriers(uses, ring=True):
     """Where a persistent step loop needs a grid-wide barrier.
 
     ``uses``: per phase ``(reads, writes)``, two sets of hashable signal keys, in
     step order; the list repeats every step.  Phase p needs a barrier before it
     when it reads or writes something that a phase since the last barrier wrote,
     or writes something one of them read (the phases of the previous step count:
-    the list is a ring).  Returns one bool per phase."""
+    the list is a ring, unless ``ring=False``: one pass per launch).  Returns one
+    bool per phase."""
     uses = [(set(r), set(w)) for r, w in uses]
     flags = [False] * len(uses)
     read_acc, write_acc = set(), set()
     quiet_laps = 0
-    # Replay the ring exactly as the kernel runs it (a flagged phase clears what has accumulated)
-    # and flag every conflict met, until two whole laps add nothing.
-    while quiet_laps < 2:
+    # Replay the list exactly as the kernel runs it (a flagged phase clears what has accumulated)
+    # and flag every conflict met; for a ring, until two whole laps add nothing.
+    while True:
         added = False
         for i, (reads, writes) in enumerate(uses):
             if not flags[i] and (write_acc & (reads | writes) or read_acc & writes):
@@ -177,6 +178,8 @@ def phase_barriers(uses):
             read_acc |= reads
             write_acc |= writes
         quiet_laps = 0 if added else quiet_laps + 1
+        if not ring or quiet_laps >= 2:
+            break
     return flags
 
 
@@ -252,16 +255,67 @@ class StepLoop:
         self.close()
 
 
+class PhaseGroup(Plan):
+    """Consecutive tiny plans (a clock update, a one-item node function, a few probes ...) as ONE
+    launch: the single-CTA step-loop kernel runs them as phases of one pass, with a CTA barrier
+    where one depends on another.  Each of them alone is a launch gap with almost no work."""
+
+    def __init__(self, queue, plans):
+        self.members = list(plans)
+        self.loop = StepLoop(self.members, phase_barriers([p.signal_use for p in self.members], ring=False))
+        self.loop.finalize(1)
+        loop = self.loop
+        Plan.__init__(self, queue, lambda stream: loop.run(stream, 1), (256,), n_launches=1, name="phase_group",
+                      tag=" + ".join(p.name for p in self.members))
+
+
+def phase_blocks(plan):
+    """Thread blocks of a plan's phase form (None: it has none)."""
+    if getattr(plan, "phase", None) is None or getattr(plan, "signal_use", None) is None:
+        return None
+    if getattr(plan, "_phase_blocks", None) is None:
+        probe = StepLoop([plan], [False])
+        plan._phase_blocks = probe.total_blocks
+        probe.close()
+    return plan._phase_blocks
+
+
+def group_tiny_plans(plans, max_blocks=4):
+    """Replace every run of two or more consecutive device plans whose phase forms add up to at
+    most ``max_blocks`` thread blocks by one ``PhaseGroup``."""
+    out, run, blocks = [], [], 0
+
+    def flush():
+        nonlocal run, blocks
+        out.extend([PhaseGroup(run[0].queue, run)] if len(run) >= 2 else run)
+        run, blocks = [], 0
+
+    for p in plans:
+        b = phase_blocks(p) if hasattr(p, "enqueue") else None
+        if b is None or b > max_blocks:
+            flush()
+            out.append(p)
+            continue
+        if blocks + b > max_blocks:
+            flush()
+        run.append(p)
+        blocks += b
+    flush()
+    return out
+
+
 class Plans:
     """Ordered plan list = one simulator step; replays it n times."""
 
-    def __init__(self, planlist, profiling, use_graph=True, unroll=1, step_loop=False, max_ctas=0):
+    def __init__(self, planlist, profiling, use_graph=True, unroll=1, step_loop=False, max_ctas=0, group_tiny=False):
         self.plans = list(planlist)
         self.profiling = profiling
         self.use_graph = use_graph
         self.unroll = max(1, int(unroll))
         self._segments = None  # list of ("graph", _Graph, _Graph_unrolled) / ("python", plan)
         self.kernel_launches = 0  # device kernels issued so far (graph nodes count)
+        self.group_tiny = bool(group_tiny)
+        self._launch_plans = None  # what a captured step launches: self.plans with tiny runs grouped
         # persistent step loop (step_loop: False, True or "auto" = only where it pays): needs every
         # plan to have a phase form and to declare the signals it touches
         self.step_loop = None
@@ -292,11 +346,13 @@ class Plans:
 
     @property
     def launches_per_step(self):
-        return sum(getattr(p, "n_launches", 0) for p in self.plans)
+        plans = self.plans if (self.profiling or not self.use_graph) else self.launch_plans()
+        return sum(getattr(p, "n_launches", 0) for p in plans)
 
     def invalidate(self):
         """Drop captured graphs (call after changing the plan list)."""
         self._segments = None
+        self._launch_plans = None
         if self.step_loop is not None:
             self.step_loop.close()
             self.step_loop = None
@@ -340,10 +396,16 @@ class Plans:
                 gc.enable()
         return _Graph(g.value)
 
+    def launch_plans(self):
+        """The plans a captured step launches (runs of tiny plans grouped into one launch each)."""
+        if self._launch_plans is None:
+            self._launch_plans = group_tiny_plans(self.plans) if self.group_tiny else list(self.plans)
+        return self._launch_plans
+
     def _build_segments(self):
         segments = []
         run = []
-        for p in self.plans:
+        for p in self.launch_plans():
             if hasattr(p, "enqueue"):
                 run.append(p)
             else:

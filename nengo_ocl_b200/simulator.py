@@ -335,6 +335,7 @@ class Simulator:
         if self._exchange is not None or stream_inputs:
             step_loop = False
         self._plans = Plans(plans, self.profiling, unroll=graph_unroll, step_loop=step_loop,
+                            group_tiny=os.environ.get("NENGO_B200_GROUP_TINY", "1") != "0",
                             max_ctas=1 if step_loop == "single" else int(os.environ.get("NENGO_B200_STEP_LOOP_CTAS", "0")))
         self._status_plans = [p for p in plans if getattr(p, "status", None) is not None]
         self.rng = None

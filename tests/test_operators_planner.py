@@ -243,3 +243,12 @@ def test_step_loop_barriers_follow_the_signal_dependencies():
     # independent phases that only rewrite their own outputs: one barrier per step keeps the steps apart
     assert phase_barriers([(set(), {"a"}), (set(), {"b"})]) == [True, False]
     assert phase_barriers([({"k"}, {"a"}), ({"k"}, {"b"}), ({"a", "b"}, {"c"})]) == [True, False, True]
+
+
+def test_phase_barriers_of_a_single_pass():
+    """A group of plans launched once per step is not a ring: only conflicts inside the pass count."""
+    from nengo_ocl_b200.plan import phase_barriers
+
+    uses = [(set(), {"t"}), ({"t"}, {"y"}), ({"q"}, {"z"})]
+    assert phase_barriers(uses, ring=False) == [False, True, False]
+    assert phase_barriers(uses, ring=True) == [True, True, False]

@@ -90,3 +90,22 @@ def test_models_without_a_phase_form_keep_the_graph_path():
     with Simulator(None, model=mdl, step_loop=True) as sim:
         assert sim._plans.step_loop is None
         sim.run_steps(5)
+
+
+def test_tiny_consecutive_plans_share_one_launch(monkeypatch):
+    """Graph path: the clock update and the one-item node function of the graph model are one
+    launch (a PhaseGroup), and the step is bit-identical to the ungrouped one."""
+    mdl = MODELS["watts_strogatz"]()
+    with Simulator(None, model=mdl, step_loop=False) as grouped:
+        names = [p.name for p in grouped._plans.launch_plans()]
+        assert "phase_group" in names and len(names) < len(grouped._plans)
+        assert grouped._plans.launches_per_step < sum(p.n_launches for p in grouped._plans)
+        grouped.run_steps(60)
+        monkeypatch.setenv("NENGO_B200_GROUP_TINY", "0")
+        with Simulator(None, model=mdl, step_loop=False) as plain:
+            assert len(plain._plans.launch_plans()) == len(plain._plans)
+            plain.run_steps(60)
+            for sig in stored_signals(grouped, mdl):
+                assert np.array_equal(np.asarray(grouped.signals[sig]), np.asarray(plain.signals[sig])), sig
+            for p in mdl.probes:
+                assert np.array_equal(grouped.data[p], plain.data[p])
