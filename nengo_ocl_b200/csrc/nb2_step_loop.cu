@@ -298,11 +298,13 @@ extern "C" int nb2_step_loop_finalize(void* loop, int max_ctas) {
   NB2_REQUIRE(!L->phases.empty() && L->phases.size() <= NB2_STEP_LOOP_MAX_PHASES, "number of phases");
   NB2_CUDA(cudaGetDevice(&L->device));
   L->smem = ((sizeof(LoopPool) + 15) & ~size_t(15)) + L->phases.size() * sizeof(StepPhase);
+  // the attribute belongs to the kernel, not to this loop: always ask for what the longest phase list needs
+  const size_t smem_max = ((sizeof(LoopPool) + 15) & ~size_t(15)) + NB2_STEP_LOOP_MAX_PHASES * sizeof(StepPhase);
   int widest = 1;
   for (const StepPhase& p : L->phases) widest = p.n_vblocks > widest ? p.n_vblocks : widest;
   if (widest == 1 || max_ctas == 1) {
     L->grid = 1;
-    NB2_CUDA(nb2_step_loop_single_prepare(L->smem));
+    NB2_CUDA(nb2_step_loop_single_prepare(smem_max));
   } else {
     int coop = 0, sms = 0;
     NB2_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, L->device));
@@ -311,7 +313,7 @@ extern "C" int nb2_step_loop_finalize(void* loop, int max_ctas) {
       nb2_set_error("the device does not support cooperative launches");
       return NB2_ERR_LIMIT;
     }
-    NB2_CUDA(cudaFuncSetAttribute(nb2_step_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L->smem));
+    NB2_CUDA(cudaFuncSetAttribute(nb2_step_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
     int per_sm = 0;
     NB2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nb2_step_loop_kernel, LOOP_THREADS, L->smem));
     NB2_REQUIRE(per_sm >= 1, "the step loop kernel does not fit on a multiprocessor");
