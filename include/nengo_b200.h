@@ -57,6 +57,8 @@ int nb2_device_sync(void);
 int nb2_event_create(void** event);
 int nb2_event_destroy(void* event);
 int nb2_event_record(void* event, void* stream);
+/* the work submitted to `stream` after this call waits for `event` (while capturing: a graph edge) */
+int nb2_stream_wait_event(void* stream, void* event);
 int nb2_event_sync(void* event);
 int nb2_event_elapsed_ms(void* start, void* stop, float* ms);
 /* Step-loop replay: Plans.call_n_times (plan.py:128-149) becomes a captured

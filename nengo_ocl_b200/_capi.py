@@ -61,6 +61,7 @@ _SIGNATURES = {
     "nb2_event_create": [POINTER(c_void_p)],
     "nb2_event_destroy": [_P],
     "nb2_event_record": [_P, _P],
+    "nb2_stream_wait_event": [_P, _P],
     "nb2_event_sync": [_P],
     "nb2_event_elapsed_ms": [_P, _P, POINTER(c_float)],
     "nb2_graph_begin": [_P],

@@ -159,6 +159,11 @@ int nb2_event_record(void* event, void* stream) {
   return NB2_OK;
 }
 
+int nb2_stream_wait_event(void* stream, void* event) {
+  NB2_CUDA(cudaStreamWaitEvent(nb2_stream(stream), (cudaEvent_t)event, 0));
+  return NB2_OK;
+}
+
 int nb2_event_sync(void* event) {
   NB2_CUDA(cudaEventSynchronize((cudaEvent_t)event));
   return NB2_OK;

@@ -267,6 +267,8 @@ class PhaseGroup(Plan):
         loop = self.loop
         Plan.__init__(self, queue, lambda stream: loop.run(stream, 1), (256,), n_launches=1, name="phase_group",
                       tag=" + ".join(p.name for p in self.members))
+        self.signal_use = (set().union(*[set(p.signal_use[0]) for p in self.members]),
+                           set().union(*[set(p.signal_use[1]) for p in self.members]))
 
 
 def phase_blocks(plan):
@@ -307,7 +309,8 @@ def group_tiny_plans(plans, max_blocks=4):
 class Plans:
     """Ordered plan list = one simulator step; replays it n times."""
 
-    def __init__(self, planlist, profiling, use_graph=True, unroll=1, step_loop=False, max_ctas=0, group_tiny=False):
+    def __init__(self, planlist, profiling, use_graph=True, unroll=1, step_loop=False, max_ctas=0, group_tiny=False,
+                 parallel=False):
         self.plans = list(planlist)
         self.profiling = profiling
         self.use_graph = use_graph
@@ -315,6 +318,8 @@ class Plans:
         self._segments = None  # list of ("graph", _Graph, _Graph_unrolled) / ("python", plan)
         self.kernel_launches = 0  # device kernels issued so far (graph nodes count)
         self.group_tiny = bool(group_tiny)
+        self.parallel = bool(parallel)  # capture independent plans as parallel graph branches
+        self._side_streams = None
         self._launch_plans = None  # what a captured step launches: self.plans with tiny runs grouped
         # persistent step loop (step_loop: False, True or "auto" = only where it pays): needs every
         # plan to have a phase form and to declare the signals it touches
@@ -357,6 +362,22 @@ class Plans:
             self.step_loop.close()
             self.step_loop = None
 
+    def close(self):
+        """Release the step loop and the side streams of the branch capture."""
+        self.invalidate()
+        for st in self._side_streams or []:
+            try:
+                _capi.lib().nb2_stream_destroy(st)
+            except Exception:
+                pass
+        self._side_streams = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
     def check_status(self):
         """Raise if the step loop gave up a bounded barrier wait (synchronises the stream)."""
         if self.step_loop is not None and self.step_loop.status(self.queue.stream) != 0:
@@ -372,7 +393,92 @@ class Plans:
                 p.update_profiling()
 
     # -- execution ----------------------------------------------------------
+    MAX_BRANCH_PLANS = 32  # longer plan lists are captured as one chain
+    N_SIDE_STREAMS = 3
+
     def _capture(self, plans, repeat):
+        if (self.parallel and 1 < len(plans) <= self.MAX_BRANCH_PLANS
+                and all(getattr(p, "signal_use", None) is not None for p in plans)):
+            return self._capture_branches(plans, repeat)
+        return self._capture_chain(plans, repeat)
+
+    def _capture_branches(self, plans, repeat):
+        """Capture ``repeat`` passes over ``plans`` as a graph whose edges are the signal
+        dependencies (read-after-write, write-after-write, write-after-read on base signals)
+        instead of the plan order: independent plans of a step, and of consecutive steps,
+        become parallel branches.  The reference's plans run strictly in order on one queue
+        (plan.py:85-91); the values are the same, only launch gaps overlap.  Built by stream
+        capture on a few side streams joined with events."""
+        q = self.queue
+        s0 = q.stream
+        if self._side_streams is None:
+            self._side_streams = []
+            for _ in range(self.N_SIDE_STREAMS):
+                st = ctypes.c_void_p()
+                _capi.call("nb2_stream_create", ctypes.byref(st))
+                self._side_streams.append(st)
+        streams = [s0] + self._side_streams
+        events = []
+
+        def new_event(stream):
+            e = ctypes.c_void_p()
+            _capi.call("nb2_event_create", ctypes.byref(e))
+            events.append(e)
+            _capi.call("nb2_event_record", e, stream)
+            return e
+
+        import gc
+
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            _capi.call("nb2_graph_begin", s0)
+            try:
+                fork = new_event(s0)
+                joined = {0}   # streams that are part of the capture
+                tail = {}      # stream index -> node index of its last launch
+                nodes = []     # (reads, writes, stream index, event)
+                for _ in range(repeat):
+                    for p in plans:
+                        reads, writes = set(p.signal_use[0]), set(p.signal_use[1])
+                        touched = reads | writes
+                        latest = {}  # stream index -> latest node on it that this plan must follow
+                        for i, (r, w, si, _e) in enumerate(nodes):
+                            if w & touched or r & writes:
+                                latest[si] = i
+                        # continue a stream whose last launch is a dependency; else an unused one; else the
+                        # stream whose last launch is oldest (one needless edge)
+                        cands = [si for si, i in latest.items() if tail.get(si) == i]
+                        if cands:
+                            si = max(cands, key=lambda c: latest[c])
+                        else:
+                            unused = [c for c in range(len(streams)) if c not in tail]
+                            si = unused[0] if unused else min(tail, key=tail.get)
+                        if si not in joined:
+                            _capi.call("nb2_stream_wait_event", streams[si], fork)
+                            joined.add(si)
+                        for sj, i in latest.items():
+                            if sj != si:
+                                _capi.call("nb2_stream_wait_event", streams[si], nodes[i][3])
+                        p.kern(streams[si])
+                        nodes.append((reads, writes, si, new_event(streams[si])))
+                        tail[si] = len(nodes) - 1
+                for si, i in tail.items():  # every branch ends in the origin stream
+                    if si != 0:
+                        _capi.call("nb2_stream_wait_event", s0, nodes[i][3])
+            except Exception:
+                _capi.lib().nb2_graph_abort(s0)
+                raise
+            g = ctypes.c_void_p()
+            _capi.call("nb2_graph_end", s0, ctypes.byref(g))
+        finally:
+            if gc_was_on:
+                gc.enable()
+            for e in events:
+                _capi.lib().nb2_event_destroy(e)
+        return _Graph(g.value)
+
+    def _capture_chain(self, plans, repeat):
         q = self.queue
         # No device array may be released while the stream is capturing (a free is not a
         # capturable call): keep the garbage collector out of the way until the capture ends.

@@ -336,6 +336,7 @@ class Simulator:
             step_loop = False
         self._plans = Plans(plans, self.profiling, unroll=graph_unroll, step_loop=step_loop,
                             group_tiny=os.environ.get("NENGO_B200_GROUP_TINY", "1") != "0",
+                            parallel=os.environ.get("NENGO_B200_PARALLEL_GRAPH", "1") != "0",
                             max_ctas=1 if step_loop == "single" else int(os.environ.get("NENGO_B200_STEP_LOOP_CTAS", "0")))
         self._status_plans = [p for p in plans if getattr(p, "status", None) is not None]
         self.rng = None
