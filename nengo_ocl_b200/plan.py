@@ -437,20 +437,22 @@ class Plans:
                 fork = new_event(s0)
                 joined = {0}   # streams that are part of the capture
                 tail = {}      # stream index -> node index of its last launch
-                nodes = []     # (reads, writes, stream index, event)
+                nodes = []     # (reads, writes, stream index, event, weight)
                 for _ in range(repeat):
                     for p in plans:
                         reads, writes = set(p.signal_use[0]), set(p.signal_use[1])
                         touched = reads | writes
                         latest = {}  # stream index -> latest node on it that this plan must follow
-                        for i, (r, w, si, _e) in enumerate(nodes):
+                        for i, (r, w, si, _e, _w) in enumerate(nodes):
                             if w & touched or r & writes:
                                 latest[si] = i
-                        # continue a stream whose last launch is a dependency; else an unused one; else the
-                        # stream whose last launch is oldest (one needless edge)
+                        # continue a stream whose last launch is a dependency -- the heaviest one, which
+                        # finishes last: only the edge inside a stream can be a programmatic one, whose
+                        # launch latency overlaps the predecessor; else an unused stream; else the stream
+                        # whose last launch is oldest (one needless edge)
                         cands = [si for si, i in latest.items() if tail.get(si) == i]
                         if cands:
-                            si = max(cands, key=lambda c: latest[c])
+                            si = max(cands, key=lambda c: (nodes[latest[c]][4], latest[c]))
                         else:
                             unused = [c for c in range(len(streams)) if c not in tail]
                             si = unused[0] if unused else min(tail, key=tail.get)
@@ -461,7 +463,7 @@ class Plans:
                             if sj != si:
                                 _capi.call("nb2_stream_wait_event", streams[si], nodes[i][3])
                         p.kern(streams[si])
-                        nodes.append((reads, writes, si, new_event(streams[si])))
+                        nodes.append((reads, writes, si, new_event(streams[si]), self._weight(p)))
                         tail[si] = len(nodes) - 1
                 for si, i in tail.items():  # every branch ends in the origin stream
                     if si != 0:
@@ -477,6 +479,17 @@ class Plans:
             for e in events:
                 _capi.lib().nb2_event_destroy(e)
         return _Graph(g.value)
+
+    @staticmethod
+    def _weight(plan):
+        """Rough size of a plan (thread blocks), to tell the long branch from the short ones."""
+        blocks = getattr(plan, "_phase_blocks", None)
+        if blocks is None:
+            blocks = 1
+            for g in getattr(plan, "gsize", (1,)):
+                blocks *= int(g)
+            blocks = max(1, blocks // 256)
+        return blocks
 
     def _capture_chain(self, plans, repeat):
         q = self.queue
