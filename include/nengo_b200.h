@@ -225,6 +225,32 @@ int nb2_presentinput(void* stream, int n_items, int block_size, const float* pre
                      const float* T, const int* Sshape0s, const int* Sstarts, const int* Sstride0s,
                      const float* S);
 
+/* plan_whitenoise (:1573-1675), with a counter-based generator (Philox4x32-10)
+ * in place of the reference's per-work-item RANLUX states (create_rngs /
+ * init_rngs, :1486-1532): element e of item k at a step is word e % 4 of
+ * philox(counter = (step, e / 4, 0, 0), key = seeds[2k], seeds[2k+1]); the step
+ * is read from T[Tstarts[k]].  enums[k]: 0 uniform (params[2k] = low, [2k+1] =
+ * high), 1 gaussian (mean, std); scales[k]: multiply by 1/sqrt(dt); incs[k]: add
+ * to Y instead of overwriting it.  The random stream differs from RANLUX; what
+ * is done with a sample does not. */
+int nb2_whitenoise(void* stream, int n_items, int max_len, const int* shape0s, const int* Ystarts, float* Y,
+                   const int* Tstarts, const float* T, const int* enums, const float* params, const int* scales,
+                   const int* incs, const unsigned* seeds, double dt);
+
+/* plan_conv2d (:1762-1969) on one image: y[k,i,j] = sum over c, ii, jj (in that
+ * order, from zero) of filter * x[c, i*sti - pi + ii, j*stj - pj + jj], zero
+ * outside the image; the result is stored (inc == 0, the reference kernel) or
+ * added to y (inc != 0).  conv != 0: shared filters laid out
+ * [si][sj][nc][nf]; conv == 0 (local filtering): [nf][nc][si][sj][nyi][nyj].
+ * channels_last selects [rows][cols][channels] against [channels][rows][cols]
+ * for x and y.  Biases are not supported (the reference asserts them absent). */
+int nb2_conv2d(void* stream, const float* x, const float* filters, float* y, int nc, int nxi, int nxj, int nf,
+               int nyi, int nyj, int si, int sj, int sti, int stj, int pi, int pj, int channels_last, int conv, int inc);
+/* plan_pool2d (:1972-2079): average over the part of each si x sj window (stride
+ * sti, stj) that lies inside the image; x [nc][nxi][nxj], y [nc][nyi][nyj]. */
+int nb2_pool2d(void* stream, const float* x, float* y, int nc, int nyi, int nyj, int nxi, int nxj, int si, int sj,
+               int sti, int stj);
+
 /* Reset-then-accumulate in one launch: the reference runs plan_reset (:147-214)
  * and then one plan_copy(inc) (:217-304) per group of non-overlapping targets.
  * blocks [n_blocks][4] = {dst start, elements (<= 256), first source, n sources};

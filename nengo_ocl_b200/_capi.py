@@ -96,6 +96,9 @@ _SIGNATURES = {
     "nb2_exchange_wait": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_double],
     "nb2_exchange_push": [_P, _P, _P, _P, _P, c_int, c_int, c_int],
     "nb2_gather_sum": [_P, c_int, c_int, _P, _P, _P],
+    "nb2_whitenoise": [_P, c_int, c_int] + [_P] * 10 + [c_double],
+    "nb2_conv2d": [_P, _P, _P, _P] + [c_int] * 15,
+    "nb2_pool2d": [_P, _P, _P] + [c_int] * 9,
     "nb2_ensemble_step": [_P, c_int, _P, c_int, _P, _P, _P, _P, _P, c_double],
     "nb2_direct": [_P, c_int, _P, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P],
     "nb2_step_loop_create": [POINTER(c_void_p)],

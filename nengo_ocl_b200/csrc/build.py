@@ -29,6 +29,8 @@ UNITS = [
     ("nb2_elementwise.cu", ["-fmad=false"]),
     ("nb2_neurons.cu", ["-fmad=false"]),
     ("nb2_direct.cu", ["-fmad=false"]),
+    ("nb2_whitenoise.cu", ["-fmad=false"]),
+    ("nb2_conv.cu", ["-fmad=false"]),
     ("nb2_fused.cu", ["-fmad=false"]),
     ("nb2_fused_stream.cu", ["-fmad=false"]),
     ("nb2_exchange.cu", []),

@@ -504,6 +504,143 @@ def plan_direct(queue, code, init, input_names, inputs, output, tag=None):
     return plan
 
 
+# ---- convolution and pooling on one image ----------------------------------------------
+def _contiguous_item(ary):
+    assert len(ary.shape) in (1, 2)
+    assert ary.strides[-1] == ary.dtype.itemsize
+    if len(ary.shape) == 2:
+        assert ary.strides[0] == ary.dtype.itemsize * ary.shape[1]
+
+
+def plan_conv2d(queue, X, Y, filters, shape_in, shape_out, kernel_shape, conv=True, biases=None, padding=(0, 0),
+                strides=(1, 1), channels_last=True, tag=None, transposed=False, inc=False):
+    """``Y = conv(X, filters)`` (``inc``: ``Y +=``) on one image (reference: plan_conv2d, clra_nonlinearities.py:1762-1969).
+
+    ``X``, ``Y``, ``filters``: single device items (``CUDARaggedArray.getitem_device``), contiguous.
+    ``filters``: (size_i, size_j, channels, n_filters) when ``conv``; for local filtering
+    (``conv=False``) (n_filters, channels, size_i, size_j, rows_out, cols_out).  ``padding``:
+    "valid", "same" or a pair."""
+    assert biases is None, "Not tested with biases (strides may be wrong)"
+    assert not transposed
+    for ary in (X, Y, filters):
+        _contiguous_item(ary)
+        assert ary.ctype == Y.ctype
+    si, sj = (int(v) for v in kernel_shape)
+    sti, stj = (int(v) for v in strides)
+    if channels_last:
+        (nxi, nxj, nc), (nyi, nyj, nf) = shape_in, shape_out
+    else:
+        (nc, nxi, nxj), (nf, nyi, nyj) = shape_in, shape_out
+    if padding == "valid":
+        pi, pj = 0, 0
+    elif padding == "same":
+        pi, pj = (si - 1) // 2, (sj - 1) // 2
+    elif isinstance(padding, (tuple, list)) and len(padding) == 2:
+        pi, pj = padding
+    else:
+        raise ValueError("Unsupported padding (must be 'same', 'valid', or 2-tuple)")
+    assert X.size == nc * nxi * nxj and Y.size == nf * nyi * nyj
+    assert filters.size == (si * sj * nc * nf if conv else nf * nc * si * sj * nyi * nyj)
+    fn, check = _capi.lib().nb2_conv2d, _capi.check
+    args = (X.ptr, filters.ptr, Y.ptr, int(nc), int(nxi), int(nxj), int(nf), int(nyi), int(nyj), si, sj, sti, stj,
+            int(pi), int(pj), int(bool(channels_last)), int(bool(conv)), int(bool(inc)))
+
+    def launch(stream):
+        check(fn(stream, *args))
+
+    plan = Plan(queue, launch, (int(nyj), int(nyi), int(nf)), lsize=None, name="cl_conv2d", tag=tag)
+    plan.full_args = (X, filters, Y)
+    plan.flops_per_call = 2 * nyi * nyj * nf * nc * si * sj
+    plan.bw_per_call = X.nbytes + filters.nbytes + Y.nbytes
+    plan.description = "shape_in=%s, shape_out=%s, kernel=%s, conv=%s" % (shape_in, shape_out, kernel_shape, conv)
+    return plan
+
+
+def plan_pool2d(queue, X, Y, shape, pool_size, strides, tag=None):
+    """Average pooling of one (channels, rows, cols) image (reference: plan_pool2d, :1972-2079);
+    ``shape`` = (channels, rows_out, cols_out, rows_in, cols_in)."""
+    for ary in (X, Y):
+        _contiguous_item(ary)
+    assert X.ctype == Y.ctype
+    nc, nyi, nyj, nxi, nxj = (int(v) for v in shape)
+    si, sj = (int(v) for v in pool_size)
+    sti, stj = (int(v) for v in strides)
+    assert X.size == nc * nxi * nxj and Y.size == nc * nyi * nyj
+    fn, check = _capi.lib().nb2_pool2d, _capi.check
+    args = (X.ptr, Y.ptr, nc, nyi, nyj, nxi, nxj, si, sj, sti, stj)
+
+    def launch(stream):
+        check(fn(stream, *args))
+
+    plan = Plan(queue, launch, (nyj, nyi, nc), lsize=None, name="cl_pool2d", tag=tag)
+    plan.full_args = (X, Y)
+    plan.flops_per_call = X.size
+    plan.bw_per_call = X.nbytes + Y.nbytes
+    return plan
+
+
+# ---- white noise ---------------------------------------------------------------------
+def create_rngs(queue, n):
+    """Generator "states" of n noise processes.  The reference allocates up to 32 RANLUX states
+    of 28 words per process (clra_nonlinearities.py:1486-1493); the counter-based Philox
+    generator used here has no state, only a 64-bit key per process: an (n, 2) uint32 array."""
+    return to_device(queue, np.zeros((n, 2), dtype=np.uint32).view(np.int32))
+
+
+def init_rngs(queue, rngs, seeds):
+    """Write the processes' seeds as Philox keys (reference: init_rngs, :1499-1532)."""
+    seeds = [int(s) for s in seeds]
+    assert len(seeds) == rngs.shape[0]
+    keys = np.array([[s & 0xFFFFFFFF, (s >> 32) & 0xFFFFFFFF] for s in seeds], dtype=np.uint32)
+    rngs.set(keys.view(np.int32))
+
+
+_dist_enums = {"Uniform": 0, "Gaussian": 1}
+
+
+def get_dist_enums_params(dists):
+    """(enums, params) ragged arrays of a list of distributions (:1571-1574): Uniform -> 0,
+    (low, high); Gaussian -> 1, (mean, std)."""
+    from nengo_ocl_b200.raggedarray import RaggedArray
+
+    enums = [np.array([_dist_enums[type(d).__name__]]) for d in dists]
+    params = [np.array([d.low, d.high] if type(d).__name__ == "Uniform" else [d.mean, d.std], dtype=np.float32)
+              for d in dists]
+    return RaggedArray(enums, dtype=np.int32), RaggedArray(params, dtype=np.float32)
+
+
+def plan_whitenoise(queue, Y, dist_enums, dist_params, scale, inc, dt, rngs, t, tag=None):
+    """``Y[k] (+)= sample of dist k [* 1/sqrt(dt)]`` every step (reference: plan_whitenoise,
+    :1577-1675).  ``rngs``: the Philox keys from ``create_rngs`` / ``init_rngs``; ``t``: the
+    step-counter signal, one (view of the) item per process, which makes the stream a function of
+    (seed, step, element) alone.  ``scale`` / ``inc``: int32 device arrays as in the reference."""
+    N = len(Y)
+    assert N == len(dist_enums) == len(dist_params) == len(t) == scale.size == inc.size == rngs.shape[0]
+    assert dist_enums.ctype == "int"
+    for arr in [Y, dist_enums, dist_params]:
+        assert (arr.shape1s == 1).all()
+        assert (arr.stride0s == 1).all()
+        assert (arr.stride1s == 1).all()
+    assert (dist_enums.shape0s == 1).all() and (dist_params.shape0s == 2).all()
+    assert (t.shape0s == 1).all() and (t.shape1s == 1).all()
+    # one enum and two parameters per item, packed in item order
+    enums = to_device(queue, np.array([int(dist_enums[k][0, 0]) for k in range(N)], dtype=np.int32))
+    params = to_device(queue, np.array([np.asarray(dist_params[k]).reshape(2) for k in range(N)], dtype=np.float32))
+    max_len = int(max(Y.shape0s))
+    fn, check = _capi.lib().nb2_whitenoise, _capi.check
+    args = (N, max_len, Y.cl_shape0s.ptr, Y.cl_starts.ptr, Y.cl_buf.ptr, t.cl_starts.ptr, t.cl_buf.ptr, enums.ptr,
+            params.ptr, scale.ptr, inc.ptr, rngs.ptr, float(dt))
+
+    def launch(stream):
+        check(fn(stream, *args))
+
+    plan = Plan(queue, launch, (min(max_len, 256), N), lsize=(min(max_len, 256), 1), name="cl_whitenoise", tag=tag)
+    plan.full_args = (Y, t, enums, params, scale, inc, rngs)
+    plan.bw_per_call = int(Y.nbytes)
+    plan.description = _describe(Y)
+    return plan
+
+
 def plan_presentinput(queue, Y, t, signals, dt, pres_t=None, tag=None):
     """``Y[k] = signals[k][ti]`` with ``ti = step % nt`` or the presentation-time form."""
     N = len(Y)

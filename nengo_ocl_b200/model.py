@@ -75,7 +75,10 @@ class Signal:
 
     @property
     def size(self):
-        return int(np.prod(self.shape)) if self.shape else 1
+        n = 1
+        for v in self.shape:  # (a plain loop: this is called a million times while a large model is planned)
+            n *= int(v)
+        return n
 
     @property
     def initial_value(self):
@@ -229,6 +232,38 @@ class ElementwiseInc(Operator):
         self.A, self.X, self.Y = A, X, Y
         self.incs = [Y]
         self.reads = [A, X]
+
+
+class Convolution:
+    """Geometry of a convolutional transform (what nengo's ``Convolution`` transform carries):
+    ``input_shape`` / ``output_shape`` are (rows, cols, channels) when ``channels_last`` else
+    (channels, rows, cols); 1-D convolutions give (cols, channels) / (channels, cols)."""
+
+    def __init__(self, n_filters, input_shape, kernel_size=(3, 3), strides=(1, 1), padding="valid",
+                 channels_last=True):
+        self.n_filters, self.channels_last = int(n_filters), bool(channels_last)
+        self.kernel_size = tuple(int(k) for k in kernel_size)
+        self.strides = tuple(int(s) for s in strides)
+        self.padding = padding
+        self.input_shape = tuple(int(v) for v in input_shape)
+        self.dimensions = len(self.kernel_size)
+        spatial = self.input_shape[:-1] if channels_last else self.input_shape[1:]
+        out = []
+        for n, k, st in zip(spatial, self.kernel_size, self.strides):
+            out.append(-(-n // st) if padding.lower() == "same" else (n - k) // st + 1)
+        self.output_shape = tuple(out) + (self.n_filters,) if channels_last else (self.n_filters,) + tuple(out)
+        self.n_channels = self.input_shape[-1] if channels_last else self.input_shape[0]
+        self.kernel_shape = self.kernel_size + (self.n_channels, self.n_filters)
+
+
+class ConvInc(Operator):
+    """``Y += convolution(X, W)`` with W of shape kernel_size + (channels, filters)."""
+
+    def __init__(self, W, X, Y, conv, tag=None):
+        super().__init__(tag)
+        self.W, self.X, self.Y, self.conv = W, X, Y, conv
+        self.reads = [W, X]
+        self.incs = [Y]
 
 
 class SimNeurons(Operator):
@@ -439,6 +474,25 @@ class WhiteSignal(Process):
         power = np.sqrt(np.mean(sig ** 2, axis=0, keepdims=True))
         power[power == 0] = 1
         self.signal = (sig * (self.rms / power)).astype(np.float64)  # (n_steps, size_out)
+
+
+class Uniform:
+    def __init__(self, low, high):
+        self.low, self.high = float(low), float(high)
+
+
+class Gaussian:
+    def __init__(self, mean, std):
+        self.mean, self.std = float(mean), float(std)
+
+
+class WhiteNoise(Process):
+    """Independent samples of ``dist`` every step; ``scale`` multiplies them by
+    1/sqrt(dt) so that the noise power does not depend on dt (simulator.py:1245-1258)."""
+
+    def __init__(self, dist=None, scale=True, seed=None):
+        self.dist = Gaussian(0.0, 1.0) if dist is None else dist
+        self.scale, self.seed = bool(scale), seed
 
 
 # ---- probes and the model container -----------------------------------------

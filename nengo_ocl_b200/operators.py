@@ -204,6 +204,13 @@ def remove_zero_incs(operators):
     """Drop DotInc / ElementwiseInc / Copy ops whose input is known to be zero
     (only ever reset to 0, or a constant all-zero signal that nothing writes)."""
     sets, incs, _, updates = signal_io_dicts(operators)
+    writers_of = {}  # base -> its writers (looked up once per base: a graph model reads one base thousands of times)
+
+    def writers_list(base):
+        if base not in writers_of:
+            writers_of[base] = sets[base] + incs[base] + updates[base]
+        return writers_of[base]
+
     kept = []
     for op in operators:
         if type(op).__name__ not in ("DotInc", "ElementwiseInc", "Copy", "ConvInc"):
@@ -213,7 +220,7 @@ def remove_zero_incs(operators):
         for src in op.reads:
             if src.name.startswith("<Node"):
                 continue  # node outputs may change at run time
-            writers = sets[src.base] + incs[src.base] + updates[src.base]
+            writers = writers_list(src.base)
             only_zero_reset = (len(writers) == 1 and type(writers[0]).__name__ == "Reset"
                                and np.all(writers[0].value == 0))
             constant_zero = len(writers) == 0 and np.all(np.asarray(src.initial_value) == 0)

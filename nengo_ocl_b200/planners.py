@@ -8,6 +8,7 @@ instances whose written views do not overlap, and emit ``(type, [ops])``.
 sets -> incs -> reads -> updates.
 """
 
+import bisect
 from collections import defaultdict
 
 
@@ -91,6 +92,36 @@ def _dependency_graph_fast(operators):
     return {op: {operators[j] for j in edges[i]} for i, op in enumerate(operators)}
 
 
+def _extent(sig):
+    """[lo, hi) element range of a signal inside its base (what ``Signal.may_share_memory`` compares)."""
+    lo = sig.elemoffset
+    return lo, lo + sum((n - 1) * abs(st) for n, st in zip(sig.shape, sig.elemstrides)) + 1
+
+
+class _Extents:
+    """Element ranges already written in one base signal: ``overlaps`` in O(log n) (the plain
+    pairwise test is quadratic in the thousands of slices that a graph model copies into one
+    signal).  Ranges are kept sorted by start; as long as they are pairwise disjoint -- always,
+    unless one operator writes overlapping views itself -- only the last range that starts before
+    ``hi`` can overlap [lo, hi)."""
+
+    def __init__(self):
+        self.los, self.his, self.disjoint = [], [], True
+
+    def overlaps(self, lo, hi):
+        if not self.disjoint:
+            return any(l < hi and lo < h for l, h in zip(self.los, self.his))
+        k = bisect.bisect_left(self.los, hi)  # ranges [0, k) start before hi
+        return k > 0 and self.his[k - 1] > lo
+
+    def add(self, lo, hi):
+        if self.disjoint and self.overlaps(lo, hi):
+            self.disjoint = False
+        k = bisect.bisect_right(self.los, lo)
+        self.los.insert(k, lo)
+        self.his.insert(k, hi)
+
+
 def greedy_planner(operators, dependency_graph=_dependency_graph_fast):
     """Group operators by type in a dependency-respecting order."""
     edges = dependency_graph(operators)
@@ -125,12 +156,12 @@ def greedy_planner(operators, dependency_graph=_dependency_graph_fast):
                 chosen_type = t
         candidates = available[chosen_type]
 
-        written = {"sets": defaultdict(list), "incs": defaultdict(list), "updates": defaultdict(list)}
+        written = {"sets": defaultdict(_Extents), "incs": defaultdict(_Extents), "updates": defaultdict(_Extents)}
 
         def overlaps(op):
             for kind in ("sets", "incs", "updates"):
                 for s in getattr(op, kind):
-                    if any(s.may_share_memory(s2) for s2 in written[kind][s.base]):
+                    if written[kind][s.base].overlaps(*_extent(s)):
                         return True
             return False
 
@@ -143,7 +174,7 @@ def greedy_planner(operators, dependency_graph=_dependency_graph_fast):
             chosen.append(op)
             for kind in ("sets", "incs", "updates"):
                 for s in getattr(op, kind):
-                    written[kind][s.base].append(s)
+                    written[kind][s.base].add(*_extent(s))
         assert chosen
         schedule.append((chosen_type, chosen))
 

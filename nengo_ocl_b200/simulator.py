@@ -929,6 +929,53 @@ class Simulator:
                 self._device_state_to_reset.append((p.Ybufpos, np.zeros(p.Ybufpos.size, np.int32)))
         return plans
 
+    @staticmethod
+    def _conv_geometry(conv):
+        """(shape_in, shape_out, kernel_shape, strides) of a convolution as a 2-D one: a 1-D
+        convolution gets a row dimension of one (reference simulator.py:1298-1313)."""
+        assert conv.dimensions in (1, 2)
+        shape_in, shape_out = tuple(conv.input_shape), tuple(conv.output_shape)
+        kernel_shape, strides = tuple(conv.kernel_size), tuple(conv.strides)
+        if conv.dimensions == 1:
+            assert len(shape_in) == len(shape_out) == 2 and len(kernel_shape) == len(strides) == 1
+            kernel_shape, strides = (1,) + kernel_shape, (1,) + strides
+            if conv.channels_last:
+                shape_in, shape_out = (1,) + shape_in, (1,) + shape_out
+            else:
+                shape_in, shape_out = (shape_in[0], 1, shape_in[1]), (shape_out[0], 1, shape_out[1])
+        return shape_in, shape_out, kernel_shape, strides
+
+    def _plan_ConvInc(self, ops):
+        """One plan per operator (reference simulator.py:1290-1331); the result is added to Y."""
+        from nengo_ocl_b200.cura_nonlinearities import plan_conv2d
+
+        plans = []
+        for op in ops:
+            shape_in, shape_out, kernel_shape, strides = self._conv_geometry(op.conv)
+            padding = op.conv.padding.lower() if isinstance(op.conv.padding, str) else op.conv.padding
+            plans.append(plan_conv2d(
+                self.queue, X=self.all_data.getitem_device(self.sidx[op.X]),
+                Y=self.all_data.getitem_device(self.sidx[op.Y]), filters=self.all_data.getitem_device(self.sidx[op.W]),
+                biases=None, shape_in=shape_in, shape_out=shape_out, kernel_shape=kernel_shape, padding=padding,
+                strides=strides, channels_last=op.conv.channels_last, conv=True, inc=True))
+        return plans
+
+    def _plan_WhiteNoise(self, ops):
+        """simulator.py:1245-1258; seeds not given are drawn from the simulator's generator."""
+        from nengo_ocl_b200.cura_nonlinearities import create_rngs, get_dist_enums_params, init_rngs, plan_whitenoise
+
+        assert all(op.input is None for op in ops)
+        seeds = [op.process.seed if op.process.seed is not None else self.rng.randint(2 ** 31 - 1) for op in ops]
+        rngs = create_rngs(self.queue, len(ops))
+        init_rngs(self.queue, rngs, seeds)
+        Y = self.all_data[[self.sidx[op.output] for op in ops]]
+        t = self.all_data[[self.sidx[self.model.step] for _ in ops]]
+        scale = to_device(self.queue, np.array([op.process.scale for op in ops], dtype=np.int32))
+        inc = to_device(self.queue, np.array([op.mode == "inc" for op in ops], dtype=np.int32))
+        enums, params = get_dist_enums_params([op.process.dist for op in ops])
+        enums, params = CUDARaggedArray(self.queue, enums), CUDARaggedArray(self.queue, params)
+        return [plan_whitenoise(self.queue, Y, enums, params, scale, inc, self.model.dt, rngs, t)]
+
     def _plan_WhiteSignal(self, ops):
         Y = self.all_data[[self.sidx[op.output] for op in ops]]
         t = self.all_data[[self.sidx[self.model.step] for _ in ops]]

@@ -520,3 +520,53 @@ def pes_learning_shard(seed=3, n_ensembles=4096, rank=0, world=1, n_neurons=1024
                          targets=targets, exchange=exchange, segment=(lo * dimensions, n_local * dimensions),
                          rank=rank, world=world)
     return nb.model
+
+
+def white_noise_model(seed=21, n=300):
+    """Two white-noise processes: a scaled Gaussian set into a signal with a lowpass behind it, and an
+    unscaled uniform one incremented into a signal (a random walk).  Seeds are explicit, so the CPU
+    oracle draws the same Philox stream."""
+    mdl = m.Model(dt=0.001)
+    a = m.Signal(np.zeros(n), name="noise")
+    b = m.Signal(np.ones(7), name="walk")
+    fa = m.Signal(np.zeros(n), name="noise.filtered")
+    gauss = m.WhiteNoise(m.Gaussian(0.1, 0.5), scale=True, seed=seed)
+    unif = m.WhiteNoise(m.Uniform(-1, 1), scale=False, seed=(seed + 1) | (7 << 32))
+    mdl.add_op(m.SimProcess(gauss, None, a, mdl.step, mode="set"))
+    mdl.add_op(m.SimProcess(unif, None, b, mdl.step, mode="inc"))
+    mdl.add_op(m.SimProcess(m.Lowpass(0.01), a, fa, mdl.step, mode="update"))
+    probes = [mdl.add_probe(fa, label="noise.filtered"), mdl.add_probe(b, label="walk")]
+    mdl.info = dict(probes=probes, noise=a, walk=b, seeds=(gauss.seed, unif.seed))
+    return mdl
+
+
+def convolution_model(seed=31, channels_last=True, one_d=False):
+    """An image signal (a sine pattern that moves with time, from a node function) through a strided
+    "same" convolution into a rate layer, then a "valid" convolution of that layer's output: the
+    operators a nengo Convolution transform builds (Reset, ConvInc, SimNeurons)."""
+    rng = np.random.RandomState(seed)
+    mdl = m.Model(dt=0.001)
+    if one_d:
+        shape_in, k1, st1, k2 = ((16, 2) if channels_last else (2, 16)), (3,), (2,), (2,)
+    else:
+        shape_in, k1, st1, k2 = ((9, 8, 2) if channels_last else (2, 9, 8)), (3, 3), (2, 1), (2, 3)
+    conv1 = m.Convolution(5, shape_in, kernel_size=k1, strides=st1, padding="same", channels_last=channels_last)
+    conv2 = m.Convolution(3, conv1.output_shape, kernel_size=k2, strides=(1,) * len(k2), padding="valid",
+                          channels_last=channels_last)
+    n_in, n_mid, n_out = (int(np.prod(s)) for s in (shape_in, conv1.output_shape, conv2.output_shape))
+    image = m.Signal(rng.uniform(-1, 1, size=n_in), name="image")
+    w1 = m.Signal(rng.normal(scale=0.5, size=conv1.kernel_shape), name="w1", readonly=True)
+    w2 = m.Signal(rng.normal(scale=0.5, size=conv2.kernel_shape), name="w2", readonly=True)
+    j1 = m.Signal(np.zeros(n_mid), name="j1")
+    r1 = m.Signal(np.zeros(n_mid), name="r1")
+    y2 = m.Signal(np.zeros(n_out), name="y2")
+    noise = m.WhiteNoise(m.Uniform(-0.1, 0.1), scale=False, seed=seed)
+    mdl.add_op(m.SimProcess(noise, None, image, mdl.step, mode="inc"))  # the image drifts
+    mdl.add_op(m.Reset(j1))
+    mdl.add_op(m.ConvInc(w1, image, j1, conv1))
+    mdl.add_op(m.SimNeurons(m.RectifiedLinear(), j1, r1))
+    mdl.add_op(m.Reset(y2))
+    mdl.add_op(m.ConvInc(w2, r1, y2, conv2))
+    probes = [mdl.add_probe(y2, label="y2"), mdl.add_probe(j1, label="j1")]
+    mdl.info = dict(probes=probes, signals=[image, j1, r1, y2], convs=(conv1, conv2))
+    return mdl

@@ -285,6 +285,125 @@ def presentinput(Y, t, signals, dt, pres_t=None):
         Y[k][:, 0] = signals[k][ti, :]
 
 
+# ---- white noise (plan_whitenoise, clra_nonlinearities.py:1573-1675) -----------------------
+# The reference draws from RANLUX (pyopencl-ranluxcl.cl, not part of its source tree): its random
+# STREAM cannot be restated, only the use it makes of a sample (:1536-1551, :1625-1637):
+#   uniform:  low + (high - low) * u        gaussian:  mean + std * z
+#   then `sample *= 1/sqrt(dt)` (a double literal) when `scale`, then `y += sample` or `y = sample`.
+# The generator here is Philox4x32-10 (Salmon et al., SC'11, "Parallel random numbers: as easy as
+# 1, 2, 3"): counter = (step, element // 4, 0, 0), key = the 64-bit seed of the process; word e % 4
+# of the output belongs to element e.  u = (word >> 8) * 2^-24 in [0, 1); normals by Box-Muller in
+# double on the word pairs (0, 1) and (2, 3), rounded to float32 once.
+PHILOX_M0, PHILOX_M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+PHILOX_W0, PHILOX_W1 = np.uint32(0x9E3779B9), np.uint32(0xBB67AE85)
+
+
+def philox4x32_10(counter, key):
+    """Philox4x32 with 10 rounds on arrays of uint32: counter = 4 words, key = 2 words."""
+    c = [np.asarray(x, dtype=np.uint32) for x in counter]
+    k = [np.asarray(x, dtype=np.uint32) for x in key]
+    with np.errstate(over="ignore"):
+        for _ in range(10):
+            p0 = PHILOX_M0 * c[0].astype(np.uint64)
+            p1 = PHILOX_M1 * c[2].astype(np.uint64)
+            hi0, lo0 = (p0 >> np.uint64(32)).astype(np.uint32), p0.astype(np.uint32)
+            hi1, lo1 = (p1 >> np.uint64(32)).astype(np.uint32), p1.astype(np.uint32)
+            c = [hi1 ^ c[1] ^ k[0], lo1, hi0 ^ c[3] ^ k[1], lo0]
+            k = [k[0] + PHILOX_W0, k[1] + PHILOX_W1]
+    return c
+
+
+def whitenoise_samples(seed, step, m, dist_enum, params, scale, dt):
+    """The m float32 samples of one process at one step (before the inc / set)."""
+    quads = (m + 3) // 4
+    q = np.arange(quads, dtype=np.uint32)
+    zero = np.zeros(quads, dtype=np.uint32)
+    seed = int(seed)
+    w = philox4x32_10([np.full(quads, step, dtype=np.uint32), q, zero, zero],
+                      [np.full(quads, seed & 0xFFFFFFFF, dtype=np.uint32),
+                       np.full(quads, (seed >> 32) & 0xFFFFFFFF, dtype=np.uint32)])
+    p0, p1 = f32(params[0]), f32(params[1])
+    if dist_enum == 0:
+        u = [(x >> np.uint32(8)).astype(np.float32) * f32(2.0 ** -24) for x in w]
+        vals = [(p0 + ((p1 - p0) * ui).astype(np.float32)).astype(np.float32) for ui in u]
+    elif dist_enum == 1:
+        z = []
+        for a, b in ((w[0], w[1]), (w[2], w[3])):
+            u1 = ((a >> np.uint32(8)).astype(np.float64) + 1.0) * 2.0 ** -24  # (0, 1]
+            u2 = (b >> np.uint32(8)).astype(np.float64) * 2.0 ** -24          # [0, 1)
+            r = np.sqrt(-2.0 * np.log(u1))
+            z += [(r * np.cos(2.0 * np.pi * u2)).astype(np.float32), (r * np.sin(2.0 * np.pi * u2)).astype(np.float32)]
+        vals = [(p0 + (p1 * zi).astype(np.float32)).astype(np.float32) for zi in z]
+    else:
+        raise NotImplementedError(dist_enum)
+    out = np.stack(vals, axis=1).reshape(-1)[:m]
+    if scale:
+        out = (out.astype(np.float64) * (1.0 / np.sqrt(dt))).astype(np.float32)
+    return out
+
+
+def whitenoise(Y, t, dist_enums, dist_params, scales, incs, dt, seeds):
+    for k in range(len(Y)):
+        m = int(Y.shape0s[k])
+        s = whitenoise_samples(seeds[k], int(t[k][0, 0]), m, int(dist_enums[k][0, 0]),
+                               np.asarray(dist_params[k]).reshape(-1), bool(scales[k]), dt)
+        if incs[k]:
+            Y[k][:, 0] = (Y[k][:, 0] + s).astype(np.float32)
+        else:
+            Y[k][:, 0] = s
+
+
+# ---- convolution and pooling on one image -----------------------------------------
+def conv2d(x, filters, shape_in, shape_out, kernel_shape, conv=True, padding=(0, 0), strides=(1, 1),
+           channels_last=True):
+    """clra_nonlinearities.py:1799-1873: y[k,i,j] = sum over c, ii, jj (in that order, from zero) of
+    filter * x[c, i*sti - pi + ii, j*stj - pj + jj], zero outside the image, float32, each product
+    rounded before it is added.  filters: (si, sj, nc, nf) when ``conv`` else (nf, nc, si, sj, nyi, nyj)."""
+    si, sj = kernel_shape
+    sti, stj = strides
+    (nxi, nxj, nc), (nyi, nyj, nf) = (shape_in, shape_out) if channels_last else (
+        (shape_in[1], shape_in[2], shape_in[0]), (shape_out[1], shape_out[2], shape_out[0]))
+    if padding == "valid":
+        pi, pj = 0, 0
+    elif padding == "same":
+        pi, pj = (si - 1) // 2, (sj - 1) // 2
+    else:
+        pi, pj = padding
+    x = np.asarray(x, dtype=np.float32).reshape(shape_in)
+    xc = x.transpose(2, 0, 1) if channels_last else x  # (nc, nxi, nxj)
+    padded = np.zeros((nc, nxi + 2 * pi + si * sti + sti, nxj + 2 * pj + sj * stj + stj), dtype=np.float32)
+    padded[:, pi:pi + nxi, pj:pj + nxj] = xc
+    f = np.asarray(filters, dtype=np.float32)
+    f = f.reshape(si, sj, nc, nf) if conv else f.reshape(nf, nc, si, sj, nyi, nyj)
+    out = np.zeros((nf, nyi, nyj), dtype=np.float32)
+    for c in range(nc):
+        for ii in range(si):
+            for jj in range(sj):
+                patch = padded[c, ii:ii + nyi * sti:sti, jj:jj + nyj * stj:stj][:nyi, :nyj]
+                w = f[ii, jj, c, :][:, None, None] if conv else f[:, c, ii, jj]
+                out = out + (w * patch[None]).astype(np.float32)
+    return (out.transpose(1, 2, 0) if channels_last else out).reshape(-1)
+
+
+def pool2d(x, shape, pool_size, strides):
+    """clra_nonlinearities.py:1984-2030: mean over the part of each window inside the image."""
+    nc, nyi, nyj, nxi, nxj = shape
+    si, sj = pool_size
+    sti, stj = strides
+    x = np.asarray(x, dtype=np.float32).reshape(nc, nxi, nxj)
+    out = np.zeros((nc, nyi, nyj), dtype=np.float32)
+    cnt = np.zeros((nyi, nyj), dtype=np.int32)
+    for ii in range(si):
+        for jj in range(sj):
+            for i in range(nyi):
+                for j in range(nyj):
+                    xi, xj = i * sti + ii, j * stj + jj
+                    if xi < nxi and xj < nxj:
+                        out[:, i, j] = out[:, i, j] + x[:, xi, xj]
+                        cnt[i, j] += 1
+    return (out / cnt[None].astype(np.float32)).astype(np.float32).reshape(-1)
+
+
 # ---- neuron models ------------------------------------------------------------
 def _expm1(x):
     return np.expm1(x.astype(np.float64)).astype(np.float32)

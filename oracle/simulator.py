@@ -288,6 +288,15 @@ class OracleSimulator:
                 new = yi.reshape(out.shape)
             new = new.astype(np.float32)
             out[...] = out + new if op.mode == "inc" else new
+        elif "WhiteNoise" in names:
+            if proc.seed is None:
+                raise ValueError("the oracle needs an explicit seed for a WhiteNoise process")
+            it = int(self.view(self.model.step)[()])
+            dist = proc.dist
+            enum = {"Uniform": 0, "Gaussian": 1}[type(dist).__name__]
+            params = (dist.low, dist.high) if enum == 0 else (dist.mean, dist.std)
+            s = K.whitenoise_samples(proc.seed, it, out.size, enum, params, proc.scale, self.dt).reshape(out.shape)
+            out[...] = (out + s).astype(np.float32) if op.mode == "inc" else s
         elif "WhiteSignal" in names:
             it = int(self.view(self.model.step)[()])
             table = proc.signal.astype(np.float32)
@@ -300,6 +309,23 @@ class OracleSimulator:
             out[...] = table[ti].reshape(out.shape)
         else:
             raise NotImplementedError(type(proc).__name__)
+
+    def _do_ConvInc(self, op):
+        # nengo_ocl/simulator.py:1298-1313: a 1-D convolution is a 2-D one with a single row
+        conv = op.conv
+        shape_in, shape_out = tuple(conv.input_shape), tuple(conv.output_shape)
+        kernel_shape, strides = tuple(conv.kernel_size), tuple(conv.strides)
+        if conv.dimensions == 1:
+            kernel_shape, strides = (1,) + kernel_shape, (1,) + strides
+            if conv.channels_last:
+                shape_in, shape_out = (1,) + shape_in, (1,) + shape_out
+            else:
+                shape_in, shape_out = (shape_in[0], 1, shape_in[1]), (shape_out[0], 1, shape_out[1])
+        padding = op.conv.padding.lower() if isinstance(op.conv.padding, str) else op.conv.padding
+        y = self.view(op.Y)
+        out = K.conv2d(self.view(op.X), self.view(op.W), shape_in, shape_out, kernel_shape, True, padding, strides,
+                       op.conv.channels_last)
+        y[...] = (y + out.reshape(y.shape)).astype(np.float32)
 
     def _do_SimPES(self, op):
         pre = self.view(op.pre_filtered)

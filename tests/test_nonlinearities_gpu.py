@@ -341,3 +341,132 @@ def test_timeupdate_and_presentinput_match_reference_kernels(queue, golden_kerne
             t[1] = np.full((1, 1), float(s_))
             plan()
             assert np.array_equal(Y.cl_buf.get(), g["presentinput/%s" % mode][i]), (mode, s_)
+
+
+def test_whitenoise_matches_oracle(queue):
+    """plan_whitenoise (clra_nonlinearities.py:1577-1675) with the Philox generator: uniform samples are
+    exact; the gaussian ones go through log / sqrt / sincos in double on both sides and are rounded
+    once, so at most one in a million may differ (a double that lands on a float32 rounding boundary)."""
+    from nengo_ocl_b200 import model as m
+
+    sizes = [1, 3, 4, 5, 1023, 4097, 20000]
+    dists = [m.Uniform(-1, 1), m.Gaussian(0, 1), m.Gaussian(0.5, 2), m.Uniform(0, 3), m.Gaussian(-1, 0.1),
+             m.Uniform(-2, -1), m.Gaussian(0, 1)]
+    seeds = [3, 3, 2 ** 40 + 17, 11, 0, 2 ** 63 - 1, 99]
+    scales = np.array([0, 1, 1, 0, 1, 0, 0], np.int32)
+    incs = np.array([0, 0, 1, 1, 0, 0, 1], np.int32)
+    dt = 0.001
+    Yh = RA([np.full(n, 0.25) for n in sizes])
+    Y = CLRA(queue, Yh)
+    step = CLRA(queue, RA([np.zeros((1, 1))]))
+    t = step[[0] * len(sizes)]
+    enums, params = nl.get_dist_enums_params(dists)
+    rngs = nl.create_rngs(queue, len(sizes))
+    nl.init_rngs(queue, rngs, seeds)
+    plan = nl.plan_whitenoise(queue, Y, CLRA(queue, enums), CLRA(queue, params), to_device(queue, scales),
+                              to_device(queue, incs), dt, rngs, t)
+    total = differ = 0
+    for s_ in (1, 2, 77, 4000):
+        step[0] = np.full((1, 1), float(s_))
+        plan()
+        th = RA([np.full((1, 1), float(s_))] * len(sizes))
+        K.whitenoise(Yh, th, enums, params, scales, incs, dt, seeds)
+        for k, d in enumerate(dists):
+            got, want = Y[k][:, 0], Yh[k][:, 0]
+            if type(d).__name__ == "Uniform":
+                assert np.array_equal(got, want), (k, s_)
+            total += got.size
+            differ += int(np.count_nonzero(got != want))
+            assert np.allclose(got, want, rtol=1e-6, atol=1e-7)
+    assert differ <= max(1, total // 1000000), (differ, total)
+
+
+def test_whitenoise_model_matches_oracle_and_repeats_after_reset():
+    from nengo_ocl_b200 import synth
+    from nengo_ocl_b200.simulator import Simulator
+    from oracle.simulator import OracleSimulator
+
+    mdl = synth.white_noise_model(seed=21, n=300)
+    ora = OracleSimulator(mdl)
+    with Simulator(None, model=mdl) as sim:
+        for _ in range(40):
+            sim.step()
+            ora.step()
+            assert np.allclose(np.asarray(sim.signals[mdl.info["noise"]]), ora[mdl.info["noise"]], rtol=1e-6, atol=1e-7)
+            assert np.array_equal(np.asarray(sim.signals[mdl.info["walk"]]), ora[mdl.info["walk"]])
+        first = [sim.data[p].copy() for p in mdl.probes]
+        assert np.allclose(first[0], np.array(ora.probe_data[mdl.probes[0]]), rtol=1e-5, atol=1e-6)
+        assert np.array_equal(first[1], np.array(ora.probe_data[mdl.probes[1]], dtype=first[1].dtype))
+        sim.reset()
+        sim.run_steps(40)
+        for a, p in zip(first, mdl.probes):
+            assert np.array_equal(a, sim.data[p])  # the stream is a function of (seed, step, element)
+
+
+@pytest.mark.parametrize("channels_last", [True, False])
+@pytest.mark.parametrize("conv", [True, False], ids=["shared_filters", "local_filters"])
+def test_conv2d_matches_oracle(queue, rng, conv, channels_last):
+    """plan_conv2d (clra_nonlinearities.py:1762-1969): mul-add only, same loop order as the oracle,
+    no FMA contraction: bit-exact.  Geometries: valid / same / explicit padding, strides, 1 x n kernels."""
+    cases = [  # nxi, nxj, nc, nf, (si, sj), padding, strides
+        (7, 9, 3, 4, (3, 2), "valid", (1, 1)),
+        (12, 10, 2, 5, (3, 3), "same", (2, 1)),
+        (8, 8, 1, 1, (1, 1), (0, 0), (1, 1)),
+        (1, 33, 4, 6, (1, 5), "same", (1, 3)),
+        (28, 28, 1, 32, (7, 7), (1, 0), (3, 2)),
+    ]
+    for nxi, nxj, nc, nf, (si, sj), padding, (sti, stj) in cases:
+        pi, pj = (0, 0) if padding == "valid" else ((si - 1) // 2, (sj - 1) // 2) if padding == "same" else padding
+        nyi, nyj = (nxi + 2 * pi - si) // sti + 1, (nxj + 2 * pj - sj) // stj + 1
+        shape_in = (nxi, nxj, nc) if channels_last else (nc, nxi, nxj)
+        shape_out = (nyi, nyj, nf) if channels_last else (nf, nyi, nyj)
+        fshape = (si, sj, nc, nf) if conv else (nf, nc, si, sj, nyi, nyj)
+        x, f = rng.normal(size=shape_in), rng.normal(size=fshape)
+        y0 = rng.normal(size=shape_out)
+        data = CLRA(queue, RA([np.zeros(3), x.reshape(-1), f.reshape(-1), y0.reshape(-1)]))  # unaligned starts
+        want = K.conv2d(data[1], data[2], shape_in, shape_out, (si, sj), conv, padding, (sti, stj), channels_last)
+        for inc in (False, True):
+            data[3] = y0.reshape(-1, 1)
+            plan = nl.plan_conv2d(queue, data.getitem_device(1), data.getitem_device(3), data.getitem_device(2),
+                                  shape_in, shape_out, (si, sj), conv=conv, padding=padding, strides=(sti, stj),
+                                  channels_last=channels_last, inc=inc)
+            plan()
+            ref = (data.dtype.type(0) + want) if not inc else (y0.reshape(-1).astype(np.float32) + want)
+            assert np.array_equal(data[3][:, 0], ref.astype(np.float32)), (nxi, nxj, padding, inc)
+        assert plan.flops_per_call == 2 * nyi * nyj * nf * nc * si * sj
+
+
+def test_pool2d_matches_oracle(queue, rng):
+    """plan_pool2d (:1972-2079): windows that overhang the image average what lies inside."""
+    for nc, nxi, nxj, (si, sj), (sti, stj) in [(3, 8, 8, (2, 2), (2, 2)), (2, 7, 9, (3, 2), (2, 2)),
+                                                 (1, 5, 5, (3, 3), (1, 1)), (4, 30, 31, (4, 4), (3, 4))]:
+        nyi, nyj = -(-nxi // sti), -(-nxj // stj)
+        x = rng.normal(size=(nc, nxi, nxj))
+        data = CLRA(queue, RA([np.zeros(1), x.reshape(-1), np.zeros(nc * nyi * nyj)]))
+        plan = nl.plan_pool2d(queue, data.getitem_device(1), data.getitem_device(2), (nc, nyi, nyj, nxi, nxj),
+                              (si, sj), (sti, stj))
+        plan()
+        want = K.pool2d(data[1], (nc, nyi, nyj, nxi, nxj), (si, sj), (sti, stj))
+        assert np.array_equal(data[2][:, 0], want)
+
+
+@pytest.mark.parametrize("channels_last", [True, False])
+@pytest.mark.parametrize("one_d", [False, True], ids=["2d", "1d"])
+def test_convolution_model_matches_oracle(channels_last, one_d):
+    """Reset + ConvInc + rate neurons + a second ConvInc (simulator.py:1290-1331), with a drifting
+    input image: every signal bit for bit, every step."""
+    from nengo_ocl_b200 import synth
+    from nengo_ocl_b200.simulator import Simulator
+    from oracle.simulator import OracleSimulator
+
+    mdl = synth.convolution_model(channels_last=channels_last, one_d=one_d)
+    ora = OracleSimulator(mdl)
+    with Simulator(None, model=mdl) as sim:
+        assert [p.name for p in sim._plans].count("cl_conv2d") == 2
+        for _ in range(30):
+            sim.step()
+            ora.step()
+            for sig in mdl.info["signals"]:
+                assert np.array_equal(np.asarray(sim.signals[sig]).reshape(-1), ora[sig].reshape(-1)), sig
+        for p in mdl.probes:
+            assert np.array_equal(sim.data[p], np.array(ora.probe_data[p], dtype=sim.data[p].dtype))

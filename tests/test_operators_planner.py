@@ -252,3 +252,20 @@ def test_phase_barriers_of_a_single_pass():
     uses = [(set(), {"t"}), ({"t"}, {"y"}), ({"q"}, {"z"})]
     assert phase_barriers(uses, ring=False) == [False, True, False]
     assert phase_barriers(uses, ring=True) == [True, True, False]
+
+
+def test_planner_extents_agree_with_pairwise_overlap():
+    """The sorted-range structure of the planner against the pairwise test it replaces."""
+    from nengo_ocl_b200.planners import _Extents
+
+    rng = np.random.RandomState(0)
+    for trial in range(50):
+        ext, ranges = _Extents(), []
+        for _ in range(60):
+            lo = int(rng.randint(0, 400))
+            hi = lo + int(rng.randint(1, 12))
+            want = any(l < hi and lo < h for l, h in ranges)
+            assert ext.overlaps(lo, hi) == want
+            if not want or trial % 5 == 0:  # every fifth trial also stores overlapping ranges
+                ext.add(lo, hi)
+                ranges.append((lo, hi))
