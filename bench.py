@@ -354,6 +354,8 @@ def small_model_rates(ctx, capi, which=("c1", "c3", "c4", "ws_sparse"), steps_ov
         # (persistent step loop: the plans run as phases of one cooperative launch per run_steps batch)
         out[key]["step_loop"] = None if loop is None else {"phases": loop.n_phases, "barriers_per_step": loop.n_barriers,
                                                            "ctas": loop.grid}
+        if loop is not None:  # one launch per run_steps batch (a probe-drain window)
+            out[key]["launches_per_step"] = 1.0 / sim._max_steps_between_probes
         sim.close()
     return out
 

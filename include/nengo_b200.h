@@ -276,6 +276,7 @@ typedef struct {
   double dt;
   int upsample;
   int adaptive;
+  int fastlif; /* LIF only: the `fastlif` variant of the kernel text (:1079-1114) */
 } nb2_neuron_args;
 #define NB2_NEURON_LIF 0
 #define NB2_NEURON_LIF_RATE 1

@@ -34,6 +34,7 @@ class nb2_neuron_args(Structure):
         ("dt", c_double),
         ("upsample", c_int),
         ("adaptive", c_int),
+        ("fastlif", c_int),
     ]
 
 

@@ -20,25 +20,36 @@ __device__ __forceinline__ void nb2_var_store(const nb2_var& v, int block, int i
   v.buf[v.starts[block] + i] = x;
 }
 
-// LIF with exact spike-time refractory handling (plan_lif, :1071-1133).
+// LIF with exact spike-time refractory handling (plan_lif, :1071-1133); `fastlif` selects the
+// cheaper variant of the same kernel text (:1079-1114): the whole substep is integrated, a
+// refractory neuron's voltage is scaled afterwards, the spike time is interpolated linearly.
 __device__ __forceinline__ void nb2_lif_core(float J, float& V, float& W, float& S, float tau, float ref,
-                                             float amp, float dtu, float dt_inv, int upsample,
-                                             float Nadapt, bool adaptive) {
+                                             float amp, float dtu, float dtu_inv, float dt_inv, int upsample,
+                                             float Nadapt, bool adaptive, bool fastlif) {
   const float V_threshold = 1.0f;
   bool spiked = false;
   for (int ii = 0; ii < upsample; ++ii) {
     W -= dtu;
-    const float delta_t = (W > dtu) ? 0.0f : (W < 0.0f) ? dtu : dtu - W;
+    const float delta_t = fastlif ? dtu : (W > dtu) ? 0.0f : (W < 0.0f) ? dtu : dtu - W;
     float dV;
     if (adaptive) dV = -nb2_expm1_cr(-delta_t / tau) * (J - Nadapt - V);
     else dV = -nb2_expm1_cr(-delta_t / tau) * (J - V);
     V += dV;
+    if (fastlif) {
+      if (V < 0.0f || W > dtu) V = 0.0f;
+      else if (W >= 0.0f) V *= 1.0f - W * dtu_inv;
+    }
     if (V > V_threshold) {
-      const float t_spike = dtu + tau * nb2_log1p_cr(-(V - V_threshold) / (J - V_threshold));
-      W = ref + t_spike;
+      if (fastlif) {
+        const float overshoot = dtu * (V - V_threshold) / dV;
+        W = ref - overshoot + dtu;
+      } else {
+        const float t_spike = dtu + tau * nb2_log1p_cr(-(V - V_threshold) / (J - V_threshold));
+        W = ref + t_spike;
+      }
       V = 0.0f;
       spiked = true;
-    } else if (V < 0.0f) {
+    } else if (!fastlif && V < 0.0f) {
       V = 0.0f;
     }
   }
@@ -56,6 +67,7 @@ __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict
   const float dt = (float)a.dt;
   const float dtu = (float)(a.dt / a.upsample);
   const float dt_inv = (float)(1.0 / a.dt);
+  const float dtu_inv = (float)(a.upsample / a.dt);
 
   if (kind == NB2_NEURON_LIF) {
     const float J = nb2_var_load(a.J, gind1, gind0);
@@ -66,7 +78,7 @@ __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict
     const float amp = nb2_var_load(a.amp, gind1, gind0);
     float N = 0.0f, S;
     if (a.adaptive) N = nb2_var_load(a.N, gind1, gind0);
-    nb2_lif_core(J, V, W, S, tau, ref, amp, dtu, dt_inv, a.upsample, N, a.adaptive != 0);
+    nb2_lif_core(J, V, W, S, tau, ref, amp, dtu, dtu_inv, dt_inv, a.upsample, N, a.adaptive != 0, a.fastlif != 0);
     nb2_var_store(a.V, gind1, gind0, V);
     nb2_var_store(a.W, gind1, gind0, W);
     nb2_var_store(a.S, gind1, gind0, S);

@@ -672,7 +672,7 @@ def plan_presentinput(queue, Y, t, signals, dt, pres_t=None, tag=None):
 
 # ---- neuron models -----------------------------------------------------------
 def _plan_template(queue, name, kind, tag=None, blockify=True, inputs=None, outputs=None, parameters=None,
-                   dt=0.001, upsample=1, adaptive=False):
+                   dt=0.001, upsample=1, adaptive=False, fastlif=False):
     """Blocked element-wise launch over lists of vectors.
 
     Same contract as the reference's ``_plan_template``
@@ -747,6 +747,7 @@ def _plan_template(queue, name, kind, tag=None, blockify=True, inputs=None, outp
     args.dt = float(dt)
     args.upsample = int(upsample)
     args.adaptive = int(bool(adaptive))
+    args.fastlif = int(bool(fastlif))
     n_blocks = len(sizes)
     fn, check = _capi.lib().nb2_neurons, _capi.check
     args_ref = ctypes.byref(args)
@@ -770,8 +771,6 @@ def plan_lif(queue, dt, J, V, W, outS, ref, tau, amp, N=None, tau_n=None, inc_n=
     assert J.ctype == "float"
     for x in [V, W, outS]:
         assert x.ctype == J.ctype
-    if fastlif:
-        raise NotImplementedError("fastlif variant")
     inputs = dict(J=J, V=V, W=W)
     outputs = dict(outV=V, outW=W, outS=outS)
     parameters = dict(tau=tau, ref=ref, amp=amp)
@@ -783,7 +782,7 @@ def plan_lif(queue, dt, J, V, W, outS, ref, tau, amp, N=None, tau_n=None, inc_n=
         parameters.update(tau_n=tau_n, inc_n=inc_n)
     return _plan_template(queue, "cl_alif" if adaptive else "cl_lif", _capi.NEURON_LIF, inputs=inputs,
                           outputs=outputs, parameters=parameters, dt=float(dt), upsample=upsample,
-                          adaptive=adaptive, **kwargs)
+                          adaptive=adaptive, fastlif=fastlif, **kwargs)
 
 
 def plan_lif_rate(queue, dt, J, R, ref, tau, amp, N=None, tau_n=None, inc_n=None, **kwargs):

@@ -414,26 +414,42 @@ def _log1p(x):
         return np.log1p(x.astype(np.float64)).astype(np.float32)
 
 
-def lif(dt, J, V, W, tau, ref, amp, upsample=1, N=None, tau_n=None, inc_n=None):
+def lif(dt, J, V, W, tau, ref, amp, upsample=1, N=None, tau_n=None, inc_n=None, fastlif=False):
     """``cl_lif`` / ``cl_alif`` (clra_nonlinearities.py:1087-1132) on flat
-    float32 arrays; returns (V, W, S[, N])."""
+    float32 arrays; returns (V, W, S[, N]).  ``fastlif`` (:1079-1114): the whole
+    substep is always integrated, the refractory period scales the voltage
+    afterwards, and the spike time is interpolated linearly."""
     J, V, W = _f(J), _f(V).copy(), _f(W).copy()
     tau, ref, amp = _f(tau), _f(ref), _f(amp)
     dtu = f32(float(dt) / upsample)
+    dtu_inv = f32(upsample / float(dt))
     dt_inv = f32(1.0 / float(dt))
     one = f32(1)
     spiked = np.zeros(J.shape, dtype=bool)
     for _ in range(upsample):
         W = W - dtu
-        delta_t = np.where(W > dtu, f32(0), np.where(W < 0, dtu, dtu - W)).astype(np.float32)
+        if fastlif:
+            delta_t = np.full(J.shape, dtu, dtype=np.float32)
+        else:
+            delta_t = np.where(W > dtu, f32(0), np.where(W < 0, dtu, dtu - W)).astype(np.float32)
         drive = (J - _f(N) - V) if N is not None else (J - V)
-        dV = -_expm1(-delta_t / tau) * drive
-        V = V + dV
+        dV = (-_expm1(-delta_t / tau) * drive).astype(np.float32)
+        V = (V + dV).astype(np.float32)
+        if fastlif:
+            scaled = (V * (one - W * dtu_inv)).astype(np.float32)
+            V = np.where((V < 0) | (W > dtu), f32(0), np.where(W >= 0, scaled, V)).astype(np.float32)
         over = V > one
         with np.errstate(divide="ignore", invalid="ignore"):
-            t_spike = dtu + tau * _log1p(-(V - one) / (J - one))
-        W = np.where(over, ref + t_spike, W).astype(np.float32)
-        V = np.where(over, f32(0), np.where(V < 0, f32(0), V)).astype(np.float32)
+            if fastlif:
+                overshoot = (dtu * (V - one) / dV).astype(np.float32)
+                w_spike = (ref - overshoot + dtu).astype(np.float32)
+            else:
+                w_spike = ref + (dtu + tau * _log1p(-(V - one) / (J - one)))
+        W = np.where(over, w_spike, W).astype(np.float32)
+        if fastlif:
+            V = np.where(over, f32(0), V).astype(np.float32)
+        else:
+            V = np.where(over, f32(0), np.where(V < 0, f32(0), V)).astype(np.float32)
         spiked |= over
     S = np.where(spiked, amp * dt_inv, f32(0)).astype(np.float32)
     if N is not None:

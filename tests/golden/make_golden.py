@@ -173,6 +173,17 @@ def main(reference_root, write_fixtures=True):
         for nm, c in (("V", clV), ("W", clW), ("S", clS), ("N", clNa)):
             kernels["alif/%s%d" % (nm, step + 1)] = c.cl_buf._arr.copy()
 
+    # the `fastlif` variant of cl_lif (:1079-1114): three consecutive steps, upsample 1 and 2
+    for upsample in (1, 2):
+        for r, c in ((V, clV), (W, clW), (S, clS)):
+            c.cl_buf._arr[...] = r.buf
+        plan, cap, progs = capture(lambda: nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0,
+                                                       upsample=upsample, fastlif=True))
+        for step in range(3):
+            refkernels.run_plan(plan, progs[-1], "cl_lif")
+            for nm, c in (("V", clV), ("W", clW), ("S", clS)):
+                kernels["fastlif_up%d/%s%d" % (upsample, nm, step + 1)] = c.cl_buf._arr.copy()
+
     # timeupdate: 5 consecutive calls
     st = CLRA(queue, ra([np.zeros((1, 1))]))
     tm = CLRA(queue, ra([np.zeros((1, 1))]))

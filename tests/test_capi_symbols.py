@@ -35,4 +35,6 @@ def test_argument_errors_are_reported_not_raised_in_c():
 def test_neuron_args_struct_layout():
     # 10 x {ptr, ptr, float(+pad)} + double + 2 ints
     assert ctypes.sizeof(_capi.nb2_var) == 24
-    assert ctypes.sizeof(_capi.nb2_neuron_args) == 10 * 24 + 16
+    # 10 variables, double dt, int upsample / adaptive / fastlif, padded to the 8-byte alignment
+    assert ctypes.sizeof(_capi.nb2_neuron_args) == 10 * 24 + 24
+    assert _capi.nb2_neuron_args.fastlif.offset == 10 * 24 + 16

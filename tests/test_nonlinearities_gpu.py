@@ -470,3 +470,25 @@ def test_convolution_model_matches_oracle(channels_last, one_d):
                 assert np.array_equal(np.asarray(sim.signals[sig]).reshape(-1), ora[sig].reshape(-1)), sig
         for p in mdl.probes:
             assert np.array_equal(sim.data[p], np.array(ora.probe_data[p], dtype=sim.data[p].dtype))
+
+
+def test_fastlif_matches_oracle_and_reference_kernel(queue, golden_kernels):
+    """plan_lif(fastlif=True): bit-exact against the oracle; spikes and refractory times equal to the
+    reference's kernel text, voltages within one ulp of it."""
+    g = golden_kernels
+    sizes = [int(s) for s in g["lif/sizes"]]
+    split = lambda buf: RA(np.split(buf, np.cumsum(sizes)[:-1]))
+    for up in (1, 2):
+        clJ, clV, clW = (CLRA(queue, split(g["lif_up1/" + k])) for k in ("J", "V0", "W0"))
+        clS = CLRA(queue, RA([np.zeros(n) for n in sizes]))
+        clT = CLRA(queue, split(g["lif_up1/tau"]))
+        plan = nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, clT, 1.0, upsample=up, fastlif=True)
+        V, W = g["lif_up1/V0"].copy(), g["lif_up1/W0"].copy()
+        for step in range(1, 4):
+            plan()
+            V, W, S = K.lif(1e-3, g["lif_up1/J"], V, W, g["lif_up1/tau"], 2e-3, 1.0, upsample=up, fastlif=True)
+            assert np.array_equal(clV.cl_buf.get(), V)
+            assert np.array_equal(clW.cl_buf.get(), W)
+            assert np.array_equal(clS.cl_buf.get(), S)
+        key = "fastlif_up%d/" % up
+        assert np.allclose(clV.cl_buf.get(), g[key + "V3"], rtol=1e-5, atol=1e-6)

@@ -322,3 +322,21 @@ def test_timeupdate_and_presentinput_oracle_match_reference_kernels(golden_kerne
             t = RA([np.full((1, 1), s_), np.full((1, 1), s_)])
             K.presentinput(Y, t, tabs, 0.001, pres_t=pres)
             assert np.array_equal(Y.buf, g["presentinput/%s" % mode][i]), (mode, s_)
+
+
+def test_fastlif_oracle_matches_reference_kernel(golden_kernels):
+    """The `fastlif` variant of cl_lif (clra_nonlinearities.py:1079-1114), three consecutive steps of
+    the reference's kernel text at upsample 1 and 2: refractory times and spikes exactly, voltages to
+    one ulp (the reference text calls the float expm1 of the C library it is compiled with)."""
+    g = golden_kernels
+    J, tau = g["lif_up1/J"], g["lif_up1/tau"]
+    for up in (1, 2):
+        V, W = g["lif_up1/V0"].copy(), g["lif_up1/W0"].copy()
+        for step in range(1, 4):
+            V, W, S = K.lif(1e-3, J, V, W, tau, 2e-3, 1.0, upsample=up, fastlif=True)
+            key = "fastlif_up%d/" % up
+            assert np.array_equal(S, g[key + "S%d" % step])
+            assert np.allclose(W, g[key + "W%d" % step], rtol=1e-6, atol=1e-9)
+            assert np.allclose(V, g[key + "V%d" % step], rtol=2e-7, atol=1e-7)
+            V, W = g[key + "V%d" % step].copy(), g[key + "W%d" % step].copy()  # follow the reference's state
+        assert g[key + "S3"].sum() > 0
