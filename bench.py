@@ -208,8 +208,11 @@ def cpu_compiled_rate(n_ensembles, steps, warmup=3):
     from nengo_ocl_b200 import synth
     from oracle.pes_batch import PesBatch
 
-    cores = len(os.sched_getaffinity(0))
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    from oracle import cport
+
+    # all the cores this process may use, whatever OMP_NUM_THREADS a launcher exported for its workers
+    # (torchrun sets it to 1)
+    cores = cport.set_threads(len(os.sched_getaffinity(0)))
     mdl = synth.pes_learning_model(seed=3, n_ensembles=n_ensembles, n_neurons=FULL["n_neurons"],
                                    dimensions=FULL["dimensions"], n_templates=2, n_probes=2,
                                    sim_time=max(steps + warmup, 50) * 1e-3)
@@ -219,7 +222,7 @@ def cpu_compiled_rate(n_ensembles, steps, warmup=3):
     batch.run_steps(steps)
     dt_s = time.perf_counter() - t0
     return {"value": mdl.n_neurons * steps / dt_s, "unit": "neuron-updates/s",
-            "cores": int(os.environ["OMP_NUM_THREADS"]), "kind": "port",
+            "cores": cores, "kind": "port",
             "implementation": "C restatement of the reference's kernels (oracle/cport.c), gcc -O2 -fopenmp, "
                               "one loop nest per kernel launch",
             "sample": "%d of 4096 ensembles (%d neurons), %d steps, %.1f s" % (n_ensembles, mdl.n_neurons, steps,

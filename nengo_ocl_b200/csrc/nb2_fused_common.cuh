@@ -37,18 +37,19 @@ __device__ __forceinline__ float fused_lif(float J, float& V, float& W, float ta
   return spiked ? amp * dt_inv : 0.0f;
 }
 
-// The same update for four neurons of one lane.  The rare double-precision evaluations (a
+// The same update for N neurons of one lane.  The rare double-precision evaluations (a
 // neuron leaving its refractory period inside the step; a neuron that spikes) are taken out of
-// the per-neuron flow: if any of the four needs one, all four arguments are evaluated together,
+// the per-neuron flow: if any of them needs one, all the arguments are evaluated together,
 // so the warp pays the latency of one series instead of up to four in sequence.  Values are
-// identical to four calls of fused_lif.
-__device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], float (&W)[4], float (&S)[4],
+// identical to N calls of fused_lif.
+template <int N>
+__device__ __forceinline__ void fused_lifN(const float (&J)[N], float (&V)[N], float (&W)[N], float (&S)[N],
                                            float tau, float ref, float amp, float dt, float dt_inv,
                                            float em1_dt) {
-  float em1[4], arg[4];
+  float em1[N], arg[N];
   bool need = false;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < N; ++j) {
     W[j] -= dt;
     const float delta_t = (W[j] > dt) ? 0.0f : (W[j] < 0.0f) ? dt : dt - W[j];
     em1[j] = (delta_t == 0.0f) ? 0.0f : em1_dt;
@@ -59,16 +60,16 @@ __device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], f
     }
   }
   if (need) {
-    float v[4];
-    nb2_expm1_cr4(arg, v);
+    float v[N];
+    nb2_expm1_crN<N>(arg, v);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < N; ++j)
       if (arg[j] != 0.0f) em1[j] = v[j];
   }
-  float y[4];
-  bool spiked[4], any = false;
+  float y[N];
+  bool spiked[N], any = false;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < N; ++j) {
     const float dV = -em1[j] * (J[j] - V[j]);
     V[j] += dV;
     y[j] = 0.0f;
@@ -81,10 +82,10 @@ __device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], f
     }
   }
   if (any) {
-    float l[4];
-    nb2_log1p_cr4(y, l);
+    float l[N];
+    nb2_log1p_crN<N>(y, l);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < N; ++j) {
       if (spiked[j]) {
         const float t_spike = dt + tau * l[j];
         W[j] = ref + t_spike;
@@ -93,5 +94,10 @@ __device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], f
     }
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) S[j] = spiked[j] ? amp * dt_inv : 0.0f;
+  for (int j = 0; j < N; ++j) S[j] = spiked[j] ? amp * dt_inv : 0.0f;
+}
+
+__device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], float (&W)[4], float (&S)[4], float tau,
+                                           float ref, float amp, float dt, float dt_inv, float em1_dt) {
+  fused_lifN<4>(J, V, W, S, tau, ref, amp, dt, dt_inv, em1_dt);
 }

@@ -63,7 +63,9 @@
 #define ST_SLOTS NB2_STREAM_SLOTS
 #define ST_REC 32
 #define ST_MAXCOPY 8
-#define ST_ROWS 4  // neurons per lane in an E record
+#ifndef ST_ROWS
+#define ST_ROWS 3  // neurons per lane and pass of an E record (a record of the PES model holds 96 neurons)
+#endif
 #define ST_DITEMS 16  // (row, 128-column tile) pairs of a D record: two lanes each
 
 struct StreamParams {
@@ -241,11 +243,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
       // the slot's previous ensemble must have been decoded completely
       ok = stream_wait_count(&d_done[h0.z], h1.z, &s_abort, lane);
       const float em1_dt = bits(__ldg(e + E_EM1));
-      // blocks of 128 neurons: 4 per lane
+      // blocks of 32 * ST_ROWS neurons: ST_ROWS per lane
       for (int base = 0; ok && base < ne; base += 32 * ST_ROWS) {
         const int nb = min(32 * ST_ROWS, ne - base);
-        float tot[ST_ROWS];
-        int roff[ST_ROWS];
+        float tot[4];  // (block_rows_staged4 takes arrays of four; ST_ROWS of them are used)
+        int roff[4];
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
           roff[j] = base + min(lane + 32 * j, nb - 1);
@@ -255,19 +257,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
         for (int k = 0; k < n_terms; ++k) {
           const int d = __ldg(terms + k * T_STRIDE + T_D);
           const float* a = st.buf + rec[R_COPY0 + 3 * k + 2];
-          // (always four rows per lane: a short last block repeats its last neuron, which keeps
+          // (always ST_ROWS rows per lane: a short last block repeats its last neuron, which keeps
           // the kernel's code small)
-          block_rows_staged4<4>(a, st.x + xoff, d, lane, roff, tot, 1.0);
+          block_rows_staged4<ST_ROWS>(a, st.x + xoff, d, lane, roff, tot, 1.0);
           xoff += d;
         }
         // (lanes beyond the last neuron of the block recompute it; nothing of theirs is stored)
-        float Vv[ST_ROWS], Wv[ST_ROWS], Sv[ST_ROWS];
+        float Jv[ST_ROWS], Vv[ST_ROWS], Wv[ST_ROWS], Sv[ST_ROWS];
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
+          Jv[j] = tot[j];
           Vv[j] = s_V[roff[j]];
           Wv[j] = s_W[roff[j]];
         }
-        fused_lif4(tot, Vv, Wv, Sv, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
+        fused_lifN<ST_ROWS>(Jv, Vv, Wv, Sv, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
         // row j of this lane is neuron i0 + base + lane + 32 j: every array is walked with immediates
         const int first = i0 + base + lane;
         float* gV = data + eV + first;

@@ -49,33 +49,39 @@ __device__ __forceinline__ float nb2_log1p_cr(float xf) {
   if (!(fabsf(xf) <= 0.0625f)) return (float)log1p(x);
   return (float)nb2_log1p_series(x);
 }
-// Four independent evaluations at once: the series of the four arguments interleave in the
+// N independent evaluations at once: the series of the arguments interleave in the
 // pipeline (one dependent chain of fused multiply-adds each), and the library fallback is one
-// rarely taken branch for all four.
+// rarely taken branch for all of them.
 // (the library calls stay out of line: they are almost never taken, and inlined they would be
 // most of the instructions of the kernels that use them)
 static __device__ __noinline__ float nb2_expm1_library(float x) { return (float)expm1((double)x); }
 static __device__ __noinline__ float nb2_log1p_library(float x) { return (float)log1p((double)x); }
 
-__device__ __forceinline__ void nb2_expm1_cr4(const float (&x)[4], float (&out)[4]) {
-  const float big = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+template <int N>
+__device__ __forceinline__ void nb2_expm1_crN(const float (&x)[N], float (&out)[N]) {
+  float big = 0.0f;
+#pragma unroll
+  for (int j = 0; j < N; ++j) big = fmaxf(big, fabsf(x[j]));
   if (!(big <= 0.0625f)) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) out[j] = nb2_expm1_library(x[j]);
+    for (int j = 0; j < N; ++j) out[j] = nb2_expm1_library(x[j]);
     return;
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) out[j] = (float)nb2_expm1_series((double)x[j]);
+  for (int j = 0; j < N; ++j) out[j] = (float)nb2_expm1_series((double)x[j]);
 }
-__device__ __forceinline__ void nb2_log1p_cr4(const float (&x)[4], float (&out)[4]) {
-  const float big = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+template <int N>
+__device__ __forceinline__ void nb2_log1p_crN(const float (&x)[N], float (&out)[N]) {
+  float big = 0.0f;
+#pragma unroll
+  for (int j = 0; j < N; ++j) big = fmaxf(big, fabsf(x[j]));
   if (!(big <= 0.0625f)) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) out[j] = nb2_log1p_library(x[j]);
+    for (int j = 0; j < N; ++j) out[j] = nb2_log1p_library(x[j]);
     return;
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) out[j] = (float)nb2_log1p_series((double)x[j]);
+  for (int j = 0; j < N; ++j) out[j] = (float)nb2_log1p_series((double)x[j]);
 }
 
 __device__ __forceinline__ float nb2_exp_cr(float x) { return (float)exp((double)x); }

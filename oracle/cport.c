@@ -14,6 +14,21 @@
 #include <math.h>
 #include <stdint.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Thread count of the OpenMP loops below (a launcher may have exported OMP_NUM_THREADS=1 for its
+ * workers; the timed baseline asks for the cores it is allowed to use).  Returns the count in use. */
+int nb2o_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* ---- block GEMV (clra_gemv.py:1018-1058 tile kernel, :1137-1153 reduce) ----
  * One item: total[i] (already beta * y_in[i]) += alpha * tile for every

@@ -42,8 +42,15 @@ def lib():
         handle.nb2o_pes_step.argtypes = ([ctypes.c_int] * 4 + [ctypes.c_double] + [_F] * 13
                                          + [ctypes.c_float] * 8)
         handle.nb2o_pes_step.restype = None
+        handle.nb2o_set_threads.argtypes = [ctypes.c_int]
+        handle.nb2o_set_threads.restype = ctypes.c_int
         _lib = handle
     return _lib
+
+
+def set_threads(n=0):
+    """Use ``n`` OpenMP threads in the compiled kernels (0: leave as is); returns the count in use."""
+    return int(lib().nb2o_set_threads(int(n)))
 
 
 def _ptr(a):
