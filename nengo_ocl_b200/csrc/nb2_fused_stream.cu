@@ -63,8 +63,11 @@
 #define ST_SLOTS NB2_STREAM_SLOTS
 #define ST_REC 32
 #define ST_MAXCOPY 8
+#ifndef ST_L2_PREFETCH
+#define ST_L2_PREFETCH 1
+#endif
 #ifndef ST_ROWS
-#define ST_ROWS 3  // neurons per lane and pass of an E record (a record of the PES model holds 96 neurons)
+#define ST_ROWS 4  // neurons per lane and pass of an E record (3 measured no faster for the 96-neuron records of the PES model)
 #endif
 #define ST_DITEMS 16  // (row, 128-column tile) pairs of a D record: two lanes each
 
@@ -217,6 +220,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
   for (int m = 0, i = wid; i < n; ++m, i += ST_NW) {
     bool ok = mbar_wait(full, (uint32_t)(m & 1));
     const int* rec = st.rec[m & 1];
+#if ST_L2_PREFETCH
+    // The warp's next record arrived with this one: ask its arrays into L2 now, so that the bulk
+    // copies issued after this record's arithmetic find them there (a stage is then empty for the
+    // L2 latency instead of the DRAM latency).
+    if (ok && i + ST_NW < n) {
+      const int* rn = st.rec[(m + 1) & 1];
+      if (lane < rn[R_NCOPY]) l2_prefetch(p.data + rn[R_COPY0 + 3 * lane], (uint32_t)rn[R_COPY0 + 3 * lane + 1]);
+    }
+#endif
     const int4 h0 = *reinterpret_cast<const int4*>(rec);      // type, ensemble, slot, a
     const int4 h1 = *reinterpret_cast<const int4*>(rec + 4);  // b, copies, target, c
     const int* e = p.ens_table + (size_t)h0.y * E_STRIDE;
