@@ -27,6 +27,8 @@
 #endif
 #define FUSED_BATCH 4         // neurons per thread whose loads are issued together
 
+template <int V> struct FusedInt { static constexpr int value = V; };
+
 template <bool NC> __device__ __forceinline__ float fused_ld(const float* p) { return NC ? __ldg(p) : *p; }
 template <bool NC> __device__ __forceinline__ float4 fused_ld4(const float4* p) { return NC ? __ldg(p) : *p; }
 
@@ -153,43 +155,50 @@ __device__ __forceinline__ void nb2_ensemble_step_body(void* smem, int vblock, i
     float* W = data + __ldg(&e[E_W]);
     float* S = __ldg(&e[E_S]) >= 0 ? data + __ldg(&e[E_S]) : nullptr;
     float* Jout = __ldg(&e[E_J]) >= 0 ? data + __ldg(&e[E_J]) : nullptr;
-    // FUSED_BATCH neurons per thread at a time: all their loads are issued before the first use,
-    // so a thread with several neurons pays the memory latency once per batch
-    for (int i0 = t; i0 < n; i0 += FUSED_BATCH * TPE) {
-      float J[FUSED_BATCH], v[FUSED_BATCH], w[FUSED_BATCH], s[FUSED_BATCH];
+    // NB neurons per thread at a time (1, 2 or FUSED_BATCH, whichever covers the population with
+    // the fewest idle slots): all their loads are issued before the first use, so a thread with
+    // several neurons pays the memory latency once per batch
+    auto phase1 = [&](auto nb_tag) {
+      constexpr int NB = decltype(nb_tag)::value;
+      for (int i0 = t; i0 < n; i0 += NB * TPE) {
+        float J[NB], v[NB], w[NB], s[NB];
 #pragma unroll
-      for (int j = 0; j < FUSED_BATCH; ++j) {
-        const int i = i0 + j * TPE;
-        const bool ok = i < n;
-        J[j] = ok ? bias[i] : 0.0f;
-        v[j] = ok ? V[i] : 0.0f;
-        w[j] = ok ? W[i] : 0.0f;
-      }
-      int xoff = 0;
-      for (int k = 0; k < n_terms; ++k) {
-        const int d = __ldg(&terms[k * T_STRIDE + T_D]);
-        const int a0 = __ldg(&terms[k * T_STRIDE + T_A]);
-        const bool v4 = vec || ((d | a0 | xoff) & 3) == 0;
-#pragma unroll
-        for (int j = 0; j < FUSED_BATCH; ++j) {
+        for (int j = 0; j < NB; ++j) {
           const int i = i0 + j * TPE;
-          if (i < n) J[j] = fused_row_dot<NC>(data + a0 + (size_t)i * d, &s_x[grp][xoff], d, v4, J[j]);
+          const bool ok = i < n;
+          J[j] = ok ? bias[i] : 0.0f;
+          v[j] = ok ? V[i] : 0.0f;
+          w[j] = ok ? W[i] : 0.0f;
         }
-        xoff += d;
-      }
-      fused_lif4(J, v, w, s, tau, ref, amp, dt, dt_inv, em1_dt);
+        int xoff = 0;
+        for (int k = 0; k < n_terms; ++k) {
+          const int d = __ldg(&terms[k * T_STRIDE + T_D]);
+          const int a0 = __ldg(&terms[k * T_STRIDE + T_A]);
+          const bool v4 = vec || ((d | a0 | xoff) & 3) == 0;
 #pragma unroll
-      for (int j = 0; j < FUSED_BATCH; ++j) {
-        const int i = i0 + j * TPE;
-        if (i < n) {
-          V[i] = v[j];
-          W[i] = w[j];
-          if (S) S[i] = s[j];
-          if (Jout) Jout[i] = J[j];
-          s_spk[grp][i] = s[j];
+          for (int j = 0; j < NB; ++j) {
+            const int i = i0 + j * TPE;
+            if (i < n) J[j] = fused_row_dot<NC>(data + a0 + (size_t)i * d, &s_x[grp][xoff], d, v4, J[j]);
+          }
+          xoff += d;
+        }
+        fused_lifN<NB>(J, v, w, s, tau, ref, amp, dt, dt_inv, em1_dt);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const int i = i0 + j * TPE;
+          if (i < n) {
+            V[i] = v[j];
+            W[i] = w[j];
+            if (S) S[i] = s[j];
+            if (Jout) Jout[i] = J[j];
+            s_spk[grp][i] = s[j];
+          }
         }
       }
-    }
+    };
+    if (n <= TPE) phase1(FusedInt<1>());
+    else if (n <= 2 * TPE) phase1(FusedInt<2>());
+    else phase1(FusedInt<FUSED_BATCH>());
   }
   group_sync();
 

@@ -357,6 +357,9 @@ class Plans:
     def invalidate(self):
         """Drop captured graphs (call after changing the plan list)."""
         self._segments = None
+        for p in self._launch_plans or []:
+            if isinstance(p, PhaseGroup):
+                p.loop.close()
         self._launch_plans = None
         if self.step_loop is not None:
             self.step_loop.close()

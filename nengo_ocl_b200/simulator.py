@@ -458,6 +458,8 @@ class Simulator:
         for st in getattr(self, "_input_streams", []):
             _capi.lib().nb2_host_free(st["hptr"])
         self._input_streams = []
+        if getattr(self, "_plans", None) is not None:
+            self._plans.close()  # the step loop, grouped launches and side streams of the captured graph
         self.context = None
         self.queue = None
         self.all_data = None
