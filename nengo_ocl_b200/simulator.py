@@ -325,6 +325,17 @@ class Simulator:
         plans.extend(probe_plans)
         if self._exchange is not None:
             wait, push = self._exchange.plans()
+            # What the exchange kernels touch, for the dependency edges of the captured graph: the
+            # replica of the exchange signal and the exchange's control block (step counter, flags),
+            # which the wait, the push and a compute kernel that pushes its own results all use.
+            sig_base, control = exchange[0].base, self._exchange
+            for p in wait:
+                p.signal_use = ({control}, {sig_base, control})
+            for p in push:
+                p.signal_use = ({sig_base, control}, {control})
+            for p in plans:
+                if getattr(p, "fused_push", False):
+                    p.signal_use = (set(p.signal_use[0]) | {control}, set(p.signal_use[1]) | {control})
             plans = wait + plans + push
         # A model whose whole step is a handful of blocks runs n steps as ONE launch of a single-CTA
         # persistent kernel (csrc/nb2_step_loop_single.cu); the others replay a captured graph.
