@@ -433,6 +433,12 @@ int nb2_step_loop_add_presentinput(void* loop, int barrier, int n_items, int blo
 int nb2_step_loop_finalize(void* loop, int max_ctas);
 int nb2_step_loop_run(void* loop, void* stream, int n_steps);
 int nb2_step_loop_info(void* loop, int* n_phases, int* n_barriers, int* grid, int* total_vblocks);
+/* Self-test of the bounded wait: runs the cooperative loop with every barrier expecting one arrival
+ * more than the grid has CTAs, so that the first barrier can only run out; the kernel must return
+ * within the wait limit with NB2_ERR_TIMEOUT in the status word (then nb2_step_loop_clear_status).
+ * The model's state is advanced by part of a step: call it on a scratch model only. */
+int nb2_step_loop_wait_selftest(void* loop, void* stream);
+int nb2_step_loop_clear_status(void* loop, void* stream);
 int nb2_step_loop_status(void* loop, void* stream, int* status);
 
 #ifdef __cplusplus

@@ -108,6 +108,8 @@ _SIGNATURES = {
     "nb2_step_loop_run": [_P, _P, c_int],
     "nb2_step_loop_info": [_P, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)],
     "nb2_step_loop_status": [_P, _P, POINTER(c_int)],
+    "nb2_step_loop_wait_selftest": [_P, _P],
+    "nb2_step_loop_clear_status": [_P, _P],
 }
 # a phase of the step loop takes (loop, barrier) + the arguments of the launch entry point without the stream
 for _name in ("timeupdate", "gather_sum", "direct", "ensemble_step", "gemv_block", "probes", "linearfilter",

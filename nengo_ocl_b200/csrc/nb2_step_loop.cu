@@ -30,9 +30,10 @@
 #include "../../include/nengo_b200.h"
 
 __global__ void __launch_bounds__(LOOP_THREADS, LOOP_MIN_BLOCKS)
-nb2_step_loop_kernel(const StepPhase* __restrict__ phases, int n_phases, int n_steps, unsigned* counter, int* status) {
+nb2_step_loop_kernel(const StepPhase* __restrict__ phases, int n_phases, int n_steps, unsigned* counter, int* status,
+                     int barrier_extra) {
   extern __shared__ __align__(16) unsigned char dyn[];
-  nb2_step_loop_device<false>(dyn, phases, n_phases, n_steps, counter, status);
+  nb2_step_loop_device<false>(dyn, phases, n_phases, n_steps, counter, status, barrier_extra);
 }
 
 // defined in nb2_step_loop_single.cu (compiled with the default load caching)
@@ -329,11 +330,7 @@ extern "C" int nb2_step_loop_finalize(void* loop, int max_ctas) {
   return NB2_OK;
 }
 
-extern "C" int nb2_step_loop_run(void* loop, void* stream, int n_steps) {
-  Nb2StepLoop* L = loop_of(loop);
-  NB2_REQUIRE(L != NULL && L->d_phases != NULL, "the loop is not finalized");
-  if (n_steps <= 0) return NB2_OK;
-  cudaStream_t s = nb2_stream(stream);
+static int step_loop_launch(Nb2StepLoop* L, cudaStream_t s, int n_steps, int barrier_extra) {
   const StepPhase* phases = L->d_phases;
   int n_phases = (int)L->phases.size();
   unsigned* counter = L->d_counter;
@@ -343,9 +340,30 @@ extern "C" int nb2_step_loop_run(void* loop, void* stream, int n_steps) {
     return NB2_OK;
   }
   NB2_CUDA(cudaMemsetAsync(L->d_counter, 0, sizeof(unsigned), s));  // the barrier counter; the status word is sticky
-  void* args[] = {&phases, &n_phases, &n_steps, &counter, &status};
+  void* args[] = {&phases, &n_phases, &n_steps, &counter, &status, &barrier_extra};
   NB2_CUDA(cudaLaunchCooperativeKernel((const void*)nb2_step_loop_kernel, dim3(L->grid), dim3(LOOP_THREADS), args,
                                        L->smem, s));
+  return NB2_OK;
+}
+
+extern "C" int nb2_step_loop_run(void* loop, void* stream, int n_steps) {
+  Nb2StepLoop* L = loop_of(loop);
+  NB2_REQUIRE(L != NULL && L->d_phases != NULL, "the loop is not finalized");
+  if (n_steps <= 0) return NB2_OK;
+  return step_loop_launch(L, nb2_stream(stream), n_steps, 0);
+}
+
+extern "C" int nb2_step_loop_wait_selftest(void* loop, void* stream) {
+  Nb2StepLoop* L = loop_of(loop);
+  NB2_REQUIRE(L != NULL && L->d_phases != NULL, "the loop is not finalized");
+  NB2_REQUIRE(L->grid > 1, "the single-CTA form has no grid barrier");
+  return step_loop_launch(L, nb2_stream(stream), 2, 1);
+}
+
+extern "C" int nb2_step_loop_clear_status(void* loop, void* stream) {
+  Nb2StepLoop* L = loop_of(loop);
+  NB2_REQUIRE(L != NULL && L->d_counter != NULL, "the loop is not finalized");
+  NB2_CUDA(cudaMemsetAsync(L->d_counter, 0, 2 * sizeof(unsigned), nb2_stream(stream)));
   return NB2_OK;
 }
 

@@ -64,10 +64,13 @@ union LoopPool {
 };
 
 // All CTAs of the grid meet here.  Returns false when the wait ran out (or another CTA's did).
-__device__ __forceinline__ bool loop_barrier(unsigned* counter, unsigned& target, int* status, int* s_flag) {
+// `extra`: arrivals expected beyond the grid's own (0 in every real run; the self-test of the
+// time-out path passes 1, so that the wait can only run out).
+__device__ __forceinline__ bool loop_barrier(unsigned* counter, unsigned& target, int* status, int* s_flag,
+                                             int extra) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    target += gridDim.x;
+    target += gridDim.x + extra;
     __threadfence();
     atomicAdd(counter, 1u);
     unsigned spins = 0;
@@ -90,7 +93,8 @@ __device__ __forceinline__ bool loop_barrier(unsigned* counter, unsigned& target
 // multiprocessor wrote, so the translation unit may keep the default (L1) caching of global loads.
 template <bool SINGLE>
 __device__ __forceinline__ void nb2_step_loop_device(unsigned char* dyn, const StepPhase* __restrict__ phases,
-                                                     int n_phases, int n_steps, unsigned* counter, int* status) {
+                                                     int n_phases, int n_steps, unsigned* counter, int* status,
+                                                     int barrier_extra = 0) {
   LoopPool* pool = reinterpret_cast<LoopPool*>(dyn);
   StepPhase* s_ph = reinterpret_cast<StepPhase*>(dyn + ((sizeof(LoopPool) + 15) & ~size_t(15)));
   __shared__ int s_flag;
@@ -108,7 +112,7 @@ __device__ __forceinline__ void nb2_step_loop_device(unsigned char* dyn, const S
       const StepPhase& P = s_ph[ph];
       if (P.barrier && !(step == 0 && ph == 0)) {
         if (SINGLE) __syncthreads();
-        else if (!loop_barrier(counter, target, status, &s_flag)) return;
+        else if (!loop_barrier(counter, target, status, &s_flag, barrier_extra)) return;
       }
       const int nvb = P.n_vblocks;
       switch (P.kind) {

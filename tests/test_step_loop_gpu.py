@@ -109,3 +109,29 @@ def test_tiny_consecutive_plans_share_one_launch(monkeypatch):
                 assert np.array_equal(np.asarray(grouped.signals[sig]), np.asarray(plain.signals[sig])), sig
             for p in mdl.probes:
                 assert np.array_equal(grouped.data[p], plain.data[p])
+
+
+def test_grid_barrier_wait_is_bounded():
+    """A grid barrier that can only run out (it expects one arrival more than there are CTAs): the
+    kernel returns within its wait limit, records NB2_ERR_TIMEOUT, the host raises, and after the
+    status is cleared the same context and loop run the model again."""
+    import time
+
+    from nengo_ocl_b200 import _capi
+
+    mdl = MODELS["watts_strogatz"]()
+    with Simulator(None, model=mdl, step_loop=True) as sim, Simulator(None, model=mdl, step_loop=False) as plain:
+        loop = sim._plans.step_loop
+        assert loop is not None and loop.grid > 1
+        t0 = time.time()
+        _capi.call("nb2_step_loop_wait_selftest", loop.handle, sim.queue.stream)
+        assert loop.status(sim.queue.stream) == -4  # NB2_ERR_TIMEOUT; the call synchronises the stream
+        assert time.time() - t0 < 60
+        with pytest.raises(RuntimeError):
+            sim._plans.check_status()
+        _capi.call("nb2_step_loop_clear_status", loop.handle, sim.queue.stream)
+        sim.reset()
+        sim.run_steps(20)
+        plain.run_steps(20)
+        for p in mdl.probes:
+            assert np.array_equal(sim.data[p], plain.data[p])
