@@ -37,15 +37,15 @@ __device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uin
   for (int r = 0; r < 10; ++r) philox_round(c, k);
 }
 
-// grid (ceil(max quads / 256), items): one thread per four elements
+// grid (items, ceil(max quads / 256)): one thread per four elements
 __global__ void nb2_whitenoise_kernel(const int* __restrict__ shape0s, const int* __restrict__ Ystarts, float* Y,
                                       const int* __restrict__ Tstarts, const float* T,
                                       const int* __restrict__ enums, const float* __restrict__ params,
                                       const int* __restrict__ scales, const int* __restrict__ incs,
                                       const unsigned* __restrict__ seeds, double sqrt_dt_inv) {
   nb2_pdl_enter();
-  const int k = blockIdx.y;
-  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.x;
+  const int q = blockIdx.y * blockDim.x + threadIdx.x;
   const int m = shape0s[k];
   if (4 * q >= m) return;
   uint32_t c[4] = {(uint32_t)(int)T[Tstarts[k]], (uint32_t)q, 0u, 0u};
@@ -84,9 +84,10 @@ extern "C" int nb2_whitenoise(void* stream, int n_items, int max_len, const int*
                               const int* scales, const int* incs, const unsigned* seeds, double dt) {
   if (n_items == 0) return NB2_OK;
   NB2_REQUIRE(shape0s && Ystarts && Y && Tstarts && T && enums && params && scales && incs && seeds, "null pointer");
-  NB2_REQUIRE(max_len >= 1 && dt > 0 && n_items <= 65535, "sizes");
+  NB2_REQUIRE(max_len >= 1 && dt > 0, "sizes");
   const int quads = (max_len + 3) / 4;
-  nb2_launch(nb2_whitenoise_kernel, dim3((quads + 255) / 256, n_items), dim3(256), 0, nb2_stream(stream), shape0s,
+  NB2_REQUIRE((quads + 255) / 256 <= 65535, "an item of more than 67 M elements");
+  nb2_launch(nb2_whitenoise_kernel, dim3(n_items, (quads + 255) / 256), dim3(256), 0, nb2_stream(stream), shape0s,
              Ystarts, Y, Tstarts, T, enums, params, scales, incs, seeds, 1.0 / sqrt(dt));
   NB2_LAUNCH_CHECK();
   return NB2_OK;
