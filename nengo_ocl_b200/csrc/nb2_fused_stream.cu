@@ -275,12 +275,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
           xoff += d;
         }
         // (lanes beyond the last neuron of the block recompute it; nothing of theirs is stored)
-        float Jv[ST_ROWS], Vv[ST_ROWS], Wv[ST_ROWS], Sv[ST_ROWS];
+        float Jv[ST_ROWS], Vv[ST_ROWS], Wv[ST_ROWS], Sv[ST_ROWS], Pv[ST_ROWS];
 #pragma unroll
         for (int j = 0; j < ST_ROWS; ++j) {
           Jv[j] = tot[j];
           Vv[j] = s_V[roff[j]];
           Wv[j] = s_W[roff[j]];
+          Pv[j] = pf_conn >= 0 ? s_pf[roff[j]] : 0.0f;
         }
         fused_lifN<ST_ROWS>(Jv, Vv, Wv, Sv, tau, ref, amp, p.dt, p.dt_inv, em1_dt);
         // row j of this lane is neuron i0 + base + lane + 32 j: every array is walked with immediates
@@ -290,15 +291,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) nb2_ensemble_stream_kernel(cons
         float* gS = eS >= 0 ? data + eS + first : nullptr;
         float* sspk = slot.spk + first;
         if (pf_conn >= 0) {
-          const float* spf = s_pf + base + lane;
           float* spfo = slot.pfo + first;
           float* gPF = data + gpf + first;
 #pragma unroll
           for (int j = 0; j < ST_ROWS; ++j) {
             if (lane + 32 * j < nb) {
-              const float pf = spf[32 * j];
-              spfo[32 * j] = pf;
-              gPF[32 * j] = pb0 * Sv[j] - pa0 * pf;
+              spfo[32 * j] = Pv[j];
+              gPF[32 * j] = pb0 * Sv[j] - pa0 * Pv[j];
             }
           }
         }
