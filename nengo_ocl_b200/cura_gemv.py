@@ -743,13 +743,24 @@ class gemv_prog:
             tiles_per_row = ((-(-table[:, 3 * D:4 * D].astype(np.int64) // 128)) * mask).sum(axis=1)
         else:
             tiles_per_row = np.zeros(len(table), np.int64)
-        n_blocks = -(-M // 32)
+        # Rows per unit: the reference's 32, or fewer when that would leave most of the GPU idle (the
+        # dense transforms of a model are a few hundred rows: 8-row units put their tiles on separate
+        # warps of more CTAs; the sum of a row is formed in the same order either way).
+        sm_count = getattr(self.queue.device, "sm_count", 148)
+        rows_per_unit = 32
+        while rows_per_unit > 8 and int((-(-M // rows_per_unit)).sum()) < sm_count:
+            rows_per_unit //= 2
+        n_blocks = -(-M // rows_per_unit)
         rows_of = np.repeat(np.arange(len(table)), n_blocks)
         first = np.arange(int(n_blocks.sum())) - np.repeat(np.cumsum(n_blocks) - n_blocks, n_blocks)
         units = np.zeros((len(rows_of), 4), dtype=np.int32)
-        units[:, 0], units[:, 1] = rows_of, first * 32
-        units[:, 2] = np.minimum(32, M[rows_of] - first * 32)
-        small = (units[:, 2] <= 8) & (tiles_per_row[rows_of] <= 8)
+        units[:, 0], units[:, 1] = rows_of, first * rows_per_unit
+        units[:, 2] = np.minimum(rows_per_unit, M[rows_of] - first * rows_per_unit)
+        # one warp takes a unit of at most 8 rows whose tiles it can walk one after the other: up to 8
+        # tiles when there is work for every SM anyway, a single tile when the units were made small
+        # to spread the tiles of a row over warps
+        max_tiles = 8 if rows_per_unit == 32 else 1
+        small = (units[:, 2] <= 8) & (tiles_per_row[rows_of] <= max_tiles)
         cta_units, warp_units = units[~small], units[small]
         queue = self.queue
         d_table = to_device(queue, table)
