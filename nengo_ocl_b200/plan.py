@@ -193,15 +193,18 @@ class StepLoop:
     two-ensemble model well below the launch-per-plan cost, while the multi-CTA form
     (grid-wide barriers, L2-only loads) is slower than replaying a captured graph for
     models of hundreds of blocks.  ``build(..., auto=True)`` therefore returns a loop only
-    for models whose whole step is at most ``AUTO_MAX_BLOCKS`` blocks."""
+    for models whose whole step is at most ``AUTO_MAX_BLOCKS`` blocks and whose widest plan is at
+    most ``AUTO_MAX_WIDEST`` (a wider plan runs faster as a grid of its own)."""
 
-    AUTO_MAX_BLOCKS = 16
+    AUTO_MAX_BLOCKS = 16   # blocks of a whole step
+    AUTO_MAX_WIDEST = 3    # blocks of its widest plan (one CTA walks them one after the other)
 
     @classmethod
     def build(cls, plans, barriers, max_ctas=0, auto=False):
         loop = cls(plans, barriers)
         if auto:
-            if loop.total_blocks > cls.AUTO_MAX_BLOCKS:
+            widest = max(phase_blocks(p) or 0 for p in plans)
+            if loop.total_blocks > cls.AUTO_MAX_BLOCKS or widest > cls.AUTO_MAX_WIDEST:
                 loop.close()
                 return None
             max_ctas = 1
