@@ -96,8 +96,3 @@ __device__ __forceinline__ void fused_lifN(const float (&J)[N], float (&V)[N], f
 #pragma unroll
   for (int j = 0; j < N; ++j) S[j] = spiked[j] ? amp * dt_inv : 0.0f;
 }
-
-__device__ __forceinline__ void fused_lif4(const float (&J)[4], float (&V)[4], float (&W)[4], float (&S)[4], float tau,
-                                           float ref, float amp, float dt, float dt_inv, float em1_dt) {
-  fused_lifN<4>(J, V, W, S, tau, ref, amp, dt, dt_inv, em1_dt);
-}
