@@ -405,7 +405,15 @@ class Plans:
     def _capture(self, plans, repeat):
         if (self.parallel and 1 < len(plans) <= self.MAX_BRANCH_PLANS
                 and all(getattr(p, "signal_use", None) is not None for p in plans)):
-            return self._capture_branches(plans, repeat)
+            try:
+                return self._capture_branches(plans, repeat)
+            except _capi.NB2Error as err:
+                # (the capture was aborted: the stream is usable) fall back to the plain in-order graph
+                import warnings
+
+                warnings.warn("graph capture along signal dependencies failed (%s); capturing the plans in "
+                              "order instead" % err)
+                self.parallel = False
         return self._capture_chain(plans, repeat)
 
     def _capture_branches(self, plans, repeat):
