@@ -478,14 +478,20 @@ class Simulator:
         self._raggedarrays_to_reset = None
         self._cl_probe_plan = None
 
-    def _probe(self):
-        """Drain the device-side probe ring buffers into ``data``."""
-        self._probe_step_time()
+    def _probe(self, steps_run=None):
+        """Drain the device-side probe ring buffers into ``data``.  ``steps_run``: the steps simulated
+        since the last drain, when the caller knows them (``run_steps``): the step count and the time
+        are then advanced on the host exactly as the clock kernel computes them (float32 step,
+        ``float32(dt * step)``) instead of being read back."""
+        if steps_run is None:
+            self._probe_step_time()
+        else:
+            self._n_steps += int(steps_run)
+            self._time = float(np.float32(float(self.model.dt) * float(np.float32(self._n_steps))))
         plan = self._cl_probe_plan
         if plan is None:
             return
-        self.queue.finish()
-        bufpositions = plan.cl_bufpositions.get()
+        bufpositions = plan.cl_bufpositions.get()  # (a blocking copy on the stream: everything before it is done)
         for i, probe in enumerate(self.model.probes):
             n_buffered = int(bufpositions[i])
             if n_buffered:
@@ -493,8 +499,8 @@ class Simulator:
                 width = int(plan.Y.shape1s[i])
                 raw = plan.Y.cl_buf.read_region(int(plan.Y.starts[i]), n_buffered * width)
                 self._probe_outputs[probe].extend(raw.reshape((n_buffered,) + tuple(shape)))
-        plan.cl_bufpositions.fill(0)
-        self.queue.finish()
+        # (a memset on the stream, ordered before the next step: no need to wait for it)
+        _capi.call("nb2_memset", plan.cl_bufpositions.ptr, 0, plan.cl_bufpositions.nbytes, self.queue.stream)
 
     def _probe_step_time(self):
         self._n_steps = int(self.signals[self.model.step].item())
@@ -547,7 +553,7 @@ class Simulator:
             B = min(steps, self._max_steps_between_probes)
             self._upload_inputs(B)
             self._plans.call_n_times(B)
-            self._probe()
+            self._probe(steps_run=B)
             self._plans.check_status()
             for plan in self._status_plans:  # bounded waits inside the pipelined kernels
                 if int(plan.status.get()[0]) != 0:
