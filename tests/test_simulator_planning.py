@@ -104,3 +104,24 @@ def test_models_with_host_code_or_ring_buffers_keep_the_graph_path(fake):
     assert "cl_whitenoise" in names(sim2._plans)
     assert sim2._plans.step_loop is None  # the noise plan has no phase form
     sim2.close()
+
+
+def test_host_clock_matches_the_clock_kernel(fake):
+    """``run_steps`` advances ``n_steps`` / ``time`` on the host between probe drains; the values must
+    be the ones the clock kernel leaves in the step and time signals (oracle: K.timeupdate)."""
+    from nengo_ocl_b200.raggedarray import RaggedArray
+    from oracle import kernels as K
+
+    mdl = synth.two_ensemble_model(seed=0)
+    sim = sim_mod.Simulator(None, model=mdl, step_loop=False)
+    step = RaggedArray([np.zeros((1, 1))], dtype=np.float32)
+    time = RaggedArray([np.zeros((1, 1))], dtype=np.float32)
+    done = 0
+    for batch in (1, 2, 7, 256, 256, 1000, 33):
+        sim._probe(steps_run=batch)  # (the stand-in library runs nothing: only the host arithmetic)
+        for _ in range(batch):
+            K.timeupdate(step, time, mdl.dt)
+        done += batch
+        assert sim.n_steps == done == int(step[0][0, 0])
+        assert np.float32(sim.time) == time[0][0, 0]
+    sim.close()
