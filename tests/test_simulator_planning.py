@@ -125,3 +125,47 @@ def test_host_clock_matches_the_clock_kernel(fake):
         assert sim.n_steps == done == int(step[0][0, 0])
         assert np.float32(sim.time) == time[0][0, 0]
     sim.close()
+
+
+def test_plan_functions_keep_the_reference_error_conventions(fake):
+    """Argument checks of the plan functions that have no kernel-side counterpart: an unsupported
+    padding is a ValueError (clra_nonlinearities.py:1886-1893), biases are asserted absent (:1787),
+    a noise plan needs one key, one enum and two parameters per item."""
+    from nengo_ocl_b200 import cura_nonlinearities as nl
+    from nengo_ocl_b200 import model as m
+    from nengo_ocl_b200.curaggedarray import CUDARaggedArray
+    from nengo_ocl_b200.raggedarray import RaggedArray
+    from nengo_ocl_b200.runtime import CommandQueue, create_some_context, to_device
+
+    queue = CommandQueue(create_some_context())
+    data = CUDARaggedArray(queue, RaggedArray([np.zeros(2 * 5 * 5), np.zeros(3 * 3 * 2 * 4), np.zeros(4 * 3 * 3)],
+                                              dtype=np.float32))
+    X, F, Y = (data.getitem_device(i) for i in range(3))
+    args = dict(shape_in=(5, 5, 2), shape_out=(3, 3, 4), kernel_shape=(3, 3))
+    plan = nl.plan_conv2d(queue, X, Y, F, padding="valid", **args)
+    assert plan.name == "cl_conv2d" and plan.flops_per_call == 2 * 3 * 3 * 4 * 2 * 3 * 3
+    plan()
+    assert ("nb2_conv2d", 19) in fake.calls
+    with pytest.raises(ValueError):
+        nl.plan_conv2d(queue, X, Y, F, padding="full", **args)
+    with pytest.raises(AssertionError):
+        nl.plan_conv2d(queue, X, Y, F, biases=Y, **args)
+    with pytest.raises(AssertionError):  # the output does not have the size the shapes imply
+        nl.plan_conv2d(queue, X, Y, F, shape_in=(5, 5, 2), shape_out=(3, 3, 5), kernel_shape=(3, 3))
+
+    Yn = CUDARaggedArray(queue, RaggedArray([np.zeros(5), np.zeros(3)], dtype=np.float32))
+    step = CUDARaggedArray(queue, RaggedArray([np.zeros((1, 1))], dtype=np.float32))
+    enums, params = nl.get_dist_enums_params([m.Uniform(-1, 1), m.Gaussian(0, 2)])
+    assert [int(e[0, 0]) for e in enums] == [0, 1] and params[1][:, 0].tolist() == [0.0, 2.0]
+    rngs = nl.create_rngs(queue, 2)
+    nl.init_rngs(queue, rngs, [7, (5 << 32) | 9])
+    assert rngs.get().view(np.uint32).tolist() == [[7, 0], [9, 5]]
+    plan = nl.plan_whitenoise(queue, Yn, CUDARaggedArray(queue, enums), CUDARaggedArray(queue, params),
+                              to_device(queue, np.zeros(2, np.int32)), to_device(queue, np.ones(2, np.int32)), 0.001,
+                              rngs, step[[0, 0]])
+    plan()
+    assert plan.name == "cl_whitenoise" and ("nb2_whitenoise", 14) in fake.calls
+    with pytest.raises(AssertionError):
+        nl.plan_whitenoise(queue, Yn, CUDARaggedArray(queue, enums), CUDARaggedArray(queue, params),
+                           to_device(queue, np.zeros(3, np.int32)), to_device(queue, np.ones(2, np.int32)), 0.001,
+                           rngs, step[[0, 0]])
