@@ -17,6 +17,7 @@ Printed JSON (one line, rank 0):
   roofline   the fused ensemble-step kernel: algorithmic bytes per launch over
              its CUDA-event time, against the measured HBM copy bandwidth;
   gemv       the ragged gather-GEMV microbenchmark (configuration 2), GB/s;
+  lif        the stand-alone LIF kernel on 16.8 M neurons, GB/s (24 bytes per neuron);
   spmv       sparse transforms (CSR, ELLPACK) on a Watts-Strogatz adjacency, GB/s;
   small_models  simulated steps/s of configurations 1, 3, 4 and of a sparse
              recurrent population through ``run_steps``;
@@ -284,6 +285,48 @@ def gemv_microbench(queue, capi, reps=20, n_outputs=4096):
             "timing": "5 calls back to back per event pair, as inside a step loop",
             "isolated_call": {"ms_per_call": ms_alone, "achieved_gbs": plan.bw_per_call / ms_alone / 1e6},
             "status": int(plan.status.get()[0])}
+
+
+def lif_microbench(queue, capi, n_populations=16384, n_neurons=1024, reps=20):
+    """The stand-alone LIF kernel (plan_lif, clra_nonlinearities.py:1028-1146) on 16.8 M neurons:
+    four arrays of 67 MB (J, V, W, spikes), far larger than L2; input currents drawn as in the
+    reference's test_lif_step (normal, scale 1.2).  Algorithmic bytes: 24 per neuron (J read; V, W
+    read and written; spikes written; tau / ref / amp are per-population scalars); the reference
+    accounts 36 because it stores the three parameters per neuron.  The benchmark models do not
+    use this kernel (their neuron update runs inside the fused kernels); it serves populations
+    outside the fused pattern, and with the exact arithmetic (IEEE division, double-precision
+    series for expm1 / log1p) it is instruction-bound, not memory-bound."""
+    from nengo_ocl_b200 import cura_nonlinearities as nl
+    from nengo_ocl_b200.curaggedarray import CUDARaggedArray
+    from nengo_ocl_b200.raggedarray import RaggedArray
+
+    rng = np.random.RandomState(5)
+    n = n_populations * n_neurons
+    J = rng.normal(scale=1.2, size=n).astype(np.float32)
+    V = rng.uniform(0, 1, size=n).astype(np.float32)
+    W = rng.uniform(-2e-3, 2e-3, size=n).astype(np.float32)
+
+    def ragged(buf):
+        ra = RaggedArray([np.zeros(n_neurons)] * n_populations, dtype=np.float32)
+        ra.buf[...] = buf
+        return CUDARaggedArray(queue, ra)
+
+    clJ, clV, clW, clS = ragged(J), ragged(V), ragged(W), ragged(np.zeros(n, np.float32))
+    plan = nl.plan_lif(queue, 1e-3, clJ, clV, clW, clS, 2e-3, 0.02, 1.0)
+    for _ in range(3):
+        plan()
+    ev = Events(capi)
+    times, batch = [], 5
+    for _ in range(reps):
+        ev.start(queue.stream)
+        for _ in range(batch):
+            plan.kern(queue.stream)
+        times.append(ev.stop_ms(queue.stream) / batch)
+    ms = float(np.median(times))
+    return {"workload": "%d populations x %d LIF neurons" % (n_populations, n_neurons), "neurons": n,
+            "bytes_per_call": 24 * n, "ms_per_call": ms, "achieved_gbs": 24 * n / ms / 1e6,
+            "reference_accounting_gbs": 36 * n / ms / 1e6, "kernel": plan.name,
+            "note": "instruction-bound (exact arithmetic), see profiles/lif_kernel.md"}
 
 
 def spmv_microbench(queue, capi, n=1 << 20, fan_out=64, reps=10):
@@ -623,6 +666,11 @@ def main():
         line["gemv"] = gemv_microbench(q2, _capi)
         line["gemv"]["frac"] = line["gemv"]["achieved_gbs"] / peak
         line["gemv"]["isolated_call"]["frac"] = line["gemv"]["isolated_call"]["achieved_gbs"] / peak
+    if rank == 0 and not args.no_gemv and world == 1:
+        from nengo_ocl_b200.runtime import CommandQueue
+
+        line["lif"] = lif_microbench(CommandQueue(ctx), _capi)
+        line["lif"]["frac"] = line["lif"]["achieved_gbs"] / peak
     if rank == 0 and not args.no_spmv and world == 1:
         from nengo_ocl_b200.runtime import CommandQueue
 
