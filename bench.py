@@ -294,8 +294,7 @@ def lif_microbench(queue, capi, n_populations=16384, n_neurons=1024, reps=20):
     read and written; spikes written; tau / ref / amp are per-population scalars); the reference
     accounts 36 because it stores the three parameters per neuron.  The benchmark models do not
     use this kernel (their neuron update runs inside the fused kernels); it serves populations
-    outside the fused pattern, and with the exact arithmetic (IEEE division, double-precision
-    series for expm1 / log1p) it is instruction-bound, not memory-bound."""
+    outside the fused pattern."""
     from nengo_ocl_b200 import cura_nonlinearities as nl
     from nengo_ocl_b200.curaggedarray import CUDARaggedArray
     from nengo_ocl_b200.raggedarray import RaggedArray
@@ -325,8 +324,7 @@ def lif_microbench(queue, capi, n_populations=16384, n_neurons=1024, reps=20):
     ms = float(np.median(times))
     return {"workload": "%d populations x %d LIF neurons" % (n_populations, n_neurons), "neurons": n,
             "bytes_per_call": 24 * n, "ms_per_call": ms, "achieved_gbs": 24 * n / ms / 1e6,
-            "reference_accounting_gbs": 36 * n / ms / 1e6, "kernel": plan.name,
-            "note": "instruction-bound (exact arithmetic), see profiles/lif_kernel.md"}
+            "reference_accounting_gbs": 36 * n / ms / 1e6, "kernel": plan.name}
 
 
 def spmv_microbench(queue, capi, n=1 << 20, fan_out=64, reps=10):

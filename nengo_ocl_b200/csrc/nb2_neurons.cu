@@ -11,6 +11,7 @@
 // reference kernels this path is checked against.
 #include "nb2_common.cuh"
 #include "nb2_math.cuh"
+#include "nb2_fused_common.cuh"
 #include "../../include/nengo_b200.h"
 
 __device__ __forceinline__ float nb2_var_load(const nb2_var& v, int block, int i) {
@@ -130,6 +131,50 @@ __global__ void nb2_neurons_kernel(int kind, int n_blocks, const int* __restrict
   }
 }
 
+// The common LIF case -- one substep, no adaptation, tau / ref / amp one scalar each -- with four
+// neurons per thread (elements i, i + T, i + 2T, i + 3T of the block, T = threads per block, so
+// every load is contiguous across the warp).  The arithmetic is that of nb2_lif_core; what changes
+// is how often the expensive parts run: expm1(-dt / tau) for a neuron outside its refractory
+// period is one number per launch (em1_dt, rounded once from double on the host), and the
+// double-precision series for the neurons that leave the refractory period or spike is entered
+// once for the 128 neurons of a warp instead of once for every 32 (fused_lifN).
+#define LIF4_NB 4
+__global__ void __launch_bounds__(256) nb2_lif4_kernel(int n_blocks, const int* __restrict__ sizes,
+                                                       const nb2_neuron_args a, float em1_dt) {
+  nb2_pdl_enter();
+  const int block = blockIdx.x;
+  if (block >= n_blocks) return;
+  const int n = sizes[block];
+  const int t = threadIdx.x, T = blockDim.x;
+  const float dt = (float)a.dt, dt_inv = (float)(1.0 / a.dt);
+  const float tau = a.tau.value, ref = a.ref.value, amp = a.amp.value;
+  const float* J = a.J.buf + a.J.starts[block];
+  float* V = a.V.buf + a.V.starts[block];
+  float* W = a.W.buf + a.W.starts[block];
+  float* S = a.S.buf + a.S.starts[block];
+  for (int i0 = t; i0 < n; i0 += LIF4_NB * T) {
+    float Jv[LIF4_NB], Vv[LIF4_NB], Wv[LIF4_NB], Sv[LIF4_NB];
+#pragma unroll
+    for (int j = 0; j < LIF4_NB; ++j) {
+      const int i = i0 + j * T;
+      const bool ok = i < n;
+      Jv[j] = ok ? J[i] : 0.0f;  // (an idle slot holds a neuron at rest: it neither integrates nor spikes)
+      Vv[j] = ok ? V[i] : 0.0f;
+      Wv[j] = ok ? W[i] : 0.0f;
+    }
+    fused_lifN<LIF4_NB>(Jv, Vv, Wv, Sv, tau, ref, amp, dt, dt_inv, em1_dt);
+#pragma unroll
+    for (int j = 0; j < LIF4_NB; ++j) {
+      const int i = i0 + j * T;
+      if (i < n) {
+        V[i] = Vv[j];
+        W[i] = Wv[j];
+        S[i] = Sv[j];
+      }
+    }
+  }
+}
+
 extern "C" int nb2_neurons(void* stream, int kind, int n_blocks, int block_size, const int* sizes,
                            const nb2_neuron_args* args) {
   if (n_blocks == 0) return NB2_OK;
@@ -143,6 +188,16 @@ extern "C" int nb2_neurons(void* stream, int kind, int n_blocks, int block_size,
   if (args->adaptive) NB2_REQUIRE(args->N.buf, "N buffer required");
   nb2_neuron_args a = *args;
   if (a.upsample < 1) a.upsample = 1;
+  if (kind == NB2_NEURON_LIF && a.upsample == 1 && !a.adaptive && !a.fastlif && !a.tau.buf && !a.ref.buf &&
+      !a.amp.buf && a.J.starts && a.V.starts && a.W.starts && a.S.starts) {
+    // expm1 of the float quotient, evaluated in double and rounded once: what nb2_expm1_cr returns
+    const float em1_dt = (float)expm1((double)(-(float)a.dt / a.tau.value));
+    int threads = (block_size + LIF4_NB - 1) / LIF4_NB;
+    threads = threads < 32 ? 32 : (threads + 31) & ~31;
+    nb2_launch(nb2_lif4_kernel, dim3(n_blocks), dim3(threads), 0, nb2_stream(stream), n_blocks, sizes, a, em1_dt);
+    NB2_LAUNCH_CHECK();
+    return NB2_OK;
+  }
   nb2_launch(nb2_neurons_kernel, dim3(n_blocks), dim3(block_size), 0, nb2_stream(stream), kind, n_blocks, sizes, a);
   NB2_LAUNCH_CHECK();
   return NB2_OK;
